@@ -1,0 +1,175 @@
+/*
+ * oxmera_b200 — C ABI of the B200 (sm_100a) matmul backend for oxmera.
+ *
+ * This is the boundary a Rust `oxmera-b200` backend crate binds with
+ * `extern "C"` (build.rs drives nvcc).  Every entry point names the item of
+ * the oxmera reference it stands behind.  Plain pointers and sizes only; no
+ * exceptions, aborts or C++ types cross this boundary.  All functions return
+ * an oxm_status; OXM_OK is 0.
+ *
+ * Threading: every function may be called concurrently from any host thread
+ * (oxmera's `Backend: Send + Sync`, crates/oxmera-runtime/src/lib.rs:29).
+ * Work submitted through one context runs in submission order on that
+ * context's stream.  Compute calls are asynchronous; device-side failures
+ * surface from oxm_sync / oxm_d2h.
+ */
+#ifndef OXMERA_B200_H
+#define OXMERA_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define OXM_MAX_DIMS 8
+
+/* Element types.  0..5 are oxmera's DType in declaration order
+ * (crates/oxmera-core/src/dtype.rs:9-22); BF16/F16 are the two variants the
+ * backend adds to that non_exhaustive enum. */
+typedef enum {
+  OXM_F32 = 0, OXM_F64 = 1, OXM_I32 = 2, OXM_I64 = 3, OXM_U8 = 4, OXM_BOOL = 5,
+  OXM_BF16 = 6, OXM_F16 = 7
+} oxm_dtype;
+
+/* Status codes.  1..9 map one-to-one onto the variants of oxmera's Error
+ * (crates/oxmera-core/src/error.rs:12-102) in declaration order; the rest are
+ * backend conditions the Rust side folds into NotImplemented / a backend
+ * error string obtained from oxm_last_error. */
+typedef enum {
+  OXM_OK = 0,
+  OXM_SHAPE_MISMATCH = 1,
+  OXM_BROADCAST_INCOMPATIBLE = 2,
+  OXM_DTYPE_MISMATCH = 3,
+  OXM_UNSUPPORTED_DTYPE = 4,
+  OXM_DEVICE_MISMATCH = 5,
+  OXM_INDEX_OUT_OF_BOUNDS = 6,
+  OXM_RANK_MISMATCH = 7,
+  OXM_BACKEND_UNAVAILABLE = 8,
+  OXM_NOT_IMPLEMENTED = 9,
+  OXM_CUDA_ERROR = 10,      /* a CUDA runtime / driver call failed */
+  OXM_TIMEOUT = 11,         /* a bounded device-side wait expired */
+  OXM_INVALID_ARGUMENT = 12 /* null pointer, bad handle, bad option */
+} oxm_status;
+
+/* A tensor as the backend sees it: oxmera's Layout {shape, strides, offset}
+ * (crates/oxmera-core/src/layout.rs:26-34; strides are signed ELEMENT strides,
+ * offset is in elements) plus the device pointer and device index of the
+ * Storage behind it (crates/oxmera-tensor/src/storage.rs:12-17). */
+typedef struct {
+  int32_t dtype;                 /* oxm_dtype */
+  int32_t ndim;                  /* 0..OXM_MAX_DIMS */
+  int64_t shape[OXM_MAX_DIMS];
+  int64_t strides[OXM_MAX_DIMS];
+  int64_t offset;
+  void *base;                    /* device pointer to element 0 of the storage */
+  int32_t device;                /* CUDA device index (Device::Cuda{index}) */
+  int32_t reserved;
+} oxm_view;
+
+typedef struct oxm_ctx oxm_ctx;
+typedef struct oxm_event oxm_event;
+
+/* ---- backend identity and lifetime ------------------------------------
+ * One context per Device::Cuda{index}; stands behind `Backend::device()` and
+ * `Backend::name()` (crates/oxmera-runtime/src/lib.rs:29-34).  Creation fails
+ * with OXM_BACKEND_UNAVAILABLE when no sm_100 device with that index exists
+ * (crates/oxmera-runtime/src/lib.rs:36-44: "never a panic"). */
+int oxm_device_count(int *count);
+int oxm_ctx_create(int device_index, oxm_ctx **out);
+int oxm_ctx_destroy(oxm_ctx *ctx);
+int oxm_ctx_device(const oxm_ctx *ctx, int *device_index);
+const char *oxm_backend_name(void); /* "b200-tcgen05" */
+
+/* Human-readable detail of the last non-OK status returned to this thread. */
+const char *oxm_last_error(void);
+/* Stable name of a status code ("ShapeMismatch", ...). */
+const char *oxm_status_name(int status);
+
+/* ---- storage ------------------------------------------------------------
+ * Stand behind the device variant of StorageData
+ * (crates/oxmera-tensor/src/storage.rs:24-32) and the host<->device
+ * constructors a device tensor needs in place of from_vec_f32 / get_f32
+ * (crates/oxmera-tensor/src/tensor.rs:33,96).  Allocation is stream-ordered
+ * and pooled.  Copies are ordered on the context's stream; oxm_d2h returns
+ * after the bytes have landed and reports any pending device-side failure. */
+int oxm_alloc(oxm_ctx *ctx, size_t bytes, void **out);
+int oxm_free(oxm_ctx *ctx, void *ptr);
+int oxm_h2d(oxm_ctx *ctx, void *dst_device, const void *src_host, size_t bytes);
+int oxm_d2h(oxm_ctx *ctx, void *dst_host, const void *src_device, size_t bytes);
+int oxm_memset(oxm_ctx *ctx, void *dst_device, int byte, size_t bytes);
+int oxm_sync(oxm_ctx *ctx);
+/* Page-locked host staging memory (faster, truly asynchronous copies). */
+int oxm_host_alloc(size_t bytes, void **out);
+int oxm_host_free(void *ptr);
+
+/* ---- the operator surface ----------------------------------------------
+ * oxm_matmul stands behind `MatmulOps::matmul`
+ * (crates/oxmera-ops/src/lib.rs:53-59) as implemented by
+ * `CpuBackend::matmul` (crates/oxmera-cpu/src/lib.rs:71-76):
+ * [m,k] x [k,n] -> [m,n], rank 2 exactly, operands read through their views.
+ * Inner-dimension or rank violations are OXM_SHAPE_MISMATCH, differing dtypes
+ * OXM_DTYPE_MISMATCH, non-float dtypes OXM_UNSUPPORTED_DTYPE, differing
+ * devices OXM_DEVICE_MISMATCH.  `out` is caller-allocated (the host wrapper
+ * makes it fresh and contiguous, crates/oxmera-ops/src/lib.rs:16-17) and is
+ * written through its own strides, so a shard may write into a window of a
+ * parent tensor.  `out` must not alias the operands.
+ *
+ * oxm_batched_matmul is the batched extension of the same trait: rank >= 2,
+ * leading dims broadcast by NumPy rules
+ * (crates/oxmera-core/src/shape.rs:49-55), trailing two dims as above.
+ *
+ * dtypes: f32 (fp32 result; 3xTF32 tensor-core path or an FFMA tile kernel),
+ * bf16 and f16 (fp32 accumulate, result rounded to the operand dtype). */
+int oxm_matmul(oxm_ctx *ctx, const oxm_view *a, const oxm_view *b, const oxm_view *out);
+int oxm_batched_matmul(oxm_ctx *ctx, const oxm_view *a, const oxm_view *b, const oxm_view *out);
+
+/* Same operation on HOST views: `base` pointers are host memory.  The
+ * operands are staged to the device, multiplied, and the result copied back
+ * into `out`'s (contiguous) host buffer before returning.  This is what
+ * `Tensor::matmul` costs when the tensors start and end in host memory
+ * (crates/oxmera-runtime/src/lib.rs:68-69,99-102). */
+int oxm_batched_matmul_host(oxm_ctx *ctx, const oxm_view *a, const oxm_view *b, const oxm_view *out);
+
+/* Stands behind the device half of `Tensor::contiguous`
+ * (crates/oxmera-tensor/src/tensor.rs:86-90): gathers `src` (any strides, any
+ * dtype) in logical order into `dst`, a row-major contiguous view of the same
+ * shape and dtype in different storage. */
+int oxm_contiguous(oxm_ctx *ctx, const oxm_view *src, const oxm_view *dst);
+
+/* ---- instrumentation ------------------------------------------------------
+ * Not part of the reference surface: timing on the context's stream and
+ * kernel selection for tests and benchmarks. */
+int oxm_event_create(oxm_ctx *ctx, oxm_event **out);
+int oxm_event_destroy(oxm_event *ev);
+int oxm_event_record(oxm_ctx *ctx, oxm_event *ev);
+int oxm_event_elapsed_ms(oxm_event *start, oxm_event *stop, float *ms); /* syncs on stop */
+int oxm_stream_handle(oxm_ctx *ctx, void **cuda_stream);
+
+/* Seeded synthetic data written straight into device memory (f32, bf16 or
+ * f16): dist 0 = U(-1,1), dist 1 = N(0,1) * scale.  Element i depends only on
+ * (seed, stream, i). */
+int oxm_fill(oxm_ctx *ctx, void *dst_device, int dtype, int64_t n, uint64_t seed, uint64_t stream, int dist, double scale);
+
+/* Options (key, value):
+ *   "kernel"      0 auto, 1 force the SIMT FFMA kernel, 2 force the tcgen05
+ *                 kernel (packing operands it cannot address directly)
+ *   "tile_n"      0 auto, else 64 / 128 / 256
+ *   "cta_pair"    -1 auto, 0 one CTA per tile, 1 CTA pairs (cta_group::2)
+ *   "wait_limit_ms"  bound of every device-side wait (default 2000, or the
+ *                 environment variable OXM_WAIT_LIMIT_MS at context creation)
+ * Unknown keys or values are OXM_INVALID_ARGUMENT. */
+int oxm_set_option(oxm_ctx *ctx, const char *key, int64_t value);
+int oxm_get_option(oxm_ctx *ctx, const char *key, int64_t *value);
+
+/* Counters since context creation: kernels launched by this library, split by
+ * kind.  index 0 total, 1 tcgen05 gemm, 2 simt gemm, 3 pack. */
+int oxm_launch_counts(oxm_ctx *ctx, int64_t counts[4]);
+/* Name of the compute kernel the last matmul on this context selected. */
+const char *oxm_last_kernel(oxm_ctx *ctx);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,341 @@
+/*
+ * CPU oracle for the oxmera matmul path.  TEST INFRASTRUCTURE ONLY: see the
+ * header for what it restates and how it is pinned.  Plain C, no vector
+ * intrinsics, no fast-math: the loop order i-j-k and the "multiply, then add"
+ * of every term are part of the definition.
+ */
+#include "oxm_oracle.h"
+
+#include <math.h>
+#include <pthread.h>
+#include <stdlib.h>
+#include <string.h>
+
+/* ------------------------------------------------------------------ */
+/* 16-bit float conversions (round to nearest, ties to even)           */
+/* ------------------------------------------------------------------ */
+
+static inline uint32_t f32_bits(float x) {
+  uint32_t u;
+  memcpy(&u, &x, 4);
+  return u;
+}
+static inline float bits_f32(uint32_t u) {
+  float x;
+  memcpy(&x, &u, 4);
+  return x;
+}
+
+uint16_t orc_f32_to_bf16(float x) {
+  uint32_t u = f32_bits(x);
+  if ((u & 0x7fffffffu) > 0x7f800000u) return (uint16_t)((u >> 16) | 0x0040u); /* NaN */
+  uint32_t lsb = (u >> 16) & 1u;
+  u += 0x7fffu + lsb;
+  return (uint16_t)(u >> 16);
+}
+
+float orc_bf16_to_f32(uint16_t h) { return bits_f32((uint32_t)h << 16); }
+
+uint16_t orc_f32_to_f16(float x) {
+  uint32_t u = f32_bits(x);
+  uint32_t sign = (u >> 16) & 0x8000u;
+  uint32_t absu = u & 0x7fffffffu;
+  if (absu > 0x7f800000u) return (uint16_t)(sign | 0x7e00u);      /* NaN */
+  if (absu >= 0x47800000u) return (uint16_t)(sign | 0x7c00u);     /* >= 65536: inf */
+  if (absu < 0x33000001u) return (uint16_t)sign;                  /* rounds to zero */
+  int32_t exp = (int32_t)(absu >> 23) - 127;
+  uint32_t man = (absu & 0x7fffffu) | 0x800000u;                  /* 24-bit significand */
+  int shift = (exp < -14) ? (13 + (-14 - exp)) : 13;             /* bits to drop */
+  uint32_t kept = man >> shift;
+  uint32_t rem = man & ((1u << shift) - 1u);
+  uint32_t half = 1u << (shift - 1);
+  if (rem > half || (rem == half && (kept & 1u))) kept++;
+  uint32_t h;
+  if (exp < -14) {
+    h = kept; /* subnormal; a carry into bit 10 lands on the smallest normal */
+  } else {
+    h = ((uint32_t)(exp + 15) << 10) + (kept - 0x400u); /* carry bumps the exponent */
+  }
+  if (h >= 0x7c00u) h = 0x7c00u;
+  return (uint16_t)(sign | h);
+}
+
+float orc_f16_to_f32(uint16_t h) {
+  uint32_t sign = ((uint32_t)h & 0x8000u) << 16;
+  uint32_t exp = (h >> 10) & 0x1fu;
+  uint32_t man = h & 0x3ffu;
+  if (exp == 0) {
+    if (man == 0) return bits_f32(sign);
+    float v = (float)man * (1.0f / 16777216.0f); /* man * 2^-24, exact */
+    return sign ? -v : v;
+  }
+  if (exp == 31) return bits_f32(sign | 0x7f800000u | (man << 13));
+  return bits_f32(sign | ((exp + 112u) << 23) | (man << 13));
+}
+
+/* ------------------------------------------------------------------ */
+/* shapes                                                               */
+/* ------------------------------------------------------------------ */
+
+/* crates/oxmera-core/src/shape.rs:49-55: align trailing dims; each pair must
+ * be equal or contain a 1. */
+int orc_broadcast_shapes(const int64_t *lhs, int lhs_ndim, const int64_t *rhs,
+                         int rhs_ndim, int64_t *out_dims, int *out_ndim) {
+  int n = lhs_ndim > rhs_ndim ? lhs_ndim : rhs_ndim;
+  if (n > ORC_MAX_DIMS) return ORC_NOT_IMPLEMENTED;
+  for (int i = 0; i < n; ++i) {
+    int li = lhs_ndim - 1 - i, ri = rhs_ndim - 1 - i;
+    int64_t l = li >= 0 ? lhs[li] : 1;
+    int64_t r = ri >= 0 ? rhs[ri] : 1;
+    int64_t o;
+    if (l == r) o = l;
+    else if (l == 1) o = r;
+    else if (r == 1) o = l;
+    else return ORC_BROADCAST_INCOMPATIBLE;
+    out_dims[n - 1 - i] = o;
+  }
+  *out_ndim = n;
+  return ORC_OK;
+}
+
+static int is_matmul_dtype(int32_t d) { return d == ORC_F32 || d == ORC_BF16 || d == ORC_F16; }
+static int is_out_dtype(int32_t d) { return is_matmul_dtype(d) || d == ORC_F64; }
+
+int orc_check_matmul(const orc_view *a, const orc_view *b, const orc_view *out, int batched) {
+  if (a->ndim > ORC_MAX_DIMS || b->ndim > ORC_MAX_DIMS) return ORC_NOT_IMPLEMENTED;
+  if (!batched) {
+    /* rank-1 operands must refuse (a4 spec.rs:78-83). */
+    if (a->ndim != 2 || b->ndim != 2) return ORC_SHAPE_MISMATCH;
+  } else {
+    if (a->ndim < 2 || b->ndim < 2) return ORC_SHAPE_MISMATCH;
+  }
+  if (a->dtype != b->dtype) return ORC_DTYPE_MISMATCH;
+  if (!is_matmul_dtype(a->dtype)) return ORC_UNSUPPORTED_DTYPE;
+  int64_t m = a->shape[a->ndim - 2], k = a->shape[a->ndim - 1];
+  int64_t kb = b->shape[b->ndim - 2], n = b->shape[b->ndim - 1];
+  if (k != kb) return ORC_SHAPE_MISMATCH; /* a4 spec.rs:68-76 */
+  int64_t bdims[ORC_MAX_DIMS];
+  int bnd = 0;
+  int st = orc_broadcast_shapes(a->shape, a->ndim - 2, b->shape, b->ndim - 2, bdims, &bnd);
+  if (st != ORC_OK) return st;
+  if (out) {
+    if (!is_out_dtype(out->dtype)) return ORC_UNSUPPORTED_DTYPE;
+    if (out->ndim != bnd + 2) return ORC_SHAPE_MISMATCH;
+    for (int i = 0; i < bnd; ++i)
+      if (out->shape[i] != bdims[i]) return ORC_SHAPE_MISMATCH;
+    if (out->shape[bnd] != m || out->shape[bnd + 1] != n) return ORC_SHAPE_MISMATCH;
+  }
+  return ORC_OK;
+}
+
+/* ------------------------------------------------------------------ */
+/* the triple loop                                                      */
+/* ------------------------------------------------------------------ */
+
+static inline float load_as_f32(const void *base, int32_t dtype, int64_t idx) {
+  switch (dtype) {
+    case ORC_F32: return ((const float *)base)[idx];
+    case ORC_BF16: return orc_bf16_to_f32(((const uint16_t *)base)[idx]);
+    default: return orc_f16_to_f32(((const uint16_t *)base)[idx]);
+  }
+}
+
+static inline void store_from_f64(void *base, int32_t dtype, int64_t idx, double v) {
+  switch (dtype) {
+    case ORC_F64: ((double *)base)[idx] = v; break;
+    case ORC_F32: ((float *)base)[idx] = (float)v; break;
+    case ORC_BF16: ((uint16_t *)base)[idx] = orc_f32_to_bf16((float)v); break;
+    default: ((uint16_t *)base)[idx] = orc_f32_to_f16((float)v); break;
+  }
+}
+
+typedef struct {
+  const orc_view *a, *b, *out;
+  int acc_mode;
+  int64_t m, n, k, nbatch;
+  int bnd;                       /* number of batch dims of the output */
+  int64_t bdims[ORC_MAX_DIMS];
+  int64_t a_bs[ORC_MAX_DIMS], b_bs[ORC_MAX_DIMS], o_bs[ORC_MAX_DIMS]; /* 0 where broadcast */
+  int64_t next_row;              /* work counter over nbatch*m rows */
+  pthread_mutex_t mu;
+} mm_job;
+
+/* One output row: i fixed, loop j then k.  The A row is staged as f32 first
+ * (a pure copy through the view's strides; the arithmetic order is unchanged). */
+#define ROW_KERNEL(NAME, BT, BLOAD, ACC_T)                                              \
+  static void NAME(const float *arow, const BT *bptr, int64_t b_ks, int64_t b_ns,       \
+                   int64_t n, int64_t k, void *obase, int32_t odt, int64_t o_off,       \
+                   int64_t o_ns) {                                                      \
+    for (int64_t j = 0; j < n; ++j) {                                                   \
+      ACC_T acc = 0;                                                                    \
+      const BT *bp = bptr + j * b_ns;                                                   \
+      for (int64_t kk = 0; kk < k; ++kk) {                                              \
+        ACC_T prod = (ACC_T)arow[kk] * (ACC_T)BLOAD(bp[kk * b_ks]);                     \
+        acc = acc + prod;                                                               \
+      }                                                                                 \
+      store_from_f64(obase, odt, o_off + j * o_ns, (double)acc);                        \
+    }                                                                                   \
+  }
+
+#define ID_F32(x) (x)
+ROW_KERNEL(row_f32_native, float, ID_F32, float)
+ROW_KERNEL(row_f32_f64, float, ID_F32, double)
+ROW_KERNEL(row_bf16_native, uint16_t, orc_bf16_to_f32, float)
+ROW_KERNEL(row_bf16_f64, uint16_t, orc_bf16_to_f32, double)
+ROW_KERNEL(row_f16_native, uint16_t, orc_f16_to_f32, float)
+ROW_KERNEL(row_f16_f64, uint16_t, orc_f16_to_f32, double)
+
+static void *mm_worker(void *arg) {
+  mm_job *J = (mm_job *)arg;
+  const orc_view *a = J->a, *b = J->b, *o = J->out;
+  const int an = a->ndim, bn = b->ndim, on = o->ndim;
+  const int64_t a_ms = a->strides[an - 2], a_ks = a->strides[an - 1];
+  const int64_t b_ks = b->strides[bn - 2], b_ns = b->strides[bn - 1];
+  const int64_t o_ms = o->strides[on - 2], o_ns = o->strides[on - 1];
+  float *arow = (float *)malloc(sizeof(float) * (size_t)(J->k > 0 ? J->k : 1));
+  const int64_t total = J->nbatch * J->m;
+  const int64_t chunk = 4;
+  for (;;) {
+    pthread_mutex_lock(&J->mu);
+    int64_t r0 = J->next_row;
+    J->next_row += chunk;
+    pthread_mutex_unlock(&J->mu);
+    if (r0 >= total) break;
+    int64_t r1 = r0 + chunk < total ? r0 + chunk : total;
+    for (int64_t r = r0; r < r1; ++r) {
+      int64_t bi = r / J->m, i = r % J->m;
+      int64_t a_off = a->offset, b_off = b->offset, o_off = o->offset;
+      int64_t rem = bi;
+      for (int d = J->bnd - 1; d >= 0; --d) {
+        int64_t idx = rem % J->bdims[d];
+        rem /= J->bdims[d];
+        a_off += idx * J->a_bs[d];
+        b_off += idx * J->b_bs[d];
+        o_off += idx * J->o_bs[d];
+      }
+      a_off += i * a_ms;
+      o_off += i * o_ms;
+      for (int64_t kk = 0; kk < J->k; ++kk) arow[kk] = load_as_f32(a->base, a->dtype, a_off + kk * a_ks);
+      const int f64 = J->acc_mode == ORC_ACC_F64;
+      if (b->dtype == ORC_F32) {
+        const float *bp = (const float *)b->base + b_off;
+        (f64 ? row_f32_f64 : row_f32_native)(arow, bp, b_ks, b_ns, J->n, J->k, o->base, o->dtype, o_off, o_ns);
+      } else if (b->dtype == ORC_BF16) {
+        const uint16_t *bp = (const uint16_t *)b->base + b_off;
+        (f64 ? row_bf16_f64 : row_bf16_native)(arow, bp, b_ks, b_ns, J->n, J->k, o->base, o->dtype, o_off, o_ns);
+      } else {
+        const uint16_t *bp = (const uint16_t *)b->base + b_off;
+        (f64 ? row_f16_f64 : row_f16_native)(arow, bp, b_ks, b_ns, J->n, J->k, o->base, o->dtype, o_off, o_ns);
+      }
+    }
+  }
+  free(arow);
+  return NULL;
+}
+
+static int run_matmul(const orc_view *a, const orc_view *b, const orc_view *out,
+                      int acc_mode, int nthreads, int batched) {
+  int st = orc_check_matmul(a, b, out, batched);
+  if (st != ORC_OK) return st;
+  mm_job J;
+  memset(&J, 0, sizeof(J));
+  J.a = a; J.b = b; J.out = out; J.acc_mode = acc_mode;
+  J.m = a->shape[a->ndim - 2];
+  J.k = a->shape[a->ndim - 1];
+  J.n = b->shape[b->ndim - 1];
+  J.bnd = out->ndim - 2;
+  J.nbatch = 1;
+  for (int d = 0; d < J.bnd; ++d) {
+    J.bdims[d] = out->shape[d];
+    J.nbatch *= out->shape[d];
+    int ad = d - (J.bnd - (a->ndim - 2));
+    int bd = d - (J.bnd - (b->ndim - 2));
+    J.a_bs[d] = (ad >= 0 && a->shape[ad] != 1) ? a->strides[ad] : 0;
+    J.b_bs[d] = (bd >= 0 && b->shape[bd] != 1) ? b->strides[bd] : 0;
+    J.o_bs[d] = out->strides[d];
+  }
+  if (J.nbatch * J.m * J.n == 0) return ORC_OK;
+  pthread_mutex_init(&J.mu, NULL);
+  if (nthreads < 1) nthreads = 1;
+  if (nthreads > 256) nthreads = 256;
+  if ((int64_t)nthreads > J.nbatch * J.m) nthreads = (int)(J.nbatch * J.m);
+  if (nthreads == 1) {
+    mm_worker(&J);
+  } else {
+    pthread_t th[256];
+    for (int t = 0; t < nthreads; ++t) pthread_create(&th[t], NULL, mm_worker, &J);
+    for (int t = 0; t < nthreads; ++t) pthread_join(th[t], NULL);
+  }
+  pthread_mutex_destroy(&J.mu);
+  return ORC_OK;
+}
+
+int orc_matmul(const orc_view *a, const orc_view *b, const orc_view *out, int acc_mode, int nthreads) {
+  return run_matmul(a, b, out, acc_mode, nthreads, 0);
+}
+
+int orc_batched_matmul(const orc_view *a, const orc_view *b, const orc_view *out, int acc_mode, int nthreads) {
+  return run_matmul(a, b, out, acc_mode, nthreads, 1);
+}
+
+/* ------------------------------------------------------------------ */
+/* synthetic data                                                       */
+/* ------------------------------------------------------------------ */
+
+static inline uint64_t splitmix64(uint64_t x) {
+  x += 0x9E3779B97F4A7C15ull;
+  x = (x ^ (x >> 30)) * 0xBF58476D1CE4E5B9ull;
+  x = (x ^ (x >> 27)) * 0x94D049BB133111EBull;
+  return x ^ (x >> 31);
+}
+
+typedef struct {
+  void *dst;
+  int32_t dtype;
+  int64_t lo, hi;
+  uint64_t key;
+  int dist;
+  double scale;
+} fill_job;
+
+static void *fill_worker(void *arg) {
+  fill_job *F = (fill_job *)arg;
+  const double two_pi = 6.283185307179586476925286766559;
+  for (int64_t i = F->lo; i < F->hi; ++i) {
+    uint64_t h1 = splitmix64(F->key + 2ull * (uint64_t)i);
+    double v;
+    if (F->dist == 0) {
+      v = 2.0 * ((double)(h1 >> 11) * (1.0 / 9007199254740992.0)) - 1.0;
+    } else {
+      uint64_t h2 = splitmix64(F->key + 2ull * (uint64_t)i + 1ull);
+      double u1 = ((double)(h1 >> 11) + 1.0) * (1.0 / 9007199254740992.0);
+      double u2 = (double)(h2 >> 11) * (1.0 / 9007199254740992.0);
+      v = sqrt(-2.0 * log(u1)) * cos(two_pi * u2) * F->scale;
+    }
+    float f = (float)v;
+    if (F->dtype == ORC_F32) ((float *)F->dst)[i] = f;
+    else if (F->dtype == ORC_BF16) ((uint16_t *)F->dst)[i] = orc_f32_to_bf16(f);
+    else ((uint16_t *)F->dst)[i] = orc_f32_to_f16(f);
+  }
+  return NULL;
+}
+
+void orc_fill(void *dst, int32_t dtype, int64_t n, uint64_t seed, uint64_t stream,
+              int dist, double scale, int nthreads) {
+  uint64_t key = splitmix64(splitmix64(seed) ^ splitmix64(stream * 0xD1342543DE82EF95ull + 0x632BE59BD9B4E019ull));
+  if (nthreads < 1) nthreads = 1;
+  if (nthreads > 256) nthreads = 256;
+  if (n < 65536) nthreads = 1;
+  fill_job jobs[256];
+  pthread_t th[256];
+  int64_t per = (n + nthreads - 1) / nthreads;
+  for (int t = 0; t < nthreads; ++t) {
+    jobs[t].dst = dst; jobs[t].dtype = dtype; jobs[t].key = key;
+    jobs[t].dist = dist; jobs[t].scale = scale;
+    jobs[t].lo = t * per < n ? t * per : n;
+    jobs[t].hi = (t + 1) * per < n ? (t + 1) * per : n;
+  }
+  if (nthreads == 1) { fill_worker(&jobs[0]); return; }
+  for (int t = 0; t < nthreads; ++t) pthread_create(&th[t], NULL, fill_worker, &jobs[t]);
+  for (int t = 0; t < nthreads; ++t) pthread_join(th[t], NULL);
+}

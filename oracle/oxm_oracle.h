@@ -1,0 +1,109 @@
+/*
+ * CPU oracle for the oxmera matmul path.  TEST INFRASTRUCTURE ONLY.
+ *
+ * Nothing in the shipped library links, loads or calls this file.  It exists
+ * so that tests, the smoke check and the bench's CPU-baseline leg have a
+ * ground truth to compare the CUDA path against.
+ *
+ * What it restates: oxmera's CPU reference backend, whose matmul body is
+ * `todo!()` in the reference tree (crates/oxmera-cpu/src/lib.rs:71-76).  The
+ * behaviour is therefore taken from the contract and the spec that pin it:
+ *   - crates/oxmera-ops/src/lib.rs:53-59   [m,k] x [k,n] -> [m,n], rank 2,
+ *                                          typed errors, no coercion
+ *   - crates/oxmera-ops/src/lib.rs:9-19    same dtype, fresh contiguous output
+ *   - exercises/a4-reference-matmul/README.md:7-19  "three nested loops",
+ *                                          operands read through their views
+ *   - crates/oxmera-core/src/layout.rs:6-34 element strides, signed, offset in
+ *                                          elements
+ *   - crates/oxmera-core/src/shape.rs:49-55 NumPy broadcasting (batch dims)
+ *
+ * Parity pin: the hand-computed products and laws of
+ * exercises/a4-reference-matmul/tests/spec.rs:31-130 and
+ * crates/oxmera-cpu/tests/harness.rs:13-24 (restated as data in
+ * tests/golden/).  Accumulator width, summation order, 16-bit floats and
+ * batched matmul are NOT pinned by the reference; for those this file is the
+ * definition and parity is "unpinned" beyond the stated tolerances.
+ */
+#ifndef OXM_ORACLE_H
+#define OXM_ORACLE_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ORC_MAX_DIMS 8
+
+/* dtype tags: identical numbering to include/oxmera_b200.h */
+enum {
+  ORC_F32 = 0, ORC_F64 = 1, ORC_I32 = 2, ORC_I64 = 3, ORC_U8 = 4, ORC_BOOL = 5,
+  ORC_BF16 = 6, ORC_F16 = 7
+};
+
+/* status codes: identical numbering to include/oxmera_b200.h */
+enum {
+  ORC_OK = 0,
+  ORC_SHAPE_MISMATCH = 1,
+  ORC_BROADCAST_INCOMPATIBLE = 2,
+  ORC_DTYPE_MISMATCH = 3,
+  ORC_UNSUPPORTED_DTYPE = 4,
+  ORC_DEVICE_MISMATCH = 5,
+  ORC_INDEX_OUT_OF_BOUNDS = 6,
+  ORC_RANK_MISMATCH = 7,
+  ORC_BACKEND_UNAVAILABLE = 8,
+  ORC_NOT_IMPLEMENTED = 9
+};
+
+/* A tensor view over host memory: oxmera's Layout plus a storage pointer
+ * (crates/oxmera-core/src/layout.rs:26-34). */
+typedef struct {
+  int32_t dtype;
+  int32_t ndim;
+  int64_t shape[ORC_MAX_DIMS];
+  int64_t strides[ORC_MAX_DIMS]; /* elements, signed */
+  int64_t offset;                /* elements */
+  void *base;
+} orc_view;
+
+/* accumulation modes */
+enum {
+  ORC_ACC_NATIVE = 0, /* f32 running sum, k ascending: the naive reference */
+  ORC_ACC_F64 = 1     /* f64 running sum: the parity oracle for f32 */
+};
+
+/* Rank-2 matmul, exactly the MatmulOps::matmul contract.  `out` must have
+ * shape [m,n]; its dtype may be f32, f64, bf16 or f16 (the running sum is
+ * rounded to nearest-even on store). */
+int orc_matmul(const orc_view *a, const orc_view *b, const orc_view *out,
+               int acc_mode, int nthreads);
+
+/* Rank >= 2 with NumPy-broadcast leading dims (the batched extension). */
+int orc_batched_matmul(const orc_view *a, const orc_view *b,
+                       const orc_view *out, int acc_mode, int nthreads);
+
+/* Validation only: the status orc_matmul / orc_batched_matmul would return. */
+int orc_check_matmul(const orc_view *a, const orc_view *b, const orc_view *out,
+                     int batched);
+
+/* NumPy broadcast of two shapes; returns ORC_OK or
+ * ORC_BROADCAST_INCOMPATIBLE.  out_dims must hold ORC_MAX_DIMS entries. */
+int orc_broadcast_shapes(const int64_t *lhs, int lhs_ndim, const int64_t *rhs,
+                         int rhs_ndim, int64_t *out_dims, int *out_ndim);
+
+/* Round-to-nearest-even conversions shared by every test input. */
+uint16_t orc_f32_to_bf16(float x);
+float orc_bf16_to_f32(uint16_t h);
+uint16_t orc_f32_to_f16(float x);
+float orc_f16_to_f32(uint16_t h);
+
+/* Counter-based synthetic data: element i of stream (seed, stream) depends
+ * only on (seed, stream, i), so any slice can be generated anywhere.
+ * dist: 0 = U(-1,1), 1 = N(0,1) * scale.  dtype: f32, bf16 or f16. */
+void orc_fill(void *dst, int32_t dtype, int64_t n, uint64_t seed,
+              uint64_t stream, int dist, double scale, int nthreads);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

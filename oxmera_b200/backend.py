@@ -1,0 +1,343 @@
+"""The B200 backend and the dispatch seam.
+
+Mirrors oxmera-runtime (crates/oxmera-runtime/src/lib.rs:29-72): a `Backend`
+is the union of the op traits plus identity; `backend_for` resolves a device
+handle to the registered backend or raises BackendUnavailable; tensors route
+`matmul` through it.  `B200Backend` implements MatmulOps
+(crates/oxmera-ops/src/lib.rs:53-59) and its batched extension over the C ABI.
+The other op families are not part of this backend yet and report
+NotImplemented, the typed error the reference reserves for that
+(crates/oxmera-core/src/error.rs:88-101).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import threading
+from typing import Dict, List, Sequence
+
+import numpy as np
+
+from . import capi
+from .core import (BackendFault, BackendUnavailable, BroadcastIncompatible, DType, Device, DeviceMismatch,
+                   DTypeMismatch, Layout, NotImplementedOp, OxmeraError, ShapeMismatch, UnsupportedDType,
+                   broadcast_shapes)
+from .tensor import Tensor
+
+
+def _raise(status: int, op: str, a: Tensor | None = None, b: Tensor | None = None):
+    """Turn a C-ABI status into the typed error of oxmera_core::Error."""
+    detail = capi.last_error()
+    if status == capi.SHAPE_MISMATCH:
+        raise ShapeMismatch(a.shape if a is not None else (), b.shape if b is not None else (), op, detail)
+    if status == capi.BROADCAST_INCOMPATIBLE:
+        raise BroadcastIncompatible(a.shape if a is not None else (), b.shape if b is not None else (), detail)
+    if status == capi.DTYPE_MISMATCH:
+        raise DTypeMismatch(a.dtype if a is not None else None, b.dtype if b is not None else None, op, detail)
+    if status == capi.UNSUPPORTED_DTYPE:
+        raise UnsupportedDType(a.dtype if a is not None else None, op, detail)
+    if status == capi.DEVICE_MISMATCH:
+        raise DeviceMismatch(a.device() if a is not None else None, b.device() if b is not None else None, op, detail)
+    if status == capi.BACKEND_UNAVAILABLE:
+        raise BackendUnavailable(None, detail)
+    if status == capi.NOT_IMPLEMENTED:
+        raise NotImplementedOp(op, detail)
+    raise BackendFault(status, f"{op}: {capi.load().oxm_status_name(status).decode()}: {detail}")
+
+
+class B200Backend:
+    """One instance serves one Device::Cuda{index}.  Thread-safe: the C
+    library serialises launches per context (`Backend: Send + Sync`)."""
+
+    def __init__(self, index: int = 0):
+        self._lib = capi.load()
+        self._index = index
+        ctx = C.c_void_p()
+        st = self._lib.oxm_ctx_create(index, C.byref(ctx))
+        if st != capi.OK:
+            if st == capi.BACKEND_UNAVAILABLE:
+                raise BackendUnavailable(Device.cuda(index), capi.last_error())
+            _raise(st, "ctx_create")
+        self._ctx = ctx
+        self._pinned: List[int] = []
+
+    # ---- identity (crates/oxmera-runtime/src/lib.rs:30-33) ----
+    def device(self) -> Device:
+        return Device.cuda(self._index)
+
+    def name(self) -> str:
+        return self._lib.oxm_backend_name().decode()
+
+    # ---- MatmulOps ----
+    def matmul(self, lhs: Tensor, rhs: Tensor) -> Tensor:
+        """[m,k] x [k,n] -> [m,n], rank 2 exactly; a fresh contiguous tensor
+        on the operands' device (crates/oxmera-ops/src/lib.rs:16-17,53-59)."""
+        return self._mm(lhs, rhs, batched=False)
+
+    def batched_matmul(self, lhs: Tensor, rhs: Tensor) -> Tensor:
+        """Rank >= 2; leading dims broadcast by NumPy rules."""
+        return self._mm(lhs, rhs, batched=True)
+
+    def matmul_into(self, lhs: Tensor, rhs: Tensor, out: Tensor, batched: bool = True) -> Tensor:
+        """Write the product through `out`'s layout (a shard writing into a
+        window of its parent).  `out` must not alias the operands."""
+        fn = self._lib.oxm_batched_matmul if batched else self._lib.oxm_matmul
+        st = fn(self._ctx, C.byref(lhs._view()), C.byref(rhs._view()), C.byref(out._view()))
+        if st != capi.OK:
+            _raise(st, "batched_matmul" if batched else "matmul", lhs, rhs)
+        return out
+
+    def _mm(self, lhs: Tensor, rhs: Tensor, batched: bool) -> Tensor:
+        op = "batched_matmul" if batched else "matmul"
+        for t in (lhs, rhs):
+            if t.device() != self.device():
+                raise DeviceMismatch(t.device(), self.device(), op)
+        # The output shape: validation proper happens in the C library, which
+        # reports the typed error; here only enough to allocate.
+        la, lb = lhs.shape, rhs.shape
+        if len(la) >= 2 and len(lb) >= 2 and (batched or (len(la) == 2 and len(lb) == 2)):
+            try:
+                bshape = broadcast_shapes(la[:-2], lb[:-2])
+            except BroadcastIncompatible:
+                raise BroadcastIncompatible(la, lb)
+            oshape = tuple(bshape) + (la[-2], lb[-1])
+        else:
+            oshape = (1, 1)  # placeholder; the library refuses the ranks
+        out = Tensor.empty(oshape, lhs.dtype, self)
+        return self.matmul_into(lhs, rhs, out, batched)
+
+    def matmul_host(self, a: np.ndarray, b: np.ndarray, dtype: DType, out: np.ndarray | None = None) -> np.ndarray:
+        """Product of two HOST arrays (any numpy strides): staged to the
+        device, multiplied, copied back (into `out` when given, e.g. a
+        page-locked buffer).  bf16 arrays are uint16 bits."""
+        bshape = broadcast_shapes(a.shape[:-2], b.shape[:-2])
+        if out is None:
+            out = np.empty(tuple(bshape) + (a.shape[-2], b.shape[-1]), dtype=a.dtype)
+        esz = dtype.size_in_bytes()
+        va = capi.make_view(int(dtype), a.shape, [s // esz for s in a.strides], 0, a.ctypes.data, self._index)
+        vb = capi.make_view(int(dtype), b.shape, [s // esz for s in b.strides], 0, b.ctypes.data, self._index)
+        vo = capi.make_view(int(dtype), out.shape, [s // esz for s in out.strides], 0, out.ctypes.data, self._index)
+        st = self._lib.oxm_batched_matmul_host(self._ctx, C.byref(va), C.byref(vb), C.byref(vo))
+        if st != capi.OK:
+            _raise(st, "batched_matmul")
+        return out
+
+    # ---- the op families this backend does not carry yet ----
+    def _unsupported(self, op: str):
+        raise NotImplementedOp(op, f"backend {self.name()} (matmul path only)")
+
+    def neg(self, a): self._unsupported("neg")
+    def exp(self, a): self._unsupported("exp")
+    def ln(self, a): self._unsupported("ln")
+    def abs(self, a): self._unsupported("abs")
+    def add(self, lhs, rhs): self._unsupported("add")
+    def sub(self, lhs, rhs): self._unsupported("sub")
+    def mul(self, lhs, rhs): self._unsupported("mul")
+    def div(self, lhs, rhs): self._unsupported("div")
+    def sum(self, a, axes): self._unsupported("sum")
+    def max(self, a, axes): self._unsupported("max")
+
+    # ---- storage plumbing used by Tensor ----
+    def _alloc(self, nbytes: int) -> int:
+        p = C.c_void_p()
+        st = self._lib.oxm_alloc(self._ctx, nbytes, C.byref(p))
+        if st != capi.OK:
+            _raise(st, "alloc")
+        return p.value
+
+    def _free(self, ptr: int) -> None:
+        if self._ctx:
+            self._lib.oxm_free(self._ctx, ptr)
+
+    def _h2d(self, dst: int, src: int, nbytes: int) -> None:
+        st = self._lib.oxm_h2d(self._ctx, dst, src, nbytes)
+        if st != capi.OK:
+            _raise(st, "h2d")
+        # numpy buffers are pageable: the runtime stages them before returning
+
+    def _d2h(self, dst: int, src: int, nbytes: int) -> None:
+        st = self._lib.oxm_d2h(self._ctx, dst, src, nbytes)
+        if st != capi.OK:
+            _raise(st, "d2h")
+
+    def _materialize(self, t: Tensor) -> Tensor:
+        out = Tensor.empty(t.shape, t.dtype, self)
+        st = self._lib.oxm_contiguous(self._ctx, C.byref(t._view()), C.byref(out._view()))
+        if st != capi.OK:
+            _raise(st, "contiguous", t, out)
+        return out
+
+    def synthetic(self, shape: Sequence[int], dtype: DType, seed: int, stream: int, dist: str = "normal",
+                  scale: float = 1.0) -> Tensor:
+        """A contiguous tensor of seeded synthetic data generated on the device:
+        dist "uniform" = U(-1,1), "normal" = N(0,1) * scale."""
+        t = Tensor.empty(shape, dtype, self)
+        n = 1
+        for s_ in t.shape:
+            n *= s_
+        st = self._lib.oxm_fill(self._ctx, t.storage().ptr, int(dtype), n, seed, stream,
+                                0 if dist == "uniform" else 1, scale)
+        if st != capi.OK:
+            _raise(st, "fill")
+        return t
+
+    def pinned_empty(self, shape: Sequence[int], np_dtype) -> np.ndarray:
+        """A numpy array over page-locked host memory (freed with the backend)."""
+        n = int(np.prod(shape)) * np.dtype(np_dtype).itemsize
+        p = C.c_void_p()
+        st = self._lib.oxm_host_alloc(max(n, 16), C.byref(p))
+        if st != capi.OK:
+            _raise(st, "host_alloc")
+        self._pinned.append(p.value)
+        buf = (C.c_uint8 * max(n, 16)).from_address(p.value)
+        return np.frombuffer(buf, dtype=np_dtype, count=int(np.prod(shape))).reshape(shape)
+
+    def synchronize(self) -> None:
+        st = self._lib.oxm_sync(self._ctx)
+        if st != capi.OK:
+            _raise(st, "sync")
+
+    # ---- instrumentation ----
+    def set_option(self, key: str, value: int) -> None:
+        st = self._lib.oxm_set_option(self._ctx, key.encode(), value)
+        if st != capi.OK:
+            _raise(st, "set_option")
+
+    def launch_counts(self) -> Dict[str, int]:
+        arr = (C.c_int64 * 4)()
+        self._lib.oxm_launch_counts(self._ctx, arr)
+        return {"total": arr[0], "tcgen05": arr[1], "simt": arr[2], "pack": arr[3]}
+
+    def last_kernel(self) -> str:
+        return self._lib.oxm_last_kernel(self._ctx).decode()
+
+    def timer(self):
+        return _Timer(self)
+
+    def close(self) -> None:
+        if self._ctx:
+            self._lib.oxm_sync(self._ctx)
+            for p in self._pinned:
+                self._lib.oxm_host_free(p)
+            self._pinned = []
+            self._lib.oxm_ctx_destroy(self._ctx)
+            self._ctx = None
+
+
+class _Timer:
+    """CUDA events on the backend's stream."""
+
+    def __init__(self, backend: B200Backend):
+        self.b = backend
+        self.e0, self.e1 = C.c_void_p(), C.c_void_p()
+        for e in (self.e0, self.e1):
+            st = backend._lib.oxm_event_create(backend._ctx, C.byref(e))
+            if st != capi.OK:
+                _raise(st, "event_create")
+
+    def start(self):
+        self.b._lib.oxm_event_record(self.b._ctx, self.e0)
+
+    def stop(self):
+        self.b._lib.oxm_event_record(self.b._ctx, self.e1)
+
+    def elapsed_ms(self) -> float:
+        ms = C.c_float()
+        st = self.b._lib.oxm_event_elapsed_ms(self.e0, self.e1, C.byref(ms))
+        if st != capi.OK:
+            _raise(st, "event_elapsed")
+        return float(ms.value)
+
+
+# ---------------------------------------------------------------------------
+# registry (crates/oxmera-runtime/src/lib.rs:36-53)
+# ---------------------------------------------------------------------------
+_registry: Dict[Device, object] = {}
+_registry_lock = threading.Lock()
+
+
+def register_backend(backend) -> None:
+    """Register a backend for its device, replacing any previous registration."""
+    with _registry_lock:
+        _registry[backend.device()] = backend
+
+
+def backend_for(device: Device):
+    """The backend serving `device`; an unregistered device is
+    BackendUnavailable, never a crash."""
+    with _registry_lock:
+        b = _registry.get(device)
+    if b is None:
+        raise BackendUnavailable(device)
+    return b
+
+
+def unregister_all() -> None:
+    with _registry_lock:
+        _registry.clear()
+
+
+# ---------------------------------------------------------------------------
+# collective-free sharding over the GPUs of one box
+# ---------------------------------------------------------------------------
+def shard_ranges(total: int, parts: int) -> List[range]:
+    """Split [0, total) into `parts` contiguous ranges whose sizes differ by at
+    most one (the first `total % parts` ranges take the extra element)."""
+    base, extra = divmod(total, parts)
+    out, start = [], 0
+    for r in range(parts):
+        n = base + (1 if r < extra else 0)
+        out.append(range(start, start + n))
+        start += n
+    return out
+
+
+def shard_plan(a_shape: Sequence[int], b_shape: Sequence[int], parts: int):
+    """How a matmul splits across `parts` devices with no exchange step:
+    along the leading batch dim of the (broadcast) output when there is one,
+    else along the M rows of A.  Returns (axis, ranges) with axis "batch" or
+    "rows".  K is never split: that would need a reduction."""
+    bshape = broadcast_shapes(tuple(a_shape)[:-2], tuple(b_shape)[:-2])
+    if len(bshape) >= 1 and bshape[0] >= parts:
+        return "batch", shard_ranges(bshape[0], parts)
+    return "rows", shard_ranges(a_shape[-2], parts)
+
+
+def sharded_matmul_host(backends: Sequence[B200Backend], a: np.ndarray, b: np.ndarray, dtype: DType) -> np.ndarray:
+    """Multiply host arrays on several GPUs: each backend gets its slice of
+    the batch (or of A's rows) plus whatever it needs of the other operand,
+    one host thread per device; the first typed error is re-raised.  No device
+    reads another device's memory and nothing is reduced."""
+    parts = len(backends)
+    axis, ranges = shard_plan(a.shape, b.shape, parts)
+    bshape = broadcast_shapes(a.shape[:-2], b.shape[:-2])
+    out = np.empty(tuple(bshape) + (a.shape[-2], b.shape[-1]), dtype=a.dtype)
+    errors: List[BaseException] = []
+
+    def work(rank: int):
+        try:
+            rg = ranges[rank]
+            if len(rg) == 0:
+                return
+            if axis == "batch":
+                lead = len(bshape)
+                def cut(x):
+                    pos = x.ndim - 2 - lead  # index of the leading batch dim in x, if it has one
+                    if pos < 0 or x.shape[pos] == 1:
+                        return x
+                    idx = [slice(None)] * x.ndim
+                    idx[pos] = slice(rg.start, rg.stop)
+                    return x[tuple(idx)]
+                out[rg.start:rg.stop] = backends[rank].matmul_host(cut(a), cut(b), dtype)
+            else:
+                out[..., rg.start:rg.stop, :] = backends[rank].matmul_host(a[..., rg.start:rg.stop, :], b, dtype)
+        except BaseException as e:  # propagate to the caller's thread
+            errors.append(e)
+
+    threads = [threading.Thread(target=work, args=(r,)) for r in range(parts)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    if errors:
+        raise errors[0]
+    return out

@@ -1,0 +1,882 @@
+// C ABI of the oxmera B200 backend (declared in include/oxmera_b200.h):
+// argument validation with oxmera's typed errors, view normalisation, kernel
+// selection and launch.  No CPU compute path exists here: an operation either
+// runs on the GPU or returns an error.
+#include "../../include/oxmera_b200.h"
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "gemm_tcgen05.cuh"
+#include "kernels_simt.cuh"
+
+namespace {
+
+using namespace oxm;
+
+thread_local std::string g_last_error;
+
+int fail(int status, const char *fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof(buf), fmt, ap);
+  va_end(ap);
+  g_last_error = buf;
+  return status;
+}
+
+#define CUDA_TRY(expr)                                                                   \
+  do {                                                                                   \
+    cudaError_t e__ = (expr);                                                            \
+    if (e__ != cudaSuccess)                                                              \
+      return fail(OXM_CUDA_ERROR, "%s failed: %s", #expr, cudaGetErrorString(e__));      \
+  } while (0)
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+struct Workspace {
+  void *ptr = nullptr;
+  size_t bytes = 0;
+};
+
+}  // namespace
+
+struct oxm_ctx {
+  int device = 0;
+  int num_sms = 0;
+  cudaStream_t stream = nullptr;
+  uint32_t *status_dev = nullptr;   // device status word written by kernels
+  uint32_t *status_host = nullptr;  // pinned mirror
+  EncodeTiledFn encode = nullptr;
+  std::mutex mu;
+  std::mutex host_mu;  // serialises calls that use the host staging buffers
+  Workspace pack_ws[2];
+  Workspace host_stage[3];
+  // options
+  int64_t opt_kernel = 0, opt_tile_n = 0, opt_cta_pair = -1, opt_wait_limit_ms = 2000;
+  int64_t launches[4] = {0, 0, 0, 0};
+  char last_kernel[96] = "none";
+};
+
+struct oxm_event {
+  cudaEvent_t ev = nullptr;
+  int device = 0;
+};
+
+namespace {
+
+int dtype_size(int dt) {
+  switch (dt) {
+    case OXM_F32: case OXM_I32: return 4;
+    case OXM_F64: case OXM_I64: return 8;
+    case OXM_U8: case OXM_BOOL: return 1;
+    case OXM_BF16: case OXM_F16: return 2;
+    default: return 0;
+  }
+}
+
+const char *dtype_name(int dt) {
+  static const char *names[] = {"F32", "F64", "I32", "I64", "U8", "Bool", "BF16", "F16"};
+  return (dt >= 0 && dt < 8) ? names[dt] : "?";
+}
+
+std::string shape_str(const oxm_view *v) {
+  std::string s = "[";
+  for (int i = 0; i < v->ndim; ++i) {
+    if (i) s += ", ";
+    s += std::to_string(v->shape[i]);
+  }
+  return s + "]";
+}
+
+bool is_matmul_dtype(int dt) { return dt == OXM_F32 || dt == OXM_BF16 || dt == OXM_F16; }
+
+// The checks of MatmulOps::matmul, in the order the reference's errors imply:
+// rank, device, dtype, inner dimension, batch broadcast, output shape.
+int validate(const oxm_ctx *ctx, const oxm_view *a, const oxm_view *b, const oxm_view *out, bool batched,
+             bool host_views) {
+  const char *op = batched ? "batched_matmul" : "matmul";
+  if (!ctx || !a || !b || !out) return fail(OXM_INVALID_ARGUMENT, "%s: null argument", op);
+  for (const oxm_view *v : {a, b, out}) {
+    if (v->ndim < 0 || v->ndim > OXM_MAX_DIMS) return fail(OXM_NOT_IMPLEMENTED, "%s is not implemented for rank %d", op, v->ndim);
+    for (int i = 0; i < v->ndim; ++i)
+      if (v->shape[i] < 0) return fail(OXM_INVALID_ARGUMENT, "%s: negative extent in %s", op, shape_str(v).c_str());
+  }
+  if (!batched) {
+    if (a->ndim != 2 || b->ndim != 2)
+      return fail(OXM_SHAPE_MISMATCH, "shape mismatch: expected rank-2 operands, got %s and %s in %s",
+                  shape_str(a).c_str(), shape_str(b).c_str(), op);
+  } else if (a->ndim < 2 || b->ndim < 2) {
+    return fail(OXM_SHAPE_MISMATCH, "shape mismatch: expected operands of rank >= 2, got %s and %s in %s",
+                shape_str(a).c_str(), shape_str(b).c_str(), op);
+  }
+  if (!host_views) {
+    if (a->device != b->device)
+      return fail(OXM_DEVICE_MISMATCH, "device mismatch: Cuda{index: %d} vs Cuda{index: %d} in %s", a->device, b->device, op);
+    if (a->device != ctx->device || out->device != ctx->device)
+      return fail(OXM_DEVICE_MISMATCH, "device mismatch: operands on Cuda{index: %d}, output on Cuda{index: %d}, backend serves Cuda{index: %d} in %s",
+                  a->device, out->device, ctx->device, op);
+  }
+  if (a->dtype != b->dtype)
+    return fail(OXM_DTYPE_MISMATCH, "dtype mismatch: expected %s, got %s in %s", dtype_name(a->dtype), dtype_name(b->dtype), op);
+  if (!is_matmul_dtype(a->dtype))
+    return fail(OXM_UNSUPPORTED_DTYPE, "dtype %s is not supported by %s", dtype_name(a->dtype), op);
+  if (out->dtype != a->dtype)
+    return fail(OXM_DTYPE_MISMATCH, "dtype mismatch: expected %s, got %s in %s (output)", dtype_name(a->dtype), dtype_name(out->dtype), op);
+  const int64_t m = a->shape[a->ndim - 2], k = a->shape[a->ndim - 1];
+  const int64_t kb = b->shape[b->ndim - 2], n = b->shape[b->ndim - 1];
+  if (k != kb)
+    return fail(OXM_SHAPE_MISMATCH, "shape mismatch: expected [%lld, %lld], got %s in %s (inner dimensions of %s x %s)",
+                (long long)k, (long long)n, shape_str(b).c_str(), op, shape_str(a).c_str(), shape_str(b).c_str());
+  const int abn = a->ndim - 2, bbn = b->ndim - 2;
+  const int nbd = std::max(abn, bbn);
+  int64_t bd[OXM_MAX_DIMS];
+  for (int i = 0; i < nbd; ++i) {
+    const int ai = abn - 1 - i, bi = bbn - 1 - i;
+    const int64_t l = ai >= 0 ? a->shape[ai] : 1, r = bi >= 0 ? b->shape[bi] : 1;
+    if (l != r && l != 1 && r != 1)
+      return fail(OXM_BROADCAST_INCOMPATIBLE, "cannot broadcast %s with %s", shape_str(a).c_str(), shape_str(b).c_str());
+    bd[nbd - 1 - i] = (l == 1) ? r : l;
+  }
+  bool out_ok = out->ndim == nbd + 2;
+  for (int i = 0; out_ok && i < nbd; ++i) out_ok = out->shape[i] == bd[i];
+  if (out_ok) out_ok = out->shape[nbd] == m && out->shape[nbd + 1] == n;
+  if (!out_ok) {
+    std::string exp = "[";
+    for (int i = 0; i < nbd; ++i) exp += std::to_string(bd[i]) + ", ";
+    exp += std::to_string(m) + ", " + std::to_string(n) + "]";
+    return fail(OXM_SHAPE_MISMATCH, "shape mismatch: expected %s, got %s in %s (output)", exp.c_str(), shape_str(out).c_str(), op);
+  }
+  return OXM_OK;
+}
+
+// A matmul problem with coalesced batch dims.  B is held as rows = N, so both
+// operands are "rows x K" matrices.
+struct Problem {
+  int dtype, elt;
+  int64_t M, N, K;
+  int nbd;
+  int64_t bdims[OXM_MAX_DIMS];
+  const void *a, *b;
+  void *o;
+  int64_t a_off, b_off, o_off;
+  int64_t a_rs, a_ks, b_rs, b_ks, o_rs, o_cs;
+  int64_t a_bs[OXM_MAX_DIMS], b_bs[OXM_MAX_DIMS], o_bs[OXM_MAX_DIMS];
+  int64_t nbatch;
+};
+
+Problem normalise(const oxm_view *a, const oxm_view *b, const oxm_view *out) {
+  Problem P{};
+  P.dtype = a->dtype;
+  P.elt = dtype_size(a->dtype);
+  P.M = a->shape[a->ndim - 2];
+  P.K = a->shape[a->ndim - 1];
+  P.N = b->shape[b->ndim - 1];
+  P.a = a->base; P.b = b->base; P.o = out->base;
+  P.a_off = a->offset; P.b_off = b->offset; P.o_off = out->offset;
+  P.a_rs = a->strides[a->ndim - 2]; P.a_ks = a->strides[a->ndim - 1];
+  P.b_ks = b->strides[b->ndim - 2]; P.b_rs = b->strides[b->ndim - 1];
+  P.o_rs = out->strides[out->ndim - 2]; P.o_cs = out->strides[out->ndim - 1];
+  const int nbd = out->ndim - 2;
+  // Gather batch dims (dropping extent-1 dims), broadcast strides as 0.
+  int n = 0;
+  int64_t dims[OXM_MAX_DIMS], as[OXM_MAX_DIMS], bs[OXM_MAX_DIMS], os[OXM_MAX_DIMS];
+  for (int d = 0; d < nbd; ++d) {
+    if (out->shape[d] == 1) continue;
+    const int ad = d - (nbd - (a->ndim - 2)), bd = d - (nbd - (b->ndim - 2));
+    dims[n] = out->shape[d];
+    as[n] = (ad >= 0 && a->shape[ad] != 1) ? a->strides[ad] : 0;
+    bs[n] = (bd >= 0 && b->shape[bd] != 1) ? b->strides[bd] : 0;
+    os[n] = out->strides[d];
+    ++n;
+  }
+  // Merge neighbours that every tensor walks with one stride.
+  int w = 0;
+  for (int d = 0; d < n; ++d) {
+    if (w > 0 && as[w - 1] == as[d] * dims[d] && bs[w - 1] == bs[d] * dims[d] && os[w - 1] == os[d] * dims[d]) {
+      dims[w - 1] *= dims[d];
+      as[w - 1] = as[d]; bs[w - 1] = bs[d]; os[w - 1] = os[d];
+    } else {
+      dims[w] = dims[d]; as[w] = as[d]; bs[w] = bs[d]; os[w] = os[d];
+      ++w;
+    }
+  }
+  // A single batch dim over a shared B folds into M: one tall GEMM.
+  if (w == 1 && bs[0] == 0 && as[0] == P.M * P.a_rs && os[0] == P.M * P.o_rs && P.M > 0) {
+    P.M *= dims[0];
+    w = 0;
+  }
+  P.nbd = w;
+  P.nbatch = 1;
+  for (int d = 0; d < w; ++d) {
+    P.bdims[d] = dims[d]; P.a_bs[d] = as[d]; P.b_bs[d] = bs[d]; P.o_bs[d] = os[d];
+    P.nbatch *= dims[d];
+  }
+  return P;
+}
+
+// ---------------------------------------------------------------------------
+// SIMT path
+// ---------------------------------------------------------------------------
+int launch_simt(oxm_ctx *ctx, const Problem &P) {
+  if (P.nbd > kSimtMaxBatchDims) return fail(OXM_NOT_IMPLEMENTED, "matmul is not implemented for %d batch dims", P.nbd);
+  if (P.M > INT32_MAX || P.N > INT32_MAX || P.K > INT32_MAX) return fail(OXM_NOT_IMPLEMENTED, "matmul is not implemented for extents above 2^31");
+  SimtParams p{};
+  p.a = P.a; p.b = P.b; p.out = P.o;
+  p.dtype = P.dtype; p.out_dtype = P.dtype;
+  p.M = (int32_t)P.M; p.N = (int32_t)P.N; p.K = (int32_t)P.K;
+  p.tiles_m = (int32_t)((P.M + 63) / 64); p.tiles_n = (int32_t)((P.N + 63) / 64);
+  p.a_off = P.a_off; p.b_off = P.b_off; p.o_off = P.o_off;
+  p.a_rs = P.a_rs; p.a_cs = P.a_ks; p.b_rs = P.b_ks; p.b_cs = P.b_rs; p.o_rs = P.o_rs; p.o_cs = P.o_cs;
+  p.nbd = P.nbd;
+  for (int d = 0; d < P.nbd; ++d) {
+    p.bdims[d] = (int32_t)P.bdims[d]; p.a_bs[d] = P.a_bs[d]; p.b_bs[d] = P.b_bs[d]; p.o_bs[d] = P.o_bs[d];
+  }
+  const int64_t blocks = (int64_t)p.tiles_m * p.tiles_n * P.nbatch;
+  if (blocks > INT32_MAX) return fail(OXM_NOT_IMPLEMENTED, "matmul is not implemented for %lld output tiles", (long long)blocks);
+  gemm_simt_kernel<<<(unsigned)blocks, 256, 0, ctx->stream>>>(p);
+  CUDA_TRY(cudaGetLastError());
+  ctx->launches[0]++; ctx->launches[2]++;
+  snprintf(ctx->last_kernel, sizeof(ctx->last_kernel), "gemm_simt_ffma_64x64");
+  return OXM_OK;
+}
+
+// ---------------------------------------------------------------------------
+// tensor-core path
+// ---------------------------------------------------------------------------
+
+// One operand as the TMA engine will see it.
+struct Staged {
+  const void *ptr;     // address of element (0,0) of batch 0
+  bool mn_major;
+  int64_t rows, K;     // K in staged elements
+  int64_t ld_bytes;    // stride of the non-contiguous matrix dim
+  int64_t nb;          // collapsed batch count
+  int64_t bs_bytes;    // batch stride
+  int32_t bmul[kMaxBatchDims];
+};
+
+int grow(oxm_ctx *ctx, Workspace &w, size_t bytes) {
+  if (w.bytes >= bytes) return OXM_OK;
+  if (w.ptr) CUDA_TRY(cudaFreeAsync(w.ptr, ctx->stream));
+  w.ptr = nullptr; w.bytes = 0;
+  size_t want = std::max(bytes, (size_t)1 << 20);
+  CUDA_TRY(cudaMallocAsync(&w.ptr, want, ctx->stream));
+  w.bytes = want;
+  return OXM_OK;
+}
+
+// Can the TMA engine address this operand in place?  Fills `s` when it can.
+bool stage_direct(const Problem &P, bool is_b, Staged &s) {
+  if (P.elt != 2) return false;
+  const void *base = is_b ? P.b : P.a;
+  const int64_t off = is_b ? P.b_off : P.a_off;
+  const int64_t rows = is_b ? P.N : P.M, K = P.K;
+  const int64_t rs = is_b ? P.b_rs : P.a_rs, ks = is_b ? P.b_ks : P.a_ks;
+  const int64_t *bs = is_b ? P.b_bs : P.a_bs;
+  const uintptr_t addr = reinterpret_cast<uintptr_t>(base) + off * P.elt;
+  if (addr % 16) return false;
+  auto ld_ok = [&](int64_t ld, int64_t extent) { return extent == 1 || (ld > 0 && (ld * P.elt) % 16 == 0 && ld * P.elt < (1ll << 40)); };
+  bool k_major = (ks == 1 || K == 1) && ld_ok(rs, rows);
+  bool mn_major = !k_major && (rs == 1 || rows == 1) && ld_ok(ks, K);
+  if (!k_major && !mn_major) return false;
+  if (rows >= (1ll << 31) || K >= (1ll << 31)) return false;
+  s.ptr = reinterpret_cast<const void *>(addr);
+  s.mn_major = mn_major;
+  s.rows = rows; s.K = K;
+  const int64_t inner = k_major ? K : rows;
+  const int64_t outer = k_major ? rows : K;
+  int64_t ld = k_major ? rs : ks;
+  if (outer == 1) ld = (inner * P.elt + 15) / 16 * 16 / P.elt;  // any legal value: never stepped
+  s.ld_bytes = ld * P.elt;
+  // Own (non-broadcast) batch dims must fold into one strided dim.
+  s.nb = 1; s.bs_bytes = 0;
+  int64_t inner_stride = 0;
+  bool have = false;
+  for (int d = P.nbd - 1; d >= 0; --d) {
+    if (bs[d] == 0) { s.bmul[d] = 0; continue; }
+    if (!have) { inner_stride = bs[d]; have = true; }
+    else if (bs[d] != inner_stride * s.nb) return false;
+    if (s.nb > INT32_MAX) return false;
+    s.bmul[d] = (int32_t)s.nb;
+    s.nb *= P.bdims[d];
+  }
+  if (have) {
+    if (inner_stride <= 0 || (inner_stride * P.elt) % 16 || inner_stride * P.elt >= (1ll << 40)) return false;
+    s.bs_bytes = inner_stride * P.elt;
+  } else {
+    s.bs_bytes = std::max<int64_t>(16, (s.ld_bytes * outer + 15) / 16 * 16);
+  }
+  if (s.nb >= (1ll << 31)) return false;
+  return true;
+}
+
+// Pack an operand into K-major rows in workspace `slot`.  f32 becomes the
+// three-term TF32 layout (see pack_kernel).
+int stage_packed(oxm_ctx *ctx, const Problem &P, bool is_b, int slot, Staged &s) {
+  const int64_t rows = is_b ? P.N : P.M;
+  const int64_t rs = is_b ? P.b_rs : P.a_rs, ks = is_b ? P.b_ks : P.a_ks;
+  const int64_t *bs = is_b ? P.b_bs : P.a_bs;
+  const bool split = P.elt == 4;
+  const int64_t Kp = split ? (P.K + 31) / 32 * 32 : (P.K + 7) / 8 * 8;
+  const int64_t row_elems = split ? 3 * Kp : Kp;
+  PackParams pp{};
+  pp.src = is_b ? P.b : P.a;
+  pp.elt = P.elt;
+  pp.mode = split ? (is_b ? 2 : 1) : 0;
+  pp.rows = (int32_t)rows; pp.K = (int32_t)P.K; pp.Kp = (int32_t)Kp;
+  pp.dst_row_elems = row_elems;
+  pp.src_off = is_b ? P.b_off : P.a_off;
+  pp.src_rs = rs; pp.src_ks = ks;
+  // Only the operand's own batch dims are materialised; broadcast dims stay virtual.
+  int64_t nb = 1;
+  pp.nbd = 0;
+  for (int d = 0; d < P.nbd; ++d) s.bmul[d] = 0;
+  for (int d = P.nbd - 1; d >= 0; --d) {
+    if (bs[d] == 0) continue;
+    s.bmul[d] = (int32_t)nb;
+    nb *= P.bdims[d];
+  }
+  for (int d = 0; d < P.nbd; ++d) {
+    if (bs[d] == 0) continue;
+    pp.bdims[pp.nbd] = (int32_t)P.bdims[d];
+    pp.src_bs[pp.nbd] = bs[d];
+    pp.nbd++;
+  }
+  if (rows >= (1ll << 31) || Kp >= (1ll << 30) || nb >= (1ll << 31)) return fail(OXM_NOT_IMPLEMENTED, "matmul is not implemented for extents above 2^31");
+  const size_t bytes = (size_t)nb * rows * row_elems * P.elt;
+  int st = grow(ctx, ctx->pack_ws[slot], bytes);
+  if (st) return st;
+  pp.dst = ctx->pack_ws[slot].ptr;
+  pp.tiles_r = (int32_t)((rows + 31) / 32);
+  pp.tiles_k = (int32_t)((Kp + 31) / 32);
+  const int64_t blocks = (int64_t)pp.tiles_r * pp.tiles_k * nb;
+  if (blocks > INT32_MAX) return fail(OXM_NOT_IMPLEMENTED, "matmul is not implemented for %lld pack tiles", (long long)blocks);
+  pack_kernel<<<(unsigned)blocks, 256, 0, ctx->stream>>>(pp);
+  CUDA_TRY(cudaGetLastError());
+  ctx->launches[0]++; ctx->launches[3]++;
+  s.ptr = pp.dst;
+  s.mn_major = false;
+  s.rows = rows; s.K = row_elems;
+  s.ld_bytes = row_elems * P.elt;
+  s.nb = nb;
+  s.bs_bytes = rows * row_elems * P.elt;
+  return OXM_OK;
+}
+
+int make_map(oxm_ctx *ctx, CUtensorMap *tm, const Staged &s, int dtype, int elt, int box_rows_kmajor, int box_k) {
+  const CUtensorMapDataType dt = dtype == OXM_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                : dtype == OXM_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                    : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  const cuuint32_t inner_box = (cuuint32_t)(kStageKBytes / elt);
+  cuuint64_t dims[3];
+  cuuint32_t box[3];
+  if (s.mn_major) {
+    dims[0] = (cuuint64_t)s.rows; dims[1] = (cuuint64_t)s.K;
+    box[0] = inner_box; box[1] = (cuuint32_t)box_k;
+  } else {
+    dims[0] = (cuuint64_t)s.K; dims[1] = (cuuint64_t)s.rows;
+    box[0] = inner_box; box[1] = (cuuint32_t)box_rows_kmajor;
+  }
+  dims[2] = (cuuint64_t)s.nb;
+  box[2] = 1;
+  cuuint64_t strides[2] = {(cuuint64_t)s.ld_bytes, (cuuint64_t)s.bs_bytes};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = ctx->encode(tm, dt, 3, const_cast<void *>(s.ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(OXM_CUDA_ERROR, "cuTensorMapEncodeTiled failed (%d): dims [%llu,%llu,%llu] strides [%llu,%llu] box [%u,%u,1] ptr %p",
+                (int)r, (unsigned long long)dims[0], (unsigned long long)dims[1], (unsigned long long)dims[2],
+                (unsigned long long)strides[0], (unsigned long long)strides[1], box[0], box[1], s.ptr);
+  return OXM_OK;
+}
+
+template <int BN, int STAGES, int A_MN, int B_MN, int TF32, int PAIR>
+int launch_instance(oxm_ctx *ctx, const CUtensorMap &tmA, const CUtensorMap &tmB, const GemmParams &p, int grid) {
+  using L = GemmSmem<BN, STAGES, PAIR>;
+  auto kern = gemm_tcgen05_kernel<BN, STAGES, A_MN, B_MN, TF32, PAIR>;
+  static_assert(L::kDynamic <= 232448, "shared memory budget of one SM");
+  CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic));
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3((unsigned)grid, 1, 1);
+  cfg.blockDim = dim3(kGemmThreads, 1, 1);
+  cfg.dynamicSmemBytes = L::kDynamic;
+  cfg.stream = ctx->stream;
+  cudaLaunchAttribute attr[1];
+  if (PAIR) {
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+  }
+  CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, tmA, tmB, p));
+  snprintf(ctx->last_kernel, sizeof(ctx->last_kernel), "gemm_tcgen05_%s_bn%d_s%d_%c%c_%s", TF32 ? "tf32x3" : "f16", BN,
+           STAGES, A_MN ? 'm' : 'k', B_MN ? 'n' : 'k', PAIR ? "pair" : "1cta");
+  return OXM_OK;
+}
+
+template <int BN, int STAGES, int PAIR>
+int launch_majors(oxm_ctx *ctx, bool tf32, bool a_mn, bool b_mn, const CUtensorMap &tmA, const CUtensorMap &tmB,
+                  const GemmParams &p, int grid) {
+  if (tf32) return launch_instance<BN, STAGES, 0, 0, 1, PAIR>(ctx, tmA, tmB, p, grid);
+  if (!a_mn && !b_mn) return launch_instance<BN, STAGES, 0, 0, 0, PAIR>(ctx, tmA, tmB, p, grid);
+  if (!a_mn && b_mn) return launch_instance<BN, STAGES, 0, 1, 0, PAIR>(ctx, tmA, tmB, p, grid);
+  if (a_mn && !b_mn) return launch_instance<BN, STAGES, 1, 0, 0, PAIR>(ctx, tmA, tmB, p, grid);
+  return launch_instance<BN, STAGES, 1, 1, 0, PAIR>(ctx, tmA, tmB, p, grid);
+}
+
+int launch_tcgen05(oxm_ctx *ctx, const Problem &P) {
+  if (P.nbd > kMaxBatchDims) return fail(OXM_NOT_IMPLEMENTED, "matmul is not implemented for %d batch dims", P.nbd);
+  if (P.M >= (1ll << 31) || P.N >= (1ll << 31) || P.K >= (1ll << 29) || P.nbatch >= (1ll << 31))
+    return fail(OXM_NOT_IMPLEMENTED, "matmul is not implemented for extents above 2^31");
+  const bool tf32 = P.elt == 4;
+  Staged sa{}, sb{};
+  if (!stage_direct(P, false, sa)) {
+    int st = stage_packed(ctx, P, false, 0, sa);
+    if (st) return st;
+  }
+  if (!stage_direct(P, true, sb)) {
+    int st = stage_packed(ctx, P, true, 1, sb);
+    if (st) return st;
+  }
+  const int64_t Kst = tf32 ? sa.K : P.K;  // staged contraction length
+  const int bk = kStageKBytes / P.elt;
+
+  int bn = (int)ctx->opt_tile_n;
+  if (bn == 0) bn = P.N > 128 ? 256 : (P.N > 64 ? 128 : 64);
+  int pair = ctx->opt_cta_pair < 0 ? 0 : (int)ctx->opt_cta_pair;
+  if (bn == 64) pair = 0;
+  const int tm = kTileM * (pair ? 2 : 1);
+
+  GemmParams p{};
+  p.M = (int32_t)P.M; p.N = (int32_t)P.N; p.K = (int32_t)Kst;
+  p.tiles_m = (int32_t)((P.M + tm - 1) / tm);
+  p.tiles_n = (int32_t)((P.N + bn - 1) / bn);
+  p.num_kb = (int32_t)((Kst + bk - 1) / bk);
+  p.nbatch = (int32_t)P.nbatch;
+  p.num_tiles = (int64_t)p.tiles_m * p.tiles_n * P.nbatch;
+  p.nbd = P.nbd;
+  bool vec = P.o_cs == 1 && (reinterpret_cast<uintptr_t>(P.o) + P.o_off * P.elt) % 16 == 0 && (P.o_rs * P.elt) % 16 == 0;
+  for (int d = 0; d < P.nbd; ++d) {
+    p.bdims[d] = (int32_t)P.bdims[d];
+    p.a_bmul[d] = sa.bmul[d];
+    p.b_bmul[d] = sb.bmul[d];
+    p.o_bstride[d] = P.o_bs[d];
+    if ((P.o_bs[d] * P.elt) % 16) vec = false;
+  }
+  p.out = static_cast<uint8_t *>(P.o) + P.o_off * P.elt;
+  p.out_rs = P.o_rs; p.out_cs = P.o_cs;
+  p.out_dtype = P.dtype;
+  p.out_vec = vec ? 1 : 0;
+  const uint32_t fmt = tf32 ? 2u : (P.dtype == OXM_BF16 ? 1u : 0u);
+  p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((sa.mn_major ? 1u : 0u) << 15) | ((sb.mn_major ? 1u : 0u) << 16) |
+            ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(tm >> 4) << 24);
+  p.status = ctx->status_dev;
+  p.wait_limit_ns = (uint64_t)ctx->opt_wait_limit_ms * 1000000ull;
+
+  CUtensorMap tmA, tmB;
+  int st = make_map(ctx, &tmA, sa, P.dtype, P.elt, kTileM, bk);
+  if (st) return st;
+  st = make_map(ctx, &tmB, sb, P.dtype, P.elt, pair ? bn / 2 : bn, bk);
+  if (st) return st;
+
+  int grid;
+  if (pair) grid = 2 * (int)std::min<int64_t>(p.num_tiles, ctx->num_sms / 2);
+  else grid = (int)std::min<int64_t>(p.num_tiles, ctx->num_sms);
+
+  if (!pair) {
+    if (bn == 256) st = launch_majors<256, 4, 0>(ctx, tf32, sa.mn_major, sb.mn_major, tmA, tmB, p, grid);
+    else if (bn == 128) st = launch_majors<128, 6, 0>(ctx, tf32, sa.mn_major, sb.mn_major, tmA, tmB, p, grid);
+    else st = launch_majors<64, 8, 0>(ctx, tf32, sa.mn_major, sb.mn_major, tmA, tmB, p, grid);
+  } else {
+    if (bn == 256) st = launch_majors<256, 6, 1>(ctx, tf32, sa.mn_major, sb.mn_major, tmA, tmB, p, grid);
+    else st = launch_majors<128, 8, 1>(ctx, tf32, sa.mn_major, sb.mn_major, tmA, tmB, p, grid);
+  }
+  if (st) return st;
+  ctx->launches[0]++; ctx->launches[1]++;
+  return OXM_OK;
+}
+
+int run_matmul(oxm_ctx *ctx, const oxm_view *a, const oxm_view *b, const oxm_view *out, bool batched) {
+  int st = validate(ctx, a, b, out, batched, false);
+  if (st) return st;
+  for (const oxm_view *v : {a, b, out}) {
+    int64_t numel = 1;
+    for (int i = 0; i < v->ndim; ++i) numel *= v->shape[i];
+    if (numel > 0 && v->base == nullptr) return fail(OXM_INVALID_ARGUMENT, "matmul: view with null storage");
+  }
+  Problem P = normalise(a, b, out);
+  if (P.M == 0 || P.N == 0 || P.nbatch == 0) return OXM_OK;  // nothing to write
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  CUDA_TRY(cudaSetDevice(ctx->device));
+  // Small products and empty contractions go to the FFMA kernel; the rest to
+  // the tensor cores.  Both are GPU kernels; there is no host path.
+  const double flops = 2.0 * (double)P.M * (double)P.N * (double)P.K * (double)P.nbatch;
+  bool use_tc;
+  if (ctx->opt_kernel == 1) use_tc = false;
+  else if (ctx->opt_kernel == 2) use_tc = P.K > 0;
+  else use_tc = P.K > 0 && flops >= 2.0e8;
+  return use_tc ? launch_tcgen05(ctx, P) : launch_simt(ctx, P);
+}
+
+int check_status(oxm_ctx *ctx) {
+  CUDA_TRY(cudaMemcpyAsync(ctx->status_host, ctx->status_dev, sizeof(uint32_t), cudaMemcpyDeviceToHost, ctx->stream));
+  CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+  const uint32_t s = *ctx->status_host;
+  if (s != 0) {
+    CUDA_TRY(cudaMemsetAsync(ctx->status_dev, 0, sizeof(uint32_t), ctx->stream));
+    if (s == OXM_TIMEOUT)
+      return fail(OXM_TIMEOUT, "a bounded device-side wait expired in %s; the result of that launch is undefined", ctx->last_kernel);
+    return fail(OXM_CUDA_ERROR, "device-side status %u in %s", s, ctx->last_kernel);
+  }
+  return OXM_OK;
+}
+
+// Element range [lo, hi] a view touches, relative to its base.
+void view_extent(const oxm_view *v, int64_t *lo, int64_t *hi, int64_t *numel) {
+  int64_t l = v->offset, h = v->offset, n = 1;
+  for (int i = 0; i < v->ndim; ++i) {
+    n *= v->shape[i];
+    if (v->shape[i] > 0) {
+      const int64_t span = (v->shape[i] - 1) * v->strides[i];
+      if (span > 0) h += span; else l += span;
+    }
+  }
+  *lo = l; *hi = h; *numel = n;
+}
+
+}  // namespace
+
+// ===========================================================================
+// exported functions
+// ===========================================================================
+extern "C" {
+
+const char *oxm_last_error(void) { return g_last_error.c_str(); }
+
+const char *oxm_status_name(int status) {
+  static const char *names[] = {"Ok", "ShapeMismatch", "BroadcastIncompatible", "DTypeMismatch", "UnsupportedDType",
+                                "DeviceMismatch", "IndexOutOfBounds", "RankMismatch", "BackendUnavailable",
+                                "NotImplemented", "CudaError", "Timeout", "InvalidArgument"};
+  return (status >= 0 && status <= 12) ? names[status] : "Unknown";
+}
+
+const char *oxm_backend_name(void) { return "b200-tcgen05"; }
+
+int oxm_device_count(int *count) {
+  if (!count) return fail(OXM_INVALID_ARGUMENT, "oxm_device_count: null argument");
+  int n = 0;
+  cudaError_t e = cudaGetDeviceCount(&n);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    n = 0;
+  }
+  *count = n;
+  return OXM_OK;
+}
+
+int oxm_ctx_create(int device_index, oxm_ctx **out) {
+  if (!out) return fail(OXM_INVALID_ARGUMENT, "oxm_ctx_create: null argument");
+  *out = nullptr;
+  int n = 0;
+  if (cudaGetDeviceCount(&n) != cudaSuccess) {
+    cudaGetLastError();
+    n = 0;
+  }
+  if (device_index < 0 || device_index >= n)
+    return fail(OXM_BACKEND_UNAVAILABLE, "no backend available for device Cuda { index: %d } (%d CUDA devices visible)", device_index, n);
+  cudaDeviceProp prop;
+  CUDA_TRY(cudaGetDeviceProperties(&prop, device_index));
+  if (prop.major != 10)
+    return fail(OXM_BACKEND_UNAVAILABLE, "no backend available for device Cuda { index: %d }: %s is sm_%d%d, this backend is built for sm_100a",
+                device_index, prop.name, prop.major, prop.minor);
+  CUDA_TRY(cudaSetDevice(device_index));
+  oxm_ctx *ctx = new oxm_ctx();
+  ctx->device = device_index;
+  ctx->num_sms = prop.multiProcessorCount;
+  cudaError_t e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking);
+  if (e == cudaSuccess) e = cudaMalloc(&ctx->status_dev, sizeof(uint32_t));
+  if (e == cudaSuccess) e = cudaMemset(ctx->status_dev, 0, sizeof(uint32_t));
+  if (e == cudaSuccess) e = cudaHostAlloc(&ctx->status_host, sizeof(uint32_t), cudaHostAllocDefault);
+  void *fn = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  if (e == cudaSuccess) e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
+  if (e != cudaSuccess || !fn) {
+    int st = fail(OXM_CUDA_ERROR, "context set-up failed: %s", e != cudaSuccess ? cudaGetErrorString(e) : "cuTensorMapEncodeTiled not found");
+    oxm_ctx_destroy(ctx);
+    return st;
+  }
+  ctx->encode = reinterpret_cast<EncodeTiledFn>(fn);
+  if (const char *env = getenv("OXM_WAIT_LIMIT_MS")) {
+    const long v = atol(env);
+    if (v >= 1 && v <= 600000) ctx->opt_wait_limit_ms = v;
+  }
+  // Keep freed blocks in the pool: allocation in the steady state costs no driver call.
+  cudaMemPool_t pool;
+  if (cudaDeviceGetDefaultMemPool(&pool, device_index) == cudaSuccess) {
+    uint64_t thresh = UINT64_MAX;
+    cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &thresh);
+  }
+  *out = ctx;
+  return OXM_OK;
+}
+
+int oxm_ctx_destroy(oxm_ctx *ctx) {
+  if (!ctx) return OXM_OK;
+  cudaSetDevice(ctx->device);
+  if (ctx->stream) cudaStreamSynchronize(ctx->stream);
+  for (auto &w : ctx->pack_ws) if (w.ptr) cudaFree(w.ptr);
+  for (auto &w : ctx->host_stage) if (w.ptr) cudaFree(w.ptr);
+  if (ctx->status_dev) cudaFree(ctx->status_dev);
+  if (ctx->status_host) cudaFreeHost(ctx->status_host);
+  if (ctx->stream) cudaStreamDestroy(ctx->stream);
+  delete ctx;
+  return OXM_OK;
+}
+
+int oxm_ctx_device(const oxm_ctx *ctx, int *device_index) {
+  if (!ctx || !device_index) return fail(OXM_INVALID_ARGUMENT, "oxm_ctx_device: null argument");
+  *device_index = ctx->device;
+  return OXM_OK;
+}
+
+int oxm_alloc(oxm_ctx *ctx, size_t bytes, void **out) {
+  if (!ctx || !out) return fail(OXM_INVALID_ARGUMENT, "oxm_alloc: null argument");
+  *out = nullptr;
+  CUDA_TRY(cudaSetDevice(ctx->device));
+  if (bytes == 0) bytes = 16;
+  CUDA_TRY(cudaMallocAsync(out, bytes, ctx->stream));
+  return OXM_OK;
+}
+
+int oxm_free(oxm_ctx *ctx, void *ptr) {
+  if (!ctx) return fail(OXM_INVALID_ARGUMENT, "oxm_free: null context");
+  if (!ptr) return OXM_OK;
+  CUDA_TRY(cudaSetDevice(ctx->device));
+  CUDA_TRY(cudaFreeAsync(ptr, ctx->stream));
+  return OXM_OK;
+}
+
+int oxm_h2d(oxm_ctx *ctx, void *dst_device, const void *src_host, size_t bytes) {
+  if (!ctx || (bytes && (!dst_device || !src_host))) return fail(OXM_INVALID_ARGUMENT, "oxm_h2d: null argument");
+  CUDA_TRY(cudaSetDevice(ctx->device));
+  if (bytes) CUDA_TRY(cudaMemcpyAsync(dst_device, src_host, bytes, cudaMemcpyHostToDevice, ctx->stream));
+  return OXM_OK;
+}
+
+int oxm_d2h(oxm_ctx *ctx, void *dst_host, const void *src_device, size_t bytes) {
+  if (!ctx || (bytes && (!dst_host || !src_device))) return fail(OXM_INVALID_ARGUMENT, "oxm_d2h: null argument");
+  CUDA_TRY(cudaSetDevice(ctx->device));
+  if (bytes) CUDA_TRY(cudaMemcpyAsync(dst_host, src_device, bytes, cudaMemcpyDeviceToHost, ctx->stream));
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  return check_status(ctx);
+}
+
+int oxm_memset(oxm_ctx *ctx, void *dst_device, int byte, size_t bytes) {
+  if (!ctx || (bytes && !dst_device)) return fail(OXM_INVALID_ARGUMENT, "oxm_memset: null argument");
+  CUDA_TRY(cudaSetDevice(ctx->device));
+  if (bytes) CUDA_TRY(cudaMemsetAsync(dst_device, byte, bytes, ctx->stream));
+  return OXM_OK;
+}
+
+int oxm_sync(oxm_ctx *ctx) {
+  if (!ctx) return fail(OXM_INVALID_ARGUMENT, "oxm_sync: null context");
+  CUDA_TRY(cudaSetDevice(ctx->device));
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  return check_status(ctx);
+}
+
+int oxm_host_alloc(size_t bytes, void **out) {
+  if (!out) return fail(OXM_INVALID_ARGUMENT, "oxm_host_alloc: null argument");
+  *out = nullptr;
+  CUDA_TRY(cudaHostAlloc(out, bytes ? bytes : 16, cudaHostAllocDefault));
+  return OXM_OK;
+}
+
+int oxm_host_free(void *ptr) {
+  if (ptr) CUDA_TRY(cudaFreeHost(ptr));
+  return OXM_OK;
+}
+
+int oxm_matmul(oxm_ctx *ctx, const oxm_view *a, const oxm_view *b, const oxm_view *out) {
+  return run_matmul(ctx, a, b, out, false);
+}
+
+int oxm_batched_matmul(oxm_ctx *ctx, const oxm_view *a, const oxm_view *b, const oxm_view *out) {
+  return run_matmul(ctx, a, b, out, true);
+}
+
+int oxm_batched_matmul_host(oxm_ctx *ctx, const oxm_view *a, const oxm_view *b, const oxm_view *out) {
+  int st = validate(ctx, a, b, out, true, true);
+  if (st) return st;
+  CUDA_TRY(cudaSetDevice(ctx->device));
+  std::lock_guard<std::mutex> host_lock(ctx->host_mu);
+  const oxm_view *hv[3] = {a, b, out};
+  oxm_view dv[3];
+  int64_t lo[3], hi[3], numel[3];
+  const int elt = dtype_size(a->dtype);
+  {
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    for (int i = 0; i < 3; ++i) {
+      view_extent(hv[i], &lo[i], &hi[i], &numel[i]);
+      dv[i] = *hv[i];
+      dv[i].device = ctx->device;
+      if (numel[i] == 0) { dv[i].base = nullptr; continue; }
+      if (!hv[i]->base) return fail(OXM_INVALID_ARGUMENT, "matmul: view with null storage");
+      if (i == 2 && hi[i] - lo[i] + 1 != numel[i])
+        return fail(OXM_INVALID_ARGUMENT, "matmul: a host output must be dense (the reference output is fresh and contiguous)");
+      const size_t bytes = (size_t)(hi[i] - lo[i] + 1) * elt;
+      st = grow(ctx, ctx->host_stage[i], bytes);
+      if (st) return st;
+      dv[i].base = ctx->host_stage[i].ptr;
+      dv[i].offset = hv[i]->offset - lo[i];
+      if (i < 2)
+        CUDA_TRY(cudaMemcpyAsync(dv[i].base, static_cast<const uint8_t *>(hv[i]->base) + lo[i] * elt, bytes,
+                                 cudaMemcpyHostToDevice, ctx->stream));
+    }
+  }
+  st = run_matmul(ctx, &dv[0], &dv[1], &dv[2], true);
+  if (st) return st;
+  if (numel[2] > 0)
+    CUDA_TRY(cudaMemcpyAsync(static_cast<uint8_t *>(out->base) + lo[2] * elt, dv[2].base, (size_t)numel[2] * elt,
+                             cudaMemcpyDeviceToHost, ctx->stream));
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  return check_status(ctx);
+}
+
+int oxm_contiguous(oxm_ctx *ctx, const oxm_view *src, const oxm_view *dst) {
+  if (!ctx || !src || !dst) return fail(OXM_INVALID_ARGUMENT, "contiguous: null argument");
+  if (src->ndim < 0 || src->ndim > OXM_MAX_DIMS) return fail(OXM_NOT_IMPLEMENTED, "contiguous is not implemented for rank %d", src->ndim);
+  if (src->dtype != dst->dtype)
+    return fail(OXM_DTYPE_MISMATCH, "dtype mismatch: expected %s, got %s in contiguous", dtype_name(src->dtype), dtype_name(dst->dtype));
+  if (dtype_size(src->dtype) == 0) return fail(OXM_UNSUPPORTED_DTYPE, "dtype %d is not supported by contiguous", src->dtype);
+  if (src->device != ctx->device || dst->device != ctx->device)
+    return fail(OXM_DEVICE_MISMATCH, "device mismatch: Cuda{index: %d} vs Cuda{index: %d} in contiguous", src->device, dst->device);
+  bool same = src->ndim == dst->ndim;
+  for (int i = 0; same && i < src->ndim; ++i) same = src->shape[i] == dst->shape[i];
+  if (!same) return fail(OXM_SHAPE_MISMATCH, "shape mismatch: expected %s, got %s in contiguous", shape_str(src).c_str(), shape_str(dst).c_str());
+  CopyParams p{};
+  p.n = 1;
+  int64_t expect = 1;
+  for (int i = src->ndim - 1; i >= 0; --i) {
+    if (dst->shape[i] != 1 && dst->strides[i] != expect)
+      return fail(OXM_INVALID_ARGUMENT, "contiguous: the destination view must be row-major contiguous");
+    expect *= dst->shape[i];
+    p.n *= src->shape[i];
+    p.shape[i] = src->shape[i];
+    p.strides[i] = src->strides[i];
+  }
+  if (p.n == 0) return OXM_OK;
+  if (!src->base || !dst->base) return fail(OXM_INVALID_ARGUMENT, "contiguous: view with null storage");
+  p.src = src->base; p.dst = dst->base;
+  p.elt = dtype_size(src->dtype); p.ndim = src->ndim;
+  p.src_off = src->offset; p.dst_off = dst->offset;
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  CUDA_TRY(cudaSetDevice(ctx->device));
+  const int64_t blocks = std::min<int64_t>((p.n + 255) / 256, (int64_t)ctx->num_sms * 16);
+  copy_strided_kernel<<<(unsigned)blocks, 256, 0, ctx->stream>>>(p);
+  CUDA_TRY(cudaGetLastError());
+  ctx->launches[0]++; ctx->launches[3]++;
+  return OXM_OK;
+}
+
+int oxm_fill(oxm_ctx *ctx, void *dst_device, int dtype, int64_t n, uint64_t seed, uint64_t stream, int dist, double scale) {
+  if (!ctx || (n > 0 && !dst_device)) return fail(OXM_INVALID_ARGUMENT, "oxm_fill: null argument");
+  if (!is_matmul_dtype(dtype)) return fail(OXM_UNSUPPORTED_DTYPE, "dtype %s is not supported by fill", dtype_name(dtype));
+  if (dist < 0 || dist > 1 || n < 0) return fail(OXM_INVALID_ARGUMENT, "oxm_fill: bad distribution or count");
+  if (n == 0) return OXM_OK;
+  const uint64_t key = splitmix64(splitmix64(seed) ^ splitmix64(stream * 0xD1342543DE82EF95ull + 0x632BE59BD9B4E019ull));
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  CUDA_TRY(cudaSetDevice(ctx->device));
+  const int64_t blocks = std::min<int64_t>((n + 255) / 256, (int64_t)ctx->num_sms * 32);
+  fill_kernel<<<(unsigned)blocks, 256, 0, ctx->stream>>>(dst_device, dtype, n, key, dist, (float)scale);
+  CUDA_TRY(cudaGetLastError());
+  return OXM_OK;
+}
+
+int oxm_event_create(oxm_ctx *ctx, oxm_event **out) {
+  if (!ctx || !out) return fail(OXM_INVALID_ARGUMENT, "oxm_event_create: null argument");
+  CUDA_TRY(cudaSetDevice(ctx->device));
+  oxm_event *e = new oxm_event();
+  e->device = ctx->device;
+  cudaError_t r = cudaEventCreate(&e->ev);
+  if (r != cudaSuccess) {
+    delete e;
+    return fail(OXM_CUDA_ERROR, "cudaEventCreate failed: %s", cudaGetErrorString(r));
+  }
+  *out = e;
+  return OXM_OK;
+}
+
+int oxm_event_destroy(oxm_event *ev) {
+  if (!ev) return OXM_OK;
+  cudaSetDevice(ev->device);
+  cudaEventDestroy(ev->ev);
+  delete ev;
+  return OXM_OK;
+}
+
+int oxm_event_record(oxm_ctx *ctx, oxm_event *ev) {
+  if (!ctx || !ev) return fail(OXM_INVALID_ARGUMENT, "oxm_event_record: null argument");
+  CUDA_TRY(cudaSetDevice(ctx->device));
+  CUDA_TRY(cudaEventRecord(ev->ev, ctx->stream));
+  return OXM_OK;
+}
+
+int oxm_event_elapsed_ms(oxm_event *start, oxm_event *stop, float *ms) {
+  if (!start || !stop || !ms) return fail(OXM_INVALID_ARGUMENT, "oxm_event_elapsed_ms: null argument");
+  CUDA_TRY(cudaSetDevice(stop->device));
+  CUDA_TRY(cudaEventSynchronize(stop->ev));
+  CUDA_TRY(cudaEventElapsedTime(ms, start->ev, stop->ev));
+  return OXM_OK;
+}
+
+int oxm_stream_handle(oxm_ctx *ctx, void **cuda_stream) {
+  if (!ctx || !cuda_stream) return fail(OXM_INVALID_ARGUMENT, "oxm_stream_handle: null argument");
+  *cuda_stream = ctx->stream;
+  return OXM_OK;
+}
+
+int oxm_set_option(oxm_ctx *ctx, const char *key, int64_t value) {
+  if (!ctx || !key) return fail(OXM_INVALID_ARGUMENT, "oxm_set_option: null argument");
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  if (!strcmp(key, "kernel") && value >= 0 && value <= 2) ctx->opt_kernel = value;
+  else if (!strcmp(key, "tile_n") && (value == 0 || value == 64 || value == 128 || value == 256)) ctx->opt_tile_n = value;
+  else if (!strcmp(key, "cta_pair") && value >= -1 && value <= 1) ctx->opt_cta_pair = value;
+  else if (!strcmp(key, "wait_limit_ms") && value >= 1 && value <= 600000) ctx->opt_wait_limit_ms = value;
+  else return fail(OXM_INVALID_ARGUMENT, "oxm_set_option: unknown option or value: %s = %lld", key, (long long)value);
+  return OXM_OK;
+}
+
+int oxm_get_option(oxm_ctx *ctx, const char *key, int64_t *value) {
+  if (!ctx || !key || !value) return fail(OXM_INVALID_ARGUMENT, "oxm_get_option: null argument");
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  if (!strcmp(key, "kernel")) *value = ctx->opt_kernel;
+  else if (!strcmp(key, "tile_n")) *value = ctx->opt_tile_n;
+  else if (!strcmp(key, "cta_pair")) *value = ctx->opt_cta_pair;
+  else if (!strcmp(key, "wait_limit_ms")) *value = ctx->opt_wait_limit_ms;
+  else return fail(OXM_INVALID_ARGUMENT, "oxm_get_option: unknown option: %s", key);
+  return OXM_OK;
+}
+
+int oxm_launch_counts(oxm_ctx *ctx, int64_t counts[4]) {
+  if (!ctx || !counts) return fail(OXM_INVALID_ARGUMENT, "oxm_launch_counts: null argument");
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  for (int i = 0; i < 4; ++i) counts[i] = ctx->launches[i];
+  return OXM_OK;
+}
+
+const char *oxm_last_kernel(oxm_ctx *ctx) { return ctx ? ctx->last_kernel : "none"; }
+
+}  // extern "C"

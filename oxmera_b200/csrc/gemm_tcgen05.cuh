@@ -1,0 +1,403 @@
+// The tensor-core GEMM of the oxmera B200 backend: C[b] = A[b] * B[b] with
+// fp32 accumulation in tensor memory.
+//
+// Shape of the kernel
+//   - persistent: one CTA (or one CTA pair) per SM walks a static tile list;
+//   - warp specialised: warp 0 issues TMA loads, warp 1 owns tensor memory
+//     and issues tcgen05.mma, warps 2..5 drain accumulators to global memory;
+//   - operands are staged by TMA into 128-byte-swizzled shared-memory tiles,
+//     STAGES deep, handed over with mbarriers;
+//   - two accumulators live in tensor memory so the epilogue of tile i
+//     overlaps the main loop of tile i+1;
+//   - either operand may be K-major (contraction dim contiguous) or MN-major
+//     (row/column dim contiguous): the transposed views of a linear layer's
+//     backward need no copy;
+//   - PAIR = 1 runs cta_group::2: two CTAs of a cluster share one 256-row tile,
+//     each staging its own A rows and its own half of B (no multicast).
+//
+// Every wait is bounded.  When a bound expires the waiter records
+// OXM_TIMEOUT in the status word, raises the CTA's abort flag, and every role
+// falls through to the common teardown, which frees tensor memory.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "ptx.cuh"
+
+namespace oxm {
+
+constexpr int kMaxBatchDims = 6;
+constexpr int kTileM = 128;        // accumulator rows per CTA (= TMEM lanes)
+constexpr int kStageKBytes = 128;  // contraction bytes per pipeline stage (one swizzle row)
+constexpr int kMmaKBytes = 32;     // contraction bytes per tcgen05.mma
+constexpr int kGemmThreads = 192;
+constexpr uint32_t kStatusTimeout = 11;  // OXM_TIMEOUT
+
+struct GemmParams {
+  int32_t M, N, K;           // K counts elements of the staged operands
+  int32_t tiles_m, tiles_n;  // tiles_m counts (kTileM * ctas-per-tile)-row blocks
+  int32_t num_kb;            // contraction blocks per tile
+  int32_t nbatch;
+  int64_t num_tiles;
+  int32_t nbd;               // output batch dims
+  int32_t bdims[kMaxBatchDims];
+  int32_t a_bmul[kMaxBatchDims];  // output batch index -> operand batch coordinate
+  int32_t b_bmul[kMaxBatchDims];
+  int64_t o_bstride[kMaxBatchDims];  // elements
+  void *out;
+  int64_t out_rs, out_cs;  // elements
+  int32_t out_dtype;       // 0 f32, 6 bf16, 7 f16
+  int32_t out_vec;         // rows may be written with 16-byte stores
+  uint32_t idesc;
+  uint32_t *status;
+  uint64_t wait_limit_ns;
+};
+
+template <int BN, int STAGES, int PAIR>
+struct GemmSmem {
+  static constexpr int kBNC = PAIR ? BN / 2 : BN;  // B rows staged by one CTA
+  static constexpr int kABytes = kTileM * kStageKBytes;
+  static constexpr int kBBytes = kBNC * kStageKBytes;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kBarOffset = STAGES * kStageBytes;
+  // full[STAGES] empty[STAGES] tmem_full[2] tmem_empty[2] teardown, then two u32 slots
+  static constexpr int kNumBars = 2 * STAGES + 5;
+  static constexpr int kTotal = kBarOffset + kNumBars * 8 + 16;
+  static constexpr int kDynamic = kTotal + 1024;  // room to align the base to 1 KiB
+};
+
+// Shared-memory matrix descriptor for a 128-byte-swizzled tile.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>(lbo_bytes >> 4) << 16;
+  d |= static_cast<uint64_t>(sbo_bytes >> 4) << 32;
+  d |= 1ull << 46;  // descriptor version of this architecture
+  d |= 2ull << 61;  // 128-byte swizzle
+  return d;
+}
+
+struct WaitCtx {
+  volatile int *abort_flag;  // shared memory, per CTA
+  uint32_t *status;          // global status word
+  uint64_t limit_ns;
+};
+
+// Wait for `parity` of `bar` with a time bound.  Returns false when the CTA is
+// aborting (either this wait expired or another one did).
+__device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, const WaitCtx &w) {
+  if (ptx::mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = ptx::globaltimer_ns();
+  for (;;) {
+    for (int i = 0; i < 64; ++i)
+      if (ptx::mbar_try_wait(bar, parity)) return true;
+    if (*w.abort_flag) return false;
+    if (ptx::globaltimer_ns() - t0 > w.limit_ns) {
+      *w.abort_flag = 1;
+      atomicCAS(w.status, 0u, kStatusTimeout);
+      return false;
+    }
+  }
+}
+
+struct TileCoord {
+  int32_t m_blk, n_blk;
+  int32_t a_batch, b_batch;
+  int64_t o_off;
+};
+
+template <int GROUP_M>
+__device__ __forceinline__ TileCoord decode_tile(const GemmParams &p, int64_t tile) {
+  TileCoord c;
+  const int32_t tpb = p.tiles_m * p.tiles_n;
+  int32_t batch = static_cast<int32_t>(tile / tpb);
+  const int32_t t = static_cast<int32_t>(tile - static_cast<int64_t>(batch) * tpb);
+  // Walk GROUP_M tile rows at a time so that concurrently resident CTAs share
+  // A and B panels in L2.
+  const int32_t gt = GROUP_M * p.tiles_n;
+  const int32_t g = t / gt;
+  const int32_t first = g * GROUP_M;
+  const int32_t gsz = min(GROUP_M, p.tiles_m - first);
+  const int32_t r = t - g * gt;
+  c.m_blk = first + r % gsz;
+  c.n_blk = r / gsz;
+  c.a_batch = 0;
+  c.b_batch = 0;
+  c.o_off = 0;
+  for (int d = p.nbd - 1; d >= 0; --d) {
+    const int32_t idx = batch % p.bdims[d];
+    batch /= p.bdims[d];
+    c.a_batch += idx * p.a_bmul[d];
+    c.b_batch += idx * p.b_bmul[d];
+    c.o_off += static_cast<int64_t>(idx) * p.o_bstride[d];
+  }
+  return c;
+}
+
+template <int BN, int STAGES, int A_MN, int B_MN, int TF32, int PAIR>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                    const GemmParams p) {
+  static_assert(!(TF32 && (A_MN || B_MN)), "the tf32 path stages K-major operands only");
+  static_assert(BN % 32 == 0 && BN >= 32 && BN <= 256, "tile width");
+  using L = GemmSmem<BN, STAGES, PAIR>;
+  constexpr int ELT = TF32 ? 4 : 2;
+  constexpr int BK = kStageKBytes / ELT;   // contraction elements per stage
+  constexpr int BOXW = kStageKBytes / ELT; // elements along MN in one MN-major box
+  constexpr int MMAS = kStageKBytes / kMmaKBytes;
+  constexpr int MMA_K = kMmaKBytes / ELT;  // contraction elements per tcgen05.mma
+  constexpr int TM = kTileM * (PAIR ? 2 : 1);
+  constexpr uint32_t TMEM_COLS = (2 * BN <= 32) ? 32 : (2 * BN <= 64) ? 64 : (2 * BN <= 128) ? 128 : (2 * BN <= 256) ? 256 : 512;
+  constexpr int GROUP_M = PAIR ? 8 : 16;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = ptx::smem_u32(smem_raw);
+  const uint32_t base = (raw_addr + 1023u) & ~1023u;
+  uint8_t *base_ptr = smem_raw + (base - raw_addr);
+
+  const uint32_t bars = base + L::kBarOffset;
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int a) { return bars + 8u * (2 * STAGES + a); };
+  auto tempty_bar = [&](int a) { return bars + 8u * (2 * STAGES + 2 + a); };
+  const uint32_t teardown_bar = bars + 8u * (2 * STAGES + 4);
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(base_ptr + L::kBarOffset + L::kNumBars * 8);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+  const uint32_t warp = threadIdx.x >> 5;
+  const uint32_t lane = threadIdx.x & 31;
+  const uint32_t cta_rank = PAIR ? ptx::cluster_ctarank() : 0u;
+  const bool leader = cta_rank == 0;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      ptx::mbar_init(full_bar(s), 1);
+      ptx::mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      ptx::mbar_init(tfull_bar(a), 1);
+      ptx::mbar_init(tempty_bar(a), PAIR ? 8 : 4);
+    }
+    ptx::mbar_init(teardown_bar, 1);
+    *abort_flag = 0;
+    ptx::fence_barrier_init();
+    ptx::fence_proxy_async_smem();
+  }
+  if (warp == 0 && lane == 0) {
+    ptx::prefetch_tensormap(&tmA);
+    ptx::prefetch_tensormap(&tmB);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc<PAIR>(ptx::smem_u32(tmem_slot), TMEM_COLS);
+  }
+  ptx::tc_fence_before();
+  if constexpr (PAIR) {
+    __syncthreads();
+    ptx::cluster_arrive();
+    ptx::cluster_wait();
+  } else {
+    __syncthreads();
+  }
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  WaitCtx wc{abort_flag, p.status, p.wait_limit_ns};
+  const int64_t tile_stride = PAIR ? (gridDim.x >> 1) : gridDim.x;
+  const int64_t tile_first = PAIR ? (blockIdx.x >> 1) : blockIdx.x;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      uint32_t s = 0, ph = 0;
+      bool ok = true;
+      for (int64_t tile = tile_first; ok && tile < p.num_tiles; tile += tile_stride) {
+        const TileCoord tc = decode_tile<GROUP_M>(p, tile);
+        const int32_t m0 = tc.m_blk * TM + static_cast<int32_t>(cta_rank) * kTileM;
+        const int32_t n0 = tc.n_blk * BN + static_cast<int32_t>(cta_rank) * L::kBNC;
+        for (int32_t kb = 0; kb < p.num_kb; ++kb) {
+          if (!bounded_wait(empty_bar(s), ph ^ 1u, wc)) { ok = false; break; }
+          const uint32_t sa = base + s * L::kStageBytes;
+          const uint32_t sb = sa + L::kABytes;
+          const int32_t k0 = kb * BK;
+          if constexpr (PAIR) {
+            // The leader's barrier collects the bytes of both CTAs' loads.
+            const uint32_t fb = ptx::mapa_shared(full_bar(s), 0);
+            if (leader) ptx::mbar_arrive_expect_tx(full_bar(s), 2u * L::kStageBytes);
+            if constexpr (A_MN) {
+#pragma unroll
+              for (int j = 0; j < kTileM / BOXW; ++j)
+                ptx::tma_load_3d_pair(sa + j * (BK * kStageKBytes), &tmA, fb, m0 + j * BOXW, k0, tc.a_batch);
+            } else {
+              ptx::tma_load_3d_pair(sa, &tmA, fb, k0, m0, tc.a_batch);
+            }
+            if constexpr (B_MN) {
+#pragma unroll
+              for (int j = 0; j < L::kBNC / BOXW; ++j)
+                ptx::tma_load_3d_pair(sb + j * (BK * kStageKBytes), &tmB, fb, n0 + j * BOXW, k0, tc.b_batch);
+            } else {
+              ptx::tma_load_3d_pair(sb, &tmB, fb, k0, n0, tc.b_batch);
+            }
+          } else {
+            const uint32_t fb = full_bar(s);
+            ptx::mbar_arrive_expect_tx(fb, L::kStageBytes);
+            if constexpr (A_MN) {
+#pragma unroll
+              for (int j = 0; j < kTileM / BOXW; ++j)
+                ptx::tma_load_3d(sa + j * (BK * kStageKBytes), &tmA, fb, m0 + j * BOXW, k0, tc.a_batch);
+            } else {
+              ptx::tma_load_3d(sa, &tmA, fb, k0, m0, tc.a_batch);
+            }
+            if constexpr (B_MN) {
+#pragma unroll
+              for (int j = 0; j < L::kBNC / BOXW; ++j)
+                ptx::tma_load_3d(sb + j * (BK * kStageKBytes), &tmB, fb, n0 + j * BOXW, k0, tc.b_batch);
+            } else {
+              ptx::tma_load_3d(sb, &tmB, fb, k0, n0, tc.b_batch);
+            }
+          }
+          if (++s == STAGES) { s = 0; ph ^= 1u; }
+        }
+      }
+      if (*abort_flag) {
+        // Give loads already in flight time to land before shared memory goes away.
+        const uint64_t t0 = ptx::globaltimer_ns();
+        while (ptx::globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0 && leader) {
+      // K-major tile: rows of 128 B, 8-row swizzle atoms 1 KiB apart.
+      // MN-major tile: boxes of BK rows x 128 B; LBO = one box, 8-row groups 1 KiB apart.
+      constexpr uint32_t A_LBO = A_MN ? BK * kStageKBytes : 16;
+      constexpr uint32_t B_LBO = B_MN ? BK * kStageKBytes : 16;
+      constexpr uint32_t A_ADV = (A_MN ? MMA_K * kStageKBytes : kMmaKBytes) >> 4;
+      constexpr uint32_t B_ADV = (B_MN ? MMA_K * kStageKBytes : kMmaKBytes) >> 4;
+      uint32_t s = 0, ph = 0, as = 0, aph = 0;
+      bool ok = true;
+      for (int64_t tile = tile_first; ok && tile < p.num_tiles; tile += tile_stride) {
+        if (!bounded_wait(tempty_bar(as), aph ^ 1u, wc)) break;
+        ptx::tc_fence_after();
+        const uint32_t d_tmem = tmem_base + as * BN;
+        for (int32_t kb = 0; kb < p.num_kb; ++kb) {
+          if (!bounded_wait(full_bar(s), ph, wc)) { ok = false; break; }
+          ptx::tc_fence_after();
+          const uint32_t sa = base + s * L::kStageBytes;
+          const uint32_t sb = sa + L::kABytes;
+          const uint64_t adesc = make_smem_desc(sa, A_LBO, 1024);
+          const uint64_t bdesc = make_smem_desc(sb, B_LBO, 1024);
+#pragma unroll
+          for (int j = 0; j < MMAS; ++j) {
+            ptx::umma<PAIR, TF32>(d_tmem, adesc + static_cast<uint64_t>(j * A_ADV),
+                                  bdesc + static_cast<uint64_t>(j * B_ADV), p.idesc,
+                                  (kb | j) != 0 ? 1u : 0u);
+          }
+          if constexpr (PAIR) ptx::umma_commit_pair(empty_bar(s), 3);
+          else ptx::umma_commit(empty_bar(s));
+          if (++s == STAGES) { s = 0; ph ^= 1u; }
+        }
+        if (!ok) break;
+        if constexpr (PAIR) ptx::umma_commit_pair(tfull_bar(as), 3);
+        else ptx::umma_commit(tfull_bar(as));
+        as ^= 1u;
+        if (as == 0) aph ^= 1u;
+      }
+      if (*abort_flag) {
+        // Let tensor-core work already issued retire before tensor memory is freed.
+        if constexpr (PAIR) ptx::umma_commit_pair(teardown_bar, 1);
+        else ptx::umma_commit(teardown_bar);
+        const uint64_t t0 = ptx::globaltimer_ns();
+        while (!ptx::mbar_try_wait(teardown_bar, 0) && ptx::globaltimer_ns() - t0 < 10000000ull) {
+        }
+      }
+    }
+    __syncwarp();
+  } else {
+    // ---------------- epilogue: TMEM -> registers -> global ----------------
+    const uint32_t q = warp & 3u;  // the TMEM lane quarter this warp may read
+    const int esz = p.out_dtype == 0 ? 4 : 2;
+    uint32_t as = 0, aph = 0;
+    for (int64_t tile = tile_first; tile < p.num_tiles; tile += tile_stride) {
+      const TileCoord tc = decode_tile<GROUP_M>(p, tile);
+      // tcgen05.ld is warp-collective: leave the loop as a whole warp or not at all.
+      const bool ready = bounded_wait(tfull_bar(as), aph, wc);
+      if (!__all_sync(0xffffffffu, ready)) break;
+      ptx::tc_fence_after();
+      const int32_t row = tc.m_blk * TM + static_cast<int32_t>(cta_rank) * kTileM + static_cast<int32_t>(q * 32u + lane);
+      const bool row_ok = row < p.M;
+      uint8_t *rowp = static_cast<uint8_t *>(p.out) + (tc.o_off + static_cast<int64_t>(row) * p.out_rs) * esz;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t v[32];
+        ptx::tmem_ld_32x32(tmem_base + as * BN + c * 32 + ((q * 32u) << 16), v);
+        ptx::tmem_ld_wait();
+        const int32_t col0 = tc.n_blk * BN + c * 32;
+        if (row_ok && col0 < p.N) {
+          if (p.out_vec && col0 + 32 <= p.N) {
+            if (p.out_dtype == 0) {
+              uint4 *dst = reinterpret_cast<uint4 *>(rowp + static_cast<int64_t>(col0) * 4);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) dst[i] = make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+            } else {
+              uint32_t h[16];
+              if (p.out_dtype == 6) {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                  __nv_bfloat162 t = __floats2bfloat162_rn(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+                  h[i] = *reinterpret_cast<uint32_t *>(&t);
+                }
+              } else {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                  __half2 t = __floats2half2_rn(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+                  h[i] = *reinterpret_cast<uint32_t *>(&t);
+                }
+              }
+              uint4 *dst = reinterpret_cast<uint4 *>(rowp + static_cast<int64_t>(col0) * 2);
+#pragma unroll
+              for (int i = 0; i < 4; ++i) dst[i] = make_uint4(h[4 * i], h[4 * i + 1], h[4 * i + 2], h[4 * i + 3]);
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              if (col0 + i < p.N) {
+                const float f = __uint_as_float(v[i]);
+                const int64_t e = static_cast<int64_t>(col0 + i) * p.out_cs;
+                if (p.out_dtype == 0) reinterpret_cast<float *>(rowp)[e] = f;
+                else if (p.out_dtype == 6) reinterpret_cast<__nv_bfloat16 *>(rowp)[e] = __float2bfloat16_rn(f);
+                else reinterpret_cast<__half *>(rowp)[e] = __float2half_rn(f);
+              }
+            }
+          }
+        }
+      }
+      // This accumulator may be overwritten once all four quarters have been read.
+      ptx::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        if constexpr (PAIR) ptx::mbar_arrive_cluster(ptx::mapa_shared(tempty_bar(as), 0));
+        else ptx::mbar_arrive(tempty_bar(as));
+      }
+      as ^= 1u;
+      if (as == 0) aph ^= 1u;
+    }
+    __syncwarp();
+  }
+
+  // ---------------- teardown ----------------
+  ptx::tc_fence_before();
+  __syncthreads();
+  if constexpr (PAIR) {
+    // Neither CTA may leave while its peer can still touch its shared or tensor memory.
+    ptx::cluster_arrive();
+    ptx::cluster_wait();
+  }
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc<PAIR>(tmem_base, TMEM_COLS);
+  }
+}
+
+}  // namespace oxm

@@ -1,0 +1,270 @@
+// SIMT kernels of the backend: the FFMA tile GEMM that reads any strided view
+// directly, and the pack kernel that lays an arbitrary view out as K-major
+// rows for the tensor-core path (splitting f32 into TF32 hi/lo parts on the way).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <cstdint>
+
+namespace oxm {
+
+constexpr int kSimtMaxBatchDims = 6;
+
+__device__ __forceinline__ float load_elem(const void *base, int dtype, int64_t idx) {
+  if (dtype == 0) return static_cast<const float *>(base)[idx];
+  if (dtype == 6) return __bfloat162float(static_cast<const __nv_bfloat16 *>(base)[idx]);
+  return __half2float(static_cast<const __half *>(base)[idx]);
+}
+
+__device__ __forceinline__ void store_elem(void *base, int dtype, int64_t idx, float v) {
+  if (dtype == 0) static_cast<float *>(base)[idx] = v;
+  else if (dtype == 6) static_cast<__nv_bfloat16 *>(base)[idx] = __float2bfloat16_rn(v);
+  else static_cast<__half *>(base)[idx] = __float2half_rn(v);
+}
+
+// ---------------------------------------------------------------------------
+// FFMA tile GEMM.  64x64 output tile per 256-thread CTA, 4x4 per thread, the
+// contraction walked in ascending k in blocks of 16.  Reads A, B and writes
+// C through signed element strides, so transposed / narrowed / flipped views
+// and broadcast batch dims need no preparation.
+// ---------------------------------------------------------------------------
+struct SimtParams {
+  const void *a, *b;
+  void *out;
+  int32_t dtype, out_dtype;
+  int32_t M, N, K;
+  int32_t tiles_m, tiles_n;
+  int64_t a_off, b_off, o_off;       // elements
+  int64_t a_rs, a_cs, b_rs, b_cs, o_rs, o_cs;
+  int32_t nbd;
+  int32_t bdims[kSimtMaxBatchDims];
+  int64_t a_bs[kSimtMaxBatchDims], b_bs[kSimtMaxBatchDims], o_bs[kSimtMaxBatchDims];
+};
+
+__global__ void __launch_bounds__(256) gemm_simt_kernel(const SimtParams p) {
+  constexpr int TS = 64, BK = 16;
+  __shared__ float As[BK][TS + 4];
+  __shared__ float Bs[BK][TS + 4];
+
+  const int64_t tile = blockIdx.x;
+  const int32_t tpb = p.tiles_m * p.tiles_n;
+  int32_t batch = static_cast<int32_t>(tile / tpb);
+  const int32_t t = static_cast<int32_t>(tile % tpb);
+  const int32_t m0 = (t / p.tiles_n) * TS;
+  const int32_t n0 = (t % p.tiles_n) * TS;
+  int64_t a_off = p.a_off, b_off = p.b_off, o_off = p.o_off;
+  for (int d = p.nbd - 1; d >= 0; --d) {
+    const int32_t idx = batch % p.bdims[d];
+    batch /= p.bdims[d];
+    a_off += idx * p.a_bs[d];
+    b_off += idx * p.b_bs[d];
+    o_off += idx * p.o_bs[d];
+  }
+
+  const int tx = threadIdx.x & 15;  // column group
+  const int ty = threadIdx.x >> 4;  // row group
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+
+  for (int32_t k0 = 0; k0 < p.K; k0 += BK) {
+    // 64x16 elements of A and 16x64 of B: four each per thread.
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      const int e = threadIdx.x + r * 256;
+      {
+        // A: make the faster-varying thread index follow A's unit stride.
+        int mm, kk;
+        if (p.a_cs == 1) { kk = e & 15; mm = e >> 4; } else { mm = e & 63; kk = e >> 6; }
+        const int32_t gm = m0 + mm, gk = k0 + kk;
+        float v = 0.f;
+        if (gm < p.M && gk < p.K) v = load_elem(p.a, p.dtype, a_off + gm * p.a_rs + gk * p.a_cs);
+        As[kk][mm] = v;
+      }
+      {
+        int nn, kk;
+        if (p.b_rs == 1) { kk = e & 15; nn = e >> 4; } else { nn = e & 63; kk = e >> 6; }
+        const int32_t gn = n0 + nn, gk = k0 + kk;
+        float v = 0.f;
+        if (gn < p.N && gk < p.K) v = load_elem(p.b, p.dtype, b_off + gk * p.b_rs + gn * p.b_cs);
+        Bs[kk][nn] = v;
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < BK; ++kk) {
+      float av[4], bv[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) av[i] = As[kk][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) bv[j] = Bs[kk][tx * 4 + j];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int32_t gm = m0 + ty * 4 + i;
+    if (gm >= p.M) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int32_t gn = n0 + tx * 4 + j;
+      if (gn < p.N) store_elem(p.out, p.out_dtype, o_off + gm * p.o_rs + gn * p.o_cs, acc[i][j]);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Pack: copy a [batch..., rows, K] view into contiguous K-major rows
+//   dst[b][r][kp],  kp in [0, Kp), zero padded past K.
+// mode 0: 16-bit or 32-bit copy.
+// mode 1: f32 -> three TF32 terms per 32-wide K block, laid out so that one
+//         ordinary TF32 GEMM over the tripled K computes the 3xTF32 product:
+//           A side: [hi | hi | lo]      B side: [hi | lo | hi]
+//         hi = tf32(x) (round to nearest), lo = tf32(x - hi).
+// A 32x32 tile goes through shared memory so that both the read and the write
+// are coalesced whichever of (row, k) is the source's unit stride.
+// ---------------------------------------------------------------------------
+struct PackParams {
+  const void *src;
+  void *dst;
+  int32_t elt;        // bytes per element: 2 or 4
+  int32_t mode;       // 0 copy, 1 tf32 split (A side), 2 tf32 split (B side)
+  int32_t rows, K, Kp;   // Kp: padded K of the SOURCE blocks (multiple of 32 in split mode)
+  int64_t dst_row_elems; // elements per destination row (Kp, or 3*Kp in split mode)
+  int64_t src_off, src_rs, src_ks;
+  int32_t nbd;
+  int32_t bdims[kSimtMaxBatchDims];
+  int64_t src_bs[kSimtMaxBatchDims];
+  int32_t tiles_r, tiles_k;
+};
+
+__device__ __forceinline__ float tf32_round(float x) {
+  uint32_t u;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x));
+  return __uint_as_float(u);
+}
+
+__global__ void __launch_bounds__(256) pack_kernel(const PackParams p) {
+  __shared__ uint32_t tile[32][33];
+  const int64_t blk = blockIdx.x;
+  const int32_t tpb = p.tiles_r * p.tiles_k;
+  int32_t batch = static_cast<int32_t>(blk / tpb);
+  const int32_t t = static_cast<int32_t>(blk % tpb);
+  const int32_t r0 = (t / p.tiles_k) * 32;
+  const int32_t k0 = (t % p.tiles_k) * 32;
+  const int64_t dst_batch = static_cast<int64_t>(batch) * p.rows * p.dst_row_elems;
+  int64_t src_off = p.src_off;
+  for (int d = p.nbd - 1; d >= 0; --d) {
+    const int32_t idx = batch % p.bdims[d];
+    batch /= p.bdims[d];
+    src_off += idx * p.src_bs[d];
+  }
+  const int x = threadIdx.x & 31, y = threadIdx.x >> 5;  // 32 x 8
+  const bool k_fast = (p.src_ks == 1) || (p.src_rs != 1);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int rr = k_fast ? (y + i * 8) : x;
+    const int kk = k_fast ? x : (y + i * 8);
+    const int32_t gr = r0 + rr, gk = k0 + kk;
+    uint32_t v = 0;
+    if (gr < p.rows && gk < p.K) {
+      const int64_t idx = src_off + gr * p.src_rs + gk * p.src_ks;
+      v = p.elt == 4 ? static_cast<const uint32_t *>(p.src)[idx]
+                     : static_cast<uint32_t>(static_cast<const uint16_t *>(p.src)[idx]);
+    }
+    tile[rr][kk] = v;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int rr = y + i * 8, kk = x;
+    const int32_t gr = r0 + rr, gk = k0 + kk;
+    if (gr >= p.rows || gk >= p.Kp) continue;
+    const uint32_t v = tile[rr][kk];
+    if (p.mode == 0) {
+      const int64_t o = dst_batch + static_cast<int64_t>(gr) * p.dst_row_elems + gk;
+      if (p.elt == 4) static_cast<uint32_t *>(p.dst)[o] = v;
+      else static_cast<uint16_t *>(p.dst)[o] = static_cast<uint16_t>(v);
+    } else {
+      const float xv = __uint_as_float(v);
+      float hi = tf32_round(xv);
+      float lo = tf32_round(xv - hi);
+      if (!isfinite(hi)) {  // inf / NaN, or a finite value that rounds past the largest tf32
+        hi = xv;
+        lo = 0.f;
+      }
+      // k0 is a multiple of 32, so this tile is exactly one 32-wide K block.
+      const int64_t o = dst_batch + static_cast<int64_t>(gr) * p.dst_row_elems + 3ll * k0 + kk;
+      float *d = static_cast<float *>(p.dst);
+      d[o] = hi;
+      d[o + 32] = (p.mode == 1) ? hi : lo;
+      d[o + 64] = (p.mode == 1) ? lo : hi;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Strided gather into contiguous storage: the device side of Tensor::contiguous.
+// ---------------------------------------------------------------------------
+struct CopyParams {
+  const void *src;
+  void *dst;
+  int32_t elt, ndim;
+  int64_t shape[8], strides[8];
+  int64_t src_off, dst_off, n;
+};
+
+__global__ void __launch_bounds__(256) copy_strided_kernel(const CopyParams p) {
+  for (int64_t i = blockIdx.x * 256ll + threadIdx.x; i < p.n; i += static_cast<int64_t>(gridDim.x) * 256) {
+    int64_t rem = i, off = p.src_off;
+    for (int d = p.ndim - 1; d >= 0; --d) {
+      off += (rem % p.shape[d]) * p.strides[d];
+      rem /= p.shape[d];
+    }
+    switch (p.elt) {
+      case 1: static_cast<uint8_t *>(p.dst)[p.dst_off + i] = static_cast<const uint8_t *>(p.src)[off]; break;
+      case 2: static_cast<uint16_t *>(p.dst)[p.dst_off + i] = static_cast<const uint16_t *>(p.src)[off]; break;
+      case 4: static_cast<uint32_t *>(p.dst)[p.dst_off + i] = static_cast<const uint32_t *>(p.src)[off]; break;
+      default: static_cast<uint64_t *>(p.dst)[p.dst_off + i] = static_cast<const uint64_t *>(p.src)[off]; break;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Seeded synthetic data written straight into device memory (benchmarks).
+// Counter based: element i depends only on (key, i).  dist 0: U(-1,1);
+// dist 1: N(0,1) * scale by Box-Muller.
+// ---------------------------------------------------------------------------
+__host__ __device__ __forceinline__ uint64_t splitmix64(uint64_t x) {
+  x += 0x9E3779B97F4A7C15ull;
+  x = (x ^ (x >> 30)) * 0xBF58476D1CE4E5B9ull;
+  x = (x ^ (x >> 27)) * 0x94D049BB133111EBull;
+  return x ^ (x >> 31);
+}
+
+__global__ void __launch_bounds__(256) fill_kernel(void *dst, int dtype, int64_t n, uint64_t key, int dist, float scale) {
+  for (int64_t i = blockIdx.x * 256ll + threadIdx.x; i < n; i += static_cast<int64_t>(gridDim.x) * 256) {
+    const uint64_t h1 = splitmix64(key + 2ull * static_cast<uint64_t>(i));
+    float v;
+    if (dist == 0) {
+      v = 2.0f * (static_cast<float>(h1 >> 40) * (1.0f / 16777216.0f)) - 1.0f;
+    } else {
+      const uint64_t h2 = splitmix64(key + 2ull * static_cast<uint64_t>(i) + 1ull);
+      const float u1 = (static_cast<float>(h1 >> 40) + 1.0f) * (1.0f / 16777216.0f);
+      const float u2 = static_cast<float>(h2 >> 40) * (1.0f / 16777216.0f);
+      v = sqrtf(-2.0f * logf(u1)) * cospif(2.0f * u2) * scale;
+    }
+    store_elem(dst, dtype, i, v);
+  }
+}
+
+}  // namespace oxm

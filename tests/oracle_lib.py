@@ -1,0 +1,97 @@
+"""ctypes wrapper around the CPU oracle (oracle/oxm_oracle.c) for the tests,
+the smoke check and the bench's CPU-baseline leg.  Test infrastructure: the
+package never imports this."""
+from __future__ import annotations
+
+import ctypes as C
+import importlib.util
+import os
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+MAX_DIMS = 8
+F32, F64, BF16, F16 = 0, 1, 6, 7
+ACC_NATIVE, ACC_F64 = 0, 1
+_NP = {F32: np.float32, F64: np.float64, BF16: np.uint16, F16: np.float16}
+_SIZE = {F32: 4, F64: 8, 2: 4, 3: 8, 4: 1, 5: 1, BF16: 2, F16: 2}
+
+
+class OView(C.Structure):
+    _fields_ = [("dtype", C.c_int32), ("ndim", C.c_int32), ("shape", C.c_int64 * MAX_DIMS),
+                ("strides", C.c_int64 * MAX_DIMS), ("offset", C.c_int64), ("base", C.c_void_p)]
+
+
+def _view(arr: np.ndarray, tag: int) -> OView:
+    v = OView()
+    v.dtype, v.ndim = tag, arr.ndim
+    for i in range(arr.ndim):
+        v.shape[i] = arr.shape[i]
+        v.strides[i] = arr.strides[i] // _SIZE[tag]
+    v.offset = 0
+    v.base = arr.ctypes.data
+    return v
+
+
+def _build() -> str:
+    spec = importlib.util.spec_from_file_location("oracle_build", os.path.join(ROOT, "oracle", "build.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod.build_oracle()
+
+
+class Oracle:
+    def __init__(self):
+        path = os.path.join(ROOT, "oracle", "liboxm_oracle.so")
+        if not os.path.exists(path):
+            path = _build()
+        self.lib = C.CDLL(path)
+        PV = C.POINTER(OView)
+        self.lib.orc_matmul.argtypes = [PV, PV, PV, C.c_int, C.c_int]
+        self.lib.orc_batched_matmul.argtypes = [PV, PV, PV, C.c_int, C.c_int]
+        self.lib.orc_check_matmul.argtypes = [PV, PV, PV, C.c_int]
+        self.lib.orc_broadcast_shapes.argtypes = [C.POINTER(C.c_int64), C.c_int, C.POINTER(C.c_int64), C.c_int,
+                                                  C.POINTER(C.c_int64), C.POINTER(C.c_int)]
+        self.lib.orc_f32_to_bf16.argtypes = [C.c_float]; self.lib.orc_f32_to_bf16.restype = C.c_uint16
+        self.lib.orc_bf16_to_f32.argtypes = [C.c_uint16]; self.lib.orc_bf16_to_f32.restype = C.c_float
+        self.lib.orc_f32_to_f16.argtypes = [C.c_float]; self.lib.orc_f32_to_f16.restype = C.c_uint16
+        self.lib.orc_f16_to_f32.argtypes = [C.c_uint16]; self.lib.orc_f16_to_f32.restype = C.c_float
+        self.lib.orc_fill.argtypes = [C.c_void_p, C.c_int32, C.c_int64, C.c_uint64, C.c_uint64, C.c_int, C.c_double, C.c_int]
+        self.lib.orc_fill.restype = None
+        self.threads = os.cpu_count() or 1
+
+    def matmul(self, a: np.ndarray, b: np.ndarray, tag: int, acc: int = ACC_NATIVE, out_tag: int | None = None,
+               batched: bool | None = None, nthreads: int | None = None):
+        """Returns (status, out).  a, b: numpy arrays with any strides (bf16 as
+        uint16 bits).  out_tag defaults to f32 (native) / f64 (f64 acc)."""
+        if out_tag is None:
+            out_tag = F64 if acc == ACC_F64 else F32
+        if batched is None:
+            batched = not (a.ndim == 2 and b.ndim == 2)
+        va, vb = _view(a, tag), _view(b, tag)
+        st = self.lib.orc_check_matmul(C.byref(va), C.byref(vb), None, 1 if batched else 0)
+        if st != 0:
+            return st, None
+        lead = np.broadcast_shapes(a.shape[:-2], b.shape[:-2])
+        out = np.zeros(tuple(lead) + (a.shape[-2], b.shape[-1]), dtype=_NP[out_tag])
+        vo = _view(out, out_tag)
+        fn = self.lib.orc_batched_matmul if batched else self.lib.orc_matmul
+        st = fn(C.byref(va), C.byref(vb), C.byref(vo), acc, nthreads or self.threads)
+        return st, out
+
+    def broadcast_shapes(self, lhs, rhs):
+        l = (C.c_int64 * MAX_DIMS)(*lhs)
+        r = (C.c_int64 * MAX_DIMS)(*rhs)
+        o = (C.c_int64 * MAX_DIMS)()
+        n = C.c_int()
+        st = self.lib.orc_broadcast_shapes(l, len(lhs), r, len(rhs), o, C.byref(n))
+        return st, tuple(o[i] for i in range(n.value)) if st == 0 else None
+
+    def fill(self, shape, tag: int, seed: int, stream: int, dist: str, scale: float = 1.0) -> np.ndarray:
+        """Seeded synthetic data: dist 'uniform' = U(-1,1), 'normal' = N(0,1)*scale."""
+        out = np.empty(shape, dtype=_NP[tag])
+        self.lib.orc_fill(out.ctypes.data, tag, out.size, seed, stream, 0 if dist == "uniform" else 1, scale, self.threads)
+        return out
+
+    def bf16_to_f32(self, bits: np.ndarray) -> np.ndarray:
+        return (bits.astype(np.uint32) << 16).view(np.float32)

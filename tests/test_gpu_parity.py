@@ -1,0 +1,282 @@
+"""Parity of the CUDA path with the CPU oracle, through the C ABI, on a B200.
+
+Tolerances (stated once, used everywhere below):
+  f32            max |x-y| / max(|y|, rms(Y)) <= 1e-4 against the f64-accumulated oracle
+  bf16 / f16     same measure <= 1e-2 against the oracle's f32 result on the same rounded inputs
+Small-integer products (the reference's hand cases) must be bit-exact.
+"""
+import json
+import os
+
+import numpy as np
+import pytest
+
+import oxmera_b200 as ox
+from oxmera_b200 import DType, Tensor
+from tests.oracle_lib import ACC_F64, ACC_NATIVE, BF16, F16, F32
+
+pytestmark = pytest.mark.gpu
+
+HAND = json.load(open(os.path.join(os.path.dirname(__file__), "golden", "a4_hand_cases.json")))
+TAG = {DType.F32: F32, DType.BF16: BF16, DType.F16: F16}
+TOL = {DType.F32: 1e-4, DType.BF16: 1e-2, DType.F16: 1e-2}
+KERNELS = {"auto": 0, "simt": 1, "tcgen05": 2}
+
+
+def to_f64(x, dtype):
+    if dtype == DType.BF16:
+        return ox.bf16_bits_to_f32(x).reshape(x.shape).astype(np.float64)
+    return x.astype(np.float64)
+
+
+def rel_err(got, ref):
+    ref = ref.astype(np.float64)
+    got = got.astype(np.float64)
+    rms = float(np.sqrt(np.mean(ref * ref))) if ref.size else 0.0
+    if rms == 0.0:
+        return 0.0 if np.array_equal(got, ref) else float("inf")
+    return float(np.max(np.abs(got - ref) / np.maximum(np.abs(ref), rms)))
+
+
+def oracle_ref(oracle, a, b, dtype):
+    """The reference result the tolerance is stated against."""
+    acc = ACC_F64 if dtype == DType.F32 else ACC_NATIVE
+    st, ref = oracle.matmul(a, b, TAG[dtype], acc=acc)
+    assert st == 0
+    return ref
+
+
+def fill(oracle, shape, dtype, seed, stream, dist="normal", scale=1.0):
+    return oracle.fill(shape, TAG[dtype], seed, stream, dist, scale)
+
+
+def set_kernel(backend, name, tile_n=0, pair=-1):
+    backend.set_option("kernel", KERNELS[name])
+    backend.set_option("tile_n", tile_n)
+    backend.set_option("cta_pair", pair)
+
+
+@pytest.fixture(autouse=True)
+def _reset_options(backend):
+    yield
+    set_kernel(backend, "auto")
+
+
+# ---------------------------------------------------------------------------
+# the reference's own spec (exercises/a4-reference-matmul/tests/spec.rs)
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize("kernel", list(KERNELS))
+@pytest.mark.parametrize("case", HAND["matmul"], ids=lambda c: c["name"])
+def test_hand_cases_are_bit_exact(backend, kernel, case):
+    set_kernel(backend, kernel)
+    a = Tensor.from_host(np.array(case["a"], np.float32), case["a_shape"], DType.F32, backend)
+    b = Tensor.from_host(np.array(case["b"], np.float32), case["b_shape"], DType.F32, backend)
+    if "b_permute" in case:
+        b = b.permute(case["b_permute"])
+    c = a.matmul(b)  # TensorOps -> backend_for(device) -> MatmulOps::matmul
+    assert list(c.shape) == case["expected_shape"]
+    assert c.layout().is_contiguous()
+    assert c.to_host().reshape(-1).tolist() == case["expected"]
+    idx = [s - 1 for s in case["expected_shape"]]
+    assert c.get_f32(idx) == case["expected"][-1]
+
+
+def test_typed_errors(backend):
+    f = lambda shape, dt=DType.F32: Tensor.empty(shape, dt, backend)
+    with pytest.raises(ox.ShapeMismatch) as e:
+        backend.matmul(f((2, 3)), f((4, 2)))
+    assert "matmul" in str(e.value)
+    with pytest.raises(ox.OxmeraError):
+        backend.matmul(f((6,)), f((6,)))  # rank-1 operands must refuse
+    with pytest.raises(ox.ShapeMismatch):
+        backend.matmul(f((2, 2, 3)), f((3, 2)))  # rank-2 only for matmul
+    with pytest.raises(ox.DTypeMismatch):
+        backend.matmul(f((2, 3)), f((3, 2), DType.BF16))
+    with pytest.raises(ox.UnsupportedDType):
+        backend.matmul(f((2, 3), DType.I32), f((3, 2), DType.I32))
+    with pytest.raises(ox.BroadcastIncompatible):
+        backend.batched_matmul(f((2, 4, 3)), f((3, 3, 5)))
+    with pytest.raises(ox.ShapeMismatch):
+        backend.matmul_into(f((2, 3)), f((3, 2)), f((2, 3)), batched=False)  # wrong output shape
+    # the context is still healthy
+    c = backend.matmul(Tensor.from_host(np.eye(2, dtype=np.float32), (2, 2), DType.F32, backend),
+                       Tensor.from_host(np.array([1, 2, 3, 4], np.float32), (2, 2), DType.F32, backend))
+    assert c.to_host().reshape(-1).tolist() == [1.0, 2.0, 3.0, 4.0]
+
+
+def test_unregistered_device_is_backend_unavailable(backend):
+    with pytest.raises(ox.BackendUnavailable):
+        ox.backend_for(ox.Device.cuda(63))
+    with pytest.raises(ox.BackendUnavailable):
+        ox.B200Backend(63)
+    assert ox.backend_for(ox.Device.cuda(0)) is backend
+    assert backend.name() == "b200-tcgen05"
+    with pytest.raises(ox.NotImplementedOp):
+        backend.add(None, None)
+
+
+@pytest.mark.parametrize("kernel", ["simt", "tcgen05"])
+def test_transpose_law_and_column_independence(backend, oracle, kernel):
+    set_kernel(backend, kernel)
+    spec_close = lambda x, y: np.all(np.abs(x - y) <= 1e-4 * (1 + np.maximum(np.abs(x), np.abs(y))))
+    rng = np.random.default_rng(4)
+    for _ in range(8):
+        a = Tensor.from_host(rng.uniform(-8, 8, 6).astype(np.float32), (2, 3), DType.F32, backend)
+        b = Tensor.from_host(rng.uniform(-8, 8, 6).astype(np.float32), (3, 2), DType.F32, backend)
+        ab_t = a.matmul(b).permute([1, 0]).to_host()
+        bt_at = b.permute([1, 0]).matmul(a.permute([1, 0])).to_host()
+        assert spec_close(ab_t, bt_at)
+        a3 = Tensor.from_host(rng.uniform(-8, 8, 9).astype(np.float32), (3, 3), DType.F32, backend)
+        full = a3.matmul(b).to_host()
+        for j in range(2):
+            col = a3.matmul(b.narrow(1, j, 1)).to_host()
+            assert spec_close(full[:, j], col[:, 0])
+
+
+# ---------------------------------------------------------------------------
+# shapes, dtypes and kernels
+# ---------------------------------------------------------------------------
+SHAPES = [(1, 1, 1), (2, 3, 4), (7, 5, 3), (64, 64, 64), (128, 256, 64), (129, 257, 65), (130, 70, 520),
+          (300, 520, 200), (77, 33, 1000), (256, 384, 512), (1, 300, 40), (300, 1, 40), (33, 65, 1)]
+
+
+@pytest.mark.parametrize("dtype", [DType.F32, DType.BF16, DType.F16], ids=lambda d: d.name)
+@pytest.mark.parametrize("kernel", ["simt", "tcgen05"])
+def test_shape_sweep(backend, oracle, kernel, dtype):
+    set_kernel(backend, kernel)
+    for i, (m, n, k) in enumerate(SHAPES):
+        a = fill(oracle, (m, k), dtype, 100 + i, 0)
+        b = fill(oracle, (k, n), dtype, 100 + i, 1)
+        got = backend.matmul(Tensor.from_host(a, a.shape, dtype, backend), Tensor.from_host(b, b.shape, dtype, backend))
+        err = rel_err(to_f64(got.to_host(), dtype), oracle_ref(oracle, a, b, dtype))
+        assert err <= TOL[dtype], (kernel, dtype.name, (m, n, k), err, backend.last_kernel())
+
+
+@pytest.mark.parametrize("dtype", [DType.BF16, DType.F16, DType.F32], ids=lambda d: d.name)
+@pytest.mark.parametrize("dims", [(256, 384, 320), (250, 130, 99), (512, 256, 1024)], ids=str)
+@pytest.mark.parametrize("a_t,b_t", [(0, 0), (0, 1), (1, 0), (1, 1)])
+def test_transposed_operands_need_no_copy(backend, oracle, dims, a_t, b_t, dtype):
+    """All four (A, B) major combinations: K-major and MN-major operands reach
+    the tensor cores as views.  Aligned extents take the direct TMA path,
+    unaligned ones the pack path."""
+    set_kernel(backend, "tcgen05")
+    m, n, k = dims
+    ha = fill(oracle, (k, m) if a_t else (m, k), dtype, 7, 0)
+    hb = fill(oracle, (n, k) if b_t else (k, n), dtype, 7, 1)
+    ta = Tensor.from_host(ha, ha.shape, dtype, backend)
+    tb = Tensor.from_host(hb, hb.shape, dtype, backend)
+    if a_t:
+        ha, ta = ha.T, ta.permute([1, 0])
+    if b_t:
+        hb, tb = hb.T, tb.permute([1, 0])
+    before = backend.launch_counts()
+    got = backend.matmul(ta, tb)
+    after = backend.launch_counts()
+    assert after["tcgen05"] == before["tcgen05"] + 1
+    if dtype != DType.F32 and dims != (250, 130, 99):
+        assert after["pack"] == before["pack"], "aligned 16-bit views must be read in place"
+    err = rel_err(to_f64(got.to_host(), dtype), oracle_ref(oracle, ha, hb, dtype))
+    assert err <= TOL[dtype], (dims, a_t, b_t, err, backend.last_kernel())
+
+
+@pytest.mark.parametrize("kernel", ["simt", "tcgen05"])
+@pytest.mark.parametrize("dtype", [DType.F32, DType.BF16], ids=lambda d: d.name)
+def test_narrowed_and_flipped_views(backend, oracle, kernel, dtype):
+    set_kernel(backend, kernel)
+    ha = fill(oracle, (90, 150), dtype, 21, 0)
+    hb = fill(oracle, (160, 70), dtype, 21, 1)
+    ta = Tensor.from_host(ha, ha.shape, dtype, backend)
+    tb = Tensor.from_host(hb, hb.shape, dtype, backend)
+    # odd windows: offsets that are not 16-byte aligned
+    va, vta = ha[3:80, 5:133], ta.narrow(0, 3, 77).narrow(1, 5, 128)
+    vb, vtb = hb[17:145, 1:66], tb.narrow(0, 17, 128).narrow(1, 1, 65)
+    err = rel_err(to_f64(backend.matmul(vta, vtb).to_host(), dtype), oracle_ref(oracle, va, vb, dtype))
+    assert err <= TOL[dtype]
+    # negative strides
+    fa, fta = va[::-1, ::-1], vta.flip(0).flip(1)
+    fb, ftb = vb[::-1, :], vtb.flip(0)
+    err = rel_err(to_f64(backend.matmul(fta, ftb).to_host(), dtype), oracle_ref(oracle, fa, fb, dtype))
+    assert err <= TOL[dtype]
+
+
+@pytest.mark.parametrize("kernel", ["simt", "tcgen05"])
+@pytest.mark.parametrize("dtype", [DType.F32, DType.BF16, DType.F16], ids=lambda d: d.name)
+def test_broadcast_batch_dims(backend, oracle, kernel, dtype):
+    set_kernel(backend, kernel)
+    cases = [
+        ((3, 1, 24, 40), True, (1, 5, 24, 56)),   # the strided-view config in miniature: A is a transposed view
+        ((2, 3, 40, 24), False, (2, 3, 24, 56)),  # equal batch dims
+        ((4, 64, 32), False, (32, 48)),           # shared B: folds into one tall product
+        ((64, 32), False, (5, 32, 48)),           # shared A
+        ((2, 1, 3, 16, 8), False, (4, 1, 8, 24)), # interleaved broadcast dims
+    ]
+    for i, (ashape, a_t, bshape) in enumerate(cases):
+        ha = fill(oracle, ashape, dtype, 50 + i, 0)
+        hb = fill(oracle, bshape, dtype, 50 + i, 1)
+        ta = Tensor.from_host(ha, ashape, dtype, backend)
+        tb = Tensor.from_host(hb, bshape, dtype, backend)
+        if a_t:
+            perm = list(range(len(ashape) - 2)) + [len(ashape) - 1, len(ashape) - 2]
+            ha, ta = ha.transpose(perm), ta.permute(perm)
+        got = backend.batched_matmul(ta, tb)
+        ref = oracle_ref(oracle, ha, hb, dtype)
+        assert got.shape == ref.shape
+        err = rel_err(to_f64(got.to_host(), dtype), ref)
+        assert err <= TOL[dtype], (ashape, bshape, err, backend.last_kernel())
+
+
+@pytest.mark.parametrize("tile_n", [64, 128, 256])
+@pytest.mark.parametrize("dtype", [DType.BF16, DType.F32], ids=lambda d: d.name)
+def test_tile_widths(backend, oracle, tile_n, dtype):
+    set_kernel(backend, "tcgen05", tile_n=tile_n)
+    m, n, k = 384, 640, 448
+    a, b = fill(oracle, (m, k), dtype, 31, 0), fill(oracle, (k, n), dtype, 31, 1)
+    got = backend.matmul(Tensor.from_host(a, a.shape, dtype, backend), Tensor.from_host(b, b.shape, dtype, backend))
+    assert f"bn{tile_n}" in backend.last_kernel()
+    assert rel_err(to_f64(got.to_host(), dtype), oracle_ref(oracle, a, b, dtype)) <= TOL[dtype]
+
+
+def test_empty_and_degenerate(backend):
+    z = lambda shape: Tensor.from_host(np.zeros(shape, np.float32), shape, DType.F32, backend)
+    assert backend.matmul(z((0, 3)), z((3, 2))).shape == (0, 2)
+    c = backend.matmul(Tensor.from_host(np.ones((2, 0), np.float32), (2, 0), DType.F32, backend), z((0, 2)))
+    assert c.shape == (2, 2) and not c.to_host().any()  # an empty contraction sums to zero
+    assert backend.batched_matmul(z((0, 2, 3)), z((3, 2))).shape == (0, 2, 2)
+
+
+def test_output_written_through_its_own_strides(backend, oracle):
+    """A shard writes its rows into a window of the parent output."""
+    a, b = fill(oracle, (192, 96), DType.BF16, 61, 0), fill(oracle, (96, 160), DType.BF16, 61, 1)
+    ta, tb = Tensor.from_host(a, a.shape, DType.BF16, backend), Tensor.from_host(b, b.shape, DType.BF16, backend)
+    parent = Tensor.from_host(np.zeros((192, 160), np.uint16), (192, 160), DType.BF16, backend)
+    for kernel in ("simt", "tcgen05"):
+        set_kernel(backend, kernel)
+        for r0, r1 in ((0, 64), (64, 192)):
+            backend.matmul_into(ta.narrow(0, r0, r1 - r0), tb, parent.narrow(0, r0, r1 - r0), batched=False)
+        assert rel_err(to_f64(parent.to_host(), DType.BF16), oracle_ref(oracle, a, b, DType.BF16)) <= 1e-2
+    # a transposed output view (column stride != 1)
+    out_t = Tensor.empty((160, 192), DType.BF16, backend).permute([1, 0])
+    backend.matmul_into(ta, tb, out_t, batched=False)
+    assert rel_err(to_f64(out_t.to_host(), DType.BF16), oracle_ref(oracle, a, b, DType.BF16)) <= 1e-2
+
+
+def test_host_entry_point(backend, oracle):
+    a = fill(oracle, (3, 1, 130, 70), DType.F32, 71, 0)
+    b = fill(oracle, (1, 2, 70, 90), DType.F32, 71, 1)
+    av = a.transpose(0, 1, 3, 2).copy().transpose(0, 1, 3, 2)  # M-major host view
+    got = backend.matmul_host(av, b, DType.F32)
+    assert rel_err(got, oracle_ref(oracle, av, b, DType.F32)) <= 1e-4
+    a16, b16 = fill(oracle, (200, 136), DType.BF16, 72, 0), fill(oracle, (136, 264), DType.BF16, 72, 1)
+    got = backend.matmul_host(a16, b16, DType.BF16)
+    assert rel_err(to_f64(got, DType.BF16), oracle_ref(oracle, a16, b16, DType.BF16)) <= 1e-2
+
+
+def test_sharded_host_matmul_matches_single_device(backend, oracle):
+    """The collective-free sharding driver, with two shards on one device."""
+    a = fill(oracle, (4, 96, 64), DType.BF16, 81, 0)
+    b = fill(oracle, (64, 80), DType.BF16, 81, 1)
+    whole = backend.matmul_host(a, b, DType.BF16)
+    parts = ox.sharded_matmul_host([backend, backend], a, b, DType.BF16)
+    assert np.array_equal(whole, parts)
+    rows = ox.sharded_matmul_host([backend, backend], a[0], b, DType.BF16)
+    assert np.array_equal(whole[0], rows)
