@@ -62,7 +62,7 @@ struct oxm_ctx {
   EncodeTiledFn encode = nullptr;
   std::mutex mu;
   std::mutex host_mu;  // serialises calls that use the host staging buffers
-  Workspace pack_ws[2];
+  Workspace pack_ws[3];  // packed A, packed B, split-K partial sums
   Workspace host_stage[3];
   // options
   int64_t opt_kernel = 0, opt_tile_n = 0, opt_cta_pair = -1, opt_wait_limit_ms = 2000;
@@ -455,7 +455,8 @@ int launch_tcgen05(oxm_ctx *ctx, const Problem &P) {
 
   int bn = (int)ctx->opt_tile_n;
   if (bn == 0) bn = P.N > 128 ? 256 : (P.N > 64 ? 128 : 64);
-  int pair = ctx->opt_cta_pair < 0 ? 0 : (int)ctx->opt_cta_pair;
+  // CTA pairs pay off on full-width tiles with at least two row blocks.
+  int pair = ctx->opt_cta_pair < 0 ? ((bn == 256 && P.M > kTileM) ? 1 : 0) : (int)ctx->opt_cta_pair;
   if (bn == 64) pair = 0;
   const int tm = kTileM * (pair ? 2 : 1);
 
@@ -484,6 +485,43 @@ int launch_tcgen05(oxm_ctx *ctx, const Problem &P) {
             ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(tm >> 4) << 24);
   p.status = ctx->status_dev;
   p.wait_limit_ns = (uint64_t)ctx->opt_wait_limit_ms * 1000000ull;
+  p.splits = 1;
+  p.kb_per_split = p.num_kb;
+  p.tiles_per_split = p.num_tiles;
+  p.split_ostride = 0;
+  // The tensor core adds each MMA's products into the fp32 accumulator with
+  // truncation, an error of about 2^-24 per instruction that grows with the
+  // length of the chain.  For f32 results that would pass 1e-5 beyond
+  // K = 1024, so longer contractions are cut into chains of that length whose
+  // partial sums are added afterwards in round-to-nearest fp32.
+  ReduceParams rp{};
+  const int kMaxChainKb = 3 * 1024 / 32;
+  if (tf32 && p.num_kb > kMaxChainKb) {
+    p.splits = (p.num_kb + kMaxChainKb - 1) / kMaxChainKb;
+    p.kb_per_split = (p.num_kb + p.splits - 1) / p.splits;
+    p.splits = (p.num_kb + p.kb_per_split - 1) / p.kb_per_split;
+    const int64_t slab = P.nbatch * P.M * P.N;
+    int st2 = grow(ctx, ctx->pack_ws[2], (size_t)slab * p.splits * sizeof(float));
+    if (st2) return st2;
+    rp.ws = static_cast<const float *>(ctx->pack_ws[2].ptr);
+    rp.out = static_cast<float *>(P.o);
+    rp.splits = p.splits; rp.M = p.M; rp.N = p.N;
+    rp.split_stride = slab; rp.total = slab;
+    rp.o_off = P.o_off; rp.o_rs = P.o_rs; rp.o_cs = P.o_cs;
+    rp.nbd = P.nbd;
+    int64_t dense = P.M * P.N;
+    for (int d = P.nbd - 1; d >= 0; --d) {
+      rp.bdims[d] = (int32_t)P.bdims[d];
+      rp.o_bs[d] = P.o_bs[d];
+      p.o_bstride[d] = dense;
+      dense *= P.bdims[d];
+    }
+    p.out = ctx->pack_ws[2].ptr;
+    p.out_rs = P.N; p.out_cs = 1;
+    p.out_vec = (P.N % 4 == 0) ? 1 : 0;
+    p.split_ostride = slab;
+    p.num_tiles *= p.splits;
+  }
 
   CUtensorMap tmA, tmB;
   int st = make_map(ctx, &tmA, sa, P.dtype, P.elt, kTileM, bk);
@@ -505,6 +543,12 @@ int launch_tcgen05(oxm_ctx *ctx, const Problem &P) {
   }
   if (st) return st;
   ctx->launches[0]++; ctx->launches[1]++;
+  if (p.splits > 1) {
+    const int64_t blocks = std::min<int64_t>((rp.total + 255) / 256, (int64_t)ctx->num_sms * 16);
+    splitk_reduce_kernel<<<(unsigned)blocks, 256, 0, ctx->stream>>>(rp);
+    CUDA_TRY(cudaGetLastError());
+    ctx->launches[0]++; ctx->launches[3]++;
+  }
   return OXM_OK;
 }
 

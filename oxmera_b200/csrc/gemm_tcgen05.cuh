@@ -52,6 +52,11 @@ struct GemmParams {
   uint32_t idesc;
   uint32_t *status;
   uint64_t wait_limit_ns;
+  // Split-K: the contraction is cut into `splits` chains of `kb_per_split`
+  // blocks, each written to its own slab of a partial-sum workspace.
+  int32_t splits, kb_per_split;
+  int64_t tiles_per_split;
+  int64_t split_ostride;  // elements
 };
 
 template <int BN, int STAGES, int PAIR>
@@ -104,12 +109,17 @@ __device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, cons
 struct TileCoord {
   int32_t m_blk, n_blk;
   int32_t a_batch, b_batch;
+  int32_t kb0, nkb;  // contraction blocks [kb0, kb0 + nkb) of this tile
   int64_t o_off;
 };
 
 template <int GROUP_M>
 __device__ __forceinline__ TileCoord decode_tile(const GemmParams &p, int64_t tile) {
   TileCoord c;
+  const int32_t split = static_cast<int32_t>(tile / p.tiles_per_split);
+  tile -= split * p.tiles_per_split;
+  c.kb0 = split * p.kb_per_split;
+  c.nkb = min(p.kb_per_split, p.num_kb - c.kb0);
   const int32_t tpb = p.tiles_m * p.tiles_n;
   int32_t batch = static_cast<int32_t>(tile / tpb);
   const int32_t t = static_cast<int32_t>(tile - static_cast<int64_t>(batch) * tpb);
@@ -124,7 +134,7 @@ __device__ __forceinline__ TileCoord decode_tile(const GemmParams &p, int64_t ti
   c.n_blk = r / gsz;
   c.a_batch = 0;
   c.b_batch = 0;
-  c.o_off = 0;
+  c.o_off = static_cast<int64_t>(split) * p.split_ostride;
   for (int d = p.nbd - 1; d >= 0; --d) {
     const int32_t idx = batch % p.bdims[d];
     batch /= p.bdims[d];
@@ -215,11 +225,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         const TileCoord tc = decode_tile<GROUP_M>(p, tile);
         const int32_t m0 = tc.m_blk * TM + static_cast<int32_t>(cta_rank) * kTileM;
         const int32_t n0 = tc.n_blk * BN + static_cast<int32_t>(cta_rank) * L::kBNC;
-        for (int32_t kb = 0; kb < p.num_kb; ++kb) {
+        for (int32_t kb = 0; kb < tc.nkb; ++kb) {
           if (!bounded_wait(empty_bar(s), ph ^ 1u, wc)) { ok = false; break; }
           const uint32_t sa = base + s * L::kStageBytes;
           const uint32_t sb = sa + L::kABytes;
-          const int32_t k0 = kb * BK;
+          const int32_t k0 = (tc.kb0 + kb) * BK;
           if constexpr (PAIR) {
             // The leader's barrier collects the bytes of both CTAs' loads.
             const uint32_t fb = ptx::mapa_shared(full_bar(s), 0);
@@ -278,10 +288,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       uint32_t s = 0, ph = 0, as = 0, aph = 0;
       bool ok = true;
       for (int64_t tile = tile_first; ok && tile < p.num_tiles; tile += tile_stride) {
+        const int32_t split = static_cast<int32_t>(tile / p.tiles_per_split);
+        const int32_t nkb = min(p.kb_per_split, p.num_kb - split * p.kb_per_split);
         if (!bounded_wait(tempty_bar(as), aph ^ 1u, wc)) break;
         ptx::tc_fence_after();
         const uint32_t d_tmem = tmem_base + as * BN;
-        for (int32_t kb = 0; kb < p.num_kb; ++kb) {
+        for (int32_t kb = 0; kb < nkb; ++kb) {
           if (!bounded_wait(full_bar(s), ph, wc)) { ok = false; break; }
           ptx::tc_fence_after();
           const uint32_t sa = base + s * L::kStageBytes;

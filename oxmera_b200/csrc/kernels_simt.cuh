@@ -213,6 +213,38 @@ __global__ void __launch_bounds__(256) pack_kernel(const PackParams p) {
 }
 
 // ---------------------------------------------------------------------------
+// Split-K reduction: out[b][m][n] = sum over s of ws[s][b][m][n] (f32, added in
+// ascending s with round-to-nearest), written through the output's strides.
+// ---------------------------------------------------------------------------
+struct ReduceParams {
+  const float *ws;
+  float *out;
+  int32_t splits, M, N;
+  int64_t split_stride;  // elements between partial-sum slabs
+  int64_t total;         // nbatch * M * N
+  int64_t o_off, o_rs, o_cs;
+  int32_t nbd;
+  int32_t bdims[kSimtMaxBatchDims];
+  int64_t o_bs[kSimtMaxBatchDims];
+};
+
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const ReduceParams p) {
+  const int64_t mn = static_cast<int64_t>(p.M) * p.N;
+  for (int64_t i = blockIdx.x * 256ll + threadIdx.x; i < p.total; i += static_cast<int64_t>(gridDim.x) * 256) {
+    float acc = p.ws[i];
+    for (int s = 1; s < p.splits; ++s) acc += p.ws[i + s * p.split_stride];
+    int64_t batch = i / mn;
+    const int64_t r = i - batch * mn;
+    int64_t off = p.o_off + (r / p.N) * p.o_rs + (r % p.N) * p.o_cs;
+    for (int d = p.nbd - 1; d >= 0; --d) {
+      off += (batch % p.bdims[d]) * p.o_bs[d];
+      batch /= p.bdims[d];
+    }
+    p.out[off] = acc;
+  }
+}
+
+// ---------------------------------------------------------------------------
 // Strided gather into contiguous storage: the device side of Tensor::contiguous.
 // ---------------------------------------------------------------------------
 struct CopyParams {

@@ -73,8 +73,16 @@ def check_product(backend, oracle, w, g, host, dev, rows_per_batch, max_batches)
         ref = oracle_ref(oracle, a_rows, hb[pick(hb, bi)], dtype)
         worst = max(worst, rel_err(to_f64(ho[bi][rows], dtype), ref))
     assert worst <= tol, (w.key, g.name, "sampled rows", worst, backend.last_kernel())
-    # 2. whole-output checksums in float64
-    out_round = 2.0 ** -8 if dtype != DType.F32 else 2.0 ** -20  # rounding of each stored element
+    print(f"parity {w.key}/{g.name}: sampled-row error {worst:.3e} (tolerance {tol:g}) {backend.last_kernel()}")
+    # 2. whole-output checksums in float64.  bf16/f16 results carry an unbiased
+    # rounding of 2^-9 per stored element, which sums like sqrt(n).  The f32
+    # tensor-core path accumulates with truncation, a bias that sums like n;
+    # allow a tenth of the elementwise tolerance per element.
+    def budget(count, rms):
+        if dtype == DType.F32:
+            return 1e-5 * rms * count + 1e-9
+        return 6 * 2.0 ** -8 * rms * np.sqrt(count) + 1e-9
+
     b_cache = {}
     for bi in bidx_all:
         pb = pick(hb, bi)
@@ -85,8 +93,8 @@ def check_product(backend, oracle, w, g, host, dev, rows_per_batch, max_batches)
         rms = float(np.sqrt(np.mean(Cm * Cm)))
         row_sum, row_ref = Cm.sum(axis=1), A @ B.sum(axis=1)
         col_sum, col_ref = Cm.sum(axis=0), A.sum(axis=0) @ B
-        assert np.max(np.abs(row_sum - row_ref)) <= 6 * out_round * rms * np.sqrt(n) + 1e-9, (w.key, g.name, bi, "C.1")
-        assert np.max(np.abs(col_sum - col_ref)) <= 6 * out_round * rms * np.sqrt(m) + 1e-9, (w.key, g.name, bi, "1^T.C")
+        assert np.max(np.abs(row_sum - row_ref)) <= budget(n, rms), (w.key, g.name, bi, "C.1")
+        assert np.max(np.abs(col_sum - col_ref)) <= budget(m, rms), (w.key, g.name, bi, "1^T.C")
     return out
 
 

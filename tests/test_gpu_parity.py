@@ -236,6 +236,25 @@ def test_tile_widths(backend, oracle, tile_n, dtype):
     assert rel_err(to_f64(got.to_host(), dtype), oracle_ref(oracle, a, b, dtype)) <= TOL[dtype]
 
 
+def test_long_f32_contractions_keep_their_accuracy(backend, oracle):
+    """The tensor core adds into its fp32 accumulator with truncation, so the
+    f32 path cuts contractions longer than 1024 into chains and adds the
+    partial sums in round-to-nearest: the error must not grow with K."""
+    set_kernel(backend, "tcgen05")
+    cases = [((130, 8192), (8192, 260)), ((64, 5000), (5000, 100)), ((3, 64, 4096), (4096, 96)),
+             ((2, 1, 64, 3000), (1, 2, 3000, 72))]
+    for i, (ashape, bshape) in enumerate(cases):
+        a, b = fill(oracle, ashape, DType.F32, 90 + i, 0), fill(oracle, bshape, DType.F32, 90 + i, 1)
+        before = backend.launch_counts()
+        got = backend.batched_matmul(Tensor.from_host(a, ashape, DType.F32, backend),
+                                     Tensor.from_host(b, bshape, DType.F32, backend))
+        after = backend.launch_counts()
+        assert after["pack"] - before["pack"] == 3, "two operand packs and one partial-sum reduction"
+        err = rel_err(got.to_host(), oracle_ref(oracle, a, b, DType.F32))
+        print(f"f32 K={ashape[-1]}: error {err:.3e}")
+        assert err <= 5e-5, (ashape, bshape, err)
+
+
 def test_empty_and_degenerate(backend):
     z = lambda shape: Tensor.from_host(np.zeros(shape, np.float32), shape, DType.F32, backend)
     assert backend.matmul(z((0, 3)), z((3, 2))).shape == (0, 2)
