@@ -132,6 +132,34 @@ int oxm_batched_matmul(oxm_ctx *ctx, const oxm_view *a, const oxm_view *b, const
  * (crates/oxmera-runtime/src/lib.rs:68-69,99-102). */
 int oxm_batched_matmul_host(oxm_ctx *ctx, const oxm_view *a, const oxm_view *b, const oxm_view *out);
 
+/* f32 rank-2 matmul that allocates nothing.  It has no counterpart in the
+ * oxmera reference; it exists for hosts that cannot allocate device memory
+ * while they run: one that gave all of HBM to its own arena at start-up, or a
+ * latency-critical loop where an allocator call (a possible device-wide
+ * synchronisation, a possible out-of-memory failure) is not acceptable.
+ *
+ * Same contract and typed errors as oxm_matmul for f32 operands, always on the
+ * tensor-core 3xTF32 path.  The scratch that path needs (both operands packed
+ * as TF32 hi/lo terms, plus split-K partial sums when K > 1024) lives in a
+ * fixed array of OXM_NOALLOC_SCRATCH_BYTES inside the library's device image;
+ * every GPU that loads the library holds that array until the process exits.
+ * The call makes no cudaMalloc / cudaFree / pool call.
+ *
+ * Limit: 256-byte-rounded  M*3*Kp*4 + N*3*Kp*4 (+ S*M*N*4 when K > 1024),
+ * with Kp = K rounded up to 32 and S = ceil(3*Kp / 3072), must not exceed
+ * OXM_NOALLOC_SCRATCH_BYTES; larger products are refused with
+ * OXM_NOT_IMPLEMENTED and a message that states both sizes.
+ *
+ * The first call on each device looks the array's address up (and may make
+ * the driver load the module); make that call during start-up, before any
+ * stream capture begins.  All calls share the one array: two calls whose
+ * kernels can overlap on the GPU (different contexts on the same device)
+ * race on it; calls through one context are ordered by its stream.  Nothing
+ * in the array needs clearing between calls: each call rewrites every element
+ * it later reads. */
+#define OXM_NOALLOC_SCRATCH_BYTES (32u << 20)
+int oxm_matmul_f32_noalloc(oxm_ctx *ctx, const oxm_view *a, const oxm_view *b, const oxm_view *out);
+
 /* Stands behind the device half of `Tensor::contiguous`
  * (crates/oxmera-tensor/src/tensor.rs:86-90): gathers `src` (any strides, any
  * dtype) in logical order into `dst`, a row-major contiguous view of the same

@@ -924,3 +924,185 @@ int oxm_launch_counts(oxm_ctx *ctx, int64_t counts[4]) {
 const char *oxm_last_kernel(oxm_ctx *ctx) { return ctx ? ctx->last_kernel : "none"; }
 
 }  // extern "C"
+
+// ===========================================================================
+// Allocation-free f32 matmul
+//
+// Some hosts of this library must not allocate device memory once they are
+// running: a server or training loop that handed all of HBM to its own arena
+// at start-up, or a latency-critical loop that cannot afford the device-wide
+// synchronisation and the failure modes of an allocator call in mid-flight.
+// For them the packed TF32 operands and split-K partial sums of the f32
+// tensor-core path live in a fixed array that is part of the loaded module.
+// ===========================================================================
+namespace {
+
+constexpr size_t kNoAllocScratchBytes = OXM_NOALLOC_SCRATCH_BYTES;
+
+// Every GPU that loads this library holds these 32 MiB until the process ends.
+// In host code this name is only a handle for cudaGetSymbolAddress, never an
+// address a kernel may be given.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+
+std::mutex g_noalloc_mu;
+void *g_noalloc_ptr[64] = {};  // device address of the array, per CUDA device
+
+// Resolve the array's device address once per device, with that device current.
+int noalloc_scratch(int device, unsigned char **out) {
+  if (device < 0 || device >= 64) return fail(OXM_INVALID_ARGUMENT, "matmul_f32_noalloc: device index %d out of range", device);
+  std::lock_guard<std::mutex> lock(g_noalloc_mu);
+  if (!g_noalloc_ptr[device]) {
+    CUDA_TRY(cudaSetDevice(device));
+    void *ptr = nullptr;
+    CUDA_TRY(cudaGetSymbolAddress(&ptr, g_noalloc_scratch));
+    if (!ptr) return fail(OXM_CUDA_ERROR, "matmul_f32_noalloc: cudaGetSymbolAddress returned a null address");
+    g_noalloc_ptr[device] = ptr;
+  }
+  *out = static_cast<unsigned char *>(g_noalloc_ptr[device]);
+  return OXM_OK;
+}
+
+size_t align256(size_t x) { return (x + 255) & ~static_cast<size_t>(255); }
+
+// The pack step of the f32 path, writing to a caller-chosen address.
+int pack_f32_into(oxm_ctx *ctx, const Problem &P, bool is_b, void *dst, int64_t Kp, Staged &s) {
+  const int64_t rows = is_b ? P.N : P.M;
+  PackParams pp{};
+  pp.src = is_b ? P.b : P.a;
+  pp.dst = dst;
+  pp.elt = 4;
+  pp.mode = is_b ? 2 : 1;
+  pp.rows = (int32_t)rows; pp.K = (int32_t)P.K; pp.Kp = (int32_t)Kp;
+  pp.dst_row_elems = 3 * Kp;
+  pp.src_off = is_b ? P.b_off : P.a_off;
+  pp.src_rs = is_b ? P.b_rs : P.a_rs;
+  pp.src_ks = is_b ? P.b_ks : P.a_ks;
+  pp.nbd = 0;
+  pp.tiles_r = (int32_t)((rows + 31) / 32);
+  pp.tiles_k = (int32_t)(Kp / 32);
+  const int64_t blocks = (int64_t)pp.tiles_r * pp.tiles_k;
+  pack_kernel<<<(unsigned)blocks, 256, 0, ctx->stream>>>(pp);
+  CUDA_TRY(cudaGetLastError());
+  ctx->launches[0]++; ctx->launches[3]++;
+  s = Staged{};
+  s.ptr = dst;
+  s.mn_major = false;
+  s.rows = rows; s.K = 3 * Kp;
+  s.ld_bytes = 3 * Kp * 4;
+  s.nb = 1;
+  s.bs_bytes = rows * 3 * Kp * 4;
+  return OXM_OK;
+}
+
+}  // namespace
+
+extern "C" int oxm_matmul_f32_noalloc(oxm_ctx *ctx, const oxm_view *a, const oxm_view *b, const oxm_view *out) {
+  int st = validate(ctx, a, b, out, false, false);
+  if (st) return st;
+  if (a->dtype != OXM_F32)
+    return fail(OXM_UNSUPPORTED_DTYPE, "dtype %s is not supported by matmul_f32_noalloc (f32 only)", dtype_name(a->dtype));
+  for (const oxm_view *v : {a, b, out}) {
+    if (v->shape[0] * v->shape[1] > 0 && v->base == nullptr) return fail(OXM_INVALID_ARGUMENT, "matmul_f32_noalloc: view with null storage");
+  }
+  const Problem P = normalise(a, b, out);
+  if (P.M == 0 || P.N == 0) return OXM_OK;
+  if (P.M >= (1ll << 31) || P.N >= (1ll << 31) || P.K >= (1ll << 29))
+    return fail(OXM_NOT_IMPLEMENTED, "matmul_f32_noalloc is not implemented for extents above 2^31");
+
+  // Scratch plan: [packed A | packed B | split-K partial sums], each 256-byte aligned.
+  const int64_t Kp = (P.K + 31) / 32 * 32;
+  const int32_t num_kb = (int32_t)(3 * Kp / 32);
+  const int kMaxChainKb = 3 * 1024 / 32;
+  int32_t splits = 1, kb_per_split = num_kb;
+  if (num_kb > kMaxChainKb) {
+    splits = (num_kb + kMaxChainKb - 1) / kMaxChainKb;
+    kb_per_split = (num_kb + splits - 1) / splits;
+    splits = (num_kb + kb_per_split - 1) / kb_per_split;
+  }
+  const size_t a_bytes = align256((size_t)P.M * 3 * Kp * 4);
+  const size_t b_bytes = align256((size_t)P.N * 3 * Kp * 4);
+  const size_t part_bytes = splits > 1 ? align256((size_t)splits * P.M * P.N * 4) : 0;
+  const size_t need = a_bytes + b_bytes + part_bytes;
+  if (need > kNoAllocScratchBytes)
+    return fail(OXM_NOT_IMPLEMENTED,
+                "matmul_f32_noalloc is not implemented for [%lld, %lld] x [%lld, %lld]: it needs %zu bytes of scratch "
+                "(packed operands%s) and the static scratch holds %zu; use oxm_matmul",
+                (long long)P.M, (long long)P.K, (long long)P.K, (long long)P.N, need,
+                splits > 1 ? " and split-K partial sums" : "", kNoAllocScratchBytes);
+
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  CUDA_TRY(cudaSetDevice(ctx->device));
+  if (P.K == 0) return launch_simt(ctx, P);  // an empty contraction: zeros, no scratch involved
+  unsigned char *scratch = nullptr;
+  st = noalloc_scratch(ctx->device, &scratch);
+  if (st) return st;
+
+  // The pack kernel rewrites every scratch element the GEMM will read, zero
+  // padding included, and the GEMM writes every partial sum the reduction
+  // reads: nothing left over from an earlier call is ever consumed, so no
+  // clearing pass is needed.
+  Staged sa{}, sb{};
+  st = pack_f32_into(ctx, P, false, scratch, Kp, sa);
+  if (st) return st;
+  st = pack_f32_into(ctx, P, true, scratch + a_bytes, Kp, sb);
+  if (st) return st;
+
+  const int bn = P.N > 128 ? 256 : (P.N > 64 ? 128 : 64);
+  const int pair = (bn == 256 && P.M > kTileM) ? 1 : 0;
+  const int tm = kTileM * (pair ? 2 : 1);
+  GemmParams p{};
+  p.M = (int32_t)P.M; p.N = (int32_t)P.N; p.K = (int32_t)(3 * Kp);
+  p.tiles_m = (int32_t)((P.M + tm - 1) / tm);
+  p.tiles_n = (int32_t)((P.N + bn - 1) / bn);
+  p.num_kb = num_kb;
+  p.nbatch = 1;
+  p.num_tiles = (int64_t)p.tiles_m * p.tiles_n;
+  p.nbd = 0;
+  p.out_dtype = OXM_F32;
+  p.idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(tm >> 4) << 24);
+  p.status = ctx->status_dev;
+  p.wait_limit_ns = (uint64_t)ctx->opt_wait_limit_ms * 1000000ull;
+  p.splits = splits;
+  p.kb_per_split = kb_per_split;
+  p.tiles_per_split = p.num_tiles;
+  ReduceParams rp{};
+  if (splits > 1) {
+    float *partials = reinterpret_cast<float *>(scratch + a_bytes + b_bytes);
+    p.out = partials;
+    p.out_rs = P.N; p.out_cs = 1;
+    p.out_vec = (P.N % 4 == 0) ? 1 : 0;
+    p.split_ostride = P.M * P.N;
+    p.num_tiles *= splits;
+    rp.ws = partials;
+    rp.out = static_cast<float *>(P.o);
+    rp.splits = splits; rp.M = p.M; rp.N = p.N;
+    rp.split_stride = P.M * P.N; rp.total = P.M * P.N;
+    rp.o_off = P.o_off; rp.o_rs = P.o_rs; rp.o_cs = P.o_cs;
+    rp.nbd = 0;
+  } else {
+    p.out = static_cast<uint8_t *>(P.o) + P.o_off * 4;
+    p.out_rs = P.o_rs; p.out_cs = P.o_cs;
+    p.out_vec = (P.o_cs == 1 && (reinterpret_cast<uintptr_t>(p.out) % 16) == 0 && (P.o_rs * 4) % 16 == 0) ? 1 : 0;
+    p.split_ostride = 0;
+  }
+  CUtensorMap tmA, tmB;
+  st = make_map(ctx, &tmA, sa, OXM_F32, 4, kTileM, 32);
+  if (st) return st;
+  st = make_map(ctx, &tmB, sb, OXM_F32, 4, pair ? bn / 2 : bn, 32);
+  if (st) return st;
+  const int grid = pair ? 2 * (int)std::min<int64_t>(p.num_tiles, ctx->num_sms / 2)
+                        : (int)std::min<int64_t>(p.num_tiles, ctx->num_sms);
+  if (pair) st = launch_instance<256, 6, 0, 0, 1, 1>(ctx, tmA, tmB, p, grid);
+  else if (bn == 256) st = launch_instance<256, 4, 0, 0, 1, 0>(ctx, tmA, tmB, p, grid);
+  else if (bn == 128) st = launch_instance<128, 6, 0, 0, 1, 0>(ctx, tmA, tmB, p, grid);
+  else st = launch_instance<64, 8, 0, 0, 1, 0>(ctx, tmA, tmB, p, grid);
+  if (st) return st;
+  ctx->launches[0]++; ctx->launches[1]++;
+  if (splits > 1) {
+    const int64_t blocks = std::min<int64_t>((rp.total + 255) / 256, (int64_t)ctx->num_sms * 16);
+    splitk_reduce_kernel<<<(unsigned)blocks, 256, 0, ctx->stream>>>(rp);
+    CUDA_TRY(cudaGetLastError());
+    ctx->launches[0]++; ctx->launches[3]++;
+  }
+  return OXM_OK;
+}
