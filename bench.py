@@ -34,6 +34,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 from oxmera_b200 import B200Backend, DType, Tensor, broadcast_shapes  # noqa: E402
+from oxmera_b200.dist import init_from_env  # noqa: E402
 from oxmera_b200.workloads import WORKLOADS, device_fill, gemm_views, materialise, shard_flops  # noqa: E402
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the tcgen05 GEMM
@@ -110,35 +111,6 @@ class ClockSampler(threading.Thread):
                 "reasons": sorted(seen), "samples": len(window), "window": label}
 
 
-def init_dist(n_gpus: int):
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    if world <= 1:
-        return None, 0, 1, 0
-    import torch
-    import torch.distributed as dist
-    rank, local = int(os.environ["RANK"]), int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    return dist, rank, world, local
-
-
-def barrier(dist, local):
-    if dist is not None:
-        import torch
-        t = torch.zeros(1, device=f"cuda:{local}")
-        dist.all_reduce(t)
-        torch.cuda.synchronize(local)
-
-
-def max_over_ranks(dist, local, value: float) -> float:
-    if dist is None:
-        return value
-    import torch
-    t = torch.tensor([value], dtype=torch.float64, device=f"cuda:{local}")
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    return float(t.item())
-
-
 # ---------------------------------------------------------------------------
 # the CPU reference arm (also the cpu_baseline of the main arm)
 # ---------------------------------------------------------------------------
@@ -213,7 +185,8 @@ def run_reference(args):
 # the GPU arm
 # ---------------------------------------------------------------------------
 def run_ours(args):
-    dist, rank, world, local = init_dist(args.gpus)
+    grp = init_from_env("nccl")
+    rank, world, local = grp.rank, grp.world, grp.local_rank
     w = WORKLOADS[args.workload]
     be = B200Backend(local)
     be.set_option("cta_pair", args.cta_pair)
@@ -236,7 +209,7 @@ def run_ours(args):
     for _ in range(max(args.warmup, 3)):
         step()
     be.synchronize()
-    barrier(dist, local)
+    grp.barrier()
     counts0 = be.launch_counts()
     timer = be.timer()
     t_wall0 = time.perf_counter()
@@ -247,10 +220,10 @@ def run_ours(args):
     be.synchronize()
     t_wall1 = time.perf_counter()
     ms_local = timer.elapsed_ms()
-    barrier(dist, local)
+    grp.barrier()
     counts1 = be.launch_counts()
     sampler.stop()
-    ms = max_over_ranks(dist, local, ms_local)
+    ms = grp.max_over_ranks(ms_local)
     kernel_name = be.last_kernel()
 
     flops_total = w.flops()
@@ -269,7 +242,7 @@ def run_ours(args):
         peak = peak / 2.0  # tf32 runs at half the bf16 rate; the 3-term split spends 3 MMA flops per useful one
     launches = counts1["tcgen05"] - counts0["tcgen05"]
     per_gpu_tflops = shard_flops(w, rank, world) * args.steps / (ms_local * 1e-3) / 1e12
-    achieved = max_over_ranks(dist, local, -per_gpu_tflops) * -1.0  # slowest GPU's own rate
+    achieved = grp.min_over_ranks(per_gpu_tflops)  # the slowest GPU's own rate
     roofline = {
         "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
         "traffic": NCU_TRAFFIC_BYTES.get(w.key),
@@ -311,14 +284,14 @@ def run_ours(args):
         e_steps = max(2, min(args.steps, args.e2e_steps))
         for ha, hb, ho in hwork:  # warm-up: staging buffers get allocated here
             be.matmul_host(ha, hb, w.dtype, out=ho)
-        barrier(dist, local)
+        grp.barrier()
         t0 = time.perf_counter()
         for _ in range(e_steps):
             for ha, hb, ho in hwork:
                 be.matmul_host(ha, hb, w.dtype, out=ho)  # returns after the result bytes have landed
         e_ms = (time.perf_counter() - t0) * 1e3
-        barrier(dist, local)
-        e_ms = max_over_ranks(dist, local, e_ms)
+        grp.barrier()
+        e_ms = grp.max_over_ranks(e_ms)
         e2e = {"value": flops_total * e_steps / (e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
                "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h), "steps": e_steps,
                "ms_per_step": e_ms / e_steps,
@@ -347,8 +320,7 @@ def run_ours(args):
         }
         print(json.dumps(line), flush=True)
     be.close()
-    if dist is not None:
-        dist.destroy_process_group()
+    grp.close()
 
 
 def main():
