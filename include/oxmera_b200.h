@@ -185,6 +185,7 @@ int oxm_fill(oxm_ctx *ctx, void *dst_device, int dtype, int64_t n, uint64_t seed
  *                 kernel (packing operands it cannot address directly)
  *   "tile_n"      0 auto, else 64 / 128 / 256
  *   "cta_pair"    -1 auto, 0 one CTA per tile, 1 CTA pairs (cta_group::2)
+ *   "group_m"     0 auto, else the number of tile rows walked together
  *   "wait_limit_ms"  bound of every device-side wait (default 2000, or the
  *                 environment variable OXM_WAIT_LIMIT_MS at context creation)
  * Unknown keys or values are OXM_INVALID_ARGUMENT. */

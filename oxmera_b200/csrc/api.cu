@@ -65,7 +65,7 @@ struct oxm_ctx {
   Workspace pack_ws[3];  // packed A, packed B, split-K partial sums
   Workspace host_stage[3];
   // options
-  int64_t opt_kernel = 0, opt_tile_n = 0, opt_cta_pair = -1, opt_wait_limit_ms = 2000;
+  int64_t opt_kernel = 0, opt_tile_n = 0, opt_cta_pair = -1, opt_wait_limit_ms = 2000, opt_group_m = 0;
   int64_t launches[4] = {0, 0, 0, 0};
   char last_kernel[96] = "none";
 };
@@ -489,6 +489,7 @@ int launch_tcgen05(oxm_ctx *ctx, const Problem &P) {
   p.kb_per_split = p.num_kb;
   p.tiles_per_split = p.num_tiles;
   p.split_ostride = 0;
+  p.group_m = ctx->opt_group_m > 0 ? (int32_t)ctx->opt_group_m : (pair ? 8 : 16);
   // The tensor core adds each MMA's products into the fp32 accumulator with
   // truncation, an error of about 2^-24 per instruction that grows with the
   // length of the chain.  For f32 results that would pass 1e-5 beyond
@@ -899,6 +900,7 @@ int oxm_set_option(oxm_ctx *ctx, const char *key, int64_t value) {
   else if (!strcmp(key, "tile_n") && (value == 0 || value == 64 || value == 128 || value == 256)) ctx->opt_tile_n = value;
   else if (!strcmp(key, "cta_pair") && value >= -1 && value <= 1) ctx->opt_cta_pair = value;
   else if (!strcmp(key, "wait_limit_ms") && value >= 1 && value <= 600000) ctx->opt_wait_limit_ms = value;
+  else if (!strcmp(key, "group_m") && value >= 0 && value <= 1024) ctx->opt_group_m = value;
   else return fail(OXM_INVALID_ARGUMENT, "oxm_set_option: unknown option or value: %s = %lld", key, (long long)value);
   return OXM_OK;
 }
@@ -910,6 +912,7 @@ int oxm_get_option(oxm_ctx *ctx, const char *key, int64_t *value) {
   else if (!strcmp(key, "tile_n")) *value = ctx->opt_tile_n;
   else if (!strcmp(key, "cta_pair")) *value = ctx->opt_cta_pair;
   else if (!strcmp(key, "wait_limit_ms")) *value = ctx->opt_wait_limit_ms;
+  else if (!strcmp(key, "group_m")) *value = ctx->opt_group_m;
   else return fail(OXM_INVALID_ARGUMENT, "oxm_get_option: unknown option: %s", key);
   return OXM_OK;
 }
@@ -1065,6 +1068,7 @@ extern "C" int oxm_matmul_f32_noalloc(oxm_ctx *ctx, const oxm_view *a, const oxm
   p.splits = splits;
   p.kb_per_split = kb_per_split;
   p.tiles_per_split = p.num_tiles;
+  p.group_m = pair ? 8 : 16;
   ReduceParams rp{};
   if (splits > 1) {
     float *partials = reinterpret_cast<float *>(scratch + a_bytes + b_bytes);

@@ -57,6 +57,7 @@ struct GemmParams {
   int32_t splits, kb_per_split;
   int64_t tiles_per_split;
   int64_t split_ostride;  // elements
+  int32_t group_m;        // tile rows walked together (L2 reuse)
 };
 
 template <int BN, int STAGES, int PAIR>
@@ -113,7 +114,6 @@ struct TileCoord {
   int64_t o_off;
 };
 
-template <int GROUP_M>
 __device__ __forceinline__ TileCoord decode_tile(const GemmParams &p, int64_t tile) {
   TileCoord c;
   const int32_t split = static_cast<int32_t>(tile / p.tiles_per_split);
@@ -125,6 +125,7 @@ __device__ __forceinline__ TileCoord decode_tile(const GemmParams &p, int64_t ti
   const int32_t t = static_cast<int32_t>(tile - static_cast<int64_t>(batch) * tpb);
   // Walk GROUP_M tile rows at a time so that concurrently resident CTAs share
   // A and B panels in L2.
+  const int32_t GROUP_M = p.group_m;
   const int32_t gt = GROUP_M * p.tiles_n;
   const int32_t g = t / gt;
   const int32_t first = g * GROUP_M;
@@ -159,7 +160,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   constexpr int MMA_K = kMmaKBytes / ELT;  // contraction elements per tcgen05.mma
   constexpr int TM = kTileM * (PAIR ? 2 : 1);
   constexpr uint32_t TMEM_COLS = (2 * BN <= 32) ? 32 : (2 * BN <= 64) ? 64 : (2 * BN <= 128) ? 128 : (2 * BN <= 256) ? 256 : 512;
-  constexpr int GROUP_M = PAIR ? 8 : 16;
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = ptx::smem_u32(smem_raw);
@@ -222,7 +222,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       uint32_t s = 0, ph = 0;
       bool ok = true;
       for (int64_t tile = tile_first; ok && tile < p.num_tiles; tile += tile_stride) {
-        const TileCoord tc = decode_tile<GROUP_M>(p, tile);
+        const TileCoord tc = decode_tile(p, tile);
         const int32_t m0 = tc.m_blk * TM + static_cast<int32_t>(cta_rank) * kTileM;
         const int32_t n0 = tc.n_blk * BN + static_cast<int32_t>(cta_rank) * L::kBNC;
         for (int32_t kb = 0; kb < tc.nkb; ++kb) {
@@ -332,7 +332,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     const int esz = p.out_dtype == 0 ? 4 : 2;
     uint32_t as = 0, aph = 0;
     for (int64_t tile = tile_first; tile < p.num_tiles; tile += tile_stride) {
-      const TileCoord tc = decode_tile<GROUP_M>(p, tile);
+      const TileCoord tc = decode_tile(p, tile);
       // tcgen05.ld is warp-collective: leave the loop as a whole warp or not at all.
       const bool ready = bounded_wait(tfull_bar(as), aph, wc);
       if (!__all_sync(0xffffffffu, ready)) break;
