@@ -191,6 +191,7 @@ def run_ours(args):
     be = B200Backend(local)
     be.set_option("cta_pair", args.cta_pair)
     be.set_option("tile_n", args.tile_n)
+    be.set_option("group_m", args.group_m)
     tensors = materialise(w, device_fill(be))
     work = []
     for g in w.gemms:
@@ -332,7 +333,8 @@ def main():
     ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS))
     ap.add_argument("--e2e-steps", type=int, default=10)
     ap.add_argument("--cta-pair", type=int, default=-1, choices=[-1, 0, 1], help="-1 auto, 0 one CTA per tile, 1 CTA pairs")
-    ap.add_argument("--tile-n", type=int, default=0, choices=[0, 64, 128, 256])
+    ap.add_argument("--tile-n", type=int, default=0, choices=[0, 64, 128, 256, 512])
+    ap.add_argument("--group-m", type=int, default=0)
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()

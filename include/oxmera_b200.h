@@ -183,8 +183,10 @@ int oxm_fill(oxm_ctx *ctx, void *dst_device, int dtype, int64_t n, uint64_t seed
 /* Options (key, value):
  *   "kernel"      0 auto, 1 force the SIMT FFMA kernel, 2 force the tcgen05
  *                 kernel (packing operands it cannot address directly)
- *   "tile_n"      0 auto, else 64 / 128 / 256
+ *   "tile_n"      0 auto, else 64 / 128 / 256 / 512 (512: CTA pairs only)
  *   "cta_pair"    -1 auto, 0 one CTA per tile, 1 CTA pairs (cta_group::2)
+ *   "tma_store"   1 (default) write results with bulk tensor stores when the
+ *                 output allows it, 0 always use plain strided stores
  *   "group_m"     0 auto, else the number of tile rows walked together
  *   "wait_limit_ms"  bound of every device-side wait (default 2000, or the
  *                 environment variable OXM_WAIT_LIMIT_MS at context creation)

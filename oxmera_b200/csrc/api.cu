@@ -65,7 +65,7 @@ struct oxm_ctx {
   Workspace pack_ws[3];  // packed A, packed B, split-K partial sums
   Workspace host_stage[3];
   // options
-  int64_t opt_kernel = 0, opt_tile_n = 0, opt_cta_pair = -1, opt_wait_limit_ms = 2000, opt_group_m = 0;
+  int64_t opt_kernel = 0, opt_tile_n = 0, opt_cta_pair = -1, opt_wait_limit_ms = 2000, opt_group_m = 0, opt_tma_store = 1;
   int64_t launches[4] = {0, 0, 0, 0};
   char last_kernel[96] = "none";
 };
@@ -404,14 +404,15 @@ int make_map(oxm_ctx *ctx, CUtensorMap *tm, const Staged &s, int dtype, int elt,
 }
 
 template <int BN, int STAGES, int A_MN, int B_MN, int TF32, int PAIR>
-int launch_instance(oxm_ctx *ctx, const CUtensorMap &tmA, const CUtensorMap &tmB, const GemmParams &p, int grid) {
+int launch_instance(oxm_ctx *ctx, const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap &tmC,
+                    const GemmParams &p, int grid) {
   using L = GemmSmem<BN, STAGES, PAIR>;
   auto kern = gemm_tcgen05_kernel<BN, STAGES, A_MN, B_MN, TF32, PAIR>;
   static_assert(L::kDynamic <= 232448, "shared memory budget of one SM");
   CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic));
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3((unsigned)grid, 1, 1);
-  cfg.blockDim = dim3(kGemmThreads, 1, 1);
+  cfg.blockDim = dim3(gemm_threads(BN), 1, 1);
   cfg.dynamicSmemBytes = L::kDynamic;
   cfg.stream = ctx->stream;
   cudaLaunchAttribute attr[1];
@@ -420,7 +421,7 @@ int launch_instance(oxm_ctx *ctx, const CUtensorMap &tmA, const CUtensorMap &tmB
     attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr; cfg.numAttrs = 1;
   }
-  CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, tmA, tmB, p));
+  CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmC, p));
   snprintf(ctx->last_kernel, sizeof(ctx->last_kernel), "gemm_tcgen05_%s_bn%d_s%d_%c%c_%s", TF32 ? "tf32x3" : "f16", BN,
            STAGES, A_MN ? 'm' : 'k', B_MN ? 'n' : 'k', PAIR ? "pair" : "1cta");
   return OXM_OK;
@@ -428,12 +429,35 @@ int launch_instance(oxm_ctx *ctx, const CUtensorMap &tmA, const CUtensorMap &tmB
 
 template <int BN, int STAGES, int PAIR>
 int launch_majors(oxm_ctx *ctx, bool tf32, bool a_mn, bool b_mn, const CUtensorMap &tmA, const CUtensorMap &tmB,
-                  const GemmParams &p, int grid) {
-  if (tf32) return launch_instance<BN, STAGES, 0, 0, 1, PAIR>(ctx, tmA, tmB, p, grid);
-  if (!a_mn && !b_mn) return launch_instance<BN, STAGES, 0, 0, 0, PAIR>(ctx, tmA, tmB, p, grid);
-  if (!a_mn && b_mn) return launch_instance<BN, STAGES, 0, 1, 0, PAIR>(ctx, tmA, tmB, p, grid);
-  if (a_mn && !b_mn) return launch_instance<BN, STAGES, 1, 0, 0, PAIR>(ctx, tmA, tmB, p, grid);
-  return launch_instance<BN, STAGES, 1, 1, 0, PAIR>(ctx, tmA, tmB, p, grid);
+                  const CUtensorMap &tmC, const GemmParams &p, int grid) {
+  if (tf32) return launch_instance<BN, STAGES, 0, 0, 1, PAIR>(ctx, tmA, tmB, tmC, p, grid);
+  if (!a_mn && !b_mn) return launch_instance<BN, STAGES, 0, 0, 0, PAIR>(ctx, tmA, tmB, tmC, p, grid);
+  if (!a_mn && b_mn) return launch_instance<BN, STAGES, 0, 1, 0, PAIR>(ctx, tmA, tmB, tmC, p, grid);
+  if (a_mn && !b_mn) return launch_instance<BN, STAGES, 1, 0, 0, PAIR>(ctx, tmA, tmB, tmC, p, grid);
+  return launch_instance<BN, STAGES, 1, 1, 0, PAIR>(ctx, tmA, tmB, tmC, p, grid);
+}
+
+// Store tensor map over the output: {N, M, batch} in boxes of 128 bytes x 32
+// rows.  Returns false when the output cannot be described (the kernel then
+// stores through plain strided writes).
+bool make_out_map(oxm_ctx *ctx, CUtensorMap *tm, void *ptr, int dtype, int elt, int64_t M, int64_t N, int64_t nb,
+                  int64_t rs_elems, int64_t bs_elems) {
+  if (reinterpret_cast<uintptr_t>(ptr) % 16) return false;
+  if (M > 1 && (rs_elems <= 0 || (rs_elems * elt) % 16)) return false;
+  if (nb > 1 && (bs_elems <= 0 || (bs_elems * elt) % 16)) return false;
+  if (nb >= (1ll << 31)) return false;
+  const int64_t rs_bytes = M > 1 ? rs_elems * elt : (N * elt + 15) / 16 * 16;
+  const int64_t bs_bytes = nb > 1 ? bs_elems * elt : std::max<int64_t>(16, (rs_bytes * M + 15) / 16 * 16);
+  if (rs_bytes >= (1ll << 40) || bs_bytes >= (1ll << 40)) return false;
+  const CUtensorMapDataType dt = dtype == OXM_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                : dtype == OXM_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                    : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  cuuint64_t dims[3] = {(cuuint64_t)N, (cuuint64_t)M, (cuuint64_t)nb};
+  cuuint64_t strides[2] = {(cuuint64_t)rs_bytes, (cuuint64_t)bs_bytes};
+  cuuint32_t box[3] = {(cuuint32_t)(kStageKBytes / elt), 32, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  return ctx->encode(tm, dt, 3, ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                     CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 int launch_tcgen05(oxm_ctx *ctx, const Problem &P) {
@@ -456,8 +480,19 @@ int launch_tcgen05(oxm_ctx *ctx, const Problem &P) {
   int bn = (int)ctx->opt_tile_n;
   if (bn == 0) bn = P.N > 128 ? 256 : (P.N > 64 ? 128 : 64);
   // CTA pairs pay off on full-width tiles with at least two row blocks.
-  int pair = ctx->opt_cta_pair < 0 ? ((bn == 256 && P.M > kTileM) ? 1 : 0) : (int)ctx->opt_cta_pair;
+  int pair = ctx->opt_cta_pair < 0 ? ((bn >= 256 && P.M > kTileM) ? 1 : 0) : (int)ctx->opt_cta_pair;
   if (bn == 64) pair = 0;
+  if (bn == 512 && !pair) bn = 256;  // the 512-wide tile exists only as a pair
+  if (ctx->opt_tile_n == 0 && pair && bn == 256 && P.N > 256) {
+    // 256 x 512 pair tiles move a quarter fewer operand bytes per flop but leave
+    // the epilogue exposed and halve the tile count: take them when they do not
+    // cost a wave.
+    const int64_t slots = ctx->num_sms / 2;
+    const int64_t rows = (P.M + 255) / 256;
+    const int64_t t256 = rows * ((P.N + 255) / 256) * P.nbatch, t512 = rows * ((P.N + 511) / 512) * P.nbatch;
+    const double c256 = (double)((t256 + slots - 1) / slots), c512 = 2.0 * (double)((t512 + slots - 1) / slots) / 1.04;
+    if (c512 <= c256) bn = 512;
+  }
   const int tm = kTileM * (pair ? 2 : 1);
 
   GemmParams p{};
@@ -482,7 +517,7 @@ int launch_tcgen05(oxm_ctx *ctx, const Problem &P) {
   p.out_vec = vec ? 1 : 0;
   const uint32_t fmt = tf32 ? 2u : (P.dtype == OXM_BF16 ? 1u : 0u);
   p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((sa.mn_major ? 1u : 0u) << 15) | ((sb.mn_major ? 1u : 0u) << 16) |
-            ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(tm >> 4) << 24);
+            ((uint32_t)(std::min(bn, 256) >> 3) << 17) | ((uint32_t)(tm >> 4) << 24);
   p.status = ctx->status_dev;
   p.wait_limit_ns = (uint64_t)ctx->opt_wait_limit_ms * 1000000ull;
   p.splits = 1;
@@ -524,23 +559,36 @@ int launch_tcgen05(oxm_ctx *ctx, const Problem &P) {
     p.num_tiles *= p.splits;
   }
 
-  CUtensorMap tmA, tmB;
+  CUtensorMap tmA, tmB, tmC;
+  memset(&tmC, 0, sizeof(tmC));
   int st = make_map(ctx, &tmA, sa, P.dtype, P.elt, kTileM, bk);
   if (st) return st;
-  st = make_map(ctx, &tmB, sb, P.dtype, P.elt, pair ? bn / 2 : bn, bk);
+  st = make_map(ctx, &tmB, sb, P.dtype, P.elt, pair ? std::min(bn, 256) / 2 : bn, bk);
   if (st) return st;
+  // The epilogue writes through a bulk tensor store when the output is a
+  // row-contiguous, 16-byte-aligned window whose batch dims fold into one stride.
+  if (p.splits > 1) {
+    p.out_tma = make_out_map(ctx, &tmC, p.out, OXM_F32, 4, P.M, P.N, P.nbatch * p.splits, P.N, P.M * P.N) ? 1 : 0;
+  } else if (P.o_cs == 1 || P.N == 1) {
+    bool fold = true;
+    for (int d = 0; d + 1 < P.nbd; ++d) fold = fold && P.o_bs[d] == P.o_bs[d + 1] * P.bdims[d + 1];
+    p.out_tma = fold && make_out_map(ctx, &tmC, p.out, P.dtype, P.elt, P.M, P.N, P.nbatch, P.o_rs,
+                                     P.nbd ? P.o_bs[P.nbd - 1] : 0) ? 1 : 0;
+  }
+  if (ctx->opt_tma_store == 0) p.out_tma = 0;
 
   int grid;
   if (pair) grid = 2 * (int)std::min<int64_t>(p.num_tiles, ctx->num_sms / 2);
   else grid = (int)std::min<int64_t>(p.num_tiles, ctx->num_sms);
 
   if (!pair) {
-    if (bn == 256) st = launch_majors<256, 4, 0>(ctx, tf32, sa.mn_major, sb.mn_major, tmA, tmB, p, grid);
-    else if (bn == 128) st = launch_majors<128, 6, 0>(ctx, tf32, sa.mn_major, sb.mn_major, tmA, tmB, p, grid);
-    else st = launch_majors<64, 8, 0>(ctx, tf32, sa.mn_major, sb.mn_major, tmA, tmB, p, grid);
+    if (bn == 256) st = launch_majors<256, 4, 0>(ctx, tf32, sa.mn_major, sb.mn_major, tmA, tmB, tmC, p, grid);
+    else if (bn == 128) st = launch_majors<128, 6, 0>(ctx, tf32, sa.mn_major, sb.mn_major, tmA, tmB, tmC, p, grid);
+    else st = launch_majors<64, 8, 0>(ctx, tf32, sa.mn_major, sb.mn_major, tmA, tmB, tmC, p, grid);
   } else {
-    if (bn == 256) st = launch_majors<256, 6, 1>(ctx, tf32, sa.mn_major, sb.mn_major, tmA, tmB, p, grid);
-    else st = launch_majors<128, 8, 1>(ctx, tf32, sa.mn_major, sb.mn_major, tmA, tmB, p, grid);
+    if (bn == 512) st = launch_majors<512, 4, 1>(ctx, tf32, sa.mn_major, sb.mn_major, tmA, tmB, tmC, p, grid);
+    else if (bn == 256) st = launch_majors<256, 6, 1>(ctx, tf32, sa.mn_major, sb.mn_major, tmA, tmB, tmC, p, grid);
+    else st = launch_majors<128, 8, 1>(ctx, tf32, sa.mn_major, sb.mn_major, tmA, tmB, tmC, p, grid);
   }
   if (st) return st;
   ctx->launches[0]++; ctx->launches[1]++;
@@ -897,10 +945,11 @@ int oxm_set_option(oxm_ctx *ctx, const char *key, int64_t value) {
   if (!ctx || !key) return fail(OXM_INVALID_ARGUMENT, "oxm_set_option: null argument");
   std::lock_guard<std::mutex> lock(ctx->mu);
   if (!strcmp(key, "kernel") && value >= 0 && value <= 2) ctx->opt_kernel = value;
-  else if (!strcmp(key, "tile_n") && (value == 0 || value == 64 || value == 128 || value == 256)) ctx->opt_tile_n = value;
+  else if (!strcmp(key, "tile_n") && (value == 0 || value == 64 || value == 128 || value == 256 || value == 512)) ctx->opt_tile_n = value;
   else if (!strcmp(key, "cta_pair") && value >= -1 && value <= 1) ctx->opt_cta_pair = value;
   else if (!strcmp(key, "wait_limit_ms") && value >= 1 && value <= 600000) ctx->opt_wait_limit_ms = value;
   else if (!strcmp(key, "group_m") && value >= 0 && value <= 1024) ctx->opt_group_m = value;
+  else if (!strcmp(key, "tma_store") && (value == 0 || value == 1)) ctx->opt_tma_store = value;
   else return fail(OXM_INVALID_ARGUMENT, "oxm_set_option: unknown option or value: %s = %lld", key, (long long)value);
   return OXM_OK;
 }
@@ -913,6 +962,7 @@ int oxm_get_option(oxm_ctx *ctx, const char *key, int64_t *value) {
   else if (!strcmp(key, "cta_pair")) *value = ctx->opt_cta_pair;
   else if (!strcmp(key, "wait_limit_ms")) *value = ctx->opt_wait_limit_ms;
   else if (!strcmp(key, "group_m")) *value = ctx->opt_group_m;
+  else if (!strcmp(key, "tma_store")) *value = ctx->opt_tma_store;
   else return fail(OXM_INVALID_ARGUMENT, "oxm_get_option: unknown option: %s", key);
   return OXM_OK;
 }
@@ -1089,17 +1139,19 @@ extern "C" int oxm_matmul_f32_noalloc(oxm_ctx *ctx, const oxm_view *a, const oxm
     p.out_vec = (P.o_cs == 1 && (reinterpret_cast<uintptr_t>(p.out) % 16) == 0 && (P.o_rs * 4) % 16 == 0) ? 1 : 0;
     p.split_ostride = 0;
   }
-  CUtensorMap tmA, tmB;
+  CUtensorMap tmA, tmB, tmC;
+  memset(&tmC, 0, sizeof(tmC));
+  p.out_tma = 0;  // plain strided stores: the output may be any view
   st = make_map(ctx, &tmA, sa, OXM_F32, 4, kTileM, 32);
   if (st) return st;
   st = make_map(ctx, &tmB, sb, OXM_F32, 4, pair ? bn / 2 : bn, 32);
   if (st) return st;
   const int grid = pair ? 2 * (int)std::min<int64_t>(p.num_tiles, ctx->num_sms / 2)
                         : (int)std::min<int64_t>(p.num_tiles, ctx->num_sms);
-  if (pair) st = launch_instance<256, 6, 0, 0, 1, 1>(ctx, tmA, tmB, p, grid);
-  else if (bn == 256) st = launch_instance<256, 4, 0, 0, 1, 0>(ctx, tmA, tmB, p, grid);
-  else if (bn == 128) st = launch_instance<128, 6, 0, 0, 1, 0>(ctx, tmA, tmB, p, grid);
-  else st = launch_instance<64, 8, 0, 0, 1, 0>(ctx, tmA, tmB, p, grid);
+  if (pair) st = launch_instance<256, 6, 0, 0, 1, 1>(ctx, tmA, tmB, tmC, p, grid);
+  else if (bn == 256) st = launch_instance<256, 4, 0, 0, 1, 0>(ctx, tmA, tmB, tmC, p, grid);
+  else if (bn == 128) st = launch_instance<128, 6, 0, 0, 1, 0>(ctx, tmA, tmB, tmC, p, grid);
+  else st = launch_instance<64, 8, 0, 0, 1, 0>(ctx, tmA, tmB, tmC, p, grid);
   if (st) return st;
   ctx->launches[0]++; ctx->launches[1]++;
   if (splits > 1) {

@@ -31,7 +31,10 @@ constexpr int kMaxBatchDims = 6;
 constexpr int kTileM = 128;        // accumulator rows per CTA (= TMEM lanes)
 constexpr int kStageKBytes = 128;  // contraction bytes per pipeline stage (one swizzle row)
 constexpr int kMmaKBytes = 32;     // contraction bytes per tcgen05.mma
-constexpr int kGemmThreads = 192;
+// Threads per CTA: a TMA warp, an MMA warp, and four epilogue warps per group
+// (two groups when one accumulator fills tensor memory and the epilogue is exposed).
+__host__ __device__ constexpr int gemm_epi_groups(int bn) { return bn > 256 ? 2 : 1; }
+__host__ __device__ constexpr int gemm_threads(int bn) { return 64 + 128 * gemm_epi_groups(bn); }
 constexpr uint32_t kStatusTimeout = 11;  // OXM_TIMEOUT
 
 struct GemmParams {
@@ -49,6 +52,7 @@ struct GemmParams {
   int64_t out_rs, out_cs;  // elements
   int32_t out_dtype;       // 0 f32, 6 bf16, 7 f16
   int32_t out_vec;         // rows may be written with 16-byte stores
+  int32_t out_tma;         // the output is described by the store tensor map
   uint32_t idesc;
   uint32_t *status;
   uint64_t wait_limit_ns;
@@ -66,7 +70,11 @@ struct GemmSmem {
   static constexpr int kABytes = kTileM * kStageKBytes;
   static constexpr int kBBytes = kBNC * kStageKBytes;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kBarOffset = STAGES * kStageBytes;
+  // one 32-row x 128-byte staging tile per epilogue warp for the TMA-store epilogue
+  static constexpr int kStagingOffset = STAGES * kStageBytes;
+  static constexpr int kStagingTile = 32 * kStageKBytes;
+  static constexpr int kStagingBytes = 4 * gemm_epi_groups(BN) * kStagingTile;
+  static constexpr int kBarOffset = kStagingOffset + kStagingBytes;
   // full[STAGES] empty[STAGES] tmem_full[2] tmem_empty[2] teardown, then two u32 slots
   static constexpr int kNumBars = 2 * STAGES + 5;
   static constexpr int kTotal = kBarOffset + kNumBars * 8 + 16;
@@ -111,6 +119,7 @@ struct TileCoord {
   int32_t m_blk, n_blk;
   int32_t a_batch, b_batch;
   int32_t kb0, nkb;  // contraction blocks [kb0, kb0 + nkb) of this tile
+  int32_t o_batch;   // batch coordinate of the store tensor map
   int64_t o_off;
 };
 
@@ -123,6 +132,7 @@ __device__ __forceinline__ TileCoord decode_tile(const GemmParams &p, int64_t ti
   const int32_t tpb = p.tiles_m * p.tiles_n;
   int32_t batch = static_cast<int32_t>(tile / tpb);
   const int32_t t = static_cast<int32_t>(tile - static_cast<int64_t>(batch) * tpb);
+  c.o_batch = split * p.nbatch + batch;
   // Walk GROUP_M tile rows at a time so that concurrently resident CTAs share
   // A and B panels in L2.
   const int32_t GROUP_M = p.group_m;
@@ -147,11 +157,12 @@ __device__ __forceinline__ TileCoord decode_tile(const GemmParams &p, int64_t ti
 }
 
 template <int BN, int STAGES, int A_MN, int B_MN, int TF32, int PAIR>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __launch_bounds__(gemm_threads(BN), 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                    const GemmParams p) {
+                    const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
   static_assert(!(TF32 && (A_MN || B_MN)), "the tf32 path stages K-major operands only");
-  static_assert(BN % 32 == 0 && BN >= 32 && BN <= 256, "tile width");
+  static_assert(BN % 64 == 0 && BN >= 64 && BN <= 512, "tile width");
+  static_assert(BN <= 256 || PAIR, "tiles wider than one MMA need the CTA pair");
   using L = GemmSmem<BN, STAGES, PAIR>;
   constexpr int ELT = TF32 ? 4 : 2;
   constexpr int BK = kStageKBytes / ELT;   // contraction elements per stage
@@ -159,7 +170,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   constexpr int MMAS = kStageKBytes / kMmaKBytes;
   constexpr int MMA_K = kMmaKBytes / ELT;  // contraction elements per tcgen05.mma
   constexpr int TM = kTileM * (PAIR ? 2 : 1);
-  constexpr uint32_t TMEM_COLS = (2 * BN <= 32) ? 32 : (2 * BN <= 64) ? 64 : (2 * BN <= 128) ? 128 : (2 * BN <= 256) ? 256 : 512;
+  // A tile wider than 256 columns is NSUB MMAs of SUBN columns side by side in
+  // tensor memory.  Two accumulators (epilogue overlapped with the next main
+  // loop) while they fit the 512 columns, one otherwise.
+  constexpr int NSUB = BN > 256 ? BN / 256 : 1;
+  constexpr int SUBN = BN / NSUB;
+  constexpr int SUBC = PAIR ? SUBN / 2 : SUBN;  // B rows one CTA stages per sub-tile
+  constexpr int ACC = (2 * BN <= 512) ? 2 : 1;
+  constexpr int EPI_GROUPS = gemm_epi_groups(BN);
+  constexpr int GROUP_COLS = BN / EPI_GROUPS;  // accumulator columns one epilogue warp drains
+  constexpr uint32_t TMEM_COLS = (ACC * BN <= 128) ? 128 : (ACC * BN <= 256) ? 256 : 512;
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = ptx::smem_u32(smem_raw);
@@ -187,7 +207,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
     for (int a = 0; a < 2; ++a) {
       ptx::mbar_init(tfull_bar(a), 1);
-      ptx::mbar_init(tempty_bar(a), PAIR ? 8 : 4);
+      ptx::mbar_init(tempty_bar(a), (PAIR ? 8 : 4) * EPI_GROUPS);
     }
     ptx::mbar_init(teardown_bar, 1);
     *abort_flag = 0;
@@ -197,6 +217,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   if (warp == 0 && lane == 0) {
     ptx::prefetch_tensormap(&tmA);
     ptx::prefetch_tensormap(&tmB);
+    if (p.out_tma) ptx::prefetch_tensormap(&tmC);
   }
   if (warp == 1) {
     ptx::tmem_alloc<PAIR>(ptx::smem_u32(tmem_slot), TMEM_COLS);
@@ -224,7 +245,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       for (int64_t tile = tile_first; ok && tile < p.num_tiles; tile += tile_stride) {
         const TileCoord tc = decode_tile(p, tile);
         const int32_t m0 = tc.m_blk * TM + static_cast<int32_t>(cta_rank) * kTileM;
-        const int32_t n0 = tc.n_blk * BN + static_cast<int32_t>(cta_rank) * L::kBNC;
+        const int32_t n0 = tc.n_blk * BN + static_cast<int32_t>(cta_rank) * SUBC;  // + sub * SUBN per sub-tile
         for (int32_t kb = 0; kb < tc.nkb; ++kb) {
           if (!bounded_wait(empty_bar(s), ph ^ 1u, wc)) { ok = false; break; }
           const uint32_t sa = base + s * L::kStageBytes;
@@ -241,12 +262,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             } else {
               ptx::tma_load_3d_pair(sa, &tmA, fb, k0, m0, tc.a_batch);
             }
-            if constexpr (B_MN) {
 #pragma unroll
-              for (int j = 0; j < L::kBNC / BOXW; ++j)
-                ptx::tma_load_3d_pair(sb + j * (BK * kStageKBytes), &tmB, fb, n0 + j * BOXW, k0, tc.b_batch);
-            } else {
-              ptx::tma_load_3d_pair(sb, &tmB, fb, k0, n0, tc.b_batch);
+            for (int sub = 0; sub < NSUB; ++sub) {
+              const uint32_t sbs = sb + sub * (SUBC * kStageKBytes);
+              const int32_t ns = n0 + sub * SUBN;
+              if constexpr (B_MN) {
+#pragma unroll
+                for (int j = 0; j < SUBC / BOXW; ++j)
+                  ptx::tma_load_3d_pair(sbs + j * (BK * kStageKBytes), &tmB, fb, ns + j * BOXW, k0, tc.b_batch);
+              } else {
+                ptx::tma_load_3d_pair(sbs, &tmB, fb, k0, ns, tc.b_batch);
+              }
             }
           } else {
             const uint32_t fb = full_bar(s);
@@ -260,7 +286,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             }
             if constexpr (B_MN) {
 #pragma unroll
-              for (int j = 0; j < L::kBNC / BOXW; ++j)
+              for (int j = 0; j < SUBC / BOXW; ++j)
                 ptx::tma_load_3d(sb + j * (BK * kStageKBytes), &tmB, fb, n0 + j * BOXW, k0, tc.b_batch);
             } else {
               ptx::tma_load_3d(sb, &tmB, fb, k0, n0, tc.b_batch);
@@ -302,9 +328,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           const uint64_t bdesc = make_smem_desc(sb, B_LBO, 1024);
 #pragma unroll
           for (int j = 0; j < MMAS; ++j) {
-            ptx::umma<PAIR, TF32>(d_tmem, adesc + static_cast<uint64_t>(j * A_ADV),
-                                  bdesc + static_cast<uint64_t>(j * B_ADV), p.idesc,
-                                  (kb | j) != 0 ? 1u : 0u);
+#pragma unroll
+            for (int sub = 0; sub < NSUB; ++sub) {
+              ptx::umma<PAIR, TF32>(d_tmem + sub * SUBN, adesc + static_cast<uint64_t>(j * A_ADV),
+                                    bdesc + static_cast<uint64_t>(j * B_ADV + sub * ((SUBC * kStageKBytes) >> 4)),
+                                    p.idesc, (kb | j) != 0 ? 1u : 0u);
+            }
           }
           if constexpr (PAIR) ptx::umma_commit_pair(empty_bar(s), 3);
           else ptx::umma_commit(empty_bar(s));
@@ -313,8 +342,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         if (!ok) break;
         if constexpr (PAIR) ptx::umma_commit_pair(tfull_bar(as), 3);
         else ptx::umma_commit(tfull_bar(as));
-        as ^= 1u;
-        if (as == 0) aph ^= 1u;
+        if (++as == ACC) { as = 0; aph ^= 1u; }
       }
       if (*abort_flag) {
         // Let tensor-core work already issued retire before tensor memory is freed.
@@ -329,6 +357,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   } else {
     // ---------------- epilogue: TMEM -> registers -> global ----------------
     const uint32_t q = warp & 3u;  // the TMEM lane quarter this warp may read
+    const uint32_t stage_smem = base + L::kStagingOffset + (warp - 2u) * L::kStagingTile;
     const int esz = p.out_dtype == 0 ? 4 : 2;
     uint32_t as = 0, aph = 0;
     for (int64_t tile = tile_first; tile < p.num_tiles; tile += tile_stride) {
@@ -340,61 +369,129 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       const int32_t row = tc.m_blk * TM + static_cast<int32_t>(cta_rank) * kTileM + static_cast<int32_t>(q * 32u + lane);
       const bool row_ok = row < p.M;
       uint8_t *rowp = static_cast<uint8_t *>(p.out) + (tc.o_off + static_cast<int64_t>(row) * p.out_rs) * esz;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t v[32];
-        ptx::tmem_ld_32x32(tmem_base + as * BN + c * 32 + ((q * 32u) << 16), v);
-        ptx::tmem_ld_wait();
-        const int32_t col0 = tc.n_blk * BN + c * 32;
-        if (row_ok && col0 < p.N) {
-          if (p.out_vec && col0 + 32 <= p.N) {
-            if (p.out_dtype == 0) {
-              uint4 *dst = reinterpret_cast<uint4 *>(rowp + static_cast<int64_t>(col0) * 4);
+      // One 32-column chunk of this thread's row: convert and store through the output's strides.
+      auto store_chunk = [&](const uint32_t (&v)[32], int32_t col0) {
+        if (!row_ok || col0 >= p.N) return;
+        if (p.out_vec && col0 + 32 <= p.N) {
+          if (p.out_dtype == 0) {
+            uint4 *dst = reinterpret_cast<uint4 *>(rowp + static_cast<int64_t>(col0) * 4);
 #pragma unroll
-              for (int i = 0; i < 8; ++i) dst[i] = make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-            } else {
-              uint32_t h[16];
-              if (p.out_dtype == 6) {
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                  __nv_bfloat162 t = __floats2bfloat162_rn(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
-                  h[i] = *reinterpret_cast<uint32_t *>(&t);
-                }
-              } else {
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                  __half2 t = __floats2half2_rn(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
-                  h[i] = *reinterpret_cast<uint32_t *>(&t);
-                }
-              }
-              uint4 *dst = reinterpret_cast<uint4 *>(rowp + static_cast<int64_t>(col0) * 2);
-#pragma unroll
-              for (int i = 0; i < 4; ++i) dst[i] = make_uint4(h[4 * i], h[4 * i + 1], h[4 * i + 2], h[4 * i + 3]);
-            }
+            for (int i = 0; i < 8; ++i) dst[i] = make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
           } else {
+            uint32_t h[16];
+            if (p.out_dtype == 6) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              if (col0 + i < p.N) {
-                const float f = __uint_as_float(v[i]);
-                const int64_t e = static_cast<int64_t>(col0 + i) * p.out_cs;
-                if (p.out_dtype == 0) reinterpret_cast<float *>(rowp)[e] = f;
-                else if (p.out_dtype == 6) reinterpret_cast<__nv_bfloat16 *>(rowp)[e] = __float2bfloat16_rn(f);
-                else reinterpret_cast<__half *>(rowp)[e] = __float2half_rn(f);
+              for (int i = 0; i < 16; ++i) {
+                __nv_bfloat162 t = __floats2bfloat162_rn(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+                h[i] = *reinterpret_cast<uint32_t *>(&t);
               }
+            } else {
+#pragma unroll
+              for (int i = 0; i < 16; ++i) {
+                __half2 t = __floats2half2_rn(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+                h[i] = *reinterpret_cast<uint32_t *>(&t);
+              }
+            }
+            uint4 *dst = reinterpret_cast<uint4 *>(rowp + static_cast<int64_t>(col0) * 2);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) dst[i] = make_uint4(h[4 * i], h[4 * i + 1], h[4 * i + 2], h[4 * i + 3]);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            if (col0 + i < p.N) {
+              const float f = __uint_as_float(v[i]);
+              const int64_t e = static_cast<int64_t>(col0 + i) * p.out_cs;
+              if (p.out_dtype == 0) reinterpret_cast<float *>(rowp)[e] = f;
+              else if (p.out_dtype == 6) reinterpret_cast<__nv_bfloat16 *>(rowp)[e] = __float2bfloat16_rn(f);
+              else reinterpret_cast<__half *>(rowp)[e] = __float2half_rn(f);
             }
           }
         }
+      };
+      const int32_t gcol = static_cast<int32_t>((warp - 2u) >> 2) * GROUP_COLS;  // this warp's first column
+      const uint32_t t_acc = tmem_base + as * BN + gcol + ((q * 32u) << 16);
+      const int32_t col_base = tc.n_blk * BN + gcol;
+      const int32_t row0 = row - static_cast<int32_t>(lane);  // first of this warp's 32 rows
+      // One 128-byte-wide chunk of the warp's 32 rows: staged in shared memory in
+      // the 128-byte swizzle (16-byte piece j of row r lands at piece j ^ (r & 7)),
+      // then written by one bulk tensor store, which clips at the tensor's edge.
+      auto emit = [&](const uint4 (&piece)[8], int32_t col) {
+        if (row0 >= p.M || col >= p.N) return;  // warp-uniform
+        if (lane == 0) ptx::bulk_wait_read_all();  // the previous store has released the staging tile
+        __syncwarp();
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const uint32_t addr = stage_smem + lane * kStageKBytes + ((static_cast<uint32_t>(j) ^ (lane & 7u)) << 4);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(piece[j].x), "r"(piece[j].y),
+                       "r"(piece[j].z), "r"(piece[j].w) : "memory");
+        }
+        ptx::fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          ptx::tma_store_3d(&tmC, stage_smem, col, row0, tc.o_batch);
+          ptx::bulk_commit_group();
+        }
+      };
+      constexpr int BATCH = (ACC == 1 && GROUP_COLS % 128 == 0) ? 128 : 64;  // columns drained per wait
+      constexpr int NLD = BATCH / 32;
+#pragma unroll 1
+      for (int c = 0; c < GROUP_COLS / BATCH; ++c) {
+        uint32_t v[NLD][32];
+#pragma unroll
+        for (int i = 0; i < NLD; ++i) ptx::tmem_ld_32x32(t_acc + c * BATCH + i * 32, v[i]);
+        ptx::tmem_ld_wait();
+        if (c == GROUP_COLS / BATCH - 1) {
+          // The accumulator now lives in registers: hand it back before converting and storing.
+          ptx::tc_fence_before();
+          __syncwarp();
+          if (lane == 0) {
+            if constexpr (PAIR) ptx::mbar_arrive_cluster(ptx::mapa_shared(tempty_bar(as), 0));
+            else ptx::mbar_arrive(tempty_bar(as));
+          }
+        }
+        const int32_t colb = col_base + c * BATCH;
+        if (p.out_tma) {
+          if constexpr (TF32) {
+#pragma unroll
+            for (int i = 0; i < NLD; ++i) {
+              uint4 piece[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) piece[j] = make_uint4(v[i][4 * j], v[i][4 * j + 1], v[i][4 * j + 2], v[i][4 * j + 3]);
+              emit(piece, colb + i * 32);
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < NLD / 2; ++i) {
+              uint4 piece[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                const uint32_t *src = j < 4 ? &v[2 * i][8 * j] : &v[2 * i + 1][8 * (j - 4)];
+                uint32_t h[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const float lo = __uint_as_float(src[2 * e]), hi = __uint_as_float(src[2 * e + 1]);
+                  if (p.out_dtype == 6) {
+                    __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi);
+                    h[e] = *reinterpret_cast<uint32_t *>(&t);
+                  } else {
+                    __half2 t = __floats2half2_rn(lo, hi);
+                    h[e] = *reinterpret_cast<uint32_t *>(&t);
+                  }
+                }
+                piece[j] = make_uint4(h[0], h[1], h[2], h[3]);
+              }
+              emit(piece, colb + i * 64);
+            }
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < NLD; ++i) store_chunk(v[i], colb + i * 32);
+        }
       }
-      // This accumulator may be overwritten once all four quarters have been read.
-      ptx::tc_fence_before();
-      __syncwarp();
-      if (lane == 0) {
-        if constexpr (PAIR) ptx::mbar_arrive_cluster(ptx::mapa_shared(tempty_bar(as), 0));
-        else ptx::mbar_arrive(tempty_bar(as));
-      }
-      as ^= 1u;
-      if (as == 0) aph ^= 1u;
+      if (++as == ACC) { as = 0; aph ^= 1u; }
     }
+    if (lane == 0) ptx::bulk_wait_read_all();  // staging tiles are still being read until here
     __syncwarp();
   }
 

@@ -114,6 +114,17 @@ __device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap
       : "memory");
 }
 
+// 3-D tiled store from this CTA's shared memory; completion is tracked by the
+// issuing thread's bulk async-group.  The engine clips the box at the tensor's edge.
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap *tm, uint32_t src, int32_t c0, int32_t c1, int32_t c2) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
+               ::"l"(reinterpret_cast<uint64_t>(tm)), "r"(src), "r"(c0), "r"(c1), "r"(c2)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Until the issuing thread's earlier bulk stores have finished READING shared memory.
+__device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+
 // ---- tcgen05 ---------------------------------------------------------------
 
 template <int PAIR>

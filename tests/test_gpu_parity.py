@@ -153,13 +153,13 @@ def test_shape_sweep(backend, oracle, kernel, dtype):
 
 
 @pytest.mark.parametrize("dtype", [DType.BF16, DType.F16, DType.F32], ids=lambda d: d.name)
-@pytest.mark.parametrize("dims", [(256, 384, 320), (250, 130, 99), (512, 256, 1024)], ids=str)
+@pytest.mark.parametrize("dims", [(256, 384, 320), (250, 130, 99), (512, 256, 1024), (304, 1544, 136)], ids=str)
 @pytest.mark.parametrize("a_t,b_t", [(0, 0), (0, 1), (1, 0), (1, 1)])
 def test_transposed_operands_need_no_copy(backend, oracle, dims, a_t, b_t, dtype):
     """All four (A, B) major combinations: K-major and MN-major operands reach
     the tensor cores as views.  Aligned extents take the direct TMA path,
     unaligned ones the pack path."""
-    set_kernel(backend, "tcgen05")
+    set_kernel(backend, "tcgen05", tile_n=512 if dims[1] > 1024 else 0)  # the widest case runs 256 x 512 pair tiles
     m, n, k = dims
     ha = fill(oracle, (k, m) if a_t else (m, k), dtype, 7, 0)
     hb = fill(oracle, (n, k) if b_t else (k, n), dtype, 7, 1)
@@ -225,11 +225,11 @@ def test_broadcast_batch_dims(backend, oracle, kernel, dtype):
         assert err <= TOL[dtype], (ashape, bshape, err, backend.last_kernel())
 
 
-@pytest.mark.parametrize("tile_n", [64, 128, 256])
+@pytest.mark.parametrize("tile_n", [64, 128, 256, 512])
 @pytest.mark.parametrize("dtype", [DType.BF16, DType.F32], ids=lambda d: d.name)
 def test_tile_widths(backend, oracle, tile_n, dtype):
     set_kernel(backend, "tcgen05", tile_n=tile_n)
-    m, n, k = 384, 640, 448
+    m, n, k = 384, 1100, 448
     a, b = fill(oracle, (m, k), dtype, 31, 0), fill(oracle, (k, n), dtype, 31, 1)
     got = backend.matmul(Tensor.from_host(a, a.shape, dtype, backend), Tensor.from_host(b, b.shape, dtype, backend))
     assert f"bn{tile_n}" in backend.last_kernel()
