@@ -185,6 +185,8 @@ int oxm_fill(oxm_ctx *ctx, void *dst_device, int dtype, int64_t n, uint64_t seed
  *                 kernel (packing operands it cannot address directly)
  *   "tile_n"      0 auto, else 64 / 128 / 256 / 512 (512: CTA pairs only)
  *   "cta_pair"    -1 auto, 0 one CTA per tile, 1 CTA pairs (cta_group::2)
+ *   "split_k"     -1 auto, 0 never split beyond what f32 accuracy needs, else
+ *                 the number of contraction chains
  *   "tma_store"   1 (default) write results with bulk tensor stores when the
  *                 output allows it, 0 always use plain strided stores
  *   "group_m"     0 auto, else the number of tile rows walked together

@@ -65,7 +65,7 @@ struct oxm_ctx {
   Workspace pack_ws[3];  // packed A, packed B, split-K partial sums
   Workspace host_stage[3];
   // options
-  int64_t opt_kernel = 0, opt_tile_n = 0, opt_cta_pair = -1, opt_wait_limit_ms = 2000, opt_group_m = 0, opt_tma_store = 1;
+  int64_t opt_kernel = 0, opt_tile_n = 0, opt_cta_pair = -1, opt_wait_limit_ms = 2000, opt_group_m = 0, opt_tma_store = 1, opt_split_k = -1;
   int64_t launches[4] = {0, 0, 0, 0};
   char last_kernel[96] = "none";
 };
@@ -460,6 +460,55 @@ bool make_out_map(oxm_ctx *ctx, CUtensorMap *tm, void *ptr, int dtype, int elt, 
                      CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// Tile shape, CTA pairing and split-K factor for one product.
+struct TileChoice {
+  int bn, pair, splits;
+};
+
+// The longest accumulation chain the f32 path allows, in pipeline stages (K = 1024).
+constexpr int kMaxChainKb = 3 * 1024 / 32;
+
+// Pick the configuration with the smallest modelled time.  The model counts
+// waves of tiles over the SMs (or SM pairs) at each shape's measured relative
+// rate, a per-tile cost where the epilogue is exposed, and the price of the
+// reduction pass when the contraction is split to fill an under-occupied grid.
+TileChoice choose_tiles(const oxm_ctx *ctx, const Problem &P, bool tf32, int32_t num_kb) {
+  struct Cand { int bn, pair; double us_per_kb, us_per_tile; };
+  // microseconds per pipeline stage of one tile at the ~1.45 GHz the power cap sustains
+  static const Cand cands[] = {{512, 1, 0.706 / 1.03, 2.0}, {256, 1, 0.353, 0.3}, {256, 0, 0.353 / 0.93, 0.3},
+                               {128, 0, 0.177 / 0.75, 0.3}, {128, 1, 0.177 / 0.59, 0.3}, {64, 0, 0.088 / 0.5, 0.3}};
+  const int32_t min_splits = tf32 ? std::max(1, (num_kb + kMaxChainKb - 1) / kMaxChainKb) : 1;
+  static const int mult[] = {1, 2, 3, 4, 6, 8};
+  TileChoice best{256, 0, min_splits};
+  double best_t = 1e300;
+  // A forced pairing that no candidate of the forced width has is dropped on the second pass.
+  for (int pass = 0; pass < 2 && best_t == 1e300; ++pass)
+  for (const Cand &c : cands) {
+    if (ctx->opt_tile_n && c.bn != ctx->opt_tile_n) continue;
+    if (pass == 0 && ctx->opt_cta_pair >= 0 && c.pair != ctx->opt_cta_pair) continue;
+    if (!ctx->opt_tile_n) {
+      if (c.pair && P.M <= kTileM) continue;          // nothing for the second CTA to do
+      if (c.bn > 64 && P.N <= c.bn / 2) continue;     // at least half of the tile is outside the matrix
+    }
+    const int tm = kTileM * (c.pair ? 2 : 1);
+    const int64_t tiles = ((P.M + tm - 1) / tm) * ((P.N + c.bn - 1) / c.bn) * P.nbatch;
+    const int64_t slots = c.pair ? ctx->num_sms / 2 : ctx->num_sms;
+    for (int m : mult) {
+      const int32_t splits = min_splits * m;
+      if (m > 1 && (ctx->opt_split_k == 0 || num_kb / splits < 16)) break;
+      if (ctx->opt_split_k > 0 && splits != std::max<int64_t>(min_splits, ctx->opt_split_k)) continue;
+      const double slab_bytes = (double)P.nbatch * P.M * P.N * 4.0;
+      if (splits > 1 && slab_bytes * splits > 2e9) break;
+      const int64_t waves = (tiles * splits + slots - 1) / slots;
+      const int32_t kb = (num_kb + splits - 1) / splits;
+      double t = (double)waves * (kb * c.us_per_kb + c.us_per_tile);
+      if (splits > 1) t += 4.0 + slab_bytes * (splits + 1) / 4.0e6;  // launch + traffic of the reduction
+      if (t < best_t) { best_t = t; best = TileChoice{c.bn, c.pair, splits}; }
+    }
+  }
+  return best;
+}
+
 int launch_tcgen05(oxm_ctx *ctx, const Problem &P) {
   if (P.nbd > kMaxBatchDims) return fail(OXM_NOT_IMPLEMENTED, "matmul is not implemented for %d batch dims", P.nbd);
   if (P.M >= (1ll << 31) || P.N >= (1ll << 31) || P.K >= (1ll << 29) || P.nbatch >= (1ll << 31))
@@ -477,22 +526,9 @@ int launch_tcgen05(oxm_ctx *ctx, const Problem &P) {
   const int64_t Kst = tf32 ? sa.K : P.K;  // staged contraction length
   const int bk = kStageKBytes / P.elt;
 
-  int bn = (int)ctx->opt_tile_n;
-  if (bn == 0) bn = P.N > 128 ? 256 : (P.N > 64 ? 128 : 64);
-  // CTA pairs pay off on full-width tiles with at least two row blocks.
-  int pair = ctx->opt_cta_pair < 0 ? ((bn >= 256 && P.M > kTileM) ? 1 : 0) : (int)ctx->opt_cta_pair;
-  if (bn == 64) pair = 0;
-  if (bn == 512 && !pair) bn = 256;  // the 512-wide tile exists only as a pair
-  if (ctx->opt_tile_n == 0 && pair && bn == 256 && P.N > 256) {
-    // 256 x 512 pair tiles move a quarter fewer operand bytes per flop but leave
-    // the epilogue exposed and halve the tile count: take them when they do not
-    // cost a wave.
-    const int64_t slots = ctx->num_sms / 2;
-    const int64_t rows = (P.M + 255) / 256;
-    const int64_t t256 = rows * ((P.N + 255) / 256) * P.nbatch, t512 = rows * ((P.N + 511) / 512) * P.nbatch;
-    const double c256 = (double)((t256 + slots - 1) / slots), c512 = 2.0 * (double)((t512 + slots - 1) / slots) / 1.04;
-    if (c512 <= c256) bn = 512;
-  }
+  const int32_t num_kb_all = (int32_t)((Kst + bk - 1) / bk);
+  const TileChoice choice = choose_tiles(ctx, P, tf32, num_kb_all);
+  const int bn = choice.bn, pair = choice.pair;
   const int tm = kTileM * (pair ? 2 : 1);
 
   GemmParams p{};
@@ -524,23 +560,23 @@ int launch_tcgen05(oxm_ctx *ctx, const Problem &P) {
   p.kb_per_split = p.num_kb;
   p.tiles_per_split = p.num_tiles;
   p.split_ostride = 0;
-  p.group_m = ctx->opt_group_m > 0 ? (int32_t)ctx->opt_group_m : (pair ? 8 : 16);
+  p.group_m = ctx->opt_group_m > 0 ? (int32_t)ctx->opt_group_m : (pair && bn <= 256 ? 8 : 16);
   // The tensor core adds each MMA's products into the fp32 accumulator with
   // truncation, an error of about 2^-24 per instruction that grows with the
   // length of the chain.  For f32 results that would pass 1e-5 beyond
   // K = 1024, so longer contractions are cut into chains of that length whose
   // partial sums are added afterwards in round-to-nearest fp32.
   ReduceParams rp{};
-  const int kMaxChainKb = 3 * 1024 / 32;
-  if (tf32 && p.num_kb > kMaxChainKb) {
-    p.splits = (p.num_kb + kMaxChainKb - 1) / kMaxChainKb;
+  if (choice.splits > 1) {
+    p.splits = choice.splits;
     p.kb_per_split = (p.num_kb + p.splits - 1) / p.splits;
     p.splits = (p.num_kb + p.kb_per_split - 1) / p.kb_per_split;
     const int64_t slab = P.nbatch * P.M * P.N;
     int st2 = grow(ctx, ctx->pack_ws[2], (size_t)slab * p.splits * sizeof(float));
     if (st2) return st2;
     rp.ws = static_cast<const float *>(ctx->pack_ws[2].ptr);
-    rp.out = static_cast<float *>(P.o);
+    rp.out = P.o;
+    rp.out_dtype = P.dtype;
     rp.splits = p.splits; rp.M = p.M; rp.N = p.N;
     rp.split_stride = slab; rp.total = slab;
     rp.o_off = P.o_off; rp.o_rs = P.o_rs; rp.o_cs = P.o_cs;
@@ -554,6 +590,7 @@ int launch_tcgen05(oxm_ctx *ctx, const Problem &P) {
     }
     p.out = ctx->pack_ws[2].ptr;
     p.out_rs = P.N; p.out_cs = 1;
+    p.out_dtype = OXM_F32;  // partial sums stay fp32 whatever the operand type
     p.out_vec = (P.N % 4 == 0) ? 1 : 0;
     p.split_ostride = slab;
     p.num_tiles *= p.splits;
@@ -568,7 +605,8 @@ int launch_tcgen05(oxm_ctx *ctx, const Problem &P) {
   // The epilogue writes through a bulk tensor store when the output is a
   // row-contiguous, 16-byte-aligned window whose batch dims fold into one stride.
   if (p.splits > 1) {
-    p.out_tma = make_out_map(ctx, &tmC, p.out, OXM_F32, 4, P.M, P.N, P.nbatch * p.splits, P.N, P.M * P.N) ? 1 : 0;
+    // fp32 partial sums from 16-bit operands take the strided-store epilogue
+    p.out_tma = tf32 && make_out_map(ctx, &tmC, p.out, OXM_F32, 4, P.M, P.N, P.nbatch * p.splits, P.N, P.M * P.N) ? 1 : 0;
   } else if (P.o_cs == 1 || P.N == 1) {
     bool fold = true;
     for (int d = 0; d + 1 < P.nbd; ++d) fold = fold && P.o_bs[d] == P.o_bs[d + 1] * P.bdims[d + 1];
@@ -950,6 +988,7 @@ int oxm_set_option(oxm_ctx *ctx, const char *key, int64_t value) {
   else if (!strcmp(key, "wait_limit_ms") && value >= 1 && value <= 600000) ctx->opt_wait_limit_ms = value;
   else if (!strcmp(key, "group_m") && value >= 0 && value <= 1024) ctx->opt_group_m = value;
   else if (!strcmp(key, "tma_store") && (value == 0 || value == 1)) ctx->opt_tma_store = value;
+  else if (!strcmp(key, "split_k") && value >= -1 && value <= 64) ctx->opt_split_k = value;
   else return fail(OXM_INVALID_ARGUMENT, "oxm_set_option: unknown option or value: %s = %lld", key, (long long)value);
   return OXM_OK;
 }
@@ -963,6 +1002,7 @@ int oxm_get_option(oxm_ctx *ctx, const char *key, int64_t *value) {
   else if (!strcmp(key, "wait_limit_ms")) *value = ctx->opt_wait_limit_ms;
   else if (!strcmp(key, "group_m")) *value = ctx->opt_group_m;
   else if (!strcmp(key, "tma_store")) *value = ctx->opt_tma_store;
+  else if (!strcmp(key, "split_k")) *value = ctx->opt_split_k;
   else return fail(OXM_INVALID_ARGUMENT, "oxm_get_option: unknown option: %s", key);
   return OXM_OK;
 }
@@ -1065,7 +1105,6 @@ extern "C" int oxm_matmul_f32_noalloc(oxm_ctx *ctx, const oxm_view *a, const oxm
   // Scratch plan: [packed A | packed B | split-K partial sums], each 256-byte aligned.
   const int64_t Kp = (P.K + 31) / 32 * 32;
   const int32_t num_kb = (int32_t)(3 * Kp / 32);
-  const int kMaxChainKb = 3 * 1024 / 32;
   int32_t splits = 1, kb_per_split = num_kb;
   if (num_kb > kMaxChainKb) {
     splits = (num_kb + kMaxChainKb - 1) / kMaxChainKb;
@@ -1128,7 +1167,8 @@ extern "C" int oxm_matmul_f32_noalloc(oxm_ctx *ctx, const oxm_view *a, const oxm
     p.split_ostride = P.M * P.N;
     p.num_tiles *= splits;
     rp.ws = partials;
-    rp.out = static_cast<float *>(P.o);
+    rp.out = P.o;
+    rp.out_dtype = OXM_F32;
     rp.splits = splits; rp.M = p.M; rp.N = p.N;
     rp.split_stride = P.M * P.N; rp.total = P.M * P.N;
     rp.o_off = P.o_off; rp.o_rs = P.o_rs; rp.o_cs = P.o_cs;

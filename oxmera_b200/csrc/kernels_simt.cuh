@@ -214,11 +214,13 @@ __global__ void __launch_bounds__(256) pack_kernel(const PackParams p) {
 
 // ---------------------------------------------------------------------------
 // Split-K reduction: out[b][m][n] = sum over s of ws[s][b][m][n] (f32, added in
-// ascending s with round-to-nearest), written through the output's strides.
+// ascending s with round-to-nearest), rounded to the output dtype and written
+// through the output's strides.
 // ---------------------------------------------------------------------------
 struct ReduceParams {
   const float *ws;
-  float *out;
+  void *out;
+  int32_t out_dtype;  // 0 f32, 6 bf16, 7 f16
   int32_t splits, M, N;
   int64_t split_stride;  // elements between partial-sum slabs
   int64_t total;         // nbatch * M * N
@@ -240,7 +242,7 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const ReduceParams p
       off += (batch % p.bdims[d]) * p.o_bs[d];
       batch /= p.bdims[d];
     }
-    p.out[off] = acc;
+    store_elem(p.out, p.out_dtype, off, acc);
   }
 }
 

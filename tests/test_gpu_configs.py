@@ -143,6 +143,7 @@ def test_shards_reassemble_to_the_whole(backend, oracle, key):
     host = {}
     dev = materialise(w, host_fill(oracle, backend, host))
     backend.set_option("kernel", 2)
+    backend.set_option("split_k", 0)  # one accumulation chain per element, whatever the shard's shape
     try:
         for g in w.gemms:
             a, b, _ = gemm_views(w, g, dev)
@@ -156,3 +157,4 @@ def test_shards_reassemble_to_the_whole(backend, oracle, key):
                 assert np.array_equal(np.concatenate(parts, axis=axis), whole), (w.key, g.name, world)
     finally:
         backend.set_option("kernel", 0)
+        backend.set_option("split_k", -1)

@@ -54,6 +54,7 @@ def set_kernel(backend, name, tile_n=0, pair=-1):
     backend.set_option("kernel", KERNELS[name])
     backend.set_option("tile_n", tile_n)
     backend.set_option("cta_pair", pair)
+    backend.set_option("split_k", -1)
 
 
 @pytest.fixture(autouse=True)
@@ -253,6 +254,39 @@ def test_long_f32_contractions_keep_their_accuracy(backend, oracle):
         err = rel_err(got.to_host(), oracle_ref(oracle, a, b, DType.F32))
         print(f"f32 K={ashape[-1]}: error {err:.3e}")
         assert err <= 5e-5, (ashape, bshape, err)
+
+
+@pytest.mark.parametrize("dtype", [DType.BF16, DType.F16], ids=lambda d: d.name)
+@pytest.mark.parametrize("a_t,b_t", [(0, 1), (1, 0)])
+def test_split_k_fills_small_grids(backend, oracle, dtype, a_t, b_t):
+    """A small output with a long contraction (the weight gradient of one
+    shard) is cut along K into chains whose fp32 partial sums are reduced."""
+    set_kernel(backend, "tcgen05")
+    m, n, k = 256, 520, 8192
+    ha = fill(oracle, (k, m) if a_t else (m, k), dtype, 17, 0)
+    hb = fill(oracle, (n, k) if b_t else (k, n), dtype, 17, 1)
+    ta, tb = Tensor.from_host(ha, ha.shape, dtype, backend), Tensor.from_host(hb, hb.shape, dtype, backend)
+    if a_t:
+        ha, ta = ha.T, ta.permute([1, 0])
+    if b_t:
+        hb, tb = hb.T, tb.permute([1, 0])
+    ref = oracle_ref(oracle, ha, hb, dtype)
+    for split in (-1, 0, 3, 8):
+        backend.set_option("split_k", split)
+        before = backend.launch_counts()
+        got = backend.matmul(ta, tb)
+        after = backend.launch_counts()
+        if split > 0:
+            assert after["pack"] == before["pack"] + 1, "one reduction pass"
+        if split == 0:
+            assert after["pack"] == before["pack"]
+        err = rel_err(to_f64(got.to_host(), dtype), ref)
+        assert err <= TOL[dtype], (split, err, backend.last_kernel())
+    backend.set_option("split_k", -1)
+    # the auto choice splits here: 3 column tiles cannot fill the SMs
+    before = backend.launch_counts()
+    backend.matmul(ta, tb)
+    assert backend.launch_counts()["pack"] == before["pack"] + 1
 
 
 def test_empty_and_degenerate(backend):
