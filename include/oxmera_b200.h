@@ -180,6 +180,12 @@ int oxm_stream_handle(oxm_ctx *ctx, void **cuda_stream);
  * (seed, stream, i). */
 int oxm_fill(oxm_ctx *ctx, void *dst_device, int dtype, int64_t n, uint64_t seed, uint64_t stream, int dist, double scale);
 
+/* Failure-path self-test: launches a kernel whose only thread waits, with the
+ * bound `limit_ms` (1..1000), on a barrier nothing arrives on.  Returns
+ * OXM_TIMEOUT when the wait gave up and the status word reached the host, as
+ * a stuck pipeline would report; the context stays usable.  Nothing faults. */
+int oxm_selftest_bounded_wait(oxm_ctx *ctx, int64_t limit_ms);
+
 /* Options (key, value):
  *   "kernel"      0 auto, 1 force the SIMT FFMA kernel, 2 force the tcgen05
  *                 kernel (packing operands it cannot address directly)

@@ -18,7 +18,7 @@ EXPORTS = [
     "oxm_alloc", "oxm_free", "oxm_h2d", "oxm_d2h", "oxm_memset", "oxm_sync", "oxm_host_alloc", "oxm_host_free",
     "oxm_matmul", "oxm_batched_matmul", "oxm_batched_matmul_host", "oxm_contiguous",
     "oxm_matmul_f32_noalloc",
-    "oxm_event_create", "oxm_event_destroy", "oxm_event_record", "oxm_event_elapsed_ms", "oxm_stream_handle", "oxm_fill",
+    "oxm_event_create", "oxm_event_destroy", "oxm_event_record", "oxm_event_elapsed_ms", "oxm_stream_handle", "oxm_fill", "oxm_selftest_bounded_wait",
     "oxm_set_option", "oxm_get_option", "oxm_launch_counts", "oxm_last_kernel",
 ]
 
@@ -105,6 +105,7 @@ def load() -> C.CDLL:
         "oxm_event_elapsed_ms": ([p, p, C.POINTER(C.c_float)], i),
         "oxm_stream_handle": ([p, C.POINTER(p)], i),
         "oxm_fill": ([p, p, i, i64, C.c_uint64, C.c_uint64, i, C.c_double], i),
+        "oxm_selftest_bounded_wait": ([p, i64], i),
         "oxm_set_option": ([p, C.c_char_p, i64], i),
         "oxm_get_option": ([p, C.c_char_p, C.POINTER(i64)], i),
         "oxm_launch_counts": ([p, C.POINTER(i64)], i),

@@ -936,6 +936,30 @@ int oxm_fill(oxm_ctx *ctx, void *dst_device, int dtype, int64_t n, uint64_t seed
   return OXM_OK;
 }
 
+int oxm_selftest_bounded_wait(oxm_ctx *ctx, int64_t limit_ms) {
+  if (!ctx) return fail(OXM_INVALID_ARGUMENT, "oxm_selftest_bounded_wait: null context");
+  if (limit_ms < 1 || limit_ms > 1000) return fail(OXM_INVALID_ARGUMENT, "oxm_selftest_bounded_wait: limit must be 1..1000 ms");
+  CUDA_TRY(cudaSetDevice(ctx->device));
+  uint32_t *flag = nullptr;
+  CUDA_TRY(cudaMallocAsync(&flag, sizeof(uint32_t), ctx->stream));
+  CUDA_TRY(cudaMemsetAsync(flag, 0xff, sizeof(uint32_t), ctx->stream));
+  int st;
+  uint32_t gave_up = 0;
+  {
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    snprintf(ctx->last_kernel, sizeof(ctx->last_kernel), "bounded_wait_selftest");
+    bounded_wait_selftest_kernel<<<1, 32, 0, ctx->stream>>>(ctx->status_dev, (uint64_t)limit_ms * 1000000ull, flag);
+    CUDA_TRY(cudaGetLastError());
+    CUDA_TRY(cudaMemcpyAsync(ctx->status_host, flag, sizeof(uint32_t), cudaMemcpyDeviceToHost, ctx->stream));
+    CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+    gave_up = *ctx->status_host;
+    st = check_status(ctx);  // reports and clears the status word
+  }
+  CUDA_TRY(cudaFreeAsync(flag, ctx->stream));
+  if (st == OXM_TIMEOUT && gave_up != 1) return fail(OXM_CUDA_ERROR, "bounded wait self-test: status set but the waiter did not give up");
+  return st;
+}
+
 int oxm_event_create(oxm_ctx *ctx, oxm_event **out) {
   if (!ctx || !out) return fail(OXM_INVALID_ARGUMENT, "oxm_event_create: null argument");
   CUDA_TRY(cudaSetDevice(ctx->device));

@@ -115,6 +115,22 @@ __device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, cons
   }
 }
 
+// Self-test of the bounded wait: one thread waits on a barrier that nothing
+// will ever arrive on.  The wait must give up after `limit_ns`, record
+// OXM_TIMEOUT in the status word and let the kernel return normally.
+__global__ void bounded_wait_selftest_kernel(uint32_t *status, uint64_t limit_ns, uint32_t *gave_up) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    ptx::mbar_init(ptx::smem_u32(&bar), 1);
+    ptx::fence_barrier_init();
+    WaitCtx wc{&abort_flag, status, limit_ns};
+    const bool ok = bounded_wait(ptx::smem_u32(&bar), 0, wc);
+    *gave_up = ok ? 0u : 1u;
+  }
+}
+
 struct TileCoord {
   int32_t m_blk, n_blk;
   int32_t a_batch, b_batch;

@@ -289,6 +289,39 @@ def test_split_k_fills_small_grids(backend, oracle, dtype, a_t, b_t):
     assert backend.launch_counts()["pack"] == before["pack"] + 1
 
 
+def test_expired_device_wait_is_reported_and_survivable(backend):
+    """Failure detection without a fault: a wait nothing satisfies runs out
+    after its bound, the kernel returns, the host reads OXM_TIMEOUT, and the
+    same context multiplies correctly afterwards."""
+    from oxmera_b200 import capi
+    lib = capi.load()
+    st = lib.oxm_selftest_bounded_wait(backend._ctx, 20)
+    assert st == capi.TIMEOUT, capi.last_error()
+    assert "bounded device-side wait expired" in capi.last_error()
+    backend.synchronize()  # the status word was cleared: no stale error
+    a = Tensor.from_host(np.array([1, 2, 3, 4], np.float32), (2, 2), DType.F32, backend)
+    b = Tensor.from_host(np.array([5, 6, 7, 8], np.float32), (2, 2), DType.F32, backend)
+    for kernel in ("simt", "tcgen05"):
+        set_kernel(backend, kernel)
+        assert backend.matmul(a, b).to_host().reshape(-1).tolist() == [19.0, 22.0, 43.0, 50.0]
+
+
+@pytest.mark.parametrize("dtype", [DType.BF16, DType.F32], ids=lambda d: d.name)
+def test_strided_store_epilogue_matches_the_bulk_store_epilogue(backend, oracle, dtype):
+    set_kernel(backend, "tcgen05")
+    for tile_n, (m, n, k) in ((0, (300, 520, 200)), (512, (520, 1100, 136)), (128, (77, 130, 72))):
+        backend.set_option("tile_n", tile_n)
+        a, b = fill(oracle, (3, m, k), dtype, 41, 0), fill(oracle, (3, k, n), dtype, 41, 1)
+        ta, tb = Tensor.from_host(a, a.shape, dtype, backend), Tensor.from_host(b, b.shape, dtype, backend)
+        outs = []
+        for flag in (1, 0):
+            backend.set_option("tma_store", flag)
+            outs.append(backend.batched_matmul(ta, tb).to_host())
+        backend.set_option("tma_store", 1)
+        assert np.array_equal(outs[0], outs[1]), (tile_n, m, n, k)
+        assert rel_err(to_f64(outs[0], dtype), oracle_ref(oracle, a, b, dtype)) <= TOL[dtype]
+
+
 def test_empty_and_degenerate(backend):
     z = lambda shape: Tensor.from_host(np.zeros(shape, np.float32), shape, DType.F32, backend)
     assert backend.matmul(z((0, 3)), z((3, 2))).shape == (0, 2)
