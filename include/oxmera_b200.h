@@ -127,7 +127,10 @@ int oxm_batched_matmul(oxm_ctx *ctx, const oxm_view *a, const oxm_view *b, const
 
 /* Same operation on HOST views: `base` pointers are host memory.  The
  * operands are staged to the device, multiplied, and the result copied back
- * into `out`'s (contiguous) host buffer before returning.  This is what
+ * into `out`'s (contiguous) host buffer before returning.  Large products are
+ * cut along the output's leading dim so that copy-in, multiply and copy-out
+ * of successive slices overlap (page-locked host buffers are needed for the
+ * overlap; pageable ones still give the right result).  This is what
  * `Tensor::matmul` costs when the tensors start and end in host memory
  * (crates/oxmera-runtime/src/lib.rs:68-69,99-102). */
 int oxm_batched_matmul_host(oxm_ctx *ctx, const oxm_view *a, const oxm_view *b, const oxm_view *out);
@@ -191,6 +194,8 @@ int oxm_selftest_bounded_wait(oxm_ctx *ctx, int64_t limit_ms);
  *                 kernel (packing operands it cannot address directly)
  *   "tile_n"      0 auto, else 64 / 128 / 256 / 512 (512: CTA pairs only)
  *   "cta_pair"    -1 auto, 0 one CTA per tile, 1 CTA pairs (cta_group::2)
+ *   "host_chunks" slices of the host entry point's copy/compute pipeline:
+ *                 0 auto (up to 8 for outputs of 16 MiB or more), 1 off, 2..16
  *   "split_k"     -1 auto, 0 never split beyond what f32 accuracy needs, else
  *                 the number of contraction chains
  *   "tma_store"   1 (default) write results with bulk tensor stores when the

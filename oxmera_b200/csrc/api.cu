@@ -64,8 +64,10 @@ struct oxm_ctx {
   std::mutex host_mu;  // serialises calls that use the host staging buffers
   Workspace pack_ws[3];  // packed A, packed B, split-K partial sums
   Workspace host_stage[3];
+  cudaStream_t copy_in = nullptr, copy_out = nullptr;  // host entry point: copies overlapped with compute
+  cudaEvent_t pipe_events[2 * 16 + 1] = {};
   // options
-  int64_t opt_kernel = 0, opt_tile_n = 0, opt_cta_pair = -1, opt_wait_limit_ms = 2000, opt_group_m = 0, opt_tma_store = 1, opt_split_k = -1;
+  int64_t opt_kernel = 0, opt_tile_n = 0, opt_cta_pair = -1, opt_wait_limit_ms = 2000, opt_group_m = 0, opt_tma_store = 1, opt_split_k = -1, opt_host_chunks = 0;
   int64_t launches[4] = {0, 0, 0, 0};
   char last_kernel[96] = "none";
 };
@@ -769,6 +771,9 @@ int oxm_ctx_destroy(oxm_ctx *ctx) {
   if (ctx->stream) cudaStreamSynchronize(ctx->stream);
   for (auto &w : ctx->pack_ws) if (w.ptr) cudaFree(w.ptr);
   for (auto &w : ctx->host_stage) if (w.ptr) cudaFree(w.ptr);
+  for (auto &e : ctx->pipe_events) if (e) cudaEventDestroy(e);
+  if (ctx->copy_in) cudaStreamDestroy(ctx->copy_in);
+  if (ctx->copy_out) cudaStreamDestroy(ctx->copy_out);
   if (ctx->status_dev) cudaFree(ctx->status_dev);
   if (ctx->status_host) cudaFreeHost(ctx->status_host);
   if (ctx->stream) cudaStreamDestroy(ctx->stream);
@@ -872,18 +877,108 @@ int oxm_batched_matmul_host(oxm_ctx *ctx, const oxm_view *a, const oxm_view *b, 
       if (st) return st;
       dv[i].base = ctx->host_stage[i].ptr;
       dv[i].offset = hv[i]->offset - lo[i];
-      if (i < 2)
-        CUDA_TRY(cudaMemcpyAsync(dv[i].base, static_cast<const uint8_t *>(hv[i]->base) + lo[i] * elt, bytes,
-                                 cudaMemcpyHostToDevice, ctx->stream));
     }
   }
-  st = run_matmul(ctx, &dv[0], &dv[1], &dv[2], true);
-  if (st) return st;
-  if (numel[2] > 0)
+  if (numel[2] == 0) return OXM_OK;
+
+  // Large products are cut along the output's leading dim (batch entries, or
+  // rows of a rank-2 product) so that the copy-in of slice i+1, the multiply of
+  // slice i and the copy-out of slice i-1 run at the same time on three streams.
+  int chunks = 1;
+  const int64_t lead = out->shape[0];
+  bool row_major = true;
+  {
+    int64_t expect = 1;
+    for (int d = out->ndim - 1; d >= 0; --d) {
+      if (out->shape[d] != 1 && out->strides[d] != expect) row_major = false;
+      expect *= out->shape[d];
+    }
+  }
+  const int64_t unit = out->ndim == 2 ? 512 : 1;  // rows per slice are kept a multiple of the tile height
+  if (row_major && ((size_t)numel[2] * elt >= ((size_t)16 << 20) || ctx->opt_host_chunks > 1) && lead >= 2 * unit &&
+      ctx->opt_host_chunks != 1)
+    chunks = (int)std::min<int64_t>(ctx->opt_host_chunks > 1 ? ctx->opt_host_chunks : 8, lead / unit);
+  if (chunks <= 1) {
+    for (int i = 0; i < 2; ++i)
+      if (numel[i] > 0)
+        CUDA_TRY(cudaMemcpyAsync(dv[i].base, static_cast<const uint8_t *>(hv[i]->base) + lo[i] * elt,
+                                 (size_t)(hi[i] - lo[i] + 1) * elt, cudaMemcpyHostToDevice, ctx->stream));
+    st = run_matmul(ctx, &dv[0], &dv[1], &dv[2], true);
+    if (st) return st;
     CUDA_TRY(cudaMemcpyAsync(static_cast<uint8_t *>(out->base) + lo[2] * elt, dv[2].base, (size_t)numel[2] * elt,
                              cudaMemcpyDeviceToHost, ctx->stream));
-  std::lock_guard<std::mutex> lock(ctx->mu);
-  return check_status(ctx);
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    return check_status(ctx);
+  }
+
+  if (!ctx->copy_in) {
+    CUDA_TRY(cudaStreamCreateWithFlags(&ctx->copy_in, cudaStreamNonBlocking));
+    CUDA_TRY(cudaStreamCreateWithFlags(&ctx->copy_out, cudaStreamNonBlocking));
+    for (auto &e : ctx->pipe_events) CUDA_TRY(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+  }
+  cudaEvent_t ev_alloc = ctx->pipe_events[0];
+  // Which dim of each operand follows the output's leading dim, and whether its
+  // slices are disjoint byte ranges of the host buffer (else it is copied whole).
+  int xd[2];
+  bool sliced[2];
+  for (int i = 0; i < 2; ++i) {
+    const oxm_view *v = hv[i];
+    xd[i] = out->ndim == 2 ? (i == 0 ? 0 : -1) : (v->ndim == out->ndim && v->shape[0] != 1 ? 0 : -1);
+    sliced[i] = xd[i] >= 0 && v->strides[xd[i]] > 0 &&
+                (double)v->strides[xd[i]] * (double)v->shape[xd[i]] >= 0.9 * (double)(hi[i] - lo[i] + 1);
+  }
+  CUDA_TRY(cudaEventRecord(ev_alloc, ctx->stream));  // staging buffers exist from here on
+  CUDA_TRY(cudaStreamWaitEvent(ctx->copy_in, ev_alloc, 0));
+  CUDA_TRY(cudaStreamWaitEvent(ctx->copy_out, ev_alloc, 0));
+  for (int i = 0; i < 2; ++i)
+    if (!sliced[i] && numel[i] > 0)
+      CUDA_TRY(cudaMemcpyAsync(dv[i].base, static_cast<const uint8_t *>(hv[i]->base) + lo[i] * elt,
+                               (size_t)(hi[i] - lo[i] + 1) * elt, cudaMemcpyHostToDevice, ctx->copy_in));
+  const int64_t per = ((lead + chunks - 1) / chunks + unit - 1) / unit * unit;
+  int c = 0;
+  for (int64_t i0 = 0; i0 < lead; i0 += per, ++c) {
+    const int64_t len = std::min(per, lead - i0);
+    oxm_view cv[3] = {dv[0], dv[1], dv[2]};
+    for (int i = 0; i < 2; ++i) {
+      if (xd[i] < 0) continue;
+      cv[i].shape[xd[i]] = len;
+      cv[i].offset += i0 * hv[i]->strides[xd[i]];
+      if (sliced[i]) {
+        oxm_view hs = *hv[i];
+        hs.shape[xd[i]] = len;
+        hs.offset += i0 * hv[i]->strides[xd[i]];
+        int64_t clo, chi, cn;
+        view_extent(&hs, &clo, &chi, &cn);
+        if (cn > 0)
+          CUDA_TRY(cudaMemcpyAsync(static_cast<uint8_t *>(dv[i].base) + (clo - lo[i]) * elt,
+                                   static_cast<const uint8_t *>(hv[i]->base) + clo * elt, (size_t)(chi - clo + 1) * elt,
+                                   cudaMemcpyHostToDevice, ctx->copy_in));
+      }
+    }
+    cv[2].shape[0] = len;
+    cv[2].offset += i0 * out->strides[0];
+    cudaEvent_t ev_in = ctx->pipe_events[1 + 2 * c], ev_done = ctx->pipe_events[2 + 2 * c];
+    CUDA_TRY(cudaEventRecord(ev_in, ctx->copy_in));
+    CUDA_TRY(cudaStreamWaitEvent(ctx->stream, ev_in, 0));
+    st = run_matmul(ctx, &cv[0], &cv[1], &cv[2], true);
+    if (st) break;
+    CUDA_TRY(cudaEventRecord(ev_done, ctx->stream));
+    CUDA_TRY(cudaStreamWaitEvent(ctx->copy_out, ev_done, 0));
+    const int64_t o0 = (out->offset + i0 * out->strides[0]) * elt;
+    const int64_t d0 = (dv[2].offset + i0 * out->strides[0]) * elt;
+    CUDA_TRY(cudaMemcpyAsync(static_cast<uint8_t *>(out->base) + o0, static_cast<uint8_t *>(dv[2].base) + d0,
+                             (size_t)(len * out->strides[0]) * elt, cudaMemcpyDeviceToHost, ctx->copy_out));
+  }
+  cudaError_t e1 = cudaStreamSynchronize(ctx->copy_in), e2 = cudaStreamSynchronize(ctx->copy_out);
+  int st2;
+  {
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    st2 = check_status(ctx);
+  }
+  if (st) return st;
+  if (e1 != cudaSuccess || e2 != cudaSuccess)
+    return fail(OXM_CUDA_ERROR, "host matmul copy failed: %s", cudaGetErrorString(e1 != cudaSuccess ? e1 : e2));
+  return st2;
 }
 
 int oxm_contiguous(oxm_ctx *ctx, const oxm_view *src, const oxm_view *dst) {
@@ -1013,6 +1108,7 @@ int oxm_set_option(oxm_ctx *ctx, const char *key, int64_t value) {
   else if (!strcmp(key, "group_m") && value >= 0 && value <= 1024) ctx->opt_group_m = value;
   else if (!strcmp(key, "tma_store") && (value == 0 || value == 1)) ctx->opt_tma_store = value;
   else if (!strcmp(key, "split_k") && value >= -1 && value <= 64) ctx->opt_split_k = value;
+  else if (!strcmp(key, "host_chunks") && value >= 0 && value <= 16) ctx->opt_host_chunks = value;
   else return fail(OXM_INVALID_ARGUMENT, "oxm_set_option: unknown option or value: %s = %lld", key, (long long)value);
   return OXM_OK;
 }
@@ -1027,6 +1123,7 @@ int oxm_get_option(oxm_ctx *ctx, const char *key, int64_t *value) {
   else if (!strcmp(key, "group_m")) *value = ctx->opt_group_m;
   else if (!strcmp(key, "tma_store")) *value = ctx->opt_tma_store;
   else if (!strcmp(key, "split_k")) *value = ctx->opt_split_k;
+  else if (!strcmp(key, "host_chunks")) *value = ctx->opt_host_chunks;
   else return fail(OXM_INVALID_ARGUMENT, "oxm_get_option: unknown option: %s", key);
   return OXM_OK;
 }

@@ -357,6 +357,29 @@ def test_host_entry_point(backend, oracle):
     assert rel_err(to_f64(got, DType.BF16), oracle_ref(oracle, a16, b16, DType.BF16)) <= 1e-2
 
 
+def test_host_entry_point_pipeline_matches_the_single_shot(backend, oracle):
+    """Outputs of 16 MiB or more go through the sliced copy/compute pipeline;
+    slicing must not change a bit, for rank-2 and for batched products, with
+    K-major, M-major and broadcast operands."""
+    cases = [((4096, 1040), False, (1040, 2064)),          # rank 2, rows sliced
+             ((1040, 4096), True, (1040, 2064)),           # A is M-major: copied whole, still sliced as a view
+             ((6, 640, 520), False, (520, 2304)),          # batch sliced, B shared
+             ((5, 1, 640, 520), False, (1, 3, 520, 776))]  # leading batch dim sliced, B broadcast over it
+    for i, (ashape, a_t, bshape) in enumerate(cases):
+        a, b = fill(oracle, ashape, DType.BF16, 300 + i, 0), fill(oracle, bshape, DType.BF16, 300 + i, 1)
+        av = a.T if a_t else a
+        outs = []
+        for chunks in (1, 0, 3):
+            backend.set_option("host_chunks", chunks)
+            outs.append(backend.matmul_host(av, b, DType.BF16))
+        backend.set_option("host_chunks", 0)
+        assert np.array_equal(outs[0], outs[1]) and np.array_equal(outs[0], outs[2]), (ashape, bshape)
+        sample = (slice(0, 40),) if len(outs[0].shape) == 2 else (0,) * (len(outs[0].shape) - 2)
+        a_s = av[:40] if len(outs[0].shape) == 2 else av[(0,) * (av.ndim - 2)]
+        b_s = b if b.ndim == 2 else b[(0,) * (b.ndim - 2)]
+        assert rel_err(to_f64(outs[0][sample], DType.BF16), oracle_ref(oracle, a_s, b_s, DType.BF16)) <= 1e-2
+
+
 def test_sharded_host_matmul_matches_single_device(backend, oracle):
     """The collective-free sharding driver, with two shards on one device."""
     a = fill(oracle, (4, 96, 64), DType.BF16, 81, 0)
