@@ -125,6 +125,23 @@ int oxm_host_free(void *ptr);
 int oxm_matmul(oxm_ctx *ctx, const oxm_view *a, const oxm_view *b, const oxm_view *out);
 int oxm_batched_matmul(oxm_ctx *ctx, const oxm_view *a, const oxm_view *b, const oxm_view *out);
 
+/* The product with the step a caller runs next fused into the GEMM's epilogue
+ * (fp32, before the single rounding to the output dtype):
+ *     r = sum_k a[m,k] b[k,n];  r += bias[n];  r = act(r);  r += out[m,n]
+ * each step optional.  `bias` is a rank-1 view of N elements of the operand
+ * dtype (a linear layer's forward, with `activation`); `accumulate` adds what
+ * `out` already holds (dW += dY^T.X across micro-batches).  Shapes broadcast as
+ * in oxm_batched_matmul.  oxmera reserves the crates these steps belong to
+ * (crates/oxmera-nn/src/lib.rs, crates/oxmera-autograd/src/lib.rs) and has no
+ * signature for them yet; this entry point is the backend half they will call. */
+enum { OXM_ACT_NONE = 0, OXM_ACT_RELU = 1, OXM_ACT_GELU = 2 /* 0.5 x (1 + erf(x / sqrt 2)) */ };
+typedef struct {
+  const oxm_view *bias; /* NULL for none */
+  int32_t activation;   /* OXM_ACT_* */
+  int32_t accumulate;   /* non-zero: out += result */
+} oxm_epilogue;
+int oxm_matmul_fused(oxm_ctx *ctx, const oxm_view *a, const oxm_view *b, const oxm_view *out, const oxm_epilogue *ep);
+
 /* Same operation on HOST views: `base` pointers are host memory.  The
  * operands are staged to the device, multiplied, and the result copied back
  * into `out`'s (contiguous) host buffer before returning.  Large products are

@@ -149,8 +149,30 @@ static inline void store_from_f64(void *base, int32_t dtype, int64_t idx, double
   }
 }
 
+static inline double load_as_f64(const void *base, int32_t dtype, int64_t idx) {
+  if (dtype == ORC_F64) return ((const double *)base)[idx];
+  return (double)load_as_f32(base, dtype, idx);
+}
+
+typedef struct {
+  const orc_view *bias; /* NULL for none */
+  int act, accumulate;
+} orc_epi;
+
+static inline double activate_f64(double r, int act) {
+  if (act == 1) return r > 0.0 ? r : 0.0;
+  if (act == 2) return 0.5 * r * (1.0 + erf(r * 0.70710678118654752440));
+  return r;
+}
+static inline float activate_f32(float r, int act) {
+  if (act == 1) return r > 0.0f ? r : 0.0f;
+  if (act == 2) return 0.5f * r * (1.0f + erff(r * 0.70710678118654752440f));
+  return r;
+}
+
 typedef struct {
   const orc_view *a, *b, *out;
+  orc_epi epi;
   int acc_mode;
   int64_t m, n, k, nbatch;
   int bnd;                       /* number of batch dims of the output */
@@ -162,10 +184,10 @@ typedef struct {
 
 /* One output row: i fixed, loop j then k.  The A row is staged as f32 first
  * (a pure copy through the view's strides; the arithmetic order is unchanged). */
-#define ROW_KERNEL(NAME, BT, BLOAD, ACC_T)                                              \
+#define ROW_KERNEL(NAME, BT, BLOAD, ACC_T, ACT)                                         \
   static void NAME(const float *arow, const BT *bptr, int64_t b_ks, int64_t b_ns,       \
                    int64_t n, int64_t k, void *obase, int32_t odt, int64_t o_off,       \
-                   int64_t o_ns) {                                                      \
+                   int64_t o_ns, const orc_epi *E) {                                    \
     for (int64_t j = 0; j < n; ++j) {                                                   \
       ACC_T acc = 0;                                                                    \
       const BT *bp = bptr + j * b_ns;                                                   \
@@ -173,17 +195,22 @@ typedef struct {
         ACC_T prod = (ACC_T)arow[kk] * (ACC_T)BLOAD(bp[kk * b_ks]);                     \
         acc = acc + prod;                                                               \
       }                                                                                 \
+      if (E->bias)                                                                      \
+        acc = acc + (ACC_T)load_as_f64(E->bias->base, E->bias->dtype,                   \
+                                       E->bias->offset + j * E->bias->strides[0]);      \
+      acc = ACT(acc, E->act);                                                           \
+      if (E->accumulate) acc = acc + (ACC_T)load_as_f64(obase, odt, o_off + j * o_ns);  \
       store_from_f64(obase, odt, o_off + j * o_ns, (double)acc);                        \
     }                                                                                   \
   }
 
 #define ID_F32(x) (x)
-ROW_KERNEL(row_f32_native, float, ID_F32, float)
-ROW_KERNEL(row_f32_f64, float, ID_F32, double)
-ROW_KERNEL(row_bf16_native, uint16_t, orc_bf16_to_f32, float)
-ROW_KERNEL(row_bf16_f64, uint16_t, orc_bf16_to_f32, double)
-ROW_KERNEL(row_f16_native, uint16_t, orc_f16_to_f32, float)
-ROW_KERNEL(row_f16_f64, uint16_t, orc_f16_to_f32, double)
+ROW_KERNEL(row_f32_native, float, ID_F32, float, activate_f32)
+ROW_KERNEL(row_f32_f64, float, ID_F32, double, activate_f64)
+ROW_KERNEL(row_bf16_native, uint16_t, orc_bf16_to_f32, float, activate_f32)
+ROW_KERNEL(row_bf16_f64, uint16_t, orc_bf16_to_f32, double, activate_f64)
+ROW_KERNEL(row_f16_native, uint16_t, orc_f16_to_f32, float, activate_f32)
+ROW_KERNEL(row_f16_f64, uint16_t, orc_f16_to_f32, double, activate_f64)
 
 static void *mm_worker(void *arg) {
   mm_job *J = (mm_job *)arg;
@@ -219,13 +246,13 @@ static void *mm_worker(void *arg) {
       const int f64 = J->acc_mode == ORC_ACC_F64;
       if (b->dtype == ORC_F32) {
         const float *bp = (const float *)b->base + b_off;
-        (f64 ? row_f32_f64 : row_f32_native)(arow, bp, b_ks, b_ns, J->n, J->k, o->base, o->dtype, o_off, o_ns);
+        (f64 ? row_f32_f64 : row_f32_native)(arow, bp, b_ks, b_ns, J->n, J->k, o->base, o->dtype, o_off, o_ns, &J->epi);
       } else if (b->dtype == ORC_BF16) {
         const uint16_t *bp = (const uint16_t *)b->base + b_off;
-        (f64 ? row_bf16_f64 : row_bf16_native)(arow, bp, b_ks, b_ns, J->n, J->k, o->base, o->dtype, o_off, o_ns);
+        (f64 ? row_bf16_f64 : row_bf16_native)(arow, bp, b_ks, b_ns, J->n, J->k, o->base, o->dtype, o_off, o_ns, &J->epi);
       } else {
         const uint16_t *bp = (const uint16_t *)b->base + b_off;
-        (f64 ? row_f16_f64 : row_f16_native)(arow, bp, b_ks, b_ns, J->n, J->k, o->base, o->dtype, o_off, o_ns);
+        (f64 ? row_f16_f64 : row_f16_native)(arow, bp, b_ks, b_ns, J->n, J->k, o->base, o->dtype, o_off, o_ns, &J->epi);
       }
     }
   }
@@ -234,11 +261,18 @@ static void *mm_worker(void *arg) {
 }
 
 static int run_matmul(const orc_view *a, const orc_view *b, const orc_view *out,
-                      int acc_mode, int nthreads, int batched) {
+                      int acc_mode, int nthreads, int batched, const orc_epi *epi) {
   int st = orc_check_matmul(a, b, out, batched);
   if (st != ORC_OK) return st;
   mm_job J;
   memset(&J, 0, sizeof(J));
+  if (epi) {
+    if (epi->bias) {
+      if (epi->bias->ndim != 1 || epi->bias->shape[0] != b->shape[b->ndim - 1]) return ORC_SHAPE_MISMATCH;
+      if (epi->bias->dtype != a->dtype) return ORC_DTYPE_MISMATCH;
+    }
+    J.epi = *epi;
+  }
   J.a = a; J.b = b; J.out = out; J.acc_mode = acc_mode;
   J.m = a->shape[a->ndim - 2];
   J.k = a->shape[a->ndim - 1];
@@ -271,11 +305,20 @@ static int run_matmul(const orc_view *a, const orc_view *b, const orc_view *out,
 }
 
 int orc_matmul(const orc_view *a, const orc_view *b, const orc_view *out, int acc_mode, int nthreads) {
-  return run_matmul(a, b, out, acc_mode, nthreads, 0);
+  return run_matmul(a, b, out, acc_mode, nthreads, 0, NULL);
 }
 
 int orc_batched_matmul(const orc_view *a, const orc_view *b, const orc_view *out, int acc_mode, int nthreads) {
-  return run_matmul(a, b, out, acc_mode, nthreads, 1);
+  return run_matmul(a, b, out, acc_mode, nthreads, 1, NULL);
+}
+
+int orc_matmul_fused(const orc_view *a, const orc_view *b, const orc_view *out, const orc_view *bias, int act,
+                     int accumulate, int acc_mode, int nthreads) {
+  orc_epi e;
+  e.bias = bias;
+  e.act = act;
+  e.accumulate = accumulate;
+  return run_matmul(a, b, out, acc_mode, nthreads, 1, &e);
 }
 
 /* ------------------------------------------------------------------ */

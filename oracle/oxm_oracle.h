@@ -82,6 +82,14 @@ int orc_matmul(const orc_view *a, const orc_view *b, const orc_view *out,
 int orc_batched_matmul(const orc_view *a, const orc_view *b,
                        const orc_view *out, int acc_mode, int nthreads);
 
+/* The fused form (no counterpart in the reference, whose nn / autograd crates
+ * are empty): per output element, in the accumulator's precision,
+ *   r = sum_k a b;  r += bias[n];  r = act(r);  r += out[m,n]
+ * each step optional.  `bias` is NULL or a rank-1 view of N elements;
+ * act: 0 none, 1 relu, 2 gelu = 0.5 x (1 + erf(x / sqrt 2)). */
+int orc_matmul_fused(const orc_view *a, const orc_view *b, const orc_view *out, const orc_view *bias, int act,
+                     int accumulate, int acc_mode, int nthreads);
+
 /* Validation only: the status orc_matmul / orc_batched_matmul would return. */
 int orc_check_matmul(const orc_view *a, const orc_view *b, const orc_view *out,
                      int batched);

@@ -86,6 +86,27 @@ class B200Backend:
             _raise(st, "batched_matmul" if batched else "matmul", lhs, rhs)
         return out
 
+    def matmul_fused(self, lhs: Tensor, rhs: Tensor, bias: Tensor | None = None, activation: str = "none",
+                     accumulate_into: Tensor | None = None) -> Tensor:
+        """act(lhs . rhs + bias), optionally added into an existing tensor
+        (gradient accumulation), in one kernel.  Shapes broadcast as in
+        batched_matmul; bias is a rank-1 tensor over the output's columns."""
+        if accumulate_into is None:
+            bshape = broadcast_shapes(lhs.shape[:-2], rhs.shape[:-2])
+            out = Tensor.empty(tuple(bshape) + (lhs.shape[-2], rhs.shape[-1]), lhs.dtype, self)
+        else:
+            out = accumulate_into
+        ep = capi.Epilogue()
+        bias_view = bias._view() if bias is not None else None
+        ep.bias = C.pointer(bias_view) if bias_view is not None else None
+        ep.activation = capi.ACT[activation]
+        ep.accumulate = 1 if accumulate_into is not None else 0
+        st = self._lib.oxm_matmul_fused(self._ctx, C.byref(lhs._view()), C.byref(rhs._view()), C.byref(out._view()),
+                                        C.byref(ep))
+        if st != capi.OK:
+            _raise(st, "matmul_fused", lhs, rhs)
+        return out
+
     def _mm(self, lhs: Tensor, rhs: Tensor, batched: bool) -> Tensor:
         op = "batched_matmul" if batched else "matmul"
         for t in (lhs, rhs):

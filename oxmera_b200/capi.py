@@ -17,7 +17,7 @@ EXPORTS = [
     "oxm_last_error", "oxm_status_name",
     "oxm_alloc", "oxm_free", "oxm_h2d", "oxm_d2h", "oxm_memset", "oxm_sync", "oxm_host_alloc", "oxm_host_free",
     "oxm_matmul", "oxm_batched_matmul", "oxm_batched_matmul_host", "oxm_contiguous",
-    "oxm_matmul_f32_noalloc",
+    "oxm_matmul_f32_noalloc", "oxm_matmul_fused",
     "oxm_event_create", "oxm_event_destroy", "oxm_event_record", "oxm_event_elapsed_ms", "oxm_stream_handle", "oxm_fill", "oxm_selftest_bounded_wait",
     "oxm_set_option", "oxm_get_option", "oxm_launch_counts", "oxm_last_kernel",
 ]
@@ -40,6 +40,15 @@ class View(C.Structure):
         ("device", C.c_int32),
         ("reserved", C.c_int32),
     ]
+
+
+class Epilogue(C.Structure):
+    """oxm_epilogue"""
+
+    _fields_ = [("bias", C.POINTER(View)), ("activation", C.c_int32), ("accumulate", C.c_int32)]
+
+
+ACT = {"none": 0, "relu": 1, "gelu": 2}
 
 
 def make_view(dtype: int, shape, strides, offset: int, base: int | None, device: int) -> View:
@@ -98,6 +107,7 @@ def load() -> C.CDLL:
         "oxm_batched_matmul": ([p, PV, PV, PV], i),
         "oxm_batched_matmul_host": ([p, PV, PV, PV], i),
         "oxm_contiguous": ([p, PV, PV], i),
+        "oxm_matmul_fused": ([p, PV, PV, PV, C.POINTER(Epilogue)], i),
         "oxm_matmul_f32_noalloc": ([p, PV, PV, PV], i),
         "oxm_event_create": ([p, C.POINTER(p)], i),
         "oxm_event_destroy": ([p], i),

@@ -177,6 +177,7 @@ struct Problem {
   int64_t a_rs, a_ks, b_rs, b_ks, o_rs, o_cs;
   int64_t a_bs[OXM_MAX_DIMS], b_bs[OXM_MAX_DIMS], o_bs[OXM_MAX_DIMS];
   int64_t nbatch;
+  Epilogue epi;
 };
 
 Problem normalise(const oxm_view *a, const oxm_view *b, const oxm_view *out) {
@@ -246,6 +247,7 @@ int launch_simt(oxm_ctx *ctx, const Problem &P) {
   for (int d = 0; d < P.nbd; ++d) {
     p.bdims[d] = (int32_t)P.bdims[d]; p.a_bs[d] = P.a_bs[d]; p.b_bs[d] = P.b_bs[d]; p.o_bs[d] = P.o_bs[d];
   }
+  p.epi = P.epi;
   const int64_t blocks = (int64_t)p.tiles_m * p.tiles_n * P.nbatch;
   if (blocks > INT32_MAX) return fail(OXM_NOT_IMPLEMENTED, "matmul is not implemented for %lld output tiles", (long long)blocks);
   gemm_simt_kernel<<<(unsigned)blocks, 256, 0, ctx->stream>>>(p);
@@ -563,6 +565,7 @@ int launch_tcgen05(oxm_ctx *ctx, const Problem &P) {
   p.tiles_per_split = p.num_tiles;
   p.split_ostride = 0;
   p.group_m = ctx->opt_group_m > 0 ? (int32_t)ctx->opt_group_m : (pair && bn <= 256 ? 8 : 16);
+  p.epi = P.epi;
   // The tensor core adds each MMA's products into the fp32 accumulator with
   // truncation, an error of about 2^-24 per instruction that grows with the
   // length of the chain.  For f32 results that would pass 1e-5 beyond
@@ -579,6 +582,8 @@ int launch_tcgen05(oxm_ctx *ctx, const Problem &P) {
     rp.ws = static_cast<const float *>(ctx->pack_ws[2].ptr);
     rp.out = P.o;
     rp.out_dtype = P.dtype;
+    rp.epi = P.epi;  // the reduction, not the GEMM, finishes split products
+    p.epi = Epilogue{};
     rp.splits = p.splits; rp.M = p.M; rp.N = p.N;
     rp.split_stride = slab; rp.total = slab;
     rp.o_off = P.o_off; rp.o_rs = P.o_rs; rp.o_cs = P.o_cs;
@@ -641,15 +646,40 @@ int launch_tcgen05(oxm_ctx *ctx, const Problem &P) {
   return OXM_OK;
 }
 
-int run_matmul(oxm_ctx *ctx, const oxm_view *a, const oxm_view *b, const oxm_view *out, bool batched) {
+int run_matmul(oxm_ctx *ctx, const oxm_view *a, const oxm_view *b, const oxm_view *out, bool batched,
+               const oxm_epilogue *ep = nullptr) {
   int st = validate(ctx, a, b, out, batched, false);
   if (st) return st;
+  Epilogue epi{};
+  if (ep) {
+    const char *op = "matmul_fused";
+    if (ep->activation < OXM_ACT_NONE || ep->activation > OXM_ACT_GELU)
+      return fail(OXM_INVALID_ARGUMENT, "%s: unknown activation %d", op, ep->activation);
+    if (ep->bias) {
+      const oxm_view *bv = ep->bias;
+      const int64_t n = b->shape[b->ndim - 1];
+      if (bv->ndim != 1 || bv->shape[0] != n)
+        return fail(OXM_SHAPE_MISMATCH, "shape mismatch: expected [%lld], got %s in %s (bias)", (long long)n, shape_str(bv).c_str(), op);
+      if (bv->dtype != a->dtype)
+        return fail(OXM_DTYPE_MISMATCH, "dtype mismatch: expected %s, got %s in %s (bias)", dtype_name(a->dtype), dtype_name(bv->dtype), op);
+      if (bv->device != ctx->device)
+        return fail(OXM_DEVICE_MISMATCH, "device mismatch: Cuda{index: %d} vs Cuda{index: %d} in %s (bias)", a->device, bv->device, op);
+      if (n > 0 && !bv->base) return fail(OXM_INVALID_ARGUMENT, "%s: bias view with null storage", op);
+      epi.bias = static_cast<const uint8_t *>(bv->base) + bv->offset * dtype_size(bv->dtype);
+      epi.bias_stride = bv->strides[0];
+      epi.bias_dtype = bv->dtype;
+    }
+    epi.activation = ep->activation;
+    epi.accumulate = ep->accumulate ? 1 : 0;
+    epi.any = (epi.bias || epi.activation || epi.accumulate) ? 1 : 0;
+  }
   for (const oxm_view *v : {a, b, out}) {
     int64_t numel = 1;
     for (int i = 0; i < v->ndim; ++i) numel *= v->shape[i];
     if (numel > 0 && v->base == nullptr) return fail(OXM_INVALID_ARGUMENT, "matmul: view with null storage");
   }
   Problem P = normalise(a, b, out);
+  P.epi = epi;
   if (P.M == 0 || P.N == 0 || P.nbatch == 0) return OXM_OK;  // nothing to write
   std::lock_guard<std::mutex> lock(ctx->mu);
   CUDA_TRY(cudaSetDevice(ctx->device));
@@ -851,6 +881,10 @@ int oxm_matmul(oxm_ctx *ctx, const oxm_view *a, const oxm_view *b, const oxm_vie
 
 int oxm_batched_matmul(oxm_ctx *ctx, const oxm_view *a, const oxm_view *b, const oxm_view *out) {
   return run_matmul(ctx, a, b, out, true);
+}
+
+int oxm_matmul_fused(oxm_ctx *ctx, const oxm_view *a, const oxm_view *b, const oxm_view *out, const oxm_epilogue *ep) {
+  return run_matmul(ctx, a, b, out, true, ep);
 }
 
 int oxm_batched_matmul_host(oxm_ctx *ctx, const oxm_view *a, const oxm_view *b, const oxm_view *out) {

@@ -23,6 +23,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include "elem.cuh"
 #include "ptx.cuh"
 
 namespace oxm {
@@ -62,6 +63,7 @@ struct GemmParams {
   int64_t tiles_per_split;
   int64_t split_ostride;  // elements
   int32_t group_m;        // tile rows walked together (L2 reuse)
+  Epilogue epi;           // applied here unless the contraction is split (then by the reduction)
 };
 
 template <int BN, int STAGES, int PAIR>
@@ -467,6 +469,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           }
         }
         const int32_t colb = col_base + c * BATCH;
+        if (p.epi.any) {
+          // bias, activation and accumulation on the fp32 sums, before rounding
+#pragma unroll
+          for (int i = 0; i < NLD; ++i) {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) {
+              const int32_t col = colb + i * 32 + e;
+              if (row_ok && col < p.N) {
+                const int64_t idx = tc.o_off + static_cast<int64_t>(row) * p.out_rs + static_cast<int64_t>(col) * p.out_cs;
+                v[i][e] = __float_as_uint(apply_epilogue(p.epi, __uint_as_float(v[i][e]), col, p.out, p.out_dtype, idx));
+              }
+            }
+          }
+        }
         if (p.out_tma) {
           if constexpr (TF32) {
 #pragma unroll

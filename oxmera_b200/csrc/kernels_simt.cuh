@@ -8,21 +8,11 @@
 
 #include <cstdint>
 
+#include "elem.cuh"
+
 namespace oxm {
 
 constexpr int kSimtMaxBatchDims = 6;
-
-__device__ __forceinline__ float load_elem(const void *base, int dtype, int64_t idx) {
-  if (dtype == 0) return static_cast<const float *>(base)[idx];
-  if (dtype == 6) return __bfloat162float(static_cast<const __nv_bfloat16 *>(base)[idx]);
-  return __half2float(static_cast<const __half *>(base)[idx]);
-}
-
-__device__ __forceinline__ void store_elem(void *base, int dtype, int64_t idx, float v) {
-  if (dtype == 0) static_cast<float *>(base)[idx] = v;
-  else if (dtype == 6) static_cast<__nv_bfloat16 *>(base)[idx] = __float2bfloat16_rn(v);
-  else static_cast<__half *>(base)[idx] = __float2half_rn(v);
-}
 
 // ---------------------------------------------------------------------------
 // FFMA tile GEMM.  64x64 output tile per 256-thread CTA, 4x4 per thread, the
@@ -41,6 +31,7 @@ struct SimtParams {
   int32_t nbd;
   int32_t bdims[kSimtMaxBatchDims];
   int64_t a_bs[kSimtMaxBatchDims], b_bs[kSimtMaxBatchDims], o_bs[kSimtMaxBatchDims];
+  Epilogue epi;
 };
 
 __global__ void __launch_bounds__(256) gemm_simt_kernel(const SimtParams p) {
@@ -117,7 +108,12 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const SimtParams p) {
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int32_t gn = n0 + tx * 4 + j;
-      if (gn < p.N) store_elem(p.out, p.out_dtype, o_off + gm * p.o_rs + gn * p.o_cs, acc[i][j]);
+      if (gn < p.N) {
+        const int64_t idx = o_off + gm * p.o_rs + gn * p.o_cs;
+        float r = acc[i][j];
+        if (p.epi.any) r = apply_epilogue(p.epi, r, gn, p.out, p.out_dtype, idx);
+        store_elem(p.out, p.out_dtype, idx, r);
+      }
     }
   }
 }
@@ -228,6 +224,7 @@ struct ReduceParams {
   int32_t nbd;
   int32_t bdims[kSimtMaxBatchDims];
   int64_t o_bs[kSimtMaxBatchDims];
+  Epilogue epi;
 };
 
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(const ReduceParams p) {
@@ -242,6 +239,7 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const ReduceParams p
       off += (batch % p.bdims[d]) * p.o_bs[d];
       batch /= p.bdims[d];
     }
+    if (p.epi.any) acc = apply_epilogue(p.epi, acc, r % p.N, p.out, p.out_dtype, off);
     store_elem(p.out, p.out_dtype, off, acc);
   }
 }

@@ -50,6 +50,7 @@ class Oracle:
         self.lib.orc_matmul.argtypes = [PV, PV, PV, C.c_int, C.c_int]
         self.lib.orc_batched_matmul.argtypes = [PV, PV, PV, C.c_int, C.c_int]
         self.lib.orc_check_matmul.argtypes = [PV, PV, PV, C.c_int]
+        self.lib.orc_matmul_fused.argtypes = [PV, PV, PV, PV, C.c_int, C.c_int, C.c_int, C.c_int]
         self.lib.orc_broadcast_shapes.argtypes = [C.POINTER(C.c_int64), C.c_int, C.POINTER(C.c_int64), C.c_int,
                                                   C.POINTER(C.c_int64), C.POINTER(C.c_int)]
         self.lib.orc_f32_to_bf16.argtypes = [C.c_float]; self.lib.orc_f32_to_bf16.restype = C.c_uint16
@@ -77,6 +78,20 @@ class Oracle:
         vo = _view(out, out_tag)
         fn = self.lib.orc_batched_matmul if batched else self.lib.orc_matmul
         st = fn(C.byref(va), C.byref(vb), C.byref(vo), acc, nthreads or self.threads)
+        return st, out
+
+    def matmul_fused(self, a, b, tag, bias=None, act=0, prev=None, acc=ACC_F64, nthreads=None):
+        """act(a.b + bias) (+ prev).  `prev` is the previous output as a float
+        array of the result's shape; the result has the accumulator's dtype."""
+        lead = np.broadcast_shapes(a.shape[:-2], b.shape[:-2])
+        odt = F64 if acc == ACC_F64 else F32
+        out = np.zeros(tuple(lead) + (a.shape[-2], b.shape[-1]), dtype=_NP[odt])
+        if prev is not None:
+            out[...] = prev
+        va, vb, vo = _view(a, tag), _view(b, tag), _view(out, odt)
+        vbias = _view(bias, tag) if bias is not None else None
+        st = self.lib.orc_matmul_fused(C.byref(va), C.byref(vb), C.byref(vo), C.byref(vbias) if vbias is not None else None,
+                                       act, 1 if prev is not None else 0, acc, nthreads or self.threads)
         return st, out
 
     def broadcast_shapes(self, lhs, rhs):
