@@ -142,6 +142,24 @@ typedef struct {
 } oxm_epilogue;
 int oxm_matmul_fused(oxm_ctx *ctx, const oxm_view *a, const oxm_view *b, const oxm_view *out, const oxm_epilogue *ep);
 
+/* ---- the other op families of Backend --------------------------------------
+ * Stand behind UnaryOps, BinaryOps and ReduceOps (crates/oxmera-ops/src/lib.rs:
+ * 27-50,61-69) for Device::Cuda.  Inputs are any views; `out` is a fresh
+ * row-major contiguous tensor of the result's shape and the operands' dtype
+ * (crates/oxmera-ops/src/lib.rs:16-17).  dtypes: f32, f64, bf16, f16 for
+ * everything; i32, i64 for neg, abs, add, sub, mul, sum, max.  exp / ln on
+ * integers, any op on u8 / bool, and integer div are OXM_UNSUPPORTED_DTYPE.
+ * Binary operands broadcast by NumPy rules (crates/oxmera-core/src/shape.rs:
+ * 49-55) and must share dtype and device.  oxm_reduce removes `axes` from the
+ * shape; naxes = 0 means all axes (a scalar result); a sum over an empty
+ * extent is 0, a max over one is refused ("there is no identity to invent"). */
+enum { OXM_NEG = 0, OXM_EXP = 1, OXM_LN = 2, OXM_ABS = 3 };
+enum { OXM_ADD = 0, OXM_SUB = 1, OXM_MUL = 2, OXM_DIV = 3 };
+enum { OXM_SUM = 0, OXM_MAX = 1 };
+int oxm_unary(oxm_ctx *ctx, int op, const oxm_view *a, const oxm_view *out);
+int oxm_binary(oxm_ctx *ctx, int op, const oxm_view *a, const oxm_view *b, const oxm_view *out);
+int oxm_reduce(oxm_ctx *ctx, int op, const oxm_view *a, const int32_t *axes, int naxes, const oxm_view *out);
+
 /* Same operation on HOST views: `base` pointers are host memory.  The
  * operands are staged to the device, multiplied, and the result copied back
  * into `out`'s (contiguous) host buffer before returning.  Large products are

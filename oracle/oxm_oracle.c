@@ -322,6 +322,122 @@ int orc_matmul_fused(const orc_view *a, const orc_view *b, const orc_view *out, 
 }
 
 /* ------------------------------------------------------------------ */
+/* elementwise and reductions                                           */
+/* ------------------------------------------------------------------ */
+
+static int is_int_dtype(int32_t d) { return d == ORC_I32 || d == ORC_I64; }
+static int is_float_dtype(int32_t d) { return d == ORC_F32 || d == ORC_F64 || d == ORC_BF16 || d == ORC_F16; }
+
+static double get_f(const orc_view *v, int64_t idx) { return load_as_f64(v->base, v->dtype, idx); }
+static int64_t get_i(const orc_view *v, int64_t idx) {
+  return v->dtype == ORC_I32 ? (int64_t)((const int32_t *)v->base)[idx] : ((const int64_t *)v->base)[idx];
+}
+static void put_f(const orc_view *v, int64_t idx, double x) { store_from_f64(v->base, v->dtype, idx, x); }
+static void put_i(const orc_view *v, int64_t idx, int64_t x) {
+  if (v->dtype == ORC_I32) ((int32_t *)v->base)[idx] = (int32_t)x;
+  else ((int64_t *)v->base)[idx] = x;
+}
+
+/* storage offset of the i-th element (row-major over `shape`) of an operand
+ * right-aligned against that shape, extent-1 dims broadcasting */
+static int64_t bcast_offset(const orc_view *v, const int64_t *shape, int ndim, int64_t i) {
+  int64_t off = v->offset;
+  for (int d = ndim - 1; d >= 0; --d) {
+    int64_t idx = i % shape[d];
+    i /= shape[d];
+    int vd = d - (ndim - v->ndim);
+    if (vd >= 0 && v->shape[vd] != 1) off += idx * v->strides[vd];
+  }
+  return off;
+}
+
+int orc_unary(int op, const orc_view *a, const orc_view *out) {
+  if (!(is_float_dtype(a->dtype) || is_int_dtype(a->dtype))) return ORC_UNSUPPORTED_DTYPE;
+  if ((op == 1 || op == 2) && !is_float_dtype(a->dtype)) return ORC_UNSUPPORTED_DTYPE;
+  if (out->dtype != a->dtype) return ORC_DTYPE_MISMATCH;
+  int64_t n = 1;
+  for (int d = 0; d < a->ndim; ++d) n *= a->shape[d];
+  for (int64_t i = 0; i < n; ++i) {
+    int64_t off = bcast_offset(a, a->shape, a->ndim, i);
+    if (is_int_dtype(a->dtype)) {
+      int64_t x = get_i(a, off);
+      put_i(out, out->offset + i, op == 0 ? -x : (x < 0 ? -x : x));
+    } else {
+      double x = get_f(a, off);
+      put_f(out, out->offset + i, op == 0 ? -x : op == 1 ? exp(x) : op == 2 ? log(x) : fabs(x));
+    }
+  }
+  return ORC_OK;
+}
+
+int orc_binary(int op, const orc_view *a, const orc_view *b, const orc_view *out) {
+  if (a->dtype != b->dtype) return ORC_DTYPE_MISMATCH;
+  if (!(is_float_dtype(a->dtype) || is_int_dtype(a->dtype))) return ORC_UNSUPPORTED_DTYPE;
+  if (op == 3 && !is_float_dtype(a->dtype)) return ORC_UNSUPPORTED_DTYPE;
+  int64_t shape[ORC_MAX_DIMS];
+  int nd = 0;
+  int st = orc_broadcast_shapes(a->shape, a->ndim, b->shape, b->ndim, shape, &nd);
+  if (st != ORC_OK) return st;
+  if (out->ndim != nd) return ORC_SHAPE_MISMATCH;
+  int64_t n = 1;
+  for (int d = 0; d < nd; ++d) {
+    if (out->shape[d] != shape[d]) return ORC_SHAPE_MISMATCH;
+    n *= shape[d];
+  }
+  for (int64_t i = 0; i < n; ++i) {
+    int64_t ao = bcast_offset(a, shape, nd, i), bo = bcast_offset(b, shape, nd, i);
+    if (is_int_dtype(a->dtype)) {
+      int64_t x = get_i(a, ao), y = get_i(b, bo);
+      put_i(out, out->offset + i, op == 0 ? x + y : op == 1 ? x - y : x * y);
+    } else {
+      double x = get_f(a, ao), y = get_f(b, bo);
+      put_f(out, out->offset + i, op == 0 ? x + y : op == 1 ? x - y : op == 2 ? x * y : x / y);
+    }
+  }
+  return ORC_OK;
+}
+
+int orc_reduce(int op, const orc_view *a, const int32_t *axes, int naxes, const orc_view *out) {
+  if (!(is_float_dtype(a->dtype) || is_int_dtype(a->dtype))) return ORC_UNSUPPORTED_DTYPE;
+  int reduced[ORC_MAX_DIMS] = {0};
+  if (naxes == 0) for (int d = 0; d < a->ndim; ++d) reduced[d] = 1;
+  for (int i = 0; i < naxes; ++i) {
+    if (axes[i] < 0 || axes[i] >= a->ndim || reduced[axes[i]]) return ORC_INDEX_OUT_OF_BOUNDS;
+    reduced[axes[i]] = 1;
+  }
+  int64_t kshape[ORC_MAX_DIMS], kstr[ORC_MAX_DIMS], rshape[ORC_MAX_DIMS], rstr[ORC_MAX_DIMS];
+  int nk = 0, nr = 0;
+  int64_t n_out = 1, n_red = 1;
+  for (int d = 0; d < a->ndim; ++d) {
+    if (reduced[d]) { rshape[nr] = a->shape[d]; rstr[nr] = a->strides[d]; nr++; n_red *= a->shape[d]; }
+    else { kshape[nk] = a->shape[d]; kstr[nk] = a->strides[d]; nk++; n_out *= a->shape[d]; }
+  }
+  if (out->ndim != nk) return ORC_SHAPE_MISMATCH;
+  for (int d = 0; d < nk; ++d) if (out->shape[d] != kshape[d]) return ORC_SHAPE_MISMATCH;
+  if (n_out > 0 && n_red == 0 && op == 1) return ORC_NOT_IMPLEMENTED; /* no identity to invent */
+  for (int64_t o = 0; o < n_out; ++o) {
+    int64_t base = a->offset, t = o;
+    for (int d = nk - 1; d >= 0; --d) { base += (t % kshape[d]) * kstr[d]; t /= kshape[d]; }
+    double facc = 0.0;
+    int64_t iacc = 0;
+    for (int64_t r = 0; r < n_red; ++r) {
+      int64_t off = base, u = r;
+      for (int d = nr - 1; d >= 0; --d) { off += (u % rshape[d]) * rstr[d]; u /= rshape[d]; }
+      if (is_int_dtype(a->dtype)) {
+        int64_t x = get_i(a, off);
+        iacc = (r == 0) ? x : (op == 0 ? iacc + x : (x > iacc ? x : iacc));
+      } else {
+        double x = get_f(a, off);
+        facc = (r == 0) ? x : (op == 0 ? facc + x : (x > facc ? x : facc));
+      }
+    }
+    if (is_int_dtype(a->dtype)) put_i(out, out->offset + o, iacc);
+    else put_f(out, out->offset + o, facc);
+  }
+  return ORC_OK;
+}
+
+/* ------------------------------------------------------------------ */
 /* synthetic data                                                       */
 /* ------------------------------------------------------------------ */
 

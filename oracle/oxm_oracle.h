@@ -94,6 +94,17 @@ int orc_matmul_fused(const orc_view *a, const orc_view *b, const orc_view *out, 
 int orc_check_matmul(const orc_view *a, const orc_view *b, const orc_view *out,
                      int batched);
 
+/* The other op families of oxmera's Backend (crates/oxmera-ops/src/lib.rs:27-50,
+ * 61-69), restated as plain loops: every element computed in double (i64 for
+ * integer dtypes) and rounded once on store.  `out` is row-major contiguous.
+ * unary op: 0 neg, 1 exp, 2 ln, 3 abs.  binary op: 0 add, 1 sub, 2 mul, 3 div,
+ * operands broadcast by NumPy rules.  reduce op: 0 sum, 1 max over `axes`
+ * (naxes = 0: all axes), ascending index order.  dtypes: f32, f64, i32, i64,
+ * bf16, f16 with the same refusals as the device library. */
+int orc_unary(int op, const orc_view *a, const orc_view *out);
+int orc_binary(int op, const orc_view *a, const orc_view *b, const orc_view *out);
+int orc_reduce(int op, const orc_view *a, const int32_t *axes, int naxes, const orc_view *out);
+
 /* NumPy broadcast of two shapes; returns ORC_OK or
  * ORC_BROADCAST_INCOMPATIBLE.  out_dims must hold ORC_MAX_DIMS entries. */
 int orc_broadcast_shapes(const int64_t *lhs, int lhs_ndim, const int64_t *rhs,

@@ -5,9 +5,8 @@ is the union of the op traits plus identity; `backend_for` resolves a device
 handle to the registered backend or raises BackendUnavailable; tensors route
 `matmul` through it.  `B200Backend` implements MatmulOps
 (crates/oxmera-ops/src/lib.rs:53-59) and its batched extension over the C ABI.
-The other op families are not part of this backend yet and report
-NotImplemented, the typed error the reference reserves for that
-(crates/oxmera-core/src/error.rs:88-101).
+The elementwise and reduction families (UnaryOps, BinaryOps, ReduceOps) go
+through `oxm_unary` / `oxm_binary` / `oxm_reduce`.
 """
 from __future__ import annotations
 
@@ -19,7 +18,7 @@ import numpy as np
 
 from . import capi
 from .core import (BackendFault, BackendUnavailable, BroadcastIncompatible, DType, Device, DeviceMismatch,
-                   DTypeMismatch, Layout, NotImplementedOp, OxmeraError, ShapeMismatch, UnsupportedDType,
+                   DTypeMismatch, IndexOutOfBounds, Layout, NotImplementedOp, OxmeraError, ShapeMismatch, UnsupportedDType,
                    broadcast_shapes)
 from .tensor import Tensor
 
@@ -37,6 +36,8 @@ def _raise(status: int, op: str, a: Tensor | None = None, b: Tensor | None = Non
         raise UnsupportedDType(a.dtype if a is not None else None, op, detail)
     if status == capi.DEVICE_MISMATCH:
         raise DeviceMismatch(a.device() if a is not None else None, b.device() if b is not None else None, op, detail)
+    if status == capi.INDEX_OUT_OF_BOUNDS:
+        raise IndexOutOfBounds((), a.shape if a is not None else ())
     if status == capi.BACKEND_UNAVAILABLE:
         raise BackendUnavailable(None, detail)
     if status == capi.NOT_IMPLEMENTED:
@@ -142,20 +143,46 @@ class B200Backend:
             _raise(st, "batched_matmul")
         return out
 
-    # ---- the op families this backend does not carry yet ----
-    def _unsupported(self, op: str):
-        raise NotImplementedOp(op, f"backend {self.name()} (matmul path only)")
+    # ---- UnaryOps / BinaryOps / ReduceOps (crates/oxmera-ops/src/lib.rs:27-50,61-69) ----
+    def _unary(self, op: int, name: str, a: Tensor) -> Tensor:
+        out = Tensor.empty(a.shape, a.dtype, self)
+        st = self._lib.oxm_unary(self._ctx, op, C.byref(a._view()), C.byref(out._view()))
+        if st != capi.OK:
+            _raise(st, name, a)
+        return out
 
-    def neg(self, a): self._unsupported("neg")
-    def exp(self, a): self._unsupported("exp")
-    def ln(self, a): self._unsupported("ln")
-    def abs(self, a): self._unsupported("abs")
-    def add(self, lhs, rhs): self._unsupported("add")
-    def sub(self, lhs, rhs): self._unsupported("sub")
-    def mul(self, lhs, rhs): self._unsupported("mul")
-    def div(self, lhs, rhs): self._unsupported("div")
-    def sum(self, a, axes): self._unsupported("sum")
-    def max(self, a, axes): self._unsupported("max")
+    def _binary(self, op: int, name: str, lhs: Tensor, rhs: Tensor) -> Tensor:
+        for t in (lhs, rhs):
+            if t.device() != self.device():
+                raise DeviceMismatch(t.device(), self.device(), name)
+        out = Tensor.empty(broadcast_shapes(lhs.shape, rhs.shape), lhs.dtype, self)
+        st = self._lib.oxm_binary(self._ctx, op, C.byref(lhs._view()), C.byref(rhs._view()), C.byref(out._view()))
+        if st != capi.OK:
+            _raise(st, name, lhs, rhs)
+        return out
+
+    def _reduce(self, op: int, name: str, a: Tensor, axes: Sequence[int]) -> Tensor:
+        axes = [int(x) for x in axes]
+        drop = set(axes) if axes else set(range(len(a.shape)))
+        if any(x < 0 or x >= len(a.shape) for x in axes) or len(set(axes)) != len(axes):
+            raise IndexOutOfBounds(axes, a.shape)
+        out = Tensor.empty(tuple(s for d, s in enumerate(a.shape) if d not in drop), a.dtype, self)
+        arr = (C.c_int32 * max(len(axes), 1))(*axes)
+        st = self._lib.oxm_reduce(self._ctx, op, C.byref(a._view()), arr, len(axes), C.byref(out._view()))
+        if st != capi.OK:
+            _raise(st, name, a)
+        return out
+
+    def neg(self, a): return self._unary(0, "neg", a)
+    def exp(self, a): return self._unary(1, "exp", a)
+    def ln(self, a): return self._unary(2, "ln", a)
+    def abs(self, a): return self._unary(3, "abs", a)
+    def add(self, lhs, rhs): return self._binary(0, "add", lhs, rhs)
+    def sub(self, lhs, rhs): return self._binary(1, "sub", lhs, rhs)
+    def mul(self, lhs, rhs): return self._binary(2, "mul", lhs, rhs)
+    def div(self, lhs, rhs): return self._binary(3, "div", lhs, rhs)
+    def sum(self, a, axes=()): return self._reduce(0, "sum", a, axes)
+    def max(self, a, axes=()): return self._reduce(1, "max", a, axes)
 
     # ---- storage plumbing used by Tensor ----
     def _alloc(self, nbytes: int) -> int:

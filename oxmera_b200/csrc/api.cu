@@ -16,6 +16,7 @@
 #include <string>
 #include <vector>
 
+#include "elementwise.cuh"
 #include "gemm_tcgen05.cuh"
 #include "kernels_simt.cuh"
 
@@ -1029,8 +1030,10 @@ int oxm_contiguous(oxm_ctx *ctx, const oxm_view *src, const oxm_view *dst) {
   CopyParams p{};
   p.n = 1;
   int64_t expect = 1;
+  bool empty = false;
+  for (int i = 0; i < src->ndim; ++i) empty = empty || src->shape[i] == 0;
   for (int i = src->ndim - 1; i >= 0; --i) {
-    if (dst->shape[i] != 1 && dst->strides[i] != expect)
+    if (!empty && dst->shape[i] != 1 && dst->strides[i] != expect)
       return fail(OXM_INVALID_ARGUMENT, "contiguous: the destination view must be row-major contiguous");
     expect *= dst->shape[i];
     p.n *= src->shape[i];
@@ -1088,6 +1091,324 @@ int oxm_selftest_bounded_wait(oxm_ctx *ctx, int64_t limit_ms) {
   if (st == OXM_TIMEOUT && gave_up != 1) return fail(OXM_CUDA_ERROR, "bounded wait self-test: status set but the waiter did not give up");
   return st;
 }
+
+}  // extern "C"
+
+// ---------------------------------------------------------------------------
+// UnaryOps / BinaryOps / ReduceOps
+// ---------------------------------------------------------------------------
+namespace {
+
+bool is_ew_dtype(int dt) { return dt == OXM_F32 || dt == OXM_F64 || dt == OXM_I32 || dt == OXM_I64 || dt == OXM_BF16 || dt == OXM_F16; }
+bool is_float_dtype(int dt) { return dt == OXM_F32 || dt == OXM_F64 || dt == OXM_BF16 || dt == OXM_F16; }
+
+// The output of every operation is fresh and contiguous (ops/lib.rs:16-17).
+int check_fresh_output(const oxm_view *out, const int64_t *shape, int ndim, int dtype, const char *op) {
+  bool ok = out->ndim == ndim;
+  for (int i = 0; ok && i < ndim; ++i) ok = out->shape[i] == shape[i];
+  if (!ok) {
+    oxm_view exp{};
+    exp.ndim = ndim;
+    for (int i = 0; i < ndim; ++i) exp.shape[i] = shape[i];
+    return fail(OXM_SHAPE_MISMATCH, "shape mismatch: expected %s, got %s in %s (output)", shape_str(&exp).c_str(), shape_str(out).c_str(), op);
+  }
+  if (out->dtype != dtype)
+    return fail(OXM_DTYPE_MISMATCH, "dtype mismatch: expected %s, got %s in %s (output)", dtype_name(dtype), dtype_name(out->dtype), op);
+  int64_t expect = 1;
+  for (int i = 0; i < ndim; ++i)
+    if (out->shape[i] == 0) return OXM_OK;  // an empty tensor is contiguous whatever its strides say
+  for (int i = ndim - 1; i >= 0; --i) {
+    if (out->shape[i] != 1 && out->strides[i] != expect) return fail(OXM_INVALID_ARGUMENT, "%s: the output view must be row-major contiguous", op);
+    expect *= out->shape[i];
+  }
+  return OXM_OK;
+}
+
+template <template <typename> class Launcher, typename... Args>
+int dispatch_dtype(int dtype, Args &&...args) {
+  switch (dtype) {
+    case OXM_F32: return Launcher<float>::run(args...);
+    case OXM_F64: return Launcher<double>::run(args...);
+    case OXM_I32: return Launcher<int32_t>::run(args...);
+    case OXM_I64: return Launcher<int64_t>::run(args...);
+    case OXM_BF16: return Launcher<__nv_bfloat16>::run(args...);
+    default: return Launcher<__half>::run(args...);
+  }
+}
+
+template <typename T> struct UnaryLauncher {
+  static int run(oxm_ctx *ctx, const EwParams &p, unsigned blocks) {
+    if (p.rows) ew_rows_kernel<T, false><<<blocks, 256, 0, ctx->stream>>>(p);
+    else unary_kernel<T><<<blocks, 256, 0, ctx->stream>>>(p);
+    return OXM_OK;
+  }
+};
+template <typename T> struct BinaryLauncher {
+  static int run(oxm_ctx *ctx, const EwParams &p, unsigned blocks) {
+    if (p.rows) ew_rows_kernel<T, true><<<blocks, 256, 0, ctx->stream>>>(p);
+    else binary_kernel<T><<<blocks, 256, 0, ctx->stream>>>(p);
+    return OXM_OK;
+  }
+};
+
+// Decide between the flat kernels and the row kernel, and whether rows can move 16 bytes at a time.
+unsigned ew_plan(const oxm_ctx *ctx, EwParams &p, int esz, bool binary) {
+  p.rows = 0; p.rows_vec = 0;
+  if (!p.contiguous && p.ndim >= 1 && p.shape[p.ndim - 1] >= 128) {
+    const int nd = p.ndim - 1, V = 16 / esz;
+    p.rows = 1;
+    auto ok = [&](const void *base, int64_t off, const int64_t *st) {
+      if (st[nd] != 0 && st[nd] != 1) return false;
+      if (st[nd] == 0) return true;  // a per-row scalar needs no alignment
+      if ((reinterpret_cast<uintptr_t>(base) + off * esz) % 16) return false;
+      for (int d = 0; d < nd; ++d) if (st[d] % V) return false;
+      return true;
+    };
+    p.rows_vec = (p.shape[nd] % V == 0 && reinterpret_cast<uintptr_t>(p.out) % 16 == 0 && ok(p.a, p.a_off, p.a_strides) &&
+                  (!binary || ok(p.b, p.b_off, p.b_strides))) ? 1 : 0;
+    return (unsigned)std::min<int64_t>(p.n / p.shape[nd], (int64_t)ctx->num_sms * 32);
+  }
+  return (unsigned)std::min<int64_t>((p.n + 255) / 256, (int64_t)ctx->num_sms * 16);
+}
+template <typename T> struct ReduceLauncher {
+  static int run(oxm_ctx *ctx, const ReduceOpParams &p, bool row_mode, unsigned blocks_x) {
+    const dim3 grid(blocks_x, (unsigned)p.splits, 1);
+    if (row_mode) reduce_row_kernel<T><<<grid, 256, 0, ctx->stream>>>(p);
+    else reduce_col_kernel<T><<<grid, 256, 0, ctx->stream>>>(p);
+    if (p.splits > 1) {
+      const unsigned fb = (unsigned)std::min<int64_t>((p.n_out + 255) / 256, (int64_t)ctx->num_sms * 8);
+      reduce_finish_kernel<T><<<fb, 256, 0, ctx->stream>>>(p);
+    }
+    return OXM_OK;
+  }
+};
+
+// Drop extent-1 dims and merge neighbours that are walked with one stride.
+int collapse_dims(int n, int64_t *shape, int64_t *strides) {
+  int w = 0;
+  for (int d = 0; d < n; ++d) {
+    if (shape[d] == 1) continue;
+    if (w > 0 && strides[w - 1] == strides[d] * shape[d]) {
+      shape[w - 1] *= shape[d];
+      strides[w - 1] = strides[d];
+    } else {
+      shape[w] = shape[d];
+      strides[w] = strides[d];
+      ++w;
+    }
+  }
+  return w;
+}
+
+// Fill the elementwise parameter block for output shape `shape`; operand dims
+// are right-aligned against it, extent-1 dims broadcast with stride 0.
+void ew_operand(const oxm_view *v, int ndim, int64_t *strides, int64_t *off) {
+  *off = v->offset;
+  for (int d = 0; d < ndim; ++d) {
+    const int vd = d - (ndim - v->ndim);
+    strides[d] = (vd >= 0 && v->shape[vd] != 1) ? v->strides[vd] : 0;
+  }
+}
+
+// Drop extent-1 dims and merge neighbours both operands walk with one stride.
+void ew_collapse(EwParams &p) {
+  int w = 0;
+  for (int d = 0; d < p.ndim; ++d) {
+    if (p.shape[d] == 1) continue;
+    if (w > 0 && p.a_strides[w - 1] == p.a_strides[d] * p.shape[d] && p.b_strides[w - 1] == p.b_strides[d] * p.shape[d]) {
+      p.shape[w - 1] *= p.shape[d];
+      p.a_strides[w - 1] = p.a_strides[d];
+      p.b_strides[w - 1] = p.b_strides[d];
+    } else {
+      p.shape[w] = p.shape[d];
+      p.a_strides[w] = p.a_strides[d];
+      p.b_strides[w] = p.b_strides[d];
+      ++w;
+    }
+  }
+  p.ndim = w;
+}
+
+bool ew_linear(const int64_t *shape, const int64_t *strides, int ndim) {
+  int64_t expect = 1;
+  for (int d = ndim - 1; d >= 0; --d) {
+    if (shape[d] != 1 && strides[d] != expect) return false;
+    expect *= shape[d];
+  }
+  return true;
+}
+
+}  // namespace
+
+extern "C" int oxm_unary(oxm_ctx *ctx, int op, const oxm_view *a, const oxm_view *out) {
+  static const char *names[] = {"neg", "exp", "ln", "abs"};
+  if (!ctx || !a || !out) return fail(OXM_INVALID_ARGUMENT, "unary: null argument");
+  if (op < OXM_NEG || op > OXM_ABS) return fail(OXM_INVALID_ARGUMENT, "unary: unknown operation %d", op);
+  const char *name = names[op];
+  if (a->ndim < 0 || a->ndim > OXM_MAX_DIMS) return fail(OXM_NOT_IMPLEMENTED, "%s is not implemented for rank %d", name, a->ndim);
+  if (!is_ew_dtype(a->dtype) || ((op == OXM_EXP || op == OXM_LN) && !is_float_dtype(a->dtype)))
+    return fail(OXM_UNSUPPORTED_DTYPE, "dtype %s is not supported by %s", dtype_name(a->dtype), name);
+  if (a->device != ctx->device || out->device != ctx->device)
+    return fail(OXM_DEVICE_MISMATCH, "device mismatch: Cuda{index: %d} vs Cuda{index: %d} in %s", a->device, out->device, name);
+  int st = check_fresh_output(out, a->shape, a->ndim, a->dtype, name);
+  if (st) return st;
+  EwParams p{};
+  p.op = op; p.ndim = a->ndim; p.n = 1;
+  for (int d = 0; d < a->ndim; ++d) { p.shape[d] = a->shape[d]; p.n *= a->shape[d]; }
+  if (p.n == 0) return OXM_OK;
+  if (!a->base || !out->base) return fail(OXM_INVALID_ARGUMENT, "%s: view with null storage", name);
+  ew_operand(a, a->ndim, p.a_strides, &p.a_off);
+  for (int d = 0; d < p.ndim; ++d) p.b_strides[d] = p.a_strides[d];
+  ew_collapse(p);
+  p.contiguous = ew_linear(p.shape, p.a_strides, p.ndim) ? 1 : 0;
+  p.a = a->base; p.b = a->base;
+  p.out = static_cast<uint8_t *>(out->base) + out->offset * dtype_size(out->dtype);
+  const int esz = dtype_size(a->dtype);
+  p.vec = (p.contiguous && (reinterpret_cast<uintptr_t>(p.a) + p.a_off * esz) % 16 == 0 && reinterpret_cast<uintptr_t>(p.out) % 16 == 0) ? 1 : 0;
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  CUDA_TRY(cudaSetDevice(ctx->device));
+  const unsigned blocks = ew_plan(ctx, p, esz, false);
+  dispatch_dtype<UnaryLauncher>(a->dtype, ctx, p, blocks);
+  CUDA_TRY(cudaGetLastError());
+  ctx->launches[0]++;
+  snprintf(ctx->last_kernel, sizeof(ctx->last_kernel), "unary_%s", name);
+  return OXM_OK;
+}
+
+extern "C" int oxm_binary(oxm_ctx *ctx, int op, const oxm_view *a, const oxm_view *b, const oxm_view *out) {
+  static const char *names[] = {"add", "sub", "mul", "div"};
+  if (!ctx || !a || !b || !out) return fail(OXM_INVALID_ARGUMENT, "binary: null argument");
+  if (op < OXM_ADD || op > OXM_DIV) return fail(OXM_INVALID_ARGUMENT, "binary: unknown operation %d", op);
+  const char *name = names[op];
+  for (const oxm_view *v : {a, b})
+    if (v->ndim < 0 || v->ndim > OXM_MAX_DIMS) return fail(OXM_NOT_IMPLEMENTED, "%s is not implemented for rank %d", name, v->ndim);
+  if (a->device != b->device)
+    return fail(OXM_DEVICE_MISMATCH, "device mismatch: Cuda{index: %d} vs Cuda{index: %d} in %s", a->device, b->device, name);
+  if (a->device != ctx->device || out->device != ctx->device)
+    return fail(OXM_DEVICE_MISMATCH, "device mismatch: Cuda{index: %d} vs Cuda{index: %d} in %s", a->device, out->device, name);
+  if (a->dtype != b->dtype)
+    return fail(OXM_DTYPE_MISMATCH, "dtype mismatch: expected %s, got %s in %s", dtype_name(a->dtype), dtype_name(b->dtype), name);
+  if (!is_ew_dtype(a->dtype) || (op == OXM_DIV && !is_float_dtype(a->dtype)))
+    return fail(OXM_UNSUPPORTED_DTYPE, "dtype %s is not supported by %s", dtype_name(a->dtype), name);
+  // NumPy broadcasting (shape.rs:49-55)
+  int nd = std::max(a->ndim, b->ndim);
+  int64_t shape[OXM_MAX_DIMS];
+  for (int i = 0; i < nd; ++i) {
+    const int ai = a->ndim - 1 - i, bi = b->ndim - 1 - i;
+    const int64_t l = ai >= 0 ? a->shape[ai] : 1, r = bi >= 0 ? b->shape[bi] : 1;
+    if (l != r && l != 1 && r != 1)
+      return fail(OXM_BROADCAST_INCOMPATIBLE, "cannot broadcast %s with %s", shape_str(a).c_str(), shape_str(b).c_str());
+    shape[nd - 1 - i] = l == 1 ? r : l;
+  }
+  int st = check_fresh_output(out, shape, nd, a->dtype, name);
+  if (st) return st;
+  EwParams p{};
+  p.op = op; p.ndim = nd; p.n = 1;
+  for (int d = 0; d < nd; ++d) { p.shape[d] = shape[d]; p.n *= shape[d]; }
+  if (p.n == 0) return OXM_OK;
+  if (!a->base || !b->base || !out->base) return fail(OXM_INVALID_ARGUMENT, "%s: view with null storage", name);
+  ew_operand(a, nd, p.a_strides, &p.a_off);
+  ew_operand(b, nd, p.b_strides, &p.b_off);
+  ew_collapse(p);
+  nd = p.ndim;
+  p.contiguous = (ew_linear(p.shape, p.a_strides, nd) && ew_linear(p.shape, p.b_strides, nd)) ? 1 : 0;
+  p.a = a->base; p.b = b->base;
+  p.out = static_cast<uint8_t *>(out->base) + out->offset * dtype_size(out->dtype);
+  const int esz = dtype_size(a->dtype);
+  p.vec = (p.contiguous && (reinterpret_cast<uintptr_t>(p.a) + p.a_off * esz) % 16 == 0 &&
+           (reinterpret_cast<uintptr_t>(p.b) + p.b_off * esz) % 16 == 0 && reinterpret_cast<uintptr_t>(p.out) % 16 == 0) ? 1 : 0;
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  CUDA_TRY(cudaSetDevice(ctx->device));
+  const unsigned blocks = ew_plan(ctx, p, esz, true);
+  dispatch_dtype<BinaryLauncher>(a->dtype, ctx, p, blocks);
+  CUDA_TRY(cudaGetLastError());
+  ctx->launches[0]++;
+  snprintf(ctx->last_kernel, sizeof(ctx->last_kernel), "binary_%s", name);
+  return OXM_OK;
+}
+
+extern "C" int oxm_reduce(oxm_ctx *ctx, int op, const oxm_view *a, const int32_t *axes, int naxes, const oxm_view *out) {
+  static const char *names[] = {"sum", "max"};
+  if (!ctx || !a || !out || (naxes > 0 && !axes)) return fail(OXM_INVALID_ARGUMENT, "reduce: null argument");
+  if (op < OXM_SUM || op > OXM_MAX) return fail(OXM_INVALID_ARGUMENT, "reduce: unknown operation %d", op);
+  const char *name = names[op];
+  if (a->ndim < 0 || a->ndim > OXM_MAX_DIMS) return fail(OXM_NOT_IMPLEMENTED, "%s is not implemented for rank %d", name, a->ndim);
+  if (!is_ew_dtype(a->dtype)) return fail(OXM_UNSUPPORTED_DTYPE, "dtype %s is not supported by %s", dtype_name(a->dtype), name);
+  if (a->device != ctx->device || out->device != ctx->device)
+    return fail(OXM_DEVICE_MISMATCH, "device mismatch: Cuda{index: %d} vs Cuda{index: %d} in %s", a->device, out->device, name);
+  bool reduced[OXM_MAX_DIMS] = {};
+  if (naxes == 0) {
+    for (int d = 0; d < a->ndim; ++d) reduced[d] = true;  // empty axes means all axes
+  } else {
+    for (int i = 0; i < naxes; ++i) {
+      if (axes[i] < 0 || axes[i] >= a->ndim || reduced[axes[i]])
+        return fail(OXM_INDEX_OUT_OF_BOUNDS, "index [%d] out of bounds for shape %s (axes of %s)", axes[i], shape_str(a).c_str(), name);
+      reduced[axes[i]] = true;
+    }
+  }
+  ReduceOpParams p{};
+  p.op = op; p.n_out = 1; p.n_red = 1; p.a_off = a->offset; p.splits = 1;
+  int64_t oshape[OXM_MAX_DIMS];
+  int nk_full = 0;
+  for (int d = 0; d < a->ndim; ++d) {
+    if (reduced[d]) {
+      p.red_shape[p.nred] = a->shape[d]; p.red_strides[p.nred] = a->strides[d]; p.nred++;
+      p.n_red *= a->shape[d];
+    } else {
+      oshape[nk_full++] = a->shape[d];
+      p.kept_shape[p.nkept] = a->shape[d]; p.kept_strides[p.nkept] = a->strides[d]; p.nkept++;
+      p.n_out *= a->shape[d];
+    }
+  }
+  int st = check_fresh_output(out, oshape, nk_full, a->dtype, name);
+  if (st) return st;
+  if (p.n_out == 0) return OXM_OK;
+  if (p.n_red == 0 && op == OXM_MAX)
+    return fail(OXM_NOT_IMPLEMENTED, "max is not implemented for an empty reduction extent of %s (there is no identity to invent)", shape_str(a).c_str());
+  if (!out->base || (p.n_red > 0 && !a->base)) return fail(OXM_INVALID_ARGUMENT, "%s: view with null storage", name);
+  p.a = a->base;
+  p.out = static_cast<uint8_t *>(out->base) + out->offset * dtype_size(out->dtype);
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  CUDA_TRY(cudaSetDevice(ctx->device));
+  if (p.n_red == 0) {  // an empty sum is zero
+    CUDA_TRY(cudaMemsetAsync(p.out, 0, (size_t)p.n_out * dtype_size(a->dtype), ctx->stream));
+    return OXM_OK;
+  }
+  p.nkept = collapse_dims(p.nkept, p.kept_shape, p.kept_strides);
+  p.nred = collapse_dims(p.nred, p.red_shape, p.red_strides);
+  // Threads follow whichever group owns the smallest stride, so that a warp's loads are adjacent.
+  auto min_stride = [](int n, const int64_t *st) {
+    int64_t m = INT64_MAX;
+    for (int d = 0; d < n; ++d) m = std::min<int64_t>(m, st[d] < 0 ? -st[d] : st[d]);
+    return m;
+  };
+  const bool row_mode = p.nkept == 0 || min_stride(p.nred, p.red_strides) < min_stride(p.nkept, p.kept_strides);
+  const int64_t target = (int64_t)ctx->num_sms * 8;  // CTAs wanted in flight
+  unsigned blocks_x;
+  int64_t max_splits;
+  if (row_mode) {
+    blocks_x = (unsigned)std::min<int64_t>(p.n_out, 65535 * 16);
+    max_splits = (p.n_red + 8191) / 8192;    // at least 8 Ki elements per slice
+  } else {
+    blocks_x = (unsigned)std::min<int64_t>((p.n_out + 255) / 256, (int64_t)ctx->num_sms * 16);
+    max_splits = (p.n_red + 63) / 64;        // at least 64 serial steps per thread
+  }
+  p.splits = (int32_t)std::max<int64_t>(1, std::min<int64_t>({(target + blocks_x - 1) / blocks_x, max_splits, (int64_t)1024}));
+  p.chunk = (p.n_red + p.splits - 1) / p.splits;
+  p.splits = (int32_t)((p.n_red + p.chunk - 1) / p.chunk);
+  if (p.splits > 1) {
+    st = grow(ctx, ctx->pack_ws[2], (size_t)p.splits * p.n_out * 8);
+    if (st) return st;
+    p.partial = ctx->pack_ws[2].ptr;
+  }
+  dispatch_dtype<ReduceLauncher>(a->dtype, ctx, p, row_mode, blocks_x);
+  CUDA_TRY(cudaGetLastError());
+  ctx->launches[0] += p.splits > 1 ? 2 : 1;
+  snprintf(ctx->last_kernel, sizeof(ctx->last_kernel), "reduce_%s_%s_x%d", name, row_mode ? "row" : "col", p.splits);
+  return OXM_OK;
+}
+
+extern "C" {
 
 int oxm_event_create(oxm_ctx *ctx, oxm_event **out) {
   if (!ctx || !out) return fail(OXM_INVALID_ARGUMENT, "oxm_event_create: null argument");

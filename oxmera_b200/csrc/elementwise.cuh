@@ -1,0 +1,301 @@
+// The HBM-bound half of oxmera's Backend trait on the device: UnaryOps
+// (neg, exp, ln, abs), BinaryOps (add, sub, mul, div with NumPy broadcasting)
+// and ReduceOps (sum, max over axes).  Inputs are read through their views
+// (signed element strides, broadcast dims as stride 0); outputs are fresh and
+// contiguous, so consecutive threads write consecutive elements.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <cstdint>
+
+namespace oxm {
+
+constexpr int kEwMaxDims = 8;
+
+// dtype tags of the C ABI: 0 f32, 1 f64, 2 i32, 3 i64, 6 bf16, 7 f16.
+// 16-bit floats compute in f32, f32 in f32, f64 in f64, integers in i64.
+template <typename T> struct EwTraits;
+template <> struct EwTraits<float> { using C = float; };
+template <> struct EwTraits<double> { using C = double; };
+template <> struct EwTraits<int32_t> { using C = int64_t; };
+template <> struct EwTraits<int64_t> { using C = int64_t; };
+template <> struct EwTraits<__nv_bfloat16> { using C = float; };
+template <> struct EwTraits<__half> { using C = float; };
+
+template <typename T> __device__ __forceinline__ typename EwTraits<T>::C ew_load(const T *p, int64_t i) {
+  return static_cast<typename EwTraits<T>::C>(p[i]);
+}
+template <> __device__ __forceinline__ float ew_load<__nv_bfloat16>(const __nv_bfloat16 *p, int64_t i) { return __bfloat162float(p[i]); }
+template <> __device__ __forceinline__ float ew_load<__half>(const __half *p, int64_t i) { return __half2float(p[i]); }
+
+template <typename T> __device__ __forceinline__ void ew_store(T *p, int64_t i, typename EwTraits<T>::C v) { p[i] = static_cast<T>(v); }
+template <> __device__ __forceinline__ void ew_store<__nv_bfloat16>(__nv_bfloat16 *p, int64_t i, float v) { p[i] = __float2bfloat16_rn(v); }
+template <> __device__ __forceinline__ void ew_store<__half>(__half *p, int64_t i, float v) { p[i] = __float2half_rn(v); }
+
+struct EwParams {
+  const void *a, *b;  // b unused by unary ops
+  void *out;
+  int32_t op, ndim;
+  int64_t n;          // output elements
+  int64_t shape[kEwMaxDims];
+  int64_t a_strides[kEwMaxDims], b_strides[kEwMaxDims];  // 0 where broadcast
+  int64_t a_off, b_off;
+  int32_t contiguous;  // both inputs are row-major over the output shape: offsets are linear
+  int32_t vec;         // ... and every pointer is 16-byte aligned: 16 bytes per thread per step
+  int32_t rows;        // 1: one CTA per row of the innermost dim (no per-element index arithmetic)
+  int32_t rows_vec;    // ... with inner strides 0 or 1 and 16-byte-aligned rows
+};
+
+__device__ __forceinline__ void ew_offsets(const EwParams &p, int64_t i, int64_t &ao, int64_t &bo) {
+  if (p.contiguous) {
+    ao = p.a_off + i;
+    bo = p.b_off + i;
+    return;
+  }
+  ao = p.a_off;
+  bo = p.b_off;
+  for (int d = p.ndim - 1; d >= 0; --d) {
+    const int64_t idx = i % p.shape[d];
+    i /= p.shape[d];
+    ao += idx * p.a_strides[d];
+    bo += idx * p.b_strides[d];
+  }
+}
+
+template <typename C> __device__ __forceinline__ C unary_apply(int op, C x);
+template <> __device__ __forceinline__ float unary_apply<float>(int op, float x) {
+  return op == 0 ? -x : op == 1 ? expf(x) : op == 2 ? logf(x) : fabsf(x);
+}
+template <> __device__ __forceinline__ double unary_apply<double>(int op, double x) {
+  return op == 0 ? -x : op == 1 ? exp(x) : op == 2 ? log(x) : fabs(x);
+}
+template <> __device__ __forceinline__ int64_t unary_apply<int64_t>(int op, int64_t x) {
+  return op == 0 ? -x : (x < 0 ? -x : x);  // exp / ln are refused for integers on the host
+}
+
+template <typename C> __device__ __forceinline__ C binary_apply(int op, C x, C y) {
+  return op == 0 ? x + y : op == 1 ? x - y : op == 2 ? x * y : x / y;  // integer div is refused on the host
+}
+
+// 16 bytes of T, moved with one vector load / store.
+template <typename T> struct alignas(16) EwVec { T v[16 / sizeof(T)]; };
+
+template <typename T>
+__global__ void __launch_bounds__(256) unary_kernel(const EwParams p) {
+  using C = typename EwTraits<T>::C;
+  const T *a = static_cast<const T *>(p.a);
+  T *out = static_cast<T *>(p.out);
+  int64_t first = 0;
+  if (p.vec) {
+    constexpr int V = 16 / sizeof(T);
+    const int64_t nv = p.n / V;
+    const EwVec<T> *av = reinterpret_cast<const EwVec<T> *>(a + p.a_off);
+    EwVec<T> *ov = reinterpret_cast<EwVec<T> *>(out);
+    for (int64_t i = blockIdx.x * 256ll + threadIdx.x; i < nv; i += static_cast<int64_t>(gridDim.x) * 256) {
+      const EwVec<T> x = av[i];
+      EwVec<T> r;
+#pragma unroll
+      for (int e = 0; e < V; ++e) ew_store<T>(r.v, e, unary_apply<C>(p.op, ew_load<T>(x.v, e)));
+      ov[i] = r;
+    }
+    first = nv * V;  // the ragged tail falls through to the scalar loop
+  }
+  for (int64_t i = first + blockIdx.x * 256ll + threadIdx.x; i < p.n; i += static_cast<int64_t>(gridDim.x) * 256) {
+    int64_t ao, bo;
+    ew_offsets(p, i, ao, bo);
+    ew_store<T>(out, i, unary_apply<C>(p.op, ew_load<T>(a, ao)));
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) binary_kernel(const EwParams p) {
+  using C = typename EwTraits<T>::C;
+  const T *a = static_cast<const T *>(p.a), *b = static_cast<const T *>(p.b);
+  T *out = static_cast<T *>(p.out);
+  int64_t first = 0;
+  if (p.vec) {
+    constexpr int V = 16 / sizeof(T);
+    const int64_t nv = p.n / V;
+    const EwVec<T> *av = reinterpret_cast<const EwVec<T> *>(a + p.a_off), *bv = reinterpret_cast<const EwVec<T> *>(b + p.b_off);
+    EwVec<T> *ov = reinterpret_cast<EwVec<T> *>(out);
+    for (int64_t i = blockIdx.x * 256ll + threadIdx.x; i < nv; i += static_cast<int64_t>(gridDim.x) * 256) {
+      const EwVec<T> x = av[i], y = bv[i];
+      EwVec<T> r;
+#pragma unroll
+      for (int e = 0; e < V; ++e) ew_store<T>(r.v, e, binary_apply<C>(p.op, ew_load<T>(x.v, e), ew_load<T>(y.v, e)));
+      ov[i] = r;
+    }
+    first = nv * V;
+  }
+  for (int64_t i = first + blockIdx.x * 256ll + threadIdx.x; i < p.n; i += static_cast<int64_t>(gridDim.x) * 256) {
+    int64_t ao, bo;
+    ew_offsets(p, i, ao, bo);
+    ew_store<T>(out, i, binary_apply<C>(p.op, ew_load<T>(a, ao), ew_load<T>(b, bo)));
+  }
+}
+
+// Strided or broadcast operands with a long innermost dim: one CTA per row.
+// The row's base offsets are unravelled once; along the row each operand
+// advances by its inner stride (0 for a broadcast operand), so a bias row, a
+// per-row scalar or a narrowed window all stream at full width.
+template <typename T, bool BINARY>
+__global__ void __launch_bounds__(256) ew_rows_kernel(const EwParams p) {
+  using C = typename EwTraits<T>::C;
+  constexpr int V = 16 / sizeof(T);
+  const T *a = static_cast<const T *>(p.a), *b = static_cast<const T *>(p.b);
+  T *out = static_cast<T *>(p.out);
+  const int nd = p.ndim - 1;
+  const int64_t L = p.shape[nd], rows = p.n / L;
+  const int64_t ais = p.a_strides[nd], bis = BINARY ? p.b_strides[nd] : 0;
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    int64_t ao = p.a_off, bo = p.b_off, t = row;
+    for (int d = nd - 1; d >= 0; --d) {
+      const int64_t idx = t % p.shape[d];
+      t /= p.shape[d];
+      ao += idx * p.a_strides[d];
+      bo += idx * p.b_strides[d];
+    }
+    T *orow = out + row * L;
+    if (p.rows_vec) {
+      const C a0 = ais == 0 ? ew_load<T>(a, ao) : C(0), b0 = (BINARY && bis == 0) ? ew_load<T>(b, bo) : C(0);
+      for (int64_t x = threadIdx.x; x < L / V; x += 256) {
+        EwVec<T> xa, xb, r;
+        if (ais) xa = reinterpret_cast<const EwVec<T> *>(a + ao)[x];
+        if (BINARY && bis) xb = reinterpret_cast<const EwVec<T> *>(b + bo)[x];
+#pragma unroll
+        for (int e = 0; e < V; ++e) {
+          const C va = ais ? ew_load<T>(xa.v, e) : a0;
+          if (BINARY) ew_store<T>(r.v, e, binary_apply<C>(p.op, va, bis ? ew_load<T>(xb.v, e) : b0));
+          else ew_store<T>(r.v, e, unary_apply<C>(p.op, va));
+        }
+        reinterpret_cast<EwVec<T> *>(orow)[x] = r;
+      }
+    } else {
+      for (int64_t x = threadIdx.x; x < L; x += 256) {
+        const C va = ew_load<T>(a, ao + x * ais);
+        if (BINARY) ew_store<T>(orow, x, binary_apply<C>(p.op, va, ew_load<T>(b, bo + x * bis)));
+        else ew_store<T>(orow, x, unary_apply<C>(p.op, va));
+      }
+    }
+  }
+}
+
+// Reduction.  The host splits the input's dims into kept dims (the output's
+// index space, row-major) and reduced dims, drops extent-1 dims and merges
+// neighbours that share one stride.  op 0 sum, 1 max.
+//
+// Two thread mappings, chosen by which group holds the smallest stride:
+//   ROW  one CTA per output; its 256 threads walk the reduced extent, so a
+//        reduced innermost dim is read coalesced (16-byte loads when it is
+//        contiguous), then fold through shuffles and shared memory;
+//   COL  one thread per output, consecutive threads on consecutive kept-dim
+//        elements, each walking the reduced extent serially.
+// Either way the reduced extent can be cut into `splits` slices (gridDim.y) so
+// that few-output reductions still fill the GPU; slices write partial results
+// in the compute type to a workspace and reduce_finish_kernel combines them.
+struct ReduceOpParams {
+  const void *a;
+  void *out;       // final output (splits == 1) ...
+  void *partial;   // ... or [splits][n_out] partial results in the compute type
+  int32_t op, nkept, nred, splits;
+  int64_t n_out, n_red, chunk;  // chunk: reduced elements per slice
+  int64_t kept_shape[kEwMaxDims], kept_strides[kEwMaxDims];
+  int64_t red_shape[kEwMaxDims], red_strides[kEwMaxDims];
+  int64_t a_off;
+};
+
+template <typename C> __device__ __forceinline__ C reduce_combine(int op, C x, C y) { return op == 0 ? x + y : (y > x ? y : x); }
+
+template <typename C> __device__ __forceinline__ C reduce_identity(int op);
+template <> __device__ __forceinline__ float reduce_identity<float>(int op) { return op == 0 ? 0.0f : -INFINITY; }
+template <> __device__ __forceinline__ double reduce_identity<double>(int op) { return op == 0 ? 0.0 : -static_cast<double>(INFINITY); }
+template <> __device__ __forceinline__ int64_t reduce_identity<int64_t>(int op) { return op == 0 ? 0 : INT64_MIN; }
+
+__device__ __forceinline__ int64_t unravel(int64_t i, int nd, const int64_t *shape, const int64_t *strides) {
+  int64_t off = 0;
+  for (int d = nd - 1; d >= 0; --d) {
+    off += (i % shape[d]) * strides[d];
+    i /= shape[d];
+  }
+  return off;
+}
+
+template <typename C> __device__ __forceinline__ C shfl_down(C v, int d) { return __shfl_down_sync(0xffffffffu, v, d); }
+
+template <typename T>
+__global__ void __launch_bounds__(256) reduce_row_kernel(const ReduceOpParams p) {
+  using C = typename EwTraits<T>::C;
+  constexpr int V = 16 / sizeof(T);
+  __shared__ C part[8];
+  const T *a = static_cast<const T *>(p.a);
+  const int64_t r0 = blockIdx.y * p.chunk, r1 = min(r0 + p.chunk, p.n_red);
+  for (int64_t o = blockIdx.x; o < p.n_out; o += gridDim.x) {
+    const int64_t base = p.a_off + unravel(o, p.nkept, p.kept_shape, p.kept_strides);
+    C acc = reduce_identity<C>(p.op);
+    if (p.nred == 1 && p.red_strides[0] == 1) {
+      // a contiguous run: scalar head up to a 16-byte boundary, vector body, scalar tail
+      const T *run = a + base;
+      const int64_t mis = (reinterpret_cast<uintptr_t>(run + r0) / sizeof(T)) % V;
+      const int64_t head = min((V - mis) % V, r1 - r0);
+      const int64_t nv = (r1 - r0 - head) / V;
+      if (static_cast<int64_t>(threadIdx.x) < head) acc = reduce_combine<C>(p.op, acc, ew_load<T>(run, r0 + threadIdx.x));
+      const EwVec<T> *vec = reinterpret_cast<const EwVec<T> *>(run + r0 + head);
+      for (int64_t i = threadIdx.x; i < nv; i += 256) {
+        const EwVec<T> x = vec[i];
+#pragma unroll
+        for (int e = 0; e < V; ++e) acc = reduce_combine<C>(p.op, acc, ew_load<T>(x.v, e));
+      }
+      for (int64_t r = r0 + head + nv * V + threadIdx.x; r < r1; r += 256) acc = reduce_combine<C>(p.op, acc, ew_load<T>(run, r));
+    } else if (p.nred == 1) {
+      for (int64_t r = r0 + threadIdx.x; r < r1; r += 256) acc = reduce_combine<C>(p.op, acc, ew_load<T>(a, base + r * p.red_strides[0]));
+    } else {
+      for (int64_t r = r0 + threadIdx.x; r < r1; r += 256)
+        acc = reduce_combine<C>(p.op, acc, ew_load<T>(a, base + unravel(r, p.nred, p.red_shape, p.red_strides)));
+    }
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) acc = reduce_combine<C>(p.op, acc, shfl_down<C>(acc, d));
+    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      C total = part[0];
+      for (int w = 1; w < 8; ++w) total = reduce_combine<C>(p.op, total, part[w]);
+      if (p.splits == 1) ew_store<T>(static_cast<T *>(p.out), o, total);
+      else static_cast<C *>(p.partial)[blockIdx.y * p.n_out + o] = total;
+    }
+    __syncthreads();
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) reduce_col_kernel(const ReduceOpParams p) {
+  using C = typename EwTraits<T>::C;
+  const T *a = static_cast<const T *>(p.a);
+  const int64_t r0 = blockIdx.y * p.chunk, r1 = min(r0 + p.chunk, p.n_red);
+  for (int64_t o = blockIdx.x * 256ll + threadIdx.x; o < p.n_out; o += static_cast<int64_t>(gridDim.x) * 256) {
+    const int64_t base = p.a_off + unravel(o, p.nkept, p.kept_shape, p.kept_strides);
+    C acc = reduce_identity<C>(p.op);
+    if (p.nred == 1) {
+      const int64_t rs = p.red_strides[0];
+      for (int64_t r = r0; r < r1; ++r) acc = reduce_combine<C>(p.op, acc, ew_load<T>(a, base + r * rs));
+    } else {
+      for (int64_t r = r0; r < r1; ++r) acc = reduce_combine<C>(p.op, acc, ew_load<T>(a, base + unravel(r, p.nred, p.red_shape, p.red_strides)));
+    }
+    if (p.splits == 1) ew_store<T>(static_cast<T *>(p.out), o, acc);
+    else static_cast<C *>(p.partial)[blockIdx.y * p.n_out + o] = acc;
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) reduce_finish_kernel(const ReduceOpParams p) {
+  using C = typename EwTraits<T>::C;
+  const C *partial = static_cast<const C *>(p.partial);
+  for (int64_t o = blockIdx.x * 256ll + threadIdx.x; o < p.n_out; o += static_cast<int64_t>(gridDim.x) * 256) {
+    C acc = partial[o];
+    for (int s = 1; s < p.splits; ++s) acc = reduce_combine<C>(p.op, acc, partial[s * p.n_out + o]);
+    ew_store<T>(static_cast<T *>(p.out), o, acc);
+  }
+}
+
+}  // namespace oxm

@@ -189,6 +189,28 @@ class Tensor:
         from .backend import backend_for
         return backend_for(self.device()).batched_matmul(self, rhs)
 
+    def _be(self):
+        from .backend import backend_for
+        return backend_for(self.device())
+
+    def add(self, rhs: "Tensor") -> "Tensor":
+        return self._be().add(self, rhs)
+
+    def sub(self, rhs: "Tensor") -> "Tensor":
+        return self._be().sub(self, rhs)
+
+    def mul(self, rhs: "Tensor") -> "Tensor":
+        return self._be().mul(self, rhs)
+
+    def div(self, rhs: "Tensor") -> "Tensor":
+        return self._be().div(self, rhs)
+
+    def neg(self) -> "Tensor":
+        return self._be().neg(self)
+
+    def sum(self, axes: Sequence[int] = ()) -> "Tensor":
+        return self._be().sum(self, axes)
+
     def get_f32(self, index: Sequence[int]) -> float:
         """One element, for tests (crates/oxmera-tensor/src/tensor.rs:92-100)."""
         if not self.dtype.is_float():

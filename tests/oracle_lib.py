@@ -13,7 +13,8 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 MAX_DIMS = 8
 F32, F64, BF16, F16 = 0, 1, 6, 7
 ACC_NATIVE, ACC_F64 = 0, 1
-_NP = {F32: np.float32, F64: np.float64, BF16: np.uint16, F16: np.float16}
+I32, I64 = 2, 3
+_NP = {F32: np.float32, F64: np.float64, I32: np.int32, I64: np.int64, BF16: np.uint16, F16: np.float16}
 _SIZE = {F32: 4, F64: 8, 2: 4, 3: 8, 4: 1, 5: 1, BF16: 2, F16: 2}
 
 
@@ -51,6 +52,9 @@ class Oracle:
         self.lib.orc_batched_matmul.argtypes = [PV, PV, PV, C.c_int, C.c_int]
         self.lib.orc_check_matmul.argtypes = [PV, PV, PV, C.c_int]
         self.lib.orc_matmul_fused.argtypes = [PV, PV, PV, PV, C.c_int, C.c_int, C.c_int, C.c_int]
+        self.lib.orc_unary.argtypes = [C.c_int, PV, PV]
+        self.lib.orc_binary.argtypes = [C.c_int, PV, PV, PV]
+        self.lib.orc_reduce.argtypes = [C.c_int, PV, C.POINTER(C.c_int32), C.c_int, PV]
         self.lib.orc_broadcast_shapes.argtypes = [C.POINTER(C.c_int64), C.c_int, C.POINTER(C.c_int64), C.c_int,
                                                   C.POINTER(C.c_int64), C.POINTER(C.c_int)]
         self.lib.orc_f32_to_bf16.argtypes = [C.c_float]; self.lib.orc_f32_to_bf16.restype = C.c_uint16
@@ -93,6 +97,27 @@ class Oracle:
         st = self.lib.orc_matmul_fused(C.byref(va), C.byref(vb), C.byref(vo), C.byref(vbias) if vbias is not None else None,
                                        act, 1 if prev is not None else 0, acc, nthreads or self.threads)
         return st, out
+
+    def unary(self, op: int, a: np.ndarray, tag: int):
+        out = np.zeros(a.shape, dtype=_NP[tag])
+        va, vo = _view(a, tag), _view(out, tag)
+        return self.lib.orc_unary(op, C.byref(va), C.byref(vo)), out
+
+    def binary(self, op: int, a: np.ndarray, b: np.ndarray, tag: int):
+        try:
+            shape = np.broadcast_shapes(a.shape, b.shape)
+        except ValueError:
+            return 2, None
+        out = np.zeros(shape, dtype=_NP[tag])
+        va, vb, vo = _view(a, tag), _view(b, tag), _view(out, tag)
+        return self.lib.orc_binary(op, C.byref(va), C.byref(vb), C.byref(vo)), out
+
+    def reduce(self, op: int, a: np.ndarray, axes, tag: int):
+        ax = sorted(set(axes)) if axes else list(range(a.ndim))
+        out = np.zeros([s for d, s in enumerate(a.shape) if d not in ax], dtype=_NP[tag])
+        arr = (C.c_int32 * max(len(axes), 1))(*axes)
+        va, vo = _view(a, tag), _view(out, tag)
+        return self.lib.orc_reduce(op, C.byref(va), arr, len(axes), C.byref(vo)), out
 
     def broadcast_shapes(self, lhs, rhs):
         l = (C.c_int64 * MAX_DIMS)(*lhs)

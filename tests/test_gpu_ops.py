@@ -1,0 +1,146 @@
+"""UnaryOps, BinaryOps and ReduceOps on the device against the oracle's loops,
+through the C ABI: every dtype, strided / transposed / flipped / broadcast
+views, every reduction geometry.
+
+Tolerances: results of one arithmetic operation must match the oracle's
+correctly rounded value to 2 ulp of the dtype (device exp / log are not
+correctly rounded); sums are compared as max |x-y| / max(|y|, rms) against the
+f64-accumulated oracle with 1e-5 (f32), 1e-12 (f64), 1e-2 (bf16 / f16);
+integer results and max are exact."""
+import numpy as np
+import pytest
+
+import oxmera_b200 as ox
+from oxmera_b200 import DType, Tensor
+from tests.oracle_lib import BF16, F16, F32, F64, I32, I64
+from tests.test_gpu_parity import rel_err
+
+pytestmark = pytest.mark.gpu
+
+TAGS = {DType.F32: F32, DType.F64: F64, DType.BF16: BF16, DType.F16: F16, DType.I32: I32, DType.I64: I64}
+NPDT = {DType.F32: np.float32, DType.F64: np.float64, DType.F16: np.float16, DType.I32: np.int32, DType.I64: np.int64}
+EPS = {DType.F32: 2.0 ** -23, DType.F64: 2.0 ** -52, DType.BF16: 2.0 ** -7, DType.F16: 2.0 ** -10}
+FLOATS = [DType.F32, DType.F64, DType.BF16, DType.F16]
+INTS = [DType.I32, DType.I64]
+
+
+def host(oracle, shape, dtype, seed, positive=False):
+    if dtype in INTS:
+        n = int(np.prod(shape)) if len(shape) else 1
+        return ((np.arange(n, dtype=np.int64) * 7919 + seed) % 201 - 100).astype(NPDT[dtype]).reshape(shape)
+    if dtype == DType.F64:
+        x = oracle.fill(shape, F32, seed, 0, "normal").astype(np.float64)
+    else:
+        x = oracle.fill(shape, TAGS[dtype], seed, 0, "normal")
+    if positive:
+        x = np.abs(as_f64(x, dtype)) + 0.25
+        x = ox.f32_to_bf16_bits(x.astype(np.float32)).reshape(shape) if dtype == DType.BF16 else x.astype(NPDT[dtype])
+    return x
+
+
+def as_f64(x, dtype):
+    if dtype == DType.BF16:
+        return ox.bf16_bits_to_f32(x).reshape(x.shape).astype(np.float64)
+    return x.astype(np.float64)
+
+
+def assert_close(got, ref, dtype, ulps=2):
+    if dtype in INTS:
+        assert np.array_equal(got, ref)
+        return
+    g, r = as_f64(got, dtype), as_f64(ref, dtype)
+    assert g.shape == r.shape
+    assert np.all(np.abs(g - r) <= ulps * EPS[dtype] * np.maximum(np.abs(r), 1e-30) + 1e-300), float(np.max(np.abs(g - r)))
+
+
+def views(h, t):
+    """The same views on the host array and the device tensor."""
+    yield h, t
+    if h.ndim >= 2:
+        perm = list(range(h.ndim))[::-1]
+        yield h.transpose(perm), t.permute(perm)
+        yield h[::-1], t.flip(0)
+        yield h[:, 1:], t.narrow(1, 1, h.shape[1] - 1)
+
+
+@pytest.mark.parametrize("dtype", FLOATS + INTS, ids=lambda d: d.name)
+def test_unary_ops(backend, oracle, dtype):
+    ops = [(0, backend.neg, False), (3, backend.abs, False)]
+    if dtype in FLOATS:
+        ops += [(1, backend.exp, False), (2, backend.ln, True)]
+    for op, fn, positive in ops:
+        h = host(oracle, (37, 5, 19), dtype, 10 + op, positive)
+        t = Tensor.from_host(h, h.shape, dtype, backend)
+        for hv, tv in views(h, t):
+            out = fn(tv)
+            assert out.shape == hv.shape and out.layout().is_contiguous()
+            st, ref = oracle.unary(op, hv, TAGS[dtype])
+            assert st == 0
+            assert_close(out.to_host(), ref, dtype)
+    if dtype in INTS:
+        with pytest.raises(ox.UnsupportedDType):
+            backend.exp(Tensor.from_host(host(oracle, (4,), dtype, 1), (4,), dtype, backend))
+
+
+@pytest.mark.parametrize("dtype", FLOATS + INTS, ids=lambda d: d.name)
+def test_binary_ops_broadcast(backend, oracle, dtype):
+    fns = [backend.add, backend.sub, backend.mul] + ([backend.div] if dtype in FLOATS else [])
+    cases = [((64, 33), (64, 33)), ((2, 3), (3,)), ((2, 1), (1, 3)), ((), (2, 3)), ((4, 1, 5), (3, 1)), ((130, 1, 17), (1, 9, 1)),
+             ((2, 0), (1, 1))]
+    for ls, rs in cases:
+        a, b = host(oracle, ls, dtype, 20), host(oracle, rs, dtype, 21, positive=dtype in FLOATS)
+        ta, tb = Tensor.from_host(a, ls, dtype, backend), Tensor.from_host(b, rs, dtype, backend)
+        for op, fn in enumerate(fns):
+            out = fn(ta, tb)
+            st, ref = oracle.binary(op, a, b, TAGS[dtype])
+            assert st == 0 and out.shape == ref.shape
+            assert_close(out.to_host(), ref, dtype, ulps=1)
+    # views on both sides, through the tensor surface (TensorOps)
+    a, b = host(oracle, (24, 40), dtype, 22), host(oracle, (40, 24), dtype, 23)
+    ta, tb = Tensor.from_host(a, a.shape, dtype, backend), Tensor.from_host(b, b.shape, dtype, backend)
+    got = ta.add(tb.permute([1, 0]).flip(0))
+    assert_close(got.to_host(), oracle.binary(0, a, b.T[::-1], TAGS[dtype])[1], dtype, ulps=1)
+    if dtype in INTS:
+        with pytest.raises(ox.UnsupportedDType):
+            backend.div(ta, ta)
+
+
+def test_binary_errors(backend):
+    f = lambda shape, dt=DType.F32: Tensor.empty(shape, dt, backend)
+    with pytest.raises(ox.BroadcastIncompatible):
+        backend.add(f((2, 3)), f((2, 4)))
+    with pytest.raises(ox.DTypeMismatch):
+        backend.mul(f((2, 3)), f((2, 3), DType.F64))
+    with pytest.raises(ox.UnsupportedDType):
+        backend.add(f((2, 3), DType.U8), f((2, 3), DType.U8))
+
+
+@pytest.mark.parametrize("dtype", FLOATS + INTS, ids=lambda d: d.name)
+def test_reductions(backend, oracle, dtype):
+    tol = {DType.F32: 1e-5, DType.F64: 1e-12, DType.BF16: 1e-2, DType.F16: 1e-2}
+    shapes = [((6, 7, 50), [[], [0], [2], [0, 2], [1], [0, 1, 2], [1, 2]]),
+              ((3, 70000), [[1], [0], []]),       # a long row: one CTA per output
+              ((300, 4, 200), [[0], [1], [0, 1]])]  # many outputs over kept inner dims: one thread per output
+    for shape, axes_list in shapes:
+        h = host(oracle, shape, dtype, 30)
+        t = Tensor.from_host(h, shape, dtype, backend)
+        pairs = [(h, t)]
+        if len(shape) == 3:
+            pairs.append((h.transpose(2, 0, 1), t.permute([2, 0, 1])))
+        for hv, tv in pairs:
+            for axes in axes_list:
+                for op, fn in ((0, backend.sum), (1, backend.max)):
+                    out = fn(tv, axes)
+                    st, ref = oracle.reduce(op, hv, axes, TAGS[dtype])
+                    assert st == 0 and out.shape == ref.shape
+                    if dtype in INTS or op == 1:
+                        assert np.array_equal(out.to_host(), ref), (shape, axes, op)
+                    else:
+                        exact = as_f64(hv, dtype).sum(axis=tuple(axes) if axes else None)
+                        assert rel_err(as_f64(out.to_host(), dtype), np.asarray(exact)) <= tol[dtype], (shape, axes)
+    e = Tensor.from_host(np.zeros((3, 0), np.float32), (3, 0), DType.F32, backend)
+    assert backend.sum(e, [1]).to_host().tolist() == [0.0, 0.0, 0.0]
+    with pytest.raises(ox.NotImplementedOp):
+        backend.max(e, [1])
+    with pytest.raises(ox.IndexOutOfBounds):
+        backend.sum(e, [2])

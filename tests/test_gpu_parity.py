@@ -112,8 +112,6 @@ def test_unregistered_device_is_backend_unavailable(backend):
         ox.B200Backend(63)
     assert ox.backend_for(ox.Device.cuda(0)) is backend
     assert backend.name() == "b200-tcgen05"
-    with pytest.raises(ox.NotImplementedOp):
-        backend.add(None, None)
 
 
 @pytest.mark.parametrize("kernel", ["simt", "tcgen05"])
