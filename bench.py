@@ -119,7 +119,7 @@ def cpu_reference(workload_key: str, steps: int, warmup: int, target_s: float = 
     describes it) on a row slab of every product of the workload, all host
     threads.  The slab is sized so one step takes about `target_s` seconds."""
     from tests.oracle_lib import ACC_NATIVE, BF16, F16, F32, Oracle
-    tag = {DType.F32: F32, DType.BF16: BF16, DType.F16: F16}
+    tag = {DType.F32: F32, DType.BF16: BF16, DType.F16: F16, DType.F8E4M3: 8, DType.F8E5M2: 9}
     w = WORKLOADS[workload_key]
     o = Oracle()
     cores = o.threads
@@ -197,7 +197,7 @@ def run_ours(args):
     for g in w.gemms:
         a, b, rg = gemm_views(w, g, tensors, rank, world)
         oshape = tuple(broadcast_shapes(a.shape[:-2], b.shape[:-2])) + (a.shape[-2], b.shape[-1])
-        out = Tensor.empty(oshape, w.dtype, be)  # pooled: allocated once, outside the timed region
+        out = Tensor.empty(oshape, w.result_dtype, be)  # pooled: allocated once, outside the timed region
         work.append((g, a, b, out))
     be.synchronize()
 
@@ -241,6 +241,8 @@ def run_ours(args):
     peak = peaks["bf16_tflops"] if burst else peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"])
     if w.dtype == DType.F32:
         peak = peak / 2.0  # tf32 runs at half the bf16 rate; the 3-term split spends 3 MMA flops per useful one
+    if w.dtype in (DType.F8E4M3, DType.F8E5M2):
+        peak = peak * 2.0  # no fp8 figure was measured: twice the measured bf16 rate, as the nominal rates relate
     launches = counts1["tcgen05"] - counts0["tcgen05"]
     per_gpu_tflops = shard_flops(w, rank, world) * args.steps / (ms_local * 1e-3) / 1e12
     achieved = grp.min_over_ranks(per_gpu_tflops)  # the slowest GPU's own rate
@@ -253,14 +255,15 @@ def run_ours(args):
                        + ("; halved for tf32" if w.dtype == DType.F32 else ""),
         "frac_of_burst": achieved / (peaks["bf16_tflops"] / (2.0 if w.dtype == DType.F32 else 1.0)),
         "avg_launch_ms": ms_local / max(1, launches) if launches else None,
-        "frac_of_nominal_2250": achieved / (2250.0 if w.dtype != DType.F32 else 1125.0),
+        "frac_of_nominal_2250": achieved / ({DType.F32: 1125.0, DType.F8E4M3: 4500.0, DType.F8E5M2: 4500.0}.get(w.dtype, 2250.0)),
         "note": None if w.dtype != DType.F32 else "f32 runs as three TF32 MMA terms: the tensor pipe executes 3x the algorithmic flops counted here",
     }
 
     # ---- end to end: host buffers in, host buffer out, every step ----
     e2e = None
-    if not args.no_e2e:
-        npdt = {DType.F32: np.float32, DType.BF16: np.uint16, DType.F16: np.float16}[w.dtype]
+    if not args.no_e2e and w.result_dtype == w.dtype:
+        npdt = {DType.F32: np.float32, DType.BF16: np.uint16, DType.F16: np.float16, DType.F8E4M3: np.uint8,
+                DType.F8E5M2: np.uint8}[w.dtype]
         host = {}
         for name, t in tensors.items():
             buf = be.pinned_empty(t.shape, npdt)
@@ -318,7 +321,7 @@ def run_ours(args):
             "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e,
             "gpu_launches": counts1["total"] - counts0["total"],
             "clocks": clocks,
-            "percent_of_dense_peak": 100.0 * tflops / world / (2250.0 if w.dtype != DType.F32 else 1125.0),
+            "percent_of_dense_peak": 100.0 * tflops / world / ({DType.F32: 1125.0, DType.F8E4M3: 4500.0, DType.F8E5M2: 4500.0}.get(w.dtype, 2250.0)),
         }
         print(json.dumps(line), flush=True)
     be.close()

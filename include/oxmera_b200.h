@@ -30,7 +30,9 @@ extern "C" {
  * backend adds to that non_exhaustive enum. */
 typedef enum {
   OXM_F32 = 0, OXM_F64 = 1, OXM_I32 = 2, OXM_I64 = 3, OXM_U8 = 4, OXM_BOOL = 5,
-  OXM_BF16 = 6, OXM_F16 = 7
+  OXM_BF16 = 6, OXM_F16 = 7,
+  OXM_F8E4M3 = 8, /* 1-4-3, finite only, max 448 (the "fn" encoding) */
+  OXM_F8E5M2 = 9  /* 1-5-2, IEEE-like */
 } oxm_dtype;
 
 /* Status codes.  1..9 map one-to-one onto the variants of oxmera's Error
@@ -121,7 +123,10 @@ int oxm_host_free(void *ptr);
  * (crates/oxmera-core/src/shape.rs:49-55), trailing two dims as above.
  *
  * dtypes: f32 (fp32 result; 3xTF32 tensor-core path or an FFMA tile kernel),
- * bf16 and f16 (fp32 accumulate, result rounded to the operand dtype). */
+ * bf16 and f16 (fp32 accumulate, result rounded to the operand dtype), and
+ * fp8 e4m3 / e5m2 (fp32 accumulate; `out` may be the operands' fp8 type —
+ * rounded to nearest even, saturating to the largest finite value — or bf16,
+ * f16 or f32, the one place an output may be wider than its operands). */
 int oxm_matmul(oxm_ctx *ctx, const oxm_view *a, const oxm_view *b, const oxm_view *out);
 int oxm_batched_matmul(oxm_ctx *ctx, const oxm_view *a, const oxm_view *b, const oxm_view *out);
 

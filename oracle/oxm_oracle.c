@@ -73,6 +73,44 @@ float orc_f16_to_f32(uint16_t h) {
   return bits_f32(sign | ((exp + 112u) << 23) | (man << 13));
 }
 
+/* fp8 e4m3 (bias 7, no infinities, 0x7f = NaN, max 0x7e = 448) and e5m2
+ * (bias 15, IEEE-like, max finite 0x7b = 57344). */
+float orc_fp8_to_f32(uint8_t b, int32_t dtype) {
+  const int mbits = dtype == ORC_F8E4M3 ? 3 : 2, bias = dtype == ORC_F8E4M3 ? 7 : 15;
+  const int sign = b >> 7, exp = (b & 0x7f) >> mbits, man = b & ((1 << mbits) - 1);
+  float v;
+  if (dtype == ORC_F8E4M3 && (b & 0x7f) == 0x7f) return bits_f32(0x7fc00000u);
+  if (dtype == ORC_F8E5M2 && exp == 31) v = man ? bits_f32(0x7fc00000u) : bits_f32(0x7f800000u);
+  else if (exp == 0) v = ldexpf((float)man, 1 - bias - mbits);
+  else v = ldexpf((float)((1 << mbits) | man), exp - bias - mbits);
+  return sign ? -v : v;
+}
+
+uint8_t orc_f32_to_fp8(float x, int32_t dtype) {
+  const int mbits = dtype == ORC_F8E4M3 ? 3 : 2, bias = dtype == ORC_F8E4M3 ? 7 : 15;
+  const uint8_t max_code = dtype == ORC_F8E4M3 ? 0x7e : 0x7b;
+  const uint32_t u = f32_bits(x);
+  const uint8_t sign = (uint8_t)((u >> 24) & 0x80u);
+  const uint32_t absu = u & 0x7fffffffu;
+  if (absu > 0x7f800000u) return (uint8_t)(sign | 0x7f);  /* NaN */
+  if (absu == 0) return sign;
+  int32_t exp = (int32_t)(absu >> 23) - 127;
+  uint32_t man = (absu & 0x7fffffu) | 0x800000u;
+  if ((absu >> 23) == 0) return sign;                     /* f32 subnormals are far below fp8's range */
+  if (exp > 20) return (uint8_t)(sign | max_code);        /* inf and anything huge saturate */
+  const int emin = 1 - bias;
+  int shift = 23 - mbits + (exp < emin ? emin - exp : 0);
+  if (shift > 25) return sign;                            /* below half of the smallest subnormal */
+  uint32_t kept = man >> shift;
+  const uint32_t rem = man & ((1u << shift) - 1u), half = 1u << (shift - 1);
+  if (rem > half || (rem == half && (kept & 1u))) kept++;
+  uint32_t code;
+  if (exp < emin) code = kept;                            /* a carry lands on the smallest normal */
+  else code = ((uint32_t)(exp + bias) << mbits) + (kept - (1u << mbits));
+  if (code > max_code) code = max_code;
+  return (uint8_t)(sign | code);
+}
+
 /* ------------------------------------------------------------------ */
 /* shapes                                                               */
 /* ------------------------------------------------------------------ */
@@ -98,7 +136,9 @@ int orc_broadcast_shapes(const int64_t *lhs, int lhs_ndim, const int64_t *rhs,
   return ORC_OK;
 }
 
-static int is_matmul_dtype(int32_t d) { return d == ORC_F32 || d == ORC_BF16 || d == ORC_F16; }
+static int is_matmul_dtype(int32_t d) {
+  return d == ORC_F32 || d == ORC_BF16 || d == ORC_F16 || d == ORC_F8E4M3 || d == ORC_F8E5M2;
+}
 static int is_out_dtype(int32_t d) { return is_matmul_dtype(d) || d == ORC_F64; }
 
 int orc_check_matmul(const orc_view *a, const orc_view *b, const orc_view *out, int batched) {
@@ -136,7 +176,8 @@ static inline float load_as_f32(const void *base, int32_t dtype, int64_t idx) {
   switch (dtype) {
     case ORC_F32: return ((const float *)base)[idx];
     case ORC_BF16: return orc_bf16_to_f32(((const uint16_t *)base)[idx]);
-    default: return orc_f16_to_f32(((const uint16_t *)base)[idx]);
+    case ORC_F16: return orc_f16_to_f32(((const uint16_t *)base)[idx]);
+    default: return orc_fp8_to_f32(((const uint8_t *)base)[idx], dtype);
   }
 }
 
@@ -145,7 +186,8 @@ static inline void store_from_f64(void *base, int32_t dtype, int64_t idx, double
     case ORC_F64: ((double *)base)[idx] = v; break;
     case ORC_F32: ((float *)base)[idx] = (float)v; break;
     case ORC_BF16: ((uint16_t *)base)[idx] = orc_f32_to_bf16((float)v); break;
-    default: ((uint16_t *)base)[idx] = orc_f32_to_f16((float)v); break;
+    case ORC_F16: ((uint16_t *)base)[idx] = orc_f32_to_f16((float)v); break;
+    default: ((uint8_t *)base)[idx] = orc_f32_to_fp8((float)v, dtype); break;
   }
 }
 
@@ -211,6 +253,12 @@ ROW_KERNEL(row_bf16_native, uint16_t, orc_bf16_to_f32, float, activate_f32)
 ROW_KERNEL(row_bf16_f64, uint16_t, orc_bf16_to_f32, double, activate_f64)
 ROW_KERNEL(row_f16_native, uint16_t, orc_f16_to_f32, float, activate_f32)
 ROW_KERNEL(row_f16_f64, uint16_t, orc_f16_to_f32, double, activate_f64)
+#define E4M3(x) orc_fp8_to_f32((x), ORC_F8E4M3)
+#define E5M2(x) orc_fp8_to_f32((x), ORC_F8E5M2)
+ROW_KERNEL(row_e4m3_native, uint8_t, E4M3, float, activate_f32)
+ROW_KERNEL(row_e4m3_f64, uint8_t, E4M3, double, activate_f64)
+ROW_KERNEL(row_e5m2_native, uint8_t, E5M2, float, activate_f32)
+ROW_KERNEL(row_e5m2_f64, uint8_t, E5M2, double, activate_f64)
 
 static void *mm_worker(void *arg) {
   mm_job *J = (mm_job *)arg;
@@ -250,9 +298,15 @@ static void *mm_worker(void *arg) {
       } else if (b->dtype == ORC_BF16) {
         const uint16_t *bp = (const uint16_t *)b->base + b_off;
         (f64 ? row_bf16_f64 : row_bf16_native)(arow, bp, b_ks, b_ns, J->n, J->k, o->base, o->dtype, o_off, o_ns, &J->epi);
-      } else {
+      } else if (b->dtype == ORC_F16) {
         const uint16_t *bp = (const uint16_t *)b->base + b_off;
         (f64 ? row_f16_f64 : row_f16_native)(arow, bp, b_ks, b_ns, J->n, J->k, o->base, o->dtype, o_off, o_ns, &J->epi);
+      } else if (b->dtype == ORC_F8E4M3) {
+        const uint8_t *bp = (const uint8_t *)b->base + b_off;
+        (f64 ? row_e4m3_f64 : row_e4m3_native)(arow, bp, b_ks, b_ns, J->n, J->k, o->base, o->dtype, o_off, o_ns, &J->epi);
+      } else {
+        const uint8_t *bp = (const uint8_t *)b->base + b_off;
+        (f64 ? row_e5m2_f64 : row_e5m2_native)(arow, bp, b_ks, b_ns, J->n, J->k, o->base, o->dtype, o_off, o_ns, &J->epi);
       }
     }
   }
@@ -474,7 +528,8 @@ static void *fill_worker(void *arg) {
     float f = (float)v;
     if (F->dtype == ORC_F32) ((float *)F->dst)[i] = f;
     else if (F->dtype == ORC_BF16) ((uint16_t *)F->dst)[i] = orc_f32_to_bf16(f);
-    else ((uint16_t *)F->dst)[i] = orc_f32_to_f16(f);
+    else if (F->dtype == ORC_F16) ((uint16_t *)F->dst)[i] = orc_f32_to_f16(f);
+    else ((uint8_t *)F->dst)[i] = orc_f32_to_fp8(f, F->dtype);
   }
   return NULL;
 }

@@ -38,7 +38,9 @@ extern "C" {
 /* dtype tags: identical numbering to include/oxmera_b200.h */
 enum {
   ORC_F32 = 0, ORC_F64 = 1, ORC_I32 = 2, ORC_I64 = 3, ORC_U8 = 4, ORC_BOOL = 5,
-  ORC_BF16 = 6, ORC_F16 = 7
+  ORC_BF16 = 6, ORC_F16 = 7,
+  ORC_F8E4M3 = 8, /* finite-only 1-4-3 ("fn"), max 448 */
+  ORC_F8E5M2 = 9  /* IEEE-like 1-5-2 */
 };
 
 /* status codes: identical numbering to include/oxmera_b200.h */
@@ -115,6 +117,9 @@ uint16_t orc_f32_to_bf16(float x);
 float orc_bf16_to_f32(uint16_t h);
 uint16_t orc_f32_to_f16(float x);
 float orc_f16_to_f32(uint16_t h);
+/* fp8: nearest even, saturating to the largest finite value (NaN stays NaN). */
+uint8_t orc_f32_to_fp8(float x, int32_t dtype);
+float orc_fp8_to_f32(uint8_t b, int32_t dtype);
 
 /* Counter-based synthetic data: element i of stream (seed, stream) depends
  * only on (seed, stream, i), so any slice can be generated anywhere.

@@ -78,6 +78,12 @@ class B200Backend:
         """Rank >= 2; leading dims broadcast by NumPy rules."""
         return self._mm(lhs, rhs, batched=True)
 
+    def matmul_as(self, lhs: Tensor, rhs: Tensor, out_dtype: DType) -> Tensor:
+        """Batched product of fp8 operands kept in a wider dtype (bf16, f16 or f32)."""
+        bshape = broadcast_shapes(lhs.shape[:-2], rhs.shape[:-2])
+        out = Tensor.empty(tuple(bshape) + (lhs.shape[-2], rhs.shape[-1]), out_dtype, self)
+        return self.matmul_into(lhs, rhs, out, batched=True)
+
     def matmul_into(self, lhs: Tensor, rhs: Tensor, out: Tensor, batched: bool = True) -> Tensor:
         """Write the product through `out`'s layout (a shard writing into a
         window of its parent).  `out` must not alias the operands."""

@@ -1,36 +1,41 @@
 """Build the CUDA library in-tree: oxmera_b200/liboxmera_b200.so.
 
-`python -m oxmera_b200.build [--force]`.  nvcc cross-compiles for sm_100a
-without a GPU.  This is the same command line a Rust build.rs would run.
+`python -m oxmera_b200.build [--force] [-v]`.  nvcc cross-compiles for sm_100a
+without a GPU.  The translation units compile in parallel and are linked into
+one shared library; a Rust build.rs would run the same command lines.
 """
 from __future__ import annotations
 
+import glob
 import os
 import subprocess
 import sys
+from concurrent.futures import ThreadPoolExecutor
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
-SOURCES = ["api.cu"]
-HEADERS = ["gemm_tcgen05.cuh", "kernels_simt.cuh", "ptx.cuh", os.path.join("..", "..", "include", "oxmera_b200.h")]
+OBJ = os.path.join(HERE, "build")
+SOURCES = ["api.cu", "gemm_f16_ak.cu", "gemm_f16_am.cu", "gemm_f8_ak.cu", "gemm_f8_am.cu", "gemm_tf32.cu"]
 OUT = os.path.join(HERE, "liboxmera_b200.so")
 
-NVCC_FLAGS = [
-    "-gencode", "arch=compute_100a,code=sm_100a",
-    "-O3", "-std=c++17", "-lineinfo",
-    "-shared", "-Xcompiler", "-fPIC",
-]
+NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC"]
 
 
-def nvcc_command(extra=()):
-    return ["nvcc", *NVCC_FLAGS, *extra, "-o", OUT, *[os.path.join(CSRC, s) for s in SOURCES]]
+def compile_command(src: str, verbose: bool = False):
+    obj = os.path.join(OBJ, os.path.splitext(src)[0] + ".o")
+    return ["nvcc", *NVCC_FLAGS, *(("-Xptxas", "-v") if verbose else ()), "-c", os.path.join(CSRC, src), "-o", obj], obj
+
+
+def link_command(objs):
+    return ["nvcc", "-gencode", "arch=compute_100a,code=sm_100a", "-shared", "-o", OUT, *objs]
 
 
 def is_stale() -> bool:
     if not os.path.exists(OUT):
         return True
     built = os.path.getmtime(OUT)
-    deps = [os.path.join(CSRC, s) for s in SOURCES + HEADERS]
+    deps = glob.glob(os.path.join(CSRC, "*.cu")) + glob.glob(os.path.join(CSRC, "*.cuh")) + \
+        [os.path.join(HERE, "..", "include", "oxmera_b200.h")]
     return any(os.path.getmtime(d) > built for d in deps)
 
 
@@ -38,12 +43,22 @@ def build_library(force: bool = False, verbose: bool = False) -> str:
     """Compile when the library is missing or older than its sources."""
     if not force and not is_stale():
         return OUT
-    cmd = nvcc_command(("-Xptxas", "-v") if verbose else ())
-    res = subprocess.run(cmd, capture_output=True, text=True)
+    os.makedirs(OBJ, exist_ok=True)
+
+    def run(src):
+        cmd, obj = compile_command(src, verbose)
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if res.returncode != 0:
+            raise RuntimeError(f"nvcc failed ({res.returncode}):\n{' '.join(cmd)}\n{res.stdout}\n{res.stderr}")
+        if verbose:
+            sys.stderr.write(res.stderr)
+        return obj
+
+    with ThreadPoolExecutor(max_workers=min(len(SOURCES), os.cpu_count() or 1)) as pool:
+        objs = list(pool.map(run, SOURCES))
+    res = subprocess.run(link_command(objs), capture_output=True, text=True)
     if res.returncode != 0:
-        raise RuntimeError(f"nvcc failed ({res.returncode}):\n{' '.join(cmd)}\n{res.stdout}\n{res.stderr}")
-    if verbose:
-        sys.stderr.write(res.stderr)
+        raise RuntimeError(f"link failed:\n{res.stdout}\n{res.stderr}")
     return OUT
 
 

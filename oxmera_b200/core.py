@@ -12,9 +12,9 @@ from typing import Sequence, Tuple
 
 
 class DType(enum.IntEnum):
-    """Element types.  0..5 follow crates/oxmera-core/src/dtype.rs:9-22; BF16 and
-    F16 are the two variants the B200 backend adds.  Values equal the C ABI's
-    oxm_dtype."""
+    """Element types.  0..5 follow crates/oxmera-core/src/dtype.rs:9-22; BF16,
+    F16 and the two fp8 encodings are the variants the B200 backend adds.
+    Values equal the C ABI's oxm_dtype."""
 
     F32 = 0
     F64 = 1
@@ -24,12 +24,14 @@ class DType(enum.IntEnum):
     Bool = 5
     BF16 = 6
     F16 = 7
+    F8E4M3 = 8  # 1-4-3, finite only, max 448
+    F8E5M2 = 9  # 1-5-2, IEEE-like
 
     def size_in_bytes(self) -> int:
-        return {0: 4, 1: 8, 2: 4, 3: 8, 4: 1, 5: 1, 6: 2, 7: 2}[int(self)]
+        return {0: 4, 1: 8, 2: 4, 3: 8, 4: 1, 5: 1, 6: 2, 7: 2, 8: 1, 9: 1}[int(self)]
 
     def is_float(self) -> bool:
-        return self in (DType.F32, DType.F64, DType.BF16, DType.F16)
+        return self in (DType.F32, DType.F64, DType.BF16, DType.F16, DType.F8E4M3, DType.F8E5M2)
 
 
 @dataclass(frozen=True)

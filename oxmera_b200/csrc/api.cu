@@ -17,7 +17,7 @@
 #include <vector>
 
 #include "elementwise.cuh"
-#include "gemm_tcgen05.cuh"
+#include "gemm_instances.cuh"
 #include "kernels_simt.cuh"
 
 namespace {
@@ -86,13 +86,14 @@ int dtype_size(int dt) {
     case OXM_F64: case OXM_I64: return 8;
     case OXM_U8: case OXM_BOOL: return 1;
     case OXM_BF16: case OXM_F16: return 2;
+    case OXM_F8E4M3: case OXM_F8E5M2: return 1;
     default: return 0;
   }
 }
 
 const char *dtype_name(int dt) {
-  static const char *names[] = {"F32", "F64", "I32", "I64", "U8", "Bool", "BF16", "F16"};
-  return (dt >= 0 && dt < 8) ? names[dt] : "?";
+  static const char *names[] = {"F32", "F64", "I32", "I64", "U8", "Bool", "BF16", "F16", "F8E4M3", "F8E5M2"};
+  return (dt >= 0 && dt < 10) ? names[dt] : "?";
 }
 
 std::string shape_str(const oxm_view *v) {
@@ -104,7 +105,8 @@ std::string shape_str(const oxm_view *v) {
   return s + "]";
 }
 
-bool is_matmul_dtype(int dt) { return dt == OXM_F32 || dt == OXM_BF16 || dt == OXM_F16; }
+bool is_fp8(int dt) { return dt == OXM_F8E4M3 || dt == OXM_F8E5M2; }
+bool is_matmul_dtype(int dt) { return dt == OXM_F32 || dt == OXM_BF16 || dt == OXM_F16 || is_fp8(dt); }
 
 // The checks of MatmulOps::matmul, in the order the reference's errors imply:
 // rank, device, dtype, inner dimension, batch broadcast, output shape.
@@ -136,7 +138,9 @@ int validate(const oxm_ctx *ctx, const oxm_view *a, const oxm_view *b, const oxm
     return fail(OXM_DTYPE_MISMATCH, "dtype mismatch: expected %s, got %s in %s", dtype_name(a->dtype), dtype_name(b->dtype), op);
   if (!is_matmul_dtype(a->dtype))
     return fail(OXM_UNSUPPORTED_DTYPE, "dtype %s is not supported by %s", dtype_name(a->dtype), op);
-  if (out->dtype != a->dtype)
+  // fp8 products may be kept in a wider type; everything else keeps the operands' dtype
+  const bool widened = is_fp8(a->dtype) && (out->dtype == OXM_BF16 || out->dtype == OXM_F16 || out->dtype == OXM_F32);
+  if (out->dtype != a->dtype && !widened)
     return fail(OXM_DTYPE_MISMATCH, "dtype mismatch: expected %s, got %s in %s (output)", dtype_name(a->dtype), dtype_name(out->dtype), op);
   const int64_t m = a->shape[a->ndim - 2], k = a->shape[a->ndim - 1];
   const int64_t kb = b->shape[b->ndim - 2], n = b->shape[b->ndim - 1];
@@ -168,7 +172,8 @@ int validate(const oxm_ctx *ctx, const oxm_view *a, const oxm_view *b, const oxm
 // A matmul problem with coalesced batch dims.  B is held as rows = N, so both
 // operands are "rows x K" matrices.
 struct Problem {
-  int dtype, elt;
+  int dtype, elt;          // operands
+  int out_dtype, oelt;     // output (differs from the operands' only for fp8 products)
   int64_t M, N, K;
   int nbd;
   int64_t bdims[OXM_MAX_DIMS];
@@ -185,6 +190,8 @@ Problem normalise(const oxm_view *a, const oxm_view *b, const oxm_view *out) {
   Problem P{};
   P.dtype = a->dtype;
   P.elt = dtype_size(a->dtype);
+  P.out_dtype = out->dtype;
+  P.oelt = dtype_size(out->dtype);
   P.M = a->shape[a->ndim - 2];
   P.K = a->shape[a->ndim - 1];
   P.N = b->shape[b->ndim - 1];
@@ -239,7 +246,7 @@ int launch_simt(oxm_ctx *ctx, const Problem &P) {
   if (P.M > INT32_MAX || P.N > INT32_MAX || P.K > INT32_MAX) return fail(OXM_NOT_IMPLEMENTED, "matmul is not implemented for extents above 2^31");
   SimtParams p{};
   p.a = P.a; p.b = P.b; p.out = P.o;
-  p.dtype = P.dtype; p.out_dtype = P.dtype;
+  p.dtype = P.dtype; p.out_dtype = P.out_dtype;
   p.M = (int32_t)P.M; p.N = (int32_t)P.N; p.K = (int32_t)P.K;
   p.tiles_m = (int32_t)((P.M + 63) / 64); p.tiles_n = (int32_t)((P.N + 63) / 64);
   p.a_off = P.a_off; p.b_off = P.b_off; p.o_off = P.o_off;
@@ -285,7 +292,7 @@ int grow(oxm_ctx *ctx, Workspace &w, size_t bytes) {
 
 // Can the TMA engine address this operand in place?  Fills `s` when it can.
 bool stage_direct(const Problem &P, bool is_b, Staged &s) {
-  if (P.elt != 2) return false;
+  if (P.elt != 2 && P.elt != 1) return false;  // f32 is always packed (TF32 split)
   const void *base = is_b ? P.b : P.a;
   const int64_t off = is_b ? P.b_off : P.a_off;
   const int64_t rows = is_b ? P.N : P.M, K = P.K;
@@ -335,7 +342,7 @@ int stage_packed(oxm_ctx *ctx, const Problem &P, bool is_b, int slot, Staged &s)
   const int64_t rs = is_b ? P.b_rs : P.a_rs, ks = is_b ? P.b_ks : P.a_ks;
   const int64_t *bs = is_b ? P.b_bs : P.a_bs;
   const bool split = P.elt == 4;
-  const int64_t Kp = split ? (P.K + 31) / 32 * 32 : (P.K + 7) / 8 * 8;
+  const int64_t Kp = split ? (P.K + 31) / 32 * 32 : (P.K + 15) / 16 * 16;  // rows stay 16-byte multiples
   const int64_t row_elems = split ? 3 * Kp : Kp;
   PackParams pp{};
   pp.src = is_b ? P.b : P.a;
@@ -382,9 +389,10 @@ int stage_packed(oxm_ctx *ctx, const Problem &P, bool is_b, int slot, Staged &s)
 }
 
 int make_map(oxm_ctx *ctx, CUtensorMap *tm, const Staged &s, int dtype, int elt, int box_rows_kmajor, int box_k) {
-  const CUtensorMapDataType dt = dtype == OXM_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
-                                : dtype == OXM_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
-                                                    : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  const CUtensorMapDataType dt = dtype == OXM_F32    ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                 : dtype == OXM_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                 : dtype == OXM_F16  ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                                     : CU_TENSOR_MAP_DATA_TYPE_UINT8;
   const cuuint32_t inner_box = (cuuint32_t)(kStageKBytes / elt);
   cuuint64_t dims[3];
   cuuint32_t box[3];
@@ -408,38 +416,16 @@ int make_map(oxm_ctx *ctx, CUtensorMap *tm, const Staged &s, int dtype, int elt,
   return OXM_OK;
 }
 
-template <int BN, int STAGES, int A_MN, int B_MN, int TF32, int PAIR>
-int launch_instance(oxm_ctx *ctx, const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap &tmC,
-                    const GemmParams &p, int grid) {
-  using L = GemmSmem<BN, STAGES, PAIR>;
-  auto kern = gemm_tcgen05_kernel<BN, STAGES, A_MN, B_MN, TF32, PAIR>;
-  static_assert(L::kDynamic <= 232448, "shared memory budget of one SM");
-  CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic));
-  cudaLaunchConfig_t cfg{};
-  cfg.gridDim = dim3((unsigned)grid, 1, 1);
-  cfg.blockDim = dim3(gemm_threads(BN), 1, 1);
-  cfg.dynamicSmemBytes = L::kDynamic;
-  cfg.stream = ctx->stream;
-  cudaLaunchAttribute attr[1];
-  if (PAIR) {
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr; cfg.numAttrs = 1;
-  }
-  CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmC, p));
-  snprintf(ctx->last_kernel, sizeof(ctx->last_kernel), "gemm_tcgen05_%s_bn%d_s%d_%c%c_%s", TF32 ? "tf32x3" : "f16", BN,
-           STAGES, A_MN ? 'm' : 'k', B_MN ? 'n' : 'k', PAIR ? "pair" : "1cta");
+// Launch one instance of the tensor-core GEMM (defined in the gemm_*.cu units).
+int launch_gemm(oxm_ctx *ctx, int kind, bool a_mn, bool b_mn, int bn, int pair, const CUtensorMap &tmA, const CUtensorMap &tmB,
+                const CUtensorMap &tmC, const GemmParams &p, int grid) {
+  const GemmLaunch l{bn, pair, b_mn, grid, ctx->stream};
+  const GemmLaunchFn fn = kind == 1 ? launch_gemm_tf32
+                          : kind == 2 ? (a_mn ? launch_gemm_f8_am : launch_gemm_f8_ak)
+                                      : (a_mn ? launch_gemm_f16_am : launch_gemm_f16_ak);
+  cudaError_t e = fn(l, tmA, tmB, tmC, p, ctx->last_kernel, sizeof(ctx->last_kernel));
+  if (e != cudaSuccess) return fail(OXM_CUDA_ERROR, "launch of %s failed: %s", ctx->last_kernel, cudaGetErrorString(e));
   return OXM_OK;
-}
-
-template <int BN, int STAGES, int PAIR>
-int launch_majors(oxm_ctx *ctx, bool tf32, bool a_mn, bool b_mn, const CUtensorMap &tmA, const CUtensorMap &tmB,
-                  const CUtensorMap &tmC, const GemmParams &p, int grid) {
-  if (tf32) return launch_instance<BN, STAGES, 0, 0, 1, PAIR>(ctx, tmA, tmB, tmC, p, grid);
-  if (!a_mn && !b_mn) return launch_instance<BN, STAGES, 0, 0, 0, PAIR>(ctx, tmA, tmB, tmC, p, grid);
-  if (!a_mn && b_mn) return launch_instance<BN, STAGES, 0, 1, 0, PAIR>(ctx, tmA, tmB, tmC, p, grid);
-  if (a_mn && !b_mn) return launch_instance<BN, STAGES, 1, 0, 0, PAIR>(ctx, tmA, tmB, tmC, p, grid);
-  return launch_instance<BN, STAGES, 1, 1, 0, PAIR>(ctx, tmA, tmB, tmC, p, grid);
 }
 
 // Store tensor map over the output: {N, M, batch} in boxes of 128 bytes x 32
@@ -477,7 +463,7 @@ constexpr int kMaxChainKb = 3 * 1024 / 32;
 // waves of tiles over the SMs (or SM pairs) at each shape's measured relative
 // rate, a per-tile cost where the epilogue is exposed, and the price of the
 // reduction pass when the contraction is split to fill an under-occupied grid.
-TileChoice choose_tiles(const oxm_ctx *ctx, const Problem &P, bool tf32, int32_t num_kb) {
+TileChoice choose_tiles(const oxm_ctx *ctx, const Problem &P, bool tf32, int32_t num_kb, int min_b_rows) {
   struct Cand { int bn, pair; double us_per_kb, us_per_tile; };
   // microseconds per pipeline stage of one tile at the ~1.45 GHz the power cap sustains
   static const Cand cands[] = {{512, 1, 0.706 / 1.03, 2.0}, {256, 1, 0.353, 0.3}, {256, 0, 0.353 / 0.93, 0.3},
@@ -489,11 +475,13 @@ TileChoice choose_tiles(const oxm_ctx *ctx, const Problem &P, bool tf32, int32_t
   // A forced pairing that no candidate of the forced width has is dropped on the second pass.
   for (int pass = 0; pass < 2 && best_t == 1e300; ++pass)
   for (const Cand &c : cands) {
-    if (ctx->opt_tile_n && c.bn != ctx->opt_tile_n) continue;
+    // an N-major fp8 B tile is staged in boxes of 128 columns: each CTA must own at least one
+    if ((c.pair ? c.bn / 2 : c.bn) < min_b_rows) continue;
+    if (ctx->opt_tile_n && c.bn != ctx->opt_tile_n && ctx->opt_tile_n >= min_b_rows) continue;
     if (pass == 0 && ctx->opt_cta_pair >= 0 && c.pair != ctx->opt_cta_pair) continue;
     if (!ctx->opt_tile_n) {
       if (c.pair && P.M <= kTileM) continue;          // nothing for the second CTA to do
-      if (c.bn > 64 && P.N <= c.bn / 2) continue;     // at least half of the tile is outside the matrix
+      if (c.bn > std::max(64, min_b_rows) && P.N <= c.bn / 2) continue;  // at least half of the tile is outside the matrix
     }
     const int tm = kTileM * (c.pair ? 2 : 1);
     const int64_t tiles = ((P.M + tm - 1) / tm) * ((P.N + c.bn - 1) / c.bn) * P.nbatch;
@@ -519,6 +507,7 @@ int launch_tcgen05(oxm_ctx *ctx, const Problem &P) {
   if (P.M >= (1ll << 31) || P.N >= (1ll << 31) || P.K >= (1ll << 29) || P.nbatch >= (1ll << 31))
     return fail(OXM_NOT_IMPLEMENTED, "matmul is not implemented for extents above 2^31");
   const bool tf32 = P.elt == 4;
+  const int kind = tf32 ? 1 : (P.elt == 1 ? 2 : 0);
   Staged sa{}, sb{};
   if (!stage_direct(P, false, sa)) {
     int st = stage_packed(ctx, P, false, 0, sa);
@@ -532,7 +521,7 @@ int launch_tcgen05(oxm_ctx *ctx, const Problem &P) {
   const int bk = kStageKBytes / P.elt;
 
   const int32_t num_kb_all = (int32_t)((Kst + bk - 1) / bk);
-  const TileChoice choice = choose_tiles(ctx, P, tf32, num_kb_all);
+  const TileChoice choice = choose_tiles(ctx, P, tf32, num_kb_all, (kind == 2 && sb.mn_major) ? 128 : 0);
   const int bn = choice.bn, pair = choice.pair;
   const int tm = kTileM * (pair ? 2 : 1);
 
@@ -544,19 +533,21 @@ int launch_tcgen05(oxm_ctx *ctx, const Problem &P) {
   p.nbatch = (int32_t)P.nbatch;
   p.num_tiles = (int64_t)p.tiles_m * p.tiles_n * P.nbatch;
   p.nbd = P.nbd;
-  bool vec = P.o_cs == 1 && (reinterpret_cast<uintptr_t>(P.o) + P.o_off * P.elt) % 16 == 0 && (P.o_rs * P.elt) % 16 == 0;
+  bool vec = P.o_cs == 1 && !is_fp8(P.out_dtype) && (reinterpret_cast<uintptr_t>(P.o) + P.o_off * P.oelt) % 16 == 0 &&
+             (P.o_rs * P.oelt) % 16 == 0;
   for (int d = 0; d < P.nbd; ++d) {
     p.bdims[d] = (int32_t)P.bdims[d];
     p.a_bmul[d] = sa.bmul[d];
     p.b_bmul[d] = sb.bmul[d];
     p.o_bstride[d] = P.o_bs[d];
-    if ((P.o_bs[d] * P.elt) % 16) vec = false;
+    if ((P.o_bs[d] * P.oelt) % 16) vec = false;
   }
-  p.out = static_cast<uint8_t *>(P.o) + P.o_off * P.elt;
+  p.out = static_cast<uint8_t *>(P.o) + P.o_off * P.oelt;
   p.out_rs = P.o_rs; p.out_cs = P.o_cs;
-  p.out_dtype = P.dtype;
+  p.out_dtype = P.out_dtype;
   p.out_vec = vec ? 1 : 0;
-  const uint32_t fmt = tf32 ? 2u : (P.dtype == OXM_BF16 ? 1u : 0u);
+  // format codes of the instruction descriptor: f16 0 / bf16 1 / tf32 2; in the f8f6f4 kind e4m3 0 / e5m2 1
+  const uint32_t fmt = tf32 ? 2u : (P.dtype == OXM_BF16 || P.dtype == OXM_F8E5M2) ? 1u : 0u;
   p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((sa.mn_major ? 1u : 0u) << 15) | ((sb.mn_major ? 1u : 0u) << 16) |
             ((uint32_t)(std::min(bn, 256) >> 3) << 17) | ((uint32_t)(tm >> 4) << 24);
   p.status = ctx->status_dev;
@@ -582,7 +573,7 @@ int launch_tcgen05(oxm_ctx *ctx, const Problem &P) {
     if (st2) return st2;
     rp.ws = static_cast<const float *>(ctx->pack_ws[2].ptr);
     rp.out = P.o;
-    rp.out_dtype = P.dtype;
+    rp.out_dtype = P.out_dtype;
     rp.epi = P.epi;  // the reduction, not the GEMM, finishes split products
     p.epi = Epilogue{};
     rp.splits = p.splits; rp.M = p.M; rp.N = p.N;
@@ -615,10 +606,11 @@ int launch_tcgen05(oxm_ctx *ctx, const Problem &P) {
   if (p.splits > 1) {
     // fp32 partial sums from 16-bit operands take the strided-store epilogue
     p.out_tma = tf32 && make_out_map(ctx, &tmC, p.out, OXM_F32, 4, P.M, P.N, P.nbatch * p.splits, P.N, P.M * P.N) ? 1 : 0;
-  } else if (P.o_cs == 1 || P.N == 1) {
+  } else if ((P.o_cs == 1 || P.N == 1) && (tf32 ? P.out_dtype == OXM_F32 : (P.out_dtype == OXM_BF16 || P.out_dtype == OXM_F16))) {
+    // the staged epilogue writes 4-byte chunks for the f32 path and 2-byte chunks otherwise
     bool fold = true;
     for (int d = 0; d + 1 < P.nbd; ++d) fold = fold && P.o_bs[d] == P.o_bs[d + 1] * P.bdims[d + 1];
-    p.out_tma = fold && make_out_map(ctx, &tmC, p.out, P.dtype, P.elt, P.M, P.N, P.nbatch, P.o_rs,
+    p.out_tma = fold && make_out_map(ctx, &tmC, p.out, P.out_dtype, P.oelt, P.M, P.N, P.nbatch, P.o_rs,
                                      P.nbd ? P.o_bs[P.nbd - 1] : 0) ? 1 : 0;
   }
   if (ctx->opt_tma_store == 0) p.out_tma = 0;
@@ -627,15 +619,7 @@ int launch_tcgen05(oxm_ctx *ctx, const Problem &P) {
   if (pair) grid = 2 * (int)std::min<int64_t>(p.num_tiles, ctx->num_sms / 2);
   else grid = (int)std::min<int64_t>(p.num_tiles, ctx->num_sms);
 
-  if (!pair) {
-    if (bn == 256) st = launch_majors<256, 4, 0>(ctx, tf32, sa.mn_major, sb.mn_major, tmA, tmB, tmC, p, grid);
-    else if (bn == 128) st = launch_majors<128, 6, 0>(ctx, tf32, sa.mn_major, sb.mn_major, tmA, tmB, tmC, p, grid);
-    else st = launch_majors<64, 8, 0>(ctx, tf32, sa.mn_major, sb.mn_major, tmA, tmB, tmC, p, grid);
-  } else {
-    if (bn == 512) st = launch_majors<512, 4, 1>(ctx, tf32, sa.mn_major, sb.mn_major, tmA, tmB, tmC, p, grid);
-    else if (bn == 256) st = launch_majors<256, 6, 1>(ctx, tf32, sa.mn_major, sb.mn_major, tmA, tmB, tmC, p, grid);
-    else st = launch_majors<128, 8, 1>(ctx, tf32, sa.mn_major, sb.mn_major, tmA, tmB, tmC, p, grid);
-  }
+  st = launch_gemm(ctx, kind, sa.mn_major, sb.mn_major, bn, pair, tmA, tmB, tmC, p, grid);
   if (st) return st;
   ctx->launches[0]++; ctx->launches[1]++;
   if (p.splits > 1) {
@@ -897,6 +881,7 @@ int oxm_batched_matmul_host(oxm_ctx *ctx, const oxm_view *a, const oxm_view *b, 
   oxm_view dv[3];
   int64_t lo[3], hi[3], numel[3];
   const int elt = dtype_size(a->dtype);
+  if (out->dtype != a->dtype) return fail(OXM_NOT_IMPLEMENTED, "matmul is not implemented for a widened fp8 output through the host entry point");
   {
     std::lock_guard<std::mutex> lock(ctx->mu);
     for (int i = 0; i < 3; ++i) {
@@ -1664,10 +1649,7 @@ extern "C" int oxm_matmul_f32_noalloc(oxm_ctx *ctx, const oxm_view *a, const oxm
   if (st) return st;
   const int grid = pair ? 2 * (int)std::min<int64_t>(p.num_tiles, ctx->num_sms / 2)
                         : (int)std::min<int64_t>(p.num_tiles, ctx->num_sms);
-  if (pair) st = launch_instance<256, 6, 0, 0, 1, 1>(ctx, tmA, tmB, tmC, p, grid);
-  else if (bn == 256) st = launch_instance<256, 4, 0, 0, 1, 0>(ctx, tmA, tmB, tmC, p, grid);
-  else if (bn == 128) st = launch_instance<128, 6, 0, 0, 1, 0>(ctx, tmA, tmB, tmC, p, grid);
-  else st = launch_instance<64, 8, 0, 0, 1, 0>(ctx, tmA, tmB, tmC, p, grid);
+  st = launch_gemm(ctx, 1, false, false, bn, pair, tmA, tmB, tmC, p, grid);
   if (st) return st;
   ctx->launches[0]++; ctx->launches[1]++;
   if (splits > 1) {

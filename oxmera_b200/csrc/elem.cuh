@@ -4,22 +4,27 @@
 
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
+#include <cuda_fp8.h>
 
 #include <cstdint>
 
 namespace oxm {
 
-// dtype tags are the C ABI's: 0 f32, 6 bf16, 7 f16.
+// dtype tags are the C ABI's: 0 f32, 6 bf16, 7 f16, 8 fp8 e4m3, 9 fp8 e5m2.
+// fp8 stores round to nearest even and saturate to the largest finite value.
 __device__ __forceinline__ float load_elem(const void *base, int dtype, int64_t idx) {
   if (dtype == 0) return static_cast<const float *>(base)[idx];
   if (dtype == 6) return __bfloat162float(static_cast<const __nv_bfloat16 *>(base)[idx]);
-  return __half2float(static_cast<const __half *>(base)[idx]);
+  if (dtype == 7) return __half2float(static_cast<const __half *>(base)[idx]);
+  const __nv_fp8_storage_t raw = static_cast<const __nv_fp8_storage_t *>(base)[idx];
+  return __half2float(__half(__nv_cvt_fp8_to_halfraw(raw, dtype == 8 ? __NV_E4M3 : __NV_E5M2)));
 }
 
 __device__ __forceinline__ void store_elem(void *base, int dtype, int64_t idx, float v) {
   if (dtype == 0) static_cast<float *>(base)[idx] = v;
   else if (dtype == 6) static_cast<__nv_bfloat16 *>(base)[idx] = __float2bfloat16_rn(v);
-  else static_cast<__half *>(base)[idx] = __float2half_rn(v);
+  else if (dtype == 7) static_cast<__half *>(base)[idx] = __float2half_rn(v);
+  else static_cast<__nv_fp8_storage_t *>(base)[idx] = __nv_cvt_float_to_fp8(v, __NV_SATFINITE, dtype == 8 ? __NV_E4M3 : __NV_E5M2);
 }
 
 // What happens to a dot product r of column `col` before it is stored:

@@ -51,7 +51,7 @@ struct GemmParams {
   int64_t o_bstride[kMaxBatchDims];  // elements
   void *out;
   int64_t out_rs, out_cs;  // elements
-  int32_t out_dtype;       // 0 f32, 6 bf16, 7 f16
+  int32_t out_dtype;       // 0 f32, 6 bf16, 7 f16, 8 / 9 fp8
   int32_t out_vec;         // rows may be written with 16-byte stores
   int32_t out_tma;         // the output is described by the store tensor map
   uint32_t idesc;
@@ -117,22 +117,6 @@ __device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, cons
   }
 }
 
-// Self-test of the bounded wait: one thread waits on a barrier that nothing
-// will ever arrive on.  The wait must give up after `limit_ns`, record
-// OXM_TIMEOUT in the status word and let the kernel return normally.
-__global__ void bounded_wait_selftest_kernel(uint32_t *status, uint64_t limit_ns, uint32_t *gave_up) {
-  __shared__ uint64_t bar;
-  __shared__ int abort_flag;
-  if (threadIdx.x == 0) {
-    abort_flag = 0;
-    ptx::mbar_init(ptx::smem_u32(&bar), 1);
-    ptx::fence_barrier_init();
-    WaitCtx wc{&abort_flag, status, limit_ns};
-    const bool ok = bounded_wait(ptx::smem_u32(&bar), 0, wc);
-    *gave_up = ok ? 0u : 1u;
-  }
-}
-
 struct TileCoord {
   int32_t m_blk, n_blk;
   int32_t a_batch, b_batch;
@@ -174,15 +158,15 @@ __device__ __forceinline__ TileCoord decode_tile(const GemmParams &p, int64_t ti
   return c;
 }
 
-template <int BN, int STAGES, int A_MN, int B_MN, int TF32, int PAIR>
+template <int BN, int STAGES, int A_MN, int B_MN, int KIND, int PAIR>
 __global__ void __launch_bounds__(gemm_threads(BN), 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
-  static_assert(!(TF32 && (A_MN || B_MN)), "the tf32 path stages K-major operands only");
+  static_assert(!(KIND == 1 && (A_MN || B_MN)), "the tf32 path stages K-major operands only");
   static_assert(BN % 64 == 0 && BN >= 64 && BN <= 512, "tile width");
   static_assert(BN <= 256 || PAIR, "tiles wider than one MMA need the CTA pair");
   using L = GemmSmem<BN, STAGES, PAIR>;
-  constexpr int ELT = TF32 ? 4 : 2;
+  constexpr int ELT = KIND == 1 ? 4 : KIND == 2 ? 1 : 2;  // operand bytes per element
   constexpr int BK = kStageKBytes / ELT;   // contraction elements per stage
   constexpr int BOXW = kStageKBytes / ELT; // elements along MN in one MN-major box
   constexpr int MMAS = kStageKBytes / kMmaKBytes;
@@ -348,7 +332,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           for (int j = 0; j < MMAS; ++j) {
 #pragma unroll
             for (int sub = 0; sub < NSUB; ++sub) {
-              ptx::umma<PAIR, TF32>(d_tmem + sub * SUBN, adesc + static_cast<uint64_t>(j * A_ADV),
+              ptx::umma<PAIR, KIND>(d_tmem + sub * SUBN, adesc + static_cast<uint64_t>(j * A_ADV),
                                     bdesc + static_cast<uint64_t>(j * B_ADV + sub * ((SUBC * kStageKBytes) >> 4)),
                                     p.idesc, (kb | j) != 0 ? 1u : 0u);
             }
@@ -376,7 +360,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     // ---------------- epilogue: TMEM -> registers -> global ----------------
     const uint32_t q = warp & 3u;  // the TMEM lane quarter this warp may read
     const uint32_t stage_smem = base + L::kStagingOffset + (warp - 2u) * L::kStagingTile;
-    const int esz = p.out_dtype == 0 ? 4 : 2;
+    const int esz = p.out_dtype == 0 ? 4 : (p.out_dtype >= 8 ? 1 : 2);
     uint32_t as = 0, aph = 0;
     for (int64_t tile = tile_first; tile < p.num_tiles; tile += tile_stride) {
       const TileCoord tc = decode_tile(p, tile);
@@ -420,9 +404,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             if (col0 + i < p.N) {
               const float f = __uint_as_float(v[i]);
               const int64_t e = static_cast<int64_t>(col0 + i) * p.out_cs;
-              if (p.out_dtype == 0) reinterpret_cast<float *>(rowp)[e] = f;
-              else if (p.out_dtype == 6) reinterpret_cast<__nv_bfloat16 *>(rowp)[e] = __float2bfloat16_rn(f);
-              else reinterpret_cast<__half *>(rowp)[e] = __float2half_rn(f);
+              if constexpr (KIND == 2) {
+                store_elem(rowp, p.out_dtype, e, f);  // fp8 operands: the output may be fp8 or wider
+              } else {
+                if (p.out_dtype == 0) reinterpret_cast<float *>(rowp)[e] = f;
+                else if (p.out_dtype == 6) reinterpret_cast<__nv_bfloat16 *>(rowp)[e] = __float2bfloat16_rn(f);
+                else reinterpret_cast<__half *>(rowp)[e] = __float2half_rn(f);
+              }
             }
           }
         }
@@ -484,7 +472,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           }
         }
         if (p.out_tma) {
-          if constexpr (TF32) {
+          if constexpr (KIND == 1) {
 #pragma unroll
             for (int i = 0; i < NLD; ++i) {
               uint4 piece[8];

@@ -9,10 +9,28 @@
 #include <cstdint>
 
 #include "elem.cuh"
+#include "gemm_tcgen05.cuh"
 
 namespace oxm {
 
 constexpr int kSimtMaxBatchDims = 6;
+
+// Self-test of the bounded wait: one thread waits on a barrier that nothing
+// will ever arrive on.  The wait must give up after `limit_ns`, record
+// OXM_TIMEOUT in the status word and let the kernel return normally.
+__global__ void bounded_wait_selftest_kernel(uint32_t *status, uint64_t limit_ns, uint32_t *gave_up) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    ptx::mbar_init(ptx::smem_u32(&bar), 1);
+    ptx::fence_barrier_init();
+    WaitCtx wc{&abort_flag, status, limit_ns};
+    const bool ok = bounded_wait(ptx::smem_u32(&bar), 0, wc);
+    *gave_up = ok ? 0u : 1u;
+  }
+}
+
 
 // ---------------------------------------------------------------------------
 // FFMA tile GEMM.  64x64 output tile per 256-thread CTA, 4x4 per thread, the
@@ -132,7 +150,7 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const SimtParams p) {
 struct PackParams {
   const void *src;
   void *dst;
-  int32_t elt;        // bytes per element: 2 or 4
+  int32_t elt;        // bytes per element: 1, 2 or 4
   int32_t mode;       // 0 copy, 1 tf32 split (A side), 2 tf32 split (B side)
   int32_t rows, K, Kp;   // Kp: padded K of the SOURCE blocks (multiple of 32 in split mode)
   int64_t dst_row_elems; // elements per destination row (Kp, or 3*Kp in split mode)
@@ -174,8 +192,9 @@ __global__ void __launch_bounds__(256) pack_kernel(const PackParams p) {
     uint32_t v = 0;
     if (gr < p.rows && gk < p.K) {
       const int64_t idx = src_off + gr * p.src_rs + gk * p.src_ks;
-      v = p.elt == 4 ? static_cast<const uint32_t *>(p.src)[idx]
-                     : static_cast<uint32_t>(static_cast<const uint16_t *>(p.src)[idx]);
+      v = p.elt == 4   ? static_cast<const uint32_t *>(p.src)[idx]
+          : p.elt == 2 ? static_cast<uint32_t>(static_cast<const uint16_t *>(p.src)[idx])
+                       : static_cast<uint32_t>(static_cast<const uint8_t *>(p.src)[idx]);
     }
     tile[rr][kk] = v;
   }
@@ -189,7 +208,8 @@ __global__ void __launch_bounds__(256) pack_kernel(const PackParams p) {
     if (p.mode == 0) {
       const int64_t o = dst_batch + static_cast<int64_t>(gr) * p.dst_row_elems + gk;
       if (p.elt == 4) static_cast<uint32_t *>(p.dst)[o] = v;
-      else static_cast<uint16_t *>(p.dst)[o] = static_cast<uint16_t>(v);
+      else if (p.elt == 2) static_cast<uint16_t *>(p.dst)[o] = static_cast<uint16_t>(v);
+      else static_cast<uint8_t *>(p.dst)[o] = static_cast<uint8_t>(v);
     } else {
       const float xv = __uint_as_float(v);
       float hi = tf32_round(xv);

@@ -154,33 +154,27 @@ __device__ __forceinline__ void tc_fence_after() {
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 }
 
-// D[tmem] (+)= A[smem] * B[smem].  TF32 selects kind::tf32, else kind::f16
-// (f16 and bf16 share it; the instruction descriptor names the format).
-template <int PAIR, int TF32>
+// D[tmem] (+)= A[smem] * B[smem].  KIND 0: kind::f16 (f16 and bf16; the
+// instruction descriptor names the format), 1: kind::tf32, 2: kind::f8f6f4
+// (here: e4m3 / e5m2, one byte per element).
+#define OXM_UMMA(GROUP, KINDSTR)                                                                     \
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"                                   \
+               "tcgen05.mma.cta_group::" GROUP ".kind::" KINDSTR " [%0], %1, %2, %3, p;\n\t}"        \
+               ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory")
+template <int PAIR, int KIND>
 __device__ __forceinline__ void umma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
                                      uint32_t idesc, uint32_t accumulate) {
   if constexpr (PAIR) {
-    if constexpr (TF32) {
-      asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                   "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
-                   ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
-    } else {
-      asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                   "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-                   ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
-    }
+    if constexpr (KIND == 1) OXM_UMMA("2", "tf32");
+    else if constexpr (KIND == 2) OXM_UMMA("2", "f8f6f4");
+    else OXM_UMMA("2", "f16");
   } else {
-    if constexpr (TF32) {
-      asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                   "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
-                   ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
-    } else {
-      asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                   "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-                   ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
-    }
+    if constexpr (KIND == 1) OXM_UMMA("1", "tf32");
+    else if constexpr (KIND == 2) OXM_UMMA("1", "f8f6f4");
+    else OXM_UMMA("1", "f16");
   }
 }
+#undef OXM_UMMA
 
 // Arrive on `bar` (this CTA) once every MMA issued so far by this thread has finished.
 __device__ __forceinline__ void umma_commit(uint32_t bar) {

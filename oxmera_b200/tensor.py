@@ -17,7 +17,8 @@ from .core import (DType, Device, Layout, ShapeMismatch, OxmeraError, Unsupporte
                    contiguous_strides, numel)
 
 _NP_OF = {DType.F32: np.float32, DType.F64: np.float64, DType.I32: np.int32, DType.I64: np.int64,
-          DType.U8: np.uint8, DType.Bool: np.bool_, DType.BF16: np.uint16, DType.F16: np.float16}
+          DType.U8: np.uint8, DType.Bool: np.bool_, DType.BF16: np.uint16, DType.F16: np.float16,
+          DType.F8E4M3: np.uint8, DType.F8E5M2: np.uint8}
 
 
 def f32_to_bf16_bits(x: np.ndarray) -> np.ndarray:

@@ -46,6 +46,11 @@ class Workload:
     seed: int
     tensors: Tuple[TensorSpec, ...]
     gemms: Tuple[GemmSpec, ...]
+    out_dtype: Optional[DType] = None  # fp8 products may be kept wider than their operands
+
+    @property
+    def result_dtype(self) -> DType:
+        return self.out_dtype or self.dtype
 
     def spec(self, name: str) -> TensorSpec:
         return next(t for t in self.tensors if t.name == name)
@@ -68,11 +73,11 @@ class Workload:
 
     def algorithmic_bytes(self) -> int:
         """Every unique operand element read once, every output element written once."""
-        esz = self.dtype.size_in_bytes()
+        esz, osz = self.dtype.size_in_bytes(), self.result_dtype.size_in_bytes()
         total = 0
         for g in self.gemms:
             a, b, o = self.gemm_shapes(g)
-            total += (numel(a) + numel(b) + numel(o)) * esz
+            total += (numel(a) + numel(b)) * esz + numel(o) * osz
         return total
 
 
@@ -108,6 +113,12 @@ WORKLOADS: Dict[str, Workload] = {
         (GemmSpec("Y", "X", None, "W", (1, 0), 0),          # Y  = X . W^T
          GemmSpec("dX", "dY", None, "W", None, 0),          # dX = dY . W
          GemmSpec("dW", "dY", (1, 0), "X", None, 1))),      # dW = dY^T . X   (rows of dY^T = columns of dY)
+    # beyond the reference's configurations: the same square product at the next tensor-core rate
+    "c3f8": Workload(
+        "c3f8", "fp8 e4m3 8192^3, A row-major, B column-major, N(0,1), fp32 accumulate, bf16 out, seed 2",
+        DType.F8E4M3, 2,
+        (_t("A", (8192, 8192), "normal", 1.0, 0), _t("Bt", (8192, 8192), "normal", 1.0, 1)),
+        (GemmSpec("C", "A", None, "Bt", (1, 0), 0),), DType.BF16),
 }
 
 
@@ -116,7 +127,8 @@ def scaled(w: Workload, factor: int) -> Workload:
     (tests: oracle-sized versions of the large configurations)."""
     shr = lambda s: tuple(max(64, d // factor) if d > 64 else d for d in s)
     return Workload(w.key + f"/{factor}", w.title + f" (extents / {factor})", w.dtype, w.seed,
-                    tuple(TensorSpec(t.name, shr(t.shape), t.dist, t.scale, t.stream) for t in w.tensors), w.gemms)
+                    tuple(TensorSpec(t.name, shr(t.shape), t.dist, t.scale, t.stream) for t in w.tensors), w.gemms,
+                    w.out_dtype)
 
 
 Fill = Callable[[TensorSpec, DType, int], Tensor]

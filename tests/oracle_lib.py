@@ -12,10 +12,12 @@ import numpy as np
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 MAX_DIMS = 8
 F32, F64, BF16, F16 = 0, 1, 6, 7
+F8E4M3, F8E5M2 = 8, 9
 ACC_NATIVE, ACC_F64 = 0, 1
 I32, I64 = 2, 3
-_NP = {F32: np.float32, F64: np.float64, I32: np.int32, I64: np.int64, BF16: np.uint16, F16: np.float16}
-_SIZE = {F32: 4, F64: 8, 2: 4, 3: 8, 4: 1, 5: 1, BF16: 2, F16: 2}
+_NP = {F32: np.float32, F64: np.float64, I32: np.int32, I64: np.int64, BF16: np.uint16, F16: np.float16,
+       F8E4M3: np.uint8, F8E5M2: np.uint8}
+_SIZE = {F32: 4, F64: 8, 2: 4, 3: 8, 4: 1, 5: 1, BF16: 2, F16: 2, F8E4M3: 1, F8E5M2: 1}
 
 
 class OView(C.Structure):
@@ -61,6 +63,8 @@ class Oracle:
         self.lib.orc_bf16_to_f32.argtypes = [C.c_uint16]; self.lib.orc_bf16_to_f32.restype = C.c_float
         self.lib.orc_f32_to_f16.argtypes = [C.c_float]; self.lib.orc_f32_to_f16.restype = C.c_uint16
         self.lib.orc_f16_to_f32.argtypes = [C.c_uint16]; self.lib.orc_f16_to_f32.restype = C.c_float
+        self.lib.orc_f32_to_fp8.argtypes = [C.c_float, C.c_int32]; self.lib.orc_f32_to_fp8.restype = C.c_uint8
+        self.lib.orc_fp8_to_f32.argtypes = [C.c_uint8, C.c_int32]; self.lib.orc_fp8_to_f32.restype = C.c_float
         self.lib.orc_fill.argtypes = [C.c_void_p, C.c_int32, C.c_int64, C.c_uint64, C.c_uint64, C.c_int, C.c_double, C.c_int]
         self.lib.orc_fill.restype = None
         self.threads = os.cpu_count() or 1
@@ -132,6 +136,10 @@ class Oracle:
         out = np.empty(shape, dtype=_NP[tag])
         self.lib.orc_fill(out.ctypes.data, tag, out.size, seed, stream, 0 if dist == "uniform" else 1, scale, self.threads)
         return out
+
+    def fp8_to_f32(self, bits: np.ndarray, tag: int) -> np.ndarray:
+        table = np.array([self.lib.orc_fp8_to_f32(i, tag) for i in range(256)], np.float32)
+        return table[bits]
 
     def bf16_to_f32(self, bits: np.ndarray) -> np.ndarray:
         return (bits.astype(np.uint32) << 16).view(np.float32)
