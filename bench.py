@@ -39,7 +39,7 @@ from oxmera_b200.workloads import WORKLOADS, device_fill, gemm_views, materialis
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the tcgen05 GEMM
 # on each workload, from the ncu captures summarised under profiles/.
-NCU_TRAFFIC_BYTES = {"c3": 990_657_280}  # profiles/gemm_tcgen05_pair512_c3_bf16_8192.md
+NCU_TRAFFIC_BYTES = {"c3": 971_092_480, "c3f8": 460_873_216}  # the 256x512 pair kernel on c3 (summary of the capture under profiles/)
 
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 

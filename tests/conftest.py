@@ -10,6 +10,16 @@ if ROOT not in sys.path:
 
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a B200 GPU (run with -m gpu)")
+    # The C-ABI library is built in-tree; compile it when it is not there yet
+    # (nvcc cross-compiles for sm_100a without a GPU).  A missing nvcc is not
+    # hidden: the tests that load the library then fail loudly.
+    from oxmera_b200 import capi
+    if not os.path.exists(capi.library_path()):
+        try:
+            from oxmera_b200.build import build_library
+            build_library()
+        except Exception as e:  # reported by the tests that need the library
+            sys.stderr.write(f"could not build {capi.LIB_NAME}: {e}\n")
 
 
 @pytest.fixture(scope="session")

@@ -378,6 +378,27 @@ def test_host_entry_point_pipeline_matches_the_single_shot(backend, oracle):
         assert rel_err(to_f64(outs[0][sample], DType.BF16), oracle_ref(oracle, a_s, b_s, DType.BF16)) <= 1e-2
 
 
+def test_sharded_host_matmul_across_devices(backend, oracle):
+    """One backend per visible GPU, one host thread each (needs two or more GPUs)."""
+    import ctypes as C
+    from oxmera_b200 import capi
+    n = C.c_int(0)
+    capi.load().oxm_device_count(C.byref(n))
+    if n.value < 2:
+        pytest.skip("one GPU visible")
+    world = min(n.value, 4)
+    backends = [backend] + [ox.B200Backend(i) for i in range(1, world)]
+    try:
+        a = fill(oracle, (world * 2, 300, 264), DType.BF16, 83, 0)
+        b = fill(oracle, (264, 520), DType.BF16, 83, 1)
+        assert np.array_equal(ox.sharded_matmul_host(backends, a, b, DType.BF16), backend.matmul_host(a, b, DType.BF16))
+        rows = fill(oracle, (1024, 264), DType.BF16, 84, 0)
+        assert np.array_equal(ox.sharded_matmul_host(backends, rows, b, DType.BF16), backend.matmul_host(rows, b, DType.BF16))
+    finally:
+        for be in backends[1:]:
+            be.close()
+
+
 def test_sharded_host_matmul_matches_single_device(backend, oracle):
     """The collective-free sharding driver, with two shards on one device."""
     a = fill(oracle, (4, 96, 64), DType.BF16, 81, 0)
