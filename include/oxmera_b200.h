@@ -247,8 +247,9 @@ int oxm_selftest_bounded_wait(oxm_ctx *ctx, int64_t limit_ms);
 int oxm_set_option(oxm_ctx *ctx, const char *key, int64_t value);
 int oxm_get_option(oxm_ctx *ctx, const char *key, int64_t *value);
 
-/* Counters since context creation: kernels launched by this library, split by
- * kind.  index 0 total, 1 tcgen05 gemm, 2 simt gemm, 3 pack. */
+/* Counters since context creation: kernels launched by this library.  index 0
+ * total, 1 tensor-core GEMM, 2 FFMA GEMM, 3 auxiliary kernels of a product
+ * (operand pack, split-K reduction, strided copy). */
 int oxm_launch_counts(oxm_ctx *ctx, int64_t counts[4]);
 /* Name of the compute kernel the last matmul on this context selected. */
 const char *oxm_last_kernel(oxm_ctx *ctx);

@@ -84,3 +84,28 @@ def test_shard_ranges_and_plan():
     assert ox.shard_plan((32, 2048, 4096), (4096, 11008), 8)[0] == "batch"
     assert ox.shard_plan((8192, 8192), (8192, 8192), 8)[0] == "rows"
     assert ox.shard_plan((2, 64, 32), (32, 48), 4)[0] == "rows"  # fewer batch entries than ranks
+
+
+def test_a_failing_shard_surfaces_as_the_callers_error():
+    """One host thread per device; a shard that fails (here: a device whose
+    backend raises) must end the whole call with that typed error, not a hang
+    and not a partial result."""
+    import numpy as np
+    import oxmera_b200 as ox
+
+    class Healthy:
+        def matmul_host(self, a, b, dtype, out=None):
+            return np.matmul(a.astype(np.float32), b.astype(np.float32))
+
+    class Broken:
+        def matmul_host(self, a, b, dtype, out=None):
+            raise ox.BackendFault(10, "matmul: CudaError: injected on the host")
+
+    a, b = np.ones((4, 8, 16), np.float32), np.ones((16, 8), np.float32)
+    got = ox.sharded_matmul_host([Healthy(), Healthy()], a, b, ox.DType.F32)
+    assert got.shape == (4, 8, 8) and np.all(got == 16.0)
+    with pytest.raises(ox.BackendFault) as e:
+        ox.sharded_matmul_host([Healthy(), Broken(), Healthy()], a, b, ox.DType.F32)
+    assert "injected" in str(e.value)
+    with pytest.raises(ox.BroadcastIncompatible):  # a typed error raised before any shard starts
+        ox.sharded_matmul_host([Healthy()], np.ones((2, 3, 4, 5), np.float32), np.ones((3, 1, 5, 6), np.float32), ox.DType.F32)

@@ -378,6 +378,36 @@ def test_host_entry_point_pipeline_matches_the_single_shot(backend, oracle):
         assert rel_err(to_f64(outs[0][sample], DType.BF16), oracle_ref(oracle, a_s, b_s, DType.BF16)) <= 1e-2
 
 
+def test_concurrent_callers_share_one_context(backend, oracle):
+    """`Backend: Send + Sync`: eight host threads issue products of different
+    shapes, dtypes and kernels through the same context at once."""
+    import threading
+    shapes = [(300, 200, 520), (64, 64, 64), (129, 257, 2100), (520, 1100, 136), (77, 33, 1000), (256, 384, 512),
+              (1, 300, 40), (130, 70, 520)]
+    errors, results = [], {}
+
+    def work(i):
+        try:
+            m, k, n = shapes[i]
+            dtype = (DType.BF16, DType.F32, DType.F16)[i % 3]
+            a, b = fill(oracle, (m, k), dtype, 400 + i, 0), fill(oracle, (n, k), dtype, 400 + i, 1)
+            ta = Tensor.from_host(a, a.shape, dtype, backend)
+            tb = Tensor.from_host(b, b.shape, dtype, backend).permute([1, 0])
+            for _ in range(5):
+                got = backend.matmul(ta, tb).to_host()
+            results[i] = rel_err(to_f64(got, dtype), oracle_ref(oracle, a, b.T, dtype)) <= TOL[dtype]
+        except BaseException as e:
+            errors.append(e)
+
+    threads = [threading.Thread(target=work, args=(i,)) for i in range(len(shapes))]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors
+    assert all(results.get(i) for i in range(len(shapes))), results
+
+
 def test_sharded_host_matmul_across_devices(backend, oracle):
     """One backend per visible GPU, one host thread each (needs two or more GPUs)."""
     import ctypes as C
