@@ -184,6 +184,32 @@ def run_reference(args):
 # ---------------------------------------------------------------------------
 # the GPU arm
 # ---------------------------------------------------------------------------
+def measure_brief(be, grp, w, rank, world, steps=10, warmup=3):
+    """Device-timed TFLOP/s of one configuration on this rank's shard (max over
+    ranks), with inputs generated on the device and outputs allocated once."""
+    tensors = materialise(w, device_fill(be))
+    work = []
+    for g in w.gemms:
+        a, b, _ = gemm_views(w, g, tensors, rank, world)
+        oshape = tuple(broadcast_shapes(a.shape[:-2], b.shape[:-2])) + (a.shape[-2], b.shape[-1])
+        work.append((a, b, Tensor.empty(oshape, w.result_dtype, be)))
+    for _ in range(warmup):
+        for a, b, out in work:
+            be.matmul_into(a, b, out, batched=True)
+    be.synchronize()
+    grp.barrier()
+    timer = be.timer()
+    timer.start()
+    for _ in range(steps):
+        for a, b, out in work:
+            be.matmul_into(a, b, out, batched=True)
+    timer.stop()
+    ms = grp.max_over_ranks(timer.elapsed_ms())
+    grp.barrier()
+    return {"workload": w.title, "tflops": w.flops() * steps / (ms * 1e-3) / 1e12, "ms_per_step": ms / steps,
+            "steps": steps, "kernel": be.last_kernel(), "dtype": w.dtype.name.lower()}
+
+
 def run_ours(args):
     grp = init_from_env("nccl")
     rank, world, local = grp.rank, grp.world, grp.local_rank
@@ -302,6 +328,17 @@ def run_ours(args):
                "ms_per_step": e_ms / e_steps,
                "note": "per-rank bytes; pinned host memory; oxm_batched_matmul_host per product"}
 
+    # ---- the other configurations, briefly, so one run shows all five ----
+    others = None
+    if not args.no_others:
+        others = {}
+        for opt, val in (("cta_pair", -1), ("tile_n", 0), ("group_m", 0)):
+            be.set_option(opt, val)  # the library's own choices, whatever the main run forced
+        for key in ("c1", "c2", "c4", "c5"):
+            if key == w.key:
+                continue
+            others[key] = measure_brief(be, grp, WORKLOADS[key], rank, world)
+
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu:
         cb = cpu_reference(args.workload, 1, 0, target_s=12.0)
@@ -321,6 +358,7 @@ def run_ours(args):
             "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e,
             "gpu_launches": counts1["total"] - counts0["total"],
             "clocks": clocks,
+            "other_configs": others,
             "percent_of_dense_peak": 100.0 * tflops / world / ({DType.F32: 1125.0, DType.F8E4M3: 4500.0, DType.F8E5M2: 4500.0}.get(w.dtype, 2250.0)),
         }
         print(json.dumps(line), flush=True)
@@ -341,6 +379,7 @@ def main():
     ap.add_argument("--group-m", type=int, default=0)
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-others", action="store_true", help="skip the brief measurement of the other configurations")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
