@@ -248,7 +248,9 @@ int launch_simt(oxm_ctx *ctx, const Problem &P) {
   p.a = P.a; p.b = P.b; p.out = P.o;
   p.dtype = P.dtype; p.out_dtype = P.out_dtype;
   p.M = (int32_t)P.M; p.N = (int32_t)P.N; p.K = (int32_t)P.K;
-  p.tiles_m = (int32_t)((P.M + 63) / 64); p.tiles_n = (int32_t)((P.N + 63) / 64);
+  // 64-wide tiles, or 32-wide ones when those would leave most SMs idle
+  const int ts = (((P.M + 63) / 64) * ((P.N + 63) / 64) * P.nbatch < 2 * (int64_t)ctx->num_sms) ? 32 : 64;
+  p.tiles_m = (int32_t)((P.M + ts - 1) / ts); p.tiles_n = (int32_t)((P.N + ts - 1) / ts);
   p.a_off = P.a_off; p.b_off = P.b_off; p.o_off = P.o_off;
   p.a_rs = P.a_rs; p.a_cs = P.a_ks; p.b_rs = P.b_ks; p.b_cs = P.b_rs; p.o_rs = P.o_rs; p.o_cs = P.o_cs;
   p.nbd = P.nbd;
@@ -258,10 +260,11 @@ int launch_simt(oxm_ctx *ctx, const Problem &P) {
   p.epi = P.epi;
   const int64_t blocks = (int64_t)p.tiles_m * p.tiles_n * P.nbatch;
   if (blocks > INT32_MAX) return fail(OXM_NOT_IMPLEMENTED, "matmul is not implemented for %lld output tiles", (long long)blocks);
-  gemm_simt_kernel<<<(unsigned)blocks, 256, 0, ctx->stream>>>(p);
+  if (ts == 64) gemm_simt_kernel<64><<<(unsigned)blocks, 256, 0, ctx->stream>>>(p);
+  else gemm_simt_kernel<32><<<(unsigned)blocks, 256, 0, ctx->stream>>>(p);
   CUDA_TRY(cudaGetLastError());
   ctx->launches[0]++; ctx->launches[2]++;
-  snprintf(ctx->last_kernel, sizeof(ctx->last_kernel), "gemm_simt_ffma_64x64");
+  snprintf(ctx->last_kernel, sizeof(ctx->last_kernel), "gemm_simt_ffma_%dx%d", ts, ts);
   return OXM_OK;
 }
 

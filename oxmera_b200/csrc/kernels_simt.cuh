@@ -33,8 +33,8 @@ __global__ void bounded_wait_selftest_kernel(uint32_t *status, uint64_t limit_ns
 
 
 // ---------------------------------------------------------------------------
-// FFMA tile GEMM.  64x64 output tile per 256-thread CTA, 4x4 per thread, the
-// contraction walked in ascending k in blocks of 16.  Reads A, B and writes
+// FFMA tile GEMM.  A square output tile per 256-thread CTA, the contraction
+// walked in ascending k in blocks of 16.  Reads A, B and writes
 // C through signed element strides, so transposed / narrowed / flipped views
 // and broadcast batch dims need no preparation.
 // ---------------------------------------------------------------------------
@@ -52,8 +52,11 @@ struct SimtParams {
   Epilogue epi;
 };
 
+// TS x TS output tile per 256-thread CTA (TS = 64: 4 x 4 per thread; TS = 32:
+// 2 x 2 per thread, for products with too few 64-wide tiles to fill the GPU).
+template <int TS>
 __global__ void __launch_bounds__(256) gemm_simt_kernel(const SimtParams p) {
-  constexpr int TS = 64, BK = 16;
+  constexpr int BK = 16, TT = TS / 16, PER_THREAD = TS * BK / 256;
   __shared__ float As[BK][TS + 4];
   __shared__ float Bs[BK][TS + 4];
 
@@ -74,21 +77,21 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const SimtParams p) {
 
   const int tx = threadIdx.x & 15;  // column group
   const int ty = threadIdx.x >> 4;  // row group
-  float acc[4][4];
+  float acc[TT][TT];
 #pragma unroll
-  for (int i = 0; i < 4; ++i)
+  for (int i = 0; i < TT; ++i)
 #pragma unroll
-    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+    for (int j = 0; j < TT; ++j) acc[i][j] = 0.f;
 
   for (int32_t k0 = 0; k0 < p.K; k0 += BK) {
-    // 64x16 elements of A and 16x64 of B: four each per thread.
+    // TS x 16 elements of A and 16 x TS of B
 #pragma unroll
-    for (int r = 0; r < 4; ++r) {
+    for (int r = 0; r < PER_THREAD; ++r) {
       const int e = threadIdx.x + r * 256;
       {
         // A: make the faster-varying thread index follow A's unit stride.
         int mm, kk;
-        if (p.a_cs == 1) { kk = e & 15; mm = e >> 4; } else { mm = e & 63; kk = e >> 6; }
+        if (p.a_cs == 1) { kk = e & 15; mm = e >> 4; } else { mm = e % TS; kk = e / TS; }
         const int32_t gm = m0 + mm, gk = k0 + kk;
         float v = 0.f;
         if (gm < p.M && gk < p.K) v = load_elem(p.a, p.dtype, a_off + gm * p.a_rs + gk * p.a_cs);
@@ -96,7 +99,7 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const SimtParams p) {
       }
       {
         int nn, kk;
-        if (p.b_rs == 1) { kk = e & 15; nn = e >> 4; } else { nn = e & 63; kk = e >> 6; }
+        if (p.b_rs == 1) { kk = e & 15; nn = e >> 4; } else { nn = e % TS; kk = e / TS; }
         const int32_t gn = n0 + nn, gk = k0 + kk;
         float v = 0.f;
         if (gn < p.N && gk < p.K) v = load_elem(p.b, p.dtype, b_off + gk * p.b_rs + gn * p.b_cs);
@@ -106,26 +109,26 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const SimtParams p) {
     __syncthreads();
 #pragma unroll
     for (int kk = 0; kk < BK; ++kk) {
-      float av[4], bv[4];
+      float av[TT], bv[TT];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) av[i] = As[kk][ty * 4 + i];
+      for (int i = 0; i < TT; ++i) av[i] = As[kk][ty * TT + i];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) bv[j] = Bs[kk][tx * 4 + j];
+      for (int j = 0; j < TT; ++j) bv[j] = Bs[kk][tx * TT + j];
 #pragma unroll
-      for (int i = 0; i < 4; ++i)
+      for (int i = 0; i < TT; ++i)
 #pragma unroll
-        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+        for (int j = 0; j < TT; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
     }
     __syncthreads();
   }
 
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const int32_t gm = m0 + ty * 4 + i;
+  for (int i = 0; i < TT; ++i) {
+    const int32_t gm = m0 + ty * TT + i;
     if (gm >= p.M) continue;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const int32_t gn = n0 + tx * 4 + j;
+    for (int j = 0; j < TT; ++j) {
+      const int32_t gn = n0 + tx * TT + j;
       if (gn < p.N) {
         const int64_t idx = o_off + gm * p.o_rs + gn * p.o_cs;
         float r = acc[i][j];
