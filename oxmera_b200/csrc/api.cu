@@ -1004,6 +1004,12 @@ int oxm_batched_matmul_host(oxm_ctx *ctx, const oxm_view *a, const oxm_view *b, 
   return st2;
 }
 
+namespace {
+unsigned ew_plan_tiles(const oxm_ctx *ctx, EwParams &p, bool binary, int esz);
+void ew_collapse(EwParams &p);
+bool ew_linear(const int64_t *shape, const int64_t *strides, int ndim);
+}  // namespace
+
 int oxm_contiguous(oxm_ctx *ctx, const oxm_view *src, const oxm_view *dst) {
   if (!ctx || !src || !dst) return fail(OXM_INVALID_ARGUMENT, "contiguous: null argument");
   if (src->ndim < 0 || src->ndim > OXM_MAX_DIMS) return fail(OXM_NOT_IMPLEMENTED, "contiguous is not implemented for rank %d", src->ndim);
@@ -1035,8 +1041,25 @@ int oxm_contiguous(oxm_ctx *ctx, const oxm_view *src, const oxm_view *dst) {
   p.src_off = src->offset; p.dst_off = dst->offset;
   std::lock_guard<std::mutex> lock(ctx->mu);
   CUDA_TRY(cudaSetDevice(ctx->device));
-  const int64_t blocks = std::min<int64_t>((p.n + 255) / 256, (int64_t)ctx->num_sms * 16);
-  copy_strided_kernel<<<(unsigned)blocks, 256, 0, ctx->stream>>>(p);
+  // a transposed source goes through 32x32 shared-memory tiles so that both sides move whole sectors
+  EwParams e{};
+  e.ndim = src->ndim; e.n = p.n;
+  for (int d = 0; d < src->ndim; ++d) { e.shape[d] = src->shape[d]; e.a_strides[d] = e.b_strides[d] = src->shape[d] != 1 ? src->strides[d] : 0; }
+  ew_collapse(e);
+  e.contiguous = ew_linear(e.shape, e.a_strides, e.ndim) ? 1 : 0;
+  e.a = e.b = src->base; e.a_off = e.b_off = src->offset;
+  e.out = static_cast<uint8_t *>(dst->base) + dst->offset * p.elt;
+  if (const unsigned tb = ew_plan_tiles(ctx, e, false, p.elt)) {
+    switch (p.elt) {
+      case 1: ew_tile_kernel<uint8_t, 2, true, false><<<tb, 256, 0, ctx->stream>>>(e); break;
+      case 2: ew_tile_kernel<uint16_t, 2, true, false><<<tb, 256, 0, ctx->stream>>>(e); break;
+      case 4: ew_tile_kernel<uint32_t, 2, true, false><<<tb, 256, 0, ctx->stream>>>(e); break;
+      default: ew_tile_kernel<uint64_t, 2, true, false><<<tb, 256, 0, ctx->stream>>>(e); break;
+    }
+  } else {
+    const int64_t blocks = std::min<int64_t>((p.n + 255) / 256, (int64_t)ctx->num_sms * 16);
+    copy_strided_kernel<<<(unsigned)blocks, 256, 0, ctx->stream>>>(p);
+  }
   CUDA_TRY(cudaGetLastError());
   ctx->launches[0]++; ctx->launches[3]++;
   return OXM_OK;
@@ -1126,22 +1149,55 @@ int dispatch_dtype(int dtype, Args &&...args) {
 
 template <typename T> struct UnaryLauncher {
   static int run(oxm_ctx *ctx, const EwParams &p, unsigned blocks) {
-    if (p.rows) ew_rows_kernel<T, false><<<blocks, 256, 0, ctx->stream>>>(p);
+    if (p.tile_r >= 0) ew_tile_kernel<T, 0, true, false><<<blocks, 256, 0, ctx->stream>>>(p);
+    else if (p.rows) ew_rows_kernel<T, false><<<blocks, 256, 0, ctx->stream>>>(p);
     else unary_kernel<T><<<blocks, 256, 0, ctx->stream>>>(p);
     return OXM_OK;
   }
 };
 template <typename T> struct BinaryLauncher {
   static int run(oxm_ctx *ctx, const EwParams &p, unsigned blocks) {
-    if (p.rows) ew_rows_kernel<T, true><<<blocks, 256, 0, ctx->stream>>>(p);
+    if (p.tile_r >= 0) {
+      if (p.a_turn && p.b_turn) ew_tile_kernel<T, 1, true, true><<<blocks, 256, 0, ctx->stream>>>(p);
+      else if (p.a_turn) ew_tile_kernel<T, 1, true, false><<<blocks, 256, 0, ctx->stream>>>(p);
+      else ew_tile_kernel<T, 1, false, true><<<blocks, 256, 0, ctx->stream>>>(p);
+    }
+    else if (p.rows) ew_rows_kernel<T, true><<<blocks, 256, 0, ctx->stream>>>(p);
     else binary_kernel<T><<<blocks, 256, 0, ctx->stream>>>(p);
     return OXM_OK;
   }
 };
 
-// Decide between the flat kernels and the row kernel, and whether rows can move 16 bytes at a time.
+// A transposed operand steps through the innermost dim with a stride other
+// than 0 or 1 and has its unit stride on another dim of at least 32 elements.
+// Returns that dim, or -1.
+int ew_turned_dim(const EwParams &p, const int64_t *st) {
+  const int nd = p.ndim - 1;
+  if (nd < 1 || st[nd] == 0 || st[nd] == 1) return -1;
+  for (int d = 0; d < nd; ++d)
+    if (st[d] == 1 && p.shape[d] >= 32) return d;
+  return -1;
+}
+
+// Tiles apply when some operand is transposed and all transposed operands agree on the dim.
+unsigned ew_plan_tiles(const oxm_ctx *ctx, EwParams &p, bool binary, int esz) {
+  p.tile_r = -1; p.a_turn = 0; p.b_turn = 0;
+  if (p.contiguous || p.ndim < 2 || p.shape[p.ndim - 1] < 8) return 0;
+  const int ra = ew_turned_dim(p, p.a_strides), rb = binary ? ew_turned_dim(p, p.b_strides) : -1;
+  if (ra < 0 && rb < 0) return 0;
+  if (ra >= 0 && rb >= 0 && ra != rb) return 0;
+  p.tile_r = ra >= 0 ? ra : rb;
+  p.a_turn = ra >= 0; p.b_turn = rb >= 0;
+  const int64_t R = p.shape[p.tile_r], C = p.shape[p.ndim - 1];
+  const int64_t T = esz >= 8 ? 32 : 64;  // EwTile<T>
+  const int64_t tiles = ((R + T - 1) / T) * ((C + T - 1) / T) * (p.n / (R * C));
+  return (unsigned)std::min<int64_t>(tiles, (int64_t)ctx->num_sms * 16);
+}
+
+// Decide between the flat kernels, the row kernel and the tile kernel, and whether rows can move 16 bytes at a time.
 unsigned ew_plan(const oxm_ctx *ctx, EwParams &p, int esz, bool binary) {
   p.rows = 0; p.rows_vec = 0;
+  if (const unsigned tb = ew_plan_tiles(ctx, p, binary, esz)) return tb;
   if (!p.contiguous && p.ndim >= 1 && p.shape[p.ndim - 1] >= 128) {
     const int nd = p.ndim - 1, V = 16 / esz;
     p.rows = 1;

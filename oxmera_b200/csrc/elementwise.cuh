@@ -23,6 +23,11 @@ template <> struct EwTraits<int32_t> { using C = int64_t; };
 template <> struct EwTraits<int64_t> { using C = int64_t; };
 template <> struct EwTraits<__nv_bfloat16> { using C = float; };
 template <> struct EwTraits<__half> { using C = float; };
+// raw element widths, for copies that do no arithmetic
+template <> struct EwTraits<uint8_t> { using C = uint8_t; };
+template <> struct EwTraits<uint16_t> { using C = uint16_t; };
+template <> struct EwTraits<uint32_t> { using C = uint32_t; };
+template <> struct EwTraits<uint64_t> { using C = uint64_t; };
 
 template <typename T> __device__ __forceinline__ typename EwTraits<T>::C ew_load(const T *p, int64_t i) {
   return static_cast<typename EwTraits<T>::C>(p[i]);
@@ -46,6 +51,8 @@ struct EwParams {
   int32_t vec;         // ... and every pointer is 16-byte aligned: 16 bytes per thread per step
   int32_t rows;        // 1: one CTA per row of the innermost dim (no per-element index arithmetic)
   int32_t rows_vec;    // ... with inner strides 0 or 1 and 16-byte-aligned rows
+  int32_t tile_r;      // >= 0: 32x32 tiles over (this dim, innermost dim); an operand whose unit stride is on this dim turns through shared memory
+  int32_t a_turn, b_turn;
 };
 
 __device__ __forceinline__ void ew_offsets(const EwParams &p, int64_t i, int64_t &ao, int64_t &bo) {
@@ -179,6 +186,94 @@ __global__ void __launch_bounds__(256) ew_rows_kernel(const EwParams p) {
         else ew_store<T>(orow, x, unary_apply<C>(p.op, va));
       }
     }
+  }
+}
+
+// A transposed operand: its unit stride lies on dim R, not on the innermost
+// dim C that the output is contiguous in.  Walking it along C touches one
+// element per 32-byte sector.  Here each CTA takes TILE x TILE tiles of (R, C):
+// a turned operand is read along R (coalesced) into padded shared memory and
+// read back along C; other operands are read in place.  Every thread has
+// TILE*TILE/256 independent loads in flight per phase.  Tiles are walked along
+// diagonals so that CTAs running together differ in both coordinates and a
+// power-of-two pitch does not pile their traffic onto a few DRAM channels.
+// MODE 0 unary op, 1 binary op, 2 plain copy (T is then an unsigned integer of
+// the element's width).  A_TURN / B_TURN: which operands are turned (B_TURN
+// only with MODE 1).
+template <typename T> struct EwTile { static constexpr int value = sizeof(T) >= 8 ? 32 : 64; };
+
+template <typename T, int MODE, bool A_TURN, bool B_TURN>
+__global__ void __launch_bounds__(256) ew_tile_kernel(const EwParams p) {
+  using C = typename EwTraits<T>::C;
+  constexpr int TILE = EwTile<T>::value, STEP = 256 / TILE, ITERS = TILE / STEP;
+  __shared__ T sa[A_TURN ? TILE : 1][TILE + 1], sb[B_TURN ? TILE : 1][TILE + 1];
+  const T *a = static_cast<const T *>(p.a), *b = static_cast<const T *>(p.b);
+  T *out = static_cast<T *>(p.out);
+  const int nd = p.ndim - 1, rd = p.tile_r;
+  const int64_t R = p.shape[rd], Cn = p.shape[nd];
+  const int64_t tiles_c = (Cn + TILE - 1) / TILE, tiles_r = (R + TILE - 1) / TILE;
+  const int64_t ntiles = tiles_c * tiles_r * (p.n / (R * Cn));
+  const int64_t asr = p.a_strides[rd], asc = p.a_strides[nd], bsr = p.b_strides[rd], bsc = p.b_strides[nd];
+  const int tx = threadIdx.x % TILE, ty = threadIdx.x / TILE;
+  for (int64_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+    const int64_t y = (tile / tiles_c) % tiles_r, x = tile % tiles_c;
+    const int64_t r0 = ((y + x) % tiles_r) * TILE, c0 = x * TILE;  // consecutive tiles step along a diagonal
+    int64_t t = tile / (tiles_c * tiles_r), ao = p.a_off, bo = p.b_off, oo = 0, os = Cn, osr = 0;
+    for (int d = nd - 1; d >= 0; --d) {
+      if (d == rd) {
+        osr = os;
+      } else {
+        const int64_t idx = t % p.shape[d];
+        t /= p.shape[d];
+        ao += idx * p.a_strides[d];
+        bo += idx * p.b_strides[d];
+        oo += idx * os;
+      }
+      os *= p.shape[d];
+    }
+    // every global load of the tile is issued before the first store: a turned
+    // operand along R into shared memory, any other in the output's own mapping
+    const int64_t c = c0 + tx;
+    T da[ITERS], db[MODE == 1 ? ITERS : 1];
+    {
+      const int64_t r = r0 + tx;
+      T va[ITERS], vb[MODE == 1 ? ITERS : 1];
+#pragma unroll
+      for (int i = 0; i < ITERS; ++i) {
+        const int64_t ct = c0 + ty + STEP * i, rd2 = r0 + ty + STEP * i;
+        const bool in_t = r < R && ct < Cn, in_d = rd2 < R && c < Cn;
+        if constexpr (A_TURN) { if (in_t) va[i] = a[ao + r * asr + ct * asc]; }
+        else if (in_d) da[i] = a[ao + rd2 * asr + c * asc];
+        if constexpr (MODE == 1) {
+          if constexpr (B_TURN) { if (in_t) vb[i] = b[bo + r * bsr + ct * bsc]; }
+          else if (in_d) db[i] = b[bo + rd2 * bsr + c * bsc];
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < ITERS; ++i) {
+        const int cl = ty + STEP * i;
+        if constexpr (A_TURN) sa[tx][cl] = va[i];
+        if constexpr (B_TURN) sb[tx][cl] = vb[i];
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < ITERS; ++i) {
+      const int rl = ty + STEP * i;
+      const int64_t r = r0 + rl;
+      if (r < R && c < Cn) {
+        const T ra = A_TURN ? sa[rl][tx] : da[i];
+        if constexpr (MODE == 2) {
+          out[oo + r * osr + c] = ra;
+        } else if constexpr (MODE == 1) {
+          const T rb = B_TURN ? sb[rl][tx] : db[i];
+          ew_store<T>(out, oo + r * osr + c, binary_apply<C>(p.op, ew_load<T>(&ra, 0), ew_load<T>(&rb, 0)));
+        } else {
+          ew_store<T>(out, oo + r * osr + c, unary_apply<C>(p.op, ew_load<T>(&ra, 0)));
+        }
+      }
+    }
+    __syncthreads();
   }
 }
 

@@ -144,3 +144,43 @@ def test_reductions(backend, oracle, dtype):
         backend.max(e, [1])
     with pytest.raises(ox.IndexOutOfBounds):
         backend.sum(e, [2])
+
+
+@pytest.mark.parametrize("dtype", FLOATS + INTS, ids=lambda d: d.name)
+def test_transposed_operands_take_the_tile_kernel(backend, oracle, dtype):
+    """Operands whose unit stride is not on the innermost dim (extent >= 32 on
+    the unit-stride dim): ragged 32x32 tiles, a batch dim outside and between
+    the tile dims, either or both operands turned."""
+    for shape, perm in (((70, 45), (1, 0)), ((3, 40, 50), (0, 2, 1)), ((40, 3, 50), (2, 1, 0)), ((33, 2, 2, 65), (3, 1, 2, 0))):
+        h = host(oracle, shape, dtype, 40)
+        t = Tensor.from_host(h, shape, dtype, backend)
+        hv, tv = h.transpose(perm), t.permute(list(perm))
+        out = backend.neg(tv)
+        assert backend.last_kernel() == "unary_neg" and out.layout().is_contiguous()
+        assert_close(out.to_host(), oracle.unary(0, hv, TAGS[dtype])[1], dtype)
+        assert np.array_equal(tv.contiguous().to_host(), np.ascontiguousarray(hv))
+        g = host(oracle, hv.shape, dtype, 41)           # row-major partner
+        tg = Tensor.from_host(g, g.shape, dtype, backend)
+        assert_close(backend.add(tg, tv).to_host(), oracle.binary(0, g, hv, TAGS[dtype])[1], dtype, ulps=1)
+        assert_close(backend.sub(tv, tg).to_host(), oracle.binary(1, hv, g, TAGS[dtype])[1], dtype, ulps=1)
+        h2 = host(oracle, shape, dtype, 42)             # both turned the same way
+        t2 = Tensor.from_host(h2, shape, dtype, backend)
+        assert_close(backend.mul(tv, t2.permute(list(perm))).to_host(), oracle.binary(2, hv, h2.transpose(perm), TAGS[dtype])[1], dtype, ulps=1)
+        row = host(oracle, hv.shape[-1:], dtype, 43)    # a broadcast row against a turned operand
+        trow = Tensor.from_host(row, row.shape, dtype, backend)
+        assert_close(backend.add(tv, trow).to_host(), oracle.binary(0, hv, row, TAGS[dtype])[1], dtype, ulps=1)
+
+
+@pytest.mark.parametrize("dtype", [DType.U8, DType.Bool, DType.F64, DType.BF16], ids=lambda d: d.name)
+def test_contiguous_of_transposed_views(backend, dtype):
+    rng = np.random.default_rng(5)
+    npdt = {DType.U8: np.uint8, DType.Bool: np.uint8, DType.F64: np.float64, DType.BF16: np.uint16}[dtype]
+    for shape, perm in (((130, 77), (1, 0)), ((5, 64, 48), (0, 2, 1)), ((48, 5, 64), (2, 1, 0))):
+        h = rng.integers(0, 2 if dtype == DType.Bool else 200, size=shape).astype(npdt)
+        t = Tensor.from_host(h, shape, dtype, backend)
+        got = t.permute(list(perm)).contiguous()
+        assert got.layout().is_contiguous()
+        assert np.array_equal(got.to_host(), np.ascontiguousarray(h.transpose(perm)))
+        # a window of the transposed view: offset and ragged tiles
+        w = t.permute(list(perm)).narrow(len(shape) - 1, 3, 33)
+        assert np.array_equal(w.contiguous().to_host(), np.ascontiguousarray(h.transpose(perm)[..., 3:36]))
