@@ -68,6 +68,10 @@ class ClockSampler(threading.Thread):
             self.nv = pynvml
             self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
             self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+            try:
+                self.power_limit_w = pynvml.nvmlDeviceGetEnforcedPowerLimit(self.h) / 1000.0
+            except Exception:
+                self.power_limit_w = None
             self.ok = True
         except Exception:
             self.ok = False
@@ -83,7 +87,11 @@ class ClockSampler(threading.Thread):
                     reasons = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
                 except Exception:
                     reasons = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
-                self.samples.append((time.perf_counter(), mhz, reasons))
+                try:
+                    watts = nv.nvmlDeviceGetPowerUsage(self.h) / 1000.0
+                except Exception:
+                    watts = None
+                self.samples.append((time.perf_counter(), mhz, reasons, watts))
             except Exception:
                 pass
             time.sleep(self.period)
@@ -102,13 +110,15 @@ class ClockSampler(threading.Thread):
                  0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown", 0x80: "hw_power_brake_slowdown",
                  0x100: "display_clock_setting"}
         seen = set()
-        for _, _, r in window:
+        for smp in window:
             for bit, nm in names.items():
-                if r & bit:
+                if smp[2] & bit:
                     seen.add(nm)
         mhz = sorted(s[1] for s in window)
+        watts = sorted(s[3] for s in window if s[3] is not None)
         return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": self.max_mhz,
-                "reasons": sorted(seen), "samples": len(window), "window": label}
+                "reasons": sorted(seen), "samples": len(window), "window": label,
+                "power_w": watts[len(watts) // 2] if watts else None, "power_limit_w": getattr(self, "power_limit_w", None)}
 
 
 # ---------------------------------------------------------------------------
@@ -261,8 +271,12 @@ def run_ours(args):
     # Which cuBLAS figure is the fair denominator depends on the regime the
     # timed region ran in: the burst figure while the SM clock stays near its
     # maximum, the sustained one once the 1 kW power cap has pulled it down.
+    # The power cap shows as its throttle reason, as a clock well under the
+    # maximum, or (the sampled clock lags on some boxes) as a draw at the limit.
     capped = "sw_power_cap" in clocks.get("reasons", []) or (
-        clocks.get("sm_mhz") and clocks.get("sm_max_mhz") and clocks["sm_mhz"] < 0.85 * clocks["sm_max_mhz"])
+        clocks.get("sm_mhz") and clocks.get("sm_max_mhz") and clocks["sm_mhz"] < 0.85 * clocks["sm_max_mhz"]) or (
+        clocks.get("power_w") and clocks.get("power_limit_w") and clocks["power_w"] >= 0.9 * clocks["power_limit_w"])
+    capped = bool(capped)
     burst = not capped and timed_s < 0.5
     peak = peaks["bf16_tflops"] if burst else peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"])
     if w.dtype == DType.F32:

@@ -462,19 +462,39 @@ struct TileChoice {
 // The longest accumulation chain the f32 path allows, in pipeline stages (K = 1024).
 constexpr int kMaxChainKb = 3 * 1024 / 32;
 
-// Pick the configuration with the smallest modelled time.  The model counts
-// waves of tiles over the SMs (or SM pairs) at each shape's measured relative
-// rate, a per-tile cost where the epilogue is exposed, and the price of the
-// reduction pass when the contraction is split to fill an under-occupied grid.
+// Pick the configuration with the smallest modelled time.  The model takes the
+// larger of two bounds and adds the price of the reduction pass when the
+// contraction is split:
+//   - waves of tiles over the SMs (or SM pairs), each tile costing its
+//     contraction blocks at the shape's measured rate, or its epilogue when the
+//     contraction is too short to hide it;
+//   - the unique bytes over HBM bandwidth (reads and writes at their own rates).
+// A product with one or two rows (or columns) of tiles streams every stage from
+// HBM with all CTAs in step; a stage then takes ~0.35 us whatever its size
+// (measured: [1..128, 8192] x [8192, 8192] takes 45.7 us at every tile width and
+// CTA count), so such products want a split contraction: fewer steps per CTA
+// and several slabs of the long operand in flight at once.
 TileChoice choose_tiles(const oxm_ctx *ctx, const Problem &P, bool tf32, int32_t num_kb, int min_b_rows) {
-  struct Cand { int bn, pair; double us_per_kb, us_per_tile; };
-  // microseconds per pipeline stage of one tile at the ~1.45 GHz the power cap sustains
-  static const Cand cands[] = {{512, 1, 0.706 / 1.03, 2.0}, {256, 1, 0.353, 0.3}, {256, 0, 0.353 / 0.93, 0.3},
-                               {128, 0, 0.177 / 0.75, 0.3}, {128, 1, 0.177 / 0.59, 0.3}, {64, 0, 0.088 / 0.5, 0.3}};
+  struct Cand { int bn, pair; double us_per_kb, us_epilogue; };
+  // Microseconds per pipeline stage of one tile at the ~1.45 GHz the power cap
+  // sustains, and per epilogue.  With two accumulators the epilogue hides
+  // behind the next tile's main loop unless the contraction is short; the
+  // 512-wide tile has one accumulator and always pays it.
+  static const Cand cands[] = {{512, 1, 0.706 / 1.03, 2.0}, {256, 1, 0.353, 3.0}, {256, 0, 0.353 / 0.93, 2.0},
+                               {128, 0, 0.177 / 0.75, 1.5}, {128, 1, 0.177 / 0.59, 2.0}, {64, 0, 0.088 / 0.5, 1.0}};
+  constexpr double kHbmRead = 6.0e6;    // bytes per microsecond from HBM
+  constexpr double kHbmWrite = 4.3e6;   // ... and to it (measured on products that only write)
   const int32_t min_splits = tf32 ? std::max(1, (num_kb + kMaxChainKb - 1) / kMaxChainKb) : 1;
-  static const int mult[] = {1, 2, 3, 4, 6, 8};
+  static const int mult[] = {1, 2, 3, 4, 6, 8, 12, 16, 24, 32, 48, 64};
   TileChoice best{256, 0, min_splits};
   double best_t = 1e300;
+  double a_nb = 1, b_nb = 1;  // batches each operand owns (broadcast dims repeat one copy)
+  for (int d = 0; d < P.nbd; ++d) {
+    if (P.a_bs[d] != 0) a_nb *= (double)P.bdims[d];
+    if (P.b_bs[d] != 0) b_nb *= (double)P.bdims[d];
+  }
+  const double hbm_us = (double)P.nbatch * ((double)P.M * P.N * P.oelt) / kHbmWrite +
+                        ((double)P.M * P.K * a_nb + (double)P.N * P.K * b_nb) * P.elt * (tf32 ? 3.0 : 1.0) / kHbmRead;
   // A forced pairing that no candidate of the forced width has is dropped on the second pass.
   for (int pass = 0; pass < 2 && best_t == 1e300; ++pass)
   for (const Cand &c : cands) {
@@ -489,6 +509,8 @@ TileChoice choose_tiles(const oxm_ctx *ctx, const Problem &P, bool tf32, int32_t
     const int tm = kTileM * (c.pair ? 2 : 1);
     const int64_t tiles = ((P.M + tm - 1) / tm) * ((P.N + c.bn - 1) / c.bn) * P.nbatch;
     const int64_t slots = c.pair ? ctx->num_sms / 2 : ctx->num_sms;
+    const bool streaming = (P.M + tm - 1) / tm <= 2 || (P.N + c.bn - 1) / c.bn <= 2;
+    const double kb_us = std::max(c.us_per_kb, streaming ? 0.35 : 0.0);
     for (int m : mult) {
       const int32_t splits = min_splits * m;
       if (m > 1 && (ctx->opt_split_k == 0 || num_kb / splits < 16)) break;
@@ -497,9 +519,16 @@ TileChoice choose_tiles(const oxm_ctx *ctx, const Problem &P, bool tf32, int32_t
       if (splits > 1 && slab_bytes * splits > 2e9) break;
       const int64_t waves = (tiles * splits + slots - 1) / slots;
       const int32_t kb = (num_kb + splits - 1) / splits;
-      double t = (double)waves * (kb * c.us_per_kb + c.us_per_tile);
+      // one accumulator: the epilogue is exposed, and twice as long when the main loop is too
+      // short for the previous tile's stores to drain meanwhile
+      const double tile_us = c.bn > 256 ? kb * kb_us + c.us_epilogue * (kb < 16 ? 2.0 : 1.0)
+                                        : std::max(kb * kb_us + 0.3, c.us_epilogue);
+      const double wave_us = (double)waves * tile_us;
+      double t = std::max(wave_us, hbm_us) + 0.01 * wave_us;  // the second term orders memory-bound ties
       if (splits > 1) t += 4.0 + slab_bytes * (splits + 1) / 4.0e6;  // launch + traffic of the reduction
-      if (t < best_t) { best_t = t; best = TileChoice{c.bn, c.pair, splits}; }
+      if (splits == min_splits ? t <= best_t : t < best_t) {  // ties go to the narrower, later candidate
+        best_t = t; best = TileChoice{c.bn, c.pair, splits};
+      }
     }
   }
   return best;
@@ -600,7 +629,13 @@ int launch_tcgen05(oxm_ctx *ctx, const Problem &P) {
 
   CUtensorMap tmA, tmB, tmC;
   memset(&tmC, 0, sizeof(tmC));
-  int st = make_map(ctx, &tmA, sa, P.dtype, P.elt, kTileM, bk);
+  // Rows the box would fetch beyond the matrix are zero-filled at a cost per
+  // row, so a K-major A of fewer than 128 rows gets a box of just its rows; the
+  // tile's other rows keep whatever shared memory held and feed accumulator
+  // rows that are never stored.
+  const int a_box_rows = (!pair && !sa.mn_major && P.M < kTileM) ? (int)((P.M + 7) / 8 * 8) : kTileM;
+  p.stage_tx = (uint32_t)(kStageKBytes * (a_box_rows + bn));
+  int st = make_map(ctx, &tmA, sa, P.dtype, P.elt, a_box_rows, bk);
   if (st) return st;
   st = make_map(ctx, &tmB, sb, P.dtype, P.elt, pair ? std::min(bn, 256) / 2 : bn, bk);
   if (st) return st;
@@ -677,7 +712,7 @@ int run_matmul(oxm_ctx *ctx, const oxm_view *a, const oxm_view *b, const oxm_vie
   bool use_tc;
   if (ctx->opt_kernel == 1) use_tc = false;
   else if (ctx->opt_kernel == 2) use_tc = P.K > 0;
-  else use_tc = P.K > 0 && flops >= 2.0e8;
+  else use_tc = P.K > 0 && flops >= (P.elt == 4 ? 3.0e7 : 8.0e6);
   return use_tc ? launch_tcgen05(ctx, P) : launch_simt(ctx, P);
 }
 
@@ -1702,6 +1737,7 @@ extern "C" int oxm_matmul_f32_noalloc(oxm_ctx *ctx, const oxm_view *a, const oxm
   CUtensorMap tmA, tmB, tmC;
   memset(&tmC, 0, sizeof(tmC));
   p.out_tma = 0;  // plain strided stores: the output may be any view
+  p.stage_tx = (uint32_t)(kStageKBytes * (kTileM + bn));
   st = make_map(ctx, &tmA, sa, OXM_F32, 4, kTileM, 32);
   if (st) return st;
   st = make_map(ctx, &tmB, sb, OXM_F32, 4, pair ? bn / 2 : bn, 32);

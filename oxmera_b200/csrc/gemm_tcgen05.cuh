@@ -32,9 +32,12 @@ constexpr int kMaxBatchDims = 6;
 constexpr int kTileM = 128;        // accumulator rows per CTA (= TMEM lanes)
 constexpr int kStageKBytes = 128;  // contraction bytes per pipeline stage (one swizzle row)
 constexpr int kMmaKBytes = 32;     // contraction bytes per tcgen05.mma
-// Threads per CTA: a TMA warp, an MMA warp, and four epilogue warps per group
-// (two groups when one accumulator fills tensor memory and the epilogue is exposed).
-__host__ __device__ constexpr int gemm_epi_groups(int bn) { return bn > 256 ? 2 : 1; }
+// Threads per CTA: a TMA warp, an MMA warp, and four epilogue warps per group.
+// Tiles of 256 columns and more get two groups, each draining half of the
+// columns: the per-warp chain tensor memory -> registers -> staging -> bulk
+// store is latency bound, so a second group halves the time per tile, which
+// shows wherever the epilogue is exposed (one accumulator, or short contractions).
+__host__ __device__ constexpr int gemm_epi_groups(int bn) { return bn >= 256 ? 2 : 1; }
 __host__ __device__ constexpr int gemm_threads(int bn) { return 64 + 128 * gemm_epi_groups(bn); }
 constexpr uint32_t kStatusTimeout = 11;  // OXM_TIMEOUT
 
@@ -55,6 +58,7 @@ struct GemmParams {
   int32_t out_vec;         // rows may be written with 16-byte stores
   int32_t out_tma;         // the output is described by the store tensor map
   uint32_t idesc;
+  uint32_t stage_tx;       // bytes one CTA's loads of one stage deliver (1-CTA kernels: the A box may be shorter than the tile)
   uint32_t *status;
   uint64_t wait_limit_ns;
   // Split-K: the contraction is cut into `splits` chains of `kb_per_split`
@@ -278,7 +282,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             }
           } else {
             const uint32_t fb = full_bar(s);
-            ptx::mbar_arrive_expect_tx(fb, L::kStageBytes);
+            ptx::mbar_arrive_expect_tx(fb, p.stage_tx);
             if constexpr (A_MN) {
 #pragma unroll
               for (int j = 0; j < kTileM / BOXW; ++j)
@@ -439,7 +443,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           ptx::bulk_commit_group();
         }
       };
-      constexpr int BATCH = (ACC == 1 && GROUP_COLS % 128 == 0) ? 128 : 64;  // columns drained per wait
+      constexpr int BATCH = GROUP_COLS % 128 == 0 ? 128 : 64;  // columns drained per wait
       constexpr int NLD = BATCH / 32;
 #pragma unroll 1
       for (int c = 0; c < GROUP_COLS / BATCH; ++c) {

@@ -252,18 +252,52 @@ struct ReduceParams {
 
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(const ReduceParams p) {
   const int64_t mn = static_cast<int64_t>(p.M) * p.N;
-  for (int64_t i = blockIdx.x * 256ll + threadIdx.x; i < p.total; i += static_cast<int64_t>(gridDim.x) * 256) {
-    float acc = p.ws[i];
-    for (int s = 1; s < p.splits; ++s) acc += p.ws[i + s * p.split_stride];
+  // Four neighbours of one output row per thread when rows and slabs allow 16-byte loads.
+  const bool vec = (p.N % 4 == 0) && (p.split_stride % 4 == 0) && (reinterpret_cast<uintptr_t>(p.ws) % 16 == 0);
+  const int64_t step = vec ? 4 : 1;
+  const int64_t units = p.total / step;
+  const int esz = p.out_dtype == 0 ? 4 : (p.out_dtype >= 8 ? 1 : 2);
+  for (int64_t u = blockIdx.x * 256ll + threadIdx.x; u < units; u += static_cast<int64_t>(gridDim.x) * 256) {
+    const int64_t i = u * step;
+    float acc[4];
+    if (vec) {
+      float4 t = *reinterpret_cast<const float4 *>(p.ws + i);
+      acc[0] = t.x; acc[1] = t.y; acc[2] = t.z; acc[3] = t.w;
+      for (int s = 1; s < p.splits; ++s) {
+        t = *reinterpret_cast<const float4 *>(p.ws + i + s * p.split_stride);
+        acc[0] += t.x; acc[1] += t.y; acc[2] += t.z; acc[3] += t.w;
+      }
+    } else {
+      acc[0] = p.ws[i];
+      for (int s = 1; s < p.splits; ++s) acc[0] += p.ws[i + s * p.split_stride];
+    }
     int64_t batch = i / mn;
     const int64_t r = i - batch * mn;
-    int64_t off = p.o_off + (r / p.N) * p.o_rs + (r % p.N) * p.o_cs;
+    const int32_t col = static_cast<int32_t>(r % p.N);
+    int64_t off = p.o_off + (r / p.N) * p.o_rs + col * p.o_cs;
     for (int d = p.nbd - 1; d >= 0; --d) {
       off += (batch % p.bdims[d]) * p.o_bs[d];
       batch /= p.bdims[d];
     }
-    if (p.epi.any) acc = apply_epilogue(p.epi, acc, r % p.N, p.out, p.out_dtype, off);
-    store_elem(p.out, p.out_dtype, off, acc);
+    if (p.epi.any) {
+      for (int e = 0; e < step; ++e) acc[e] = apply_epilogue(p.epi, acc[e], col + e, p.out, p.out_dtype, off + e * p.o_cs);
+    }
+    uint8_t *dst = static_cast<uint8_t *>(p.out) + off * esz;
+    if (vec && p.o_cs == 1 && p.out_dtype == 0 && reinterpret_cast<uintptr_t>(dst) % 16 == 0) {
+      *reinterpret_cast<float4 *>(dst) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    } else if (vec && p.o_cs == 1 && (p.out_dtype == 6 || p.out_dtype == 7) && reinterpret_cast<uintptr_t>(dst) % 8 == 0) {
+      uint2 w;
+      if (p.out_dtype == 6) {
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(acc[0], acc[1]), hi = __floats2bfloat162_rn(acc[2], acc[3]);
+        w.x = *reinterpret_cast<const uint32_t *>(&lo); w.y = *reinterpret_cast<const uint32_t *>(&hi);
+      } else {
+        const __half2 lo = __floats2half2_rn(acc[0], acc[1]), hi = __floats2half2_rn(acc[2], acc[3]);
+        w.x = *reinterpret_cast<const uint32_t *>(&lo); w.y = *reinterpret_cast<const uint32_t *>(&hi);
+      }
+      *reinterpret_cast<uint2 *>(dst) = w;
+    } else {
+      for (int e = 0; e < step; ++e) store_elem(p.out, p.out_dtype, off + e * p.o_cs, acc[e]);
+    }
   }
 }
 

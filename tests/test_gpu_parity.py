@@ -287,6 +287,28 @@ def test_split_k_fills_small_grids(backend, oracle, dtype, a_t, b_t):
     assert backend.launch_counts()["pack"] == before["pack"] + 1
 
 
+@pytest.mark.parametrize("dtype", [DType.BF16, DType.F32], ids=lambda d: d.name)
+@pytest.mark.parametrize("b_t", [0, 1])
+def test_skinny_products(backend, oracle, dtype, b_t):
+    """One row of tiles over a long weight matrix (a decode step): A's box
+    holds just its rows, and the automatic choice splits the contraction so
+    that every SM streams part of B.  Also the mirror case (one column of
+    tiles) and an output width that is not a multiple of four (scalar
+    reduction path)."""
+    set_kernel(backend, "auto")
+    for (m, n, k) in ((1, 1024, 4096), (8, 1024, 4096), (17, 1030, 4096), (100, 1024, 2048), (2048, 40, 4096)):
+        ha = fill(oracle, (m, k), dtype, 31, 0)
+        hb = fill(oracle, (n, k) if b_t else (k, n), dtype, 31, 1)
+        ta, tb = Tensor.from_host(ha, ha.shape, dtype, backend), Tensor.from_host(hb, hb.shape, dtype, backend)
+        if b_t:
+            hb, tb = hb.T, tb.permute([1, 0])
+        got = backend.matmul(ta, tb)
+        if 2 * m * n * k >= 3e7:
+            assert "tcgen05" in backend.last_kernel(), backend.last_kernel()
+        err = rel_err(to_f64(got.to_host(), dtype), oracle_ref(oracle, ha, hb, dtype))
+        assert err <= TOL[dtype], ((m, n, k), err, backend.last_kernel())
+
+
 def test_expired_device_wait_is_reported_and_survivable(backend):
     """Failure detection without a fault: a wait nothing satisfies runs out
     after its bound, the kernel returns, the host reads OXM_TIMEOUT, and the
