@@ -6,7 +6,7 @@
 //   oxmera-core     DType, Device, Shape, Strides, Layout, Error, Result,
 //                   broadcast_shapes, contiguous_strides
 //   oxmera-tensor   Storage, Tensor (views: reshape / permute / narrow / contiguous)
-//   oxmera-ops      MatmulOps (+ the batched extension)
+//   oxmera-ops      UnaryOps, BinaryOps, MatmulOps (+ the batched extension), ReduceOps
 //   oxmera-runtime  Backend, backend_for, register_backend, Tensor::matmul
 // Header only, C++17.  Link against liboxmera_b200.so to use B200Backend.
 #pragma once
@@ -368,6 +368,12 @@ class Tensor {
   // TensorOps (crates/oxmera-runtime/src/lib.rs:57-72): resolve the backend from the device and dispatch.
   Result<Tensor> matmul(const Tensor &rhs) const;
   Result<Tensor> batched_matmul(const Tensor &rhs) const;
+  Result<Tensor> add(const Tensor &rhs) const;
+  Result<Tensor> sub(const Tensor &rhs) const;
+  Result<Tensor> mul(const Tensor &rhs) const;
+  Result<Tensor> div(const Tensor &rhs) const;
+  Result<Tensor> neg() const;
+  Result<Tensor> sum(const std::vector<size_t> &axes) const;
 
  private:
   Tensor(std::shared_ptr<Storage> s, Layout l) : storage_(std::move(s)), layout_(std::move(l)) {}
@@ -390,11 +396,47 @@ class MatmulOps {
   }
 };
 
+namespace detail {
+template <typename... A>
+inline Result<Tensor> not_implemented(const char *op, const A &...) {
+  Error e{Error::Kind::NotImplemented};
+  e.op = op; e.detail = "this backend";
+  return e;
+}
+}  // namespace detail
+
+// crates/oxmera-ops/src/lib.rs:27-37: exp and ln are for float dtypes only.
+class UnaryOps {
+ public:
+  virtual ~UnaryOps() = default;
+  virtual Result<Tensor> neg(const Tensor &a) { return detail::not_implemented("neg", a); }
+  virtual Result<Tensor> exp(const Tensor &a) { return detail::not_implemented("exp", a); }
+  virtual Result<Tensor> ln(const Tensor &a) { return detail::not_implemented("ln", a); }
+  virtual Result<Tensor> abs(const Tensor &a) { return detail::not_implemented("abs", a); }
+};
+
+// crates/oxmera-ops/src/lib.rs:39-50: operands broadcast by NumPy's rule.
+class BinaryOps {
+ public:
+  virtual ~BinaryOps() = default;
+  virtual Result<Tensor> add(const Tensor &l, const Tensor &r) { return detail::not_implemented("add", l, r); }
+  virtual Result<Tensor> sub(const Tensor &l, const Tensor &r) { return detail::not_implemented("sub", l, r); }
+  virtual Result<Tensor> mul(const Tensor &l, const Tensor &r) { return detail::not_implemented("mul", l, r); }
+  virtual Result<Tensor> div(const Tensor &l, const Tensor &r) { return detail::not_implemented("div", l, r); }
+};
+
+// crates/oxmera-ops/src/lib.rs:61-69: the reduced axes leave the shape; no axes means all axes.
+class ReduceOps {
+ public:
+  virtual ~ReduceOps() = default;
+  virtual Result<Tensor> sum(const Tensor &a, const std::vector<size_t> &axes) { return detail::not_implemented("sum", a, axes); }
+  virtual Result<Tensor> max(const Tensor &a, const std::vector<size_t> &axes) { return detail::not_implemented("max", a, axes); }
+};
+
 // ------------------------------------------------------------- runtime ----
 
-// crates/oxmera-runtime/src/lib.rs:29-34.  The elementwise and reduction op
-// families are outside this backend's path.
-class Backend : public MatmulOps {
+// crates/oxmera-runtime/src/lib.rs:29-34: a backend is all four op families on one device.
+class Backend : public UnaryOps, public BinaryOps, public MatmulOps, public ReduceOps {
  public:
   virtual Device device() const = 0;
   virtual const char *name() const = 0;
@@ -448,6 +490,27 @@ inline Result<Tensor> Tensor::batched_matmul(const Tensor &rhs) const {
   if (b.is_err()) return b.unwrap_err();
   return b.unwrap()->batched_matmul(*this, rhs);
 }
+#define OXMERA_TENSOR_BINARY(NAME)                           \
+  inline Result<Tensor> Tensor::NAME(const Tensor &rhs) const { \
+    auto b = backend_for(device());                            \
+    if (b.is_err()) return b.unwrap_err();                     \
+    return b.unwrap()->NAME(*this, rhs);                       \
+  }
+OXMERA_TENSOR_BINARY(add)
+OXMERA_TENSOR_BINARY(sub)
+OXMERA_TENSOR_BINARY(mul)
+OXMERA_TENSOR_BINARY(div)
+#undef OXMERA_TENSOR_BINARY
+inline Result<Tensor> Tensor::neg() const {
+  auto b = backend_for(device());
+  if (b.is_err()) return b.unwrap_err();
+  return b.unwrap()->neg(*this);
+}
+inline Result<Tensor> Tensor::sum(const std::vector<size_t> &axes) const {
+  auto b = backend_for(device());
+  if (b.is_err()) return b.unwrap_err();
+  return b.unwrap()->sum(*this, axes);
+}
 inline Result<Tensor> Tensor::contiguous() const {
   if (layout_.is_contiguous()) return *this;
   if (const uint8_t *src = storage_->cpu_bytes()) {
@@ -489,6 +552,50 @@ class B200Backend : public Backend {
 
   Result<Tensor> matmul(const Tensor &lhs, const Tensor &rhs) override { return run(lhs, rhs, false); }
   Result<Tensor> batched_matmul(const Tensor &lhs, const Tensor &rhs) override { return run(lhs, rhs, true); }
+
+  Result<Tensor> neg(const Tensor &a) override { return unary(OXM_NEG, "neg", a); }
+  Result<Tensor> exp(const Tensor &a) override { return unary(OXM_EXP, "exp", a); }
+  Result<Tensor> ln(const Tensor &a) override { return unary(OXM_LN, "ln", a); }
+  Result<Tensor> abs(const Tensor &a) override { return unary(OXM_ABS, "abs", a); }
+  Result<Tensor> add(const Tensor &l, const Tensor &r) override { return binary(OXM_ADD, "add", l, r); }
+  Result<Tensor> sub(const Tensor &l, const Tensor &r) override { return binary(OXM_SUB, "sub", l, r); }
+  Result<Tensor> mul(const Tensor &l, const Tensor &r) override { return binary(OXM_MUL, "mul", l, r); }
+  Result<Tensor> div(const Tensor &l, const Tensor &r) override { return binary(OXM_DIV, "div", l, r); }
+  Result<Tensor> sum(const Tensor &a, const std::vector<size_t> &axes) override { return reduce(OXM_SUM, "sum", a, axes); }
+  Result<Tensor> max(const Tensor &a, const std::vector<size_t> &axes) override { return reduce(OXM_MAX, "max", a, axes); }
+
+  // The fused form of a linear layer's product (no counterpart in the reference's traits):
+  // out = act(lhs . rhs + bias), or out += lhs . rhs when `accumulate_into` is given.
+  Result<Tensor> matmul_fused(const Tensor &lhs, const Tensor &rhs, const Tensor *bias, int activation,
+                              const Tensor *accumulate_into = nullptr) {
+    for (const Tensor *t : {&lhs, &rhs}) {
+      if (!(t->device() == device())) {
+        Error e{Error::Kind::DeviceMismatch};
+        e.lhs_device = t->device(); e.rhs_device = device(); e.op = "matmul_fused";
+        return e;
+      }
+    }
+    if (lhs.shape().ndim() != 2 || rhs.shape().ndim() != 2) {
+      Error e{Error::Kind::NotImplemented};
+      e.op = "matmul_fused"; e.detail = "operands of rank other than 2";
+      return e;
+    }
+    Result<Tensor> out = accumulate_into ? Result<Tensor>(*accumulate_into)
+                                         : empty(Shape{lhs.shape().dims()[0], rhs.shape().dims()[1]}, lhs.dtype());
+    if (out.is_err()) return out;
+    oxm_view a = view(lhs), b = view(rhs), o = view(out.unwrap()), bv{};
+    oxm_epilogue ep{};
+    if (bias) { bv = view(*bias); ep.bias = &bv; }
+    ep.activation = activation;
+    ep.accumulate = accumulate_into ? 1 : 0;
+    const int st = oxm_matmul_fused(ctx_, &a, &b, &o, &ep);
+    if (st != OXM_OK) {
+      Error e = from_status(st, "matmul_fused", lhs.device(), rhs.device());
+      e.expected = lhs.shape(); e.got = rhs.shape();
+      return e;
+    }
+    return out;
+  }
 
   Result<Tensor> contiguous(const Tensor &t) override {
     auto out = empty(t.shape(), t.dtype());
@@ -564,6 +671,71 @@ class B200Backend : public Backend {
     e.detail = oxm_last_error();
     e.lhs_device = lhs; e.rhs_device = rhs;
     return e;
+  }
+
+  Result<Tensor> unary(int code, const char *op, const Tensor &a) {
+    if (!(a.device() == device())) {
+      Error e{Error::Kind::DeviceMismatch};
+      e.lhs_device = a.device(); e.rhs_device = device(); e.op = op;
+      return e;
+    }
+    auto out = empty(a.shape(), a.dtype());
+    if (out.is_err()) return out;
+    oxm_view v = view(a), o = view(out.unwrap());
+    const int st = oxm_unary(ctx_, code, &v, &o);
+    if (st != OXM_OK) return from_status(st, op, a.device(), device());
+    return out;
+  }
+
+  Result<Tensor> binary(int code, const char *op, const Tensor &l, const Tensor &r) {
+    for (const Tensor *t : {&l, &r}) {
+      if (!(t->device() == device())) {
+        Error e{Error::Kind::DeviceMismatch};
+        e.lhs_device = t->device(); e.rhs_device = device(); e.op = op;
+        return e;
+      }
+    }
+    auto shape = broadcast_shapes(l.shape(), r.shape());
+    if (shape.is_err()) return shape.unwrap_err();
+    auto out = empty(shape.unwrap(), l.dtype());
+    if (out.is_err()) return out;
+    oxm_view a = view(l), b = view(r), o = view(out.unwrap());
+    const int st = oxm_binary(ctx_, code, &a, &b, &o);
+    if (st != OXM_OK) {
+      Error e = from_status(st, op, l.device(), r.device());
+      e.expected = l.shape(); e.got = r.shape();
+      return e;
+    }
+    return out;
+  }
+
+  Result<Tensor> reduce(int code, const char *op, const Tensor &a, const std::vector<size_t> &axes) {
+    if (!(a.device() == device())) {
+      Error e{Error::Kind::DeviceMismatch};
+      e.lhs_device = a.device(); e.rhs_device = device(); e.op = op;
+      return e;
+    }
+    const size_t nd = a.shape().ndim();
+    std::vector<bool> gone(nd, axes.empty());
+    std::vector<int32_t> ax;
+    for (size_t x : axes) {
+      if (x >= nd || gone[x]) {
+        Error e{Error::Kind::IndexOutOfBounds};
+        e.index = {x}; e.got = a.shape();
+        return e;
+      }
+      gone[x] = true;
+      ax.push_back(static_cast<int32_t>(x));
+    }
+    Dims kept;
+    for (size_t d = 0; d < nd; ++d)
+      if (!gone[d]) kept.push_back(a.shape().dims()[d]);
+    auto out = empty(Shape(kept), a.dtype());
+    if (out.is_err()) return out;
+    oxm_view v = view(a), o = view(out.unwrap());
+    const int st = oxm_reduce(ctx_, code, &v, ax.empty() ? nullptr : ax.data(), static_cast<int>(ax.size()), &o);
+    if (st != OXM_OK) return from_status(st, op, a.device(), device());
+    return out;
   }
 
   Result<Tensor> run(const Tensor &lhs, const Tensor &rhs, bool batched) {

@@ -203,9 +203,14 @@ static void expect_tensor(const Harness &h, Result<Tensor> got, const std::vecto
   CHECK(got.unwrap().shape() == shape);
   CHECK(got.unwrap().layout().is_contiguous());  // a fresh contiguous tensor (ops/lib.rs:16-17)
   Tensor c = h.host(got.unwrap());
-  size_t idx = 0;
-  for (size_t i = 0; i < shape.dims()[0]; ++i)
-    for (size_t j = 0; j < shape.dims()[1]; ++j) CHECK(c.get_f32({i, j}).unwrap() == exp[idx++]);
+  std::vector<size_t> ix(shape.ndim(), 0);
+  for (size_t n = 0; n < shape.numel(); ++n) {  // row-major walk of any rank
+    CHECK(c.get_f32(ix).unwrap() == exp[n]);
+    for (size_t d = shape.ndim(); d-- > 0;) {
+      if (++ix[d] < shape.dims()[d]) break;
+      ix[d] = 0;
+    }
+  }
 }
 
 static void a4_reference_matmul(const Harness &h) {
@@ -298,6 +303,25 @@ int main(int argc, char **argv) {
     Tensor a = gpu->from_vec_f32({1, 2, 3, 4}, Shape{2, 2}).unwrap(), b = gpu->from_vec_f32({5, 6, 7, 8}, Shape{2, 2}).unwrap();
     CHECK(gpu->to_host(a.matmul(b).unwrap()).unwrap().get_f32({0, 1}).unwrap() == 22.0f);
     CHECK(gpu->matmul(a, t({5, 6, 7, 8}, Shape{2, 2})).unwrap_err().kind == Error::Kind::DeviceMismatch);
+    // the other op families of the Backend trait (ops/lib.rs:27-69), through the tensor surface
+    Tensor row = gpu->from_vec_f32({10, 20}, Shape{2}).unwrap();
+    expect_tensor(h, a.add(row), {11, 22, 13, 24}, Shape{2, 2});            // NumPy broadcast of a row
+    expect_tensor(h, a.sub(b), {-4, -4, -4, -4}, Shape{2, 2});
+    expect_tensor(h, a.mul(b.permute({1, 0}).unwrap()), {5, 14, 18, 32}, Shape{2, 2});  // a transposed view
+    expect_tensor(h, b.div(a), {5, 3, 7.0f / 3.0f, 2}, Shape{2, 2});
+    expect_tensor(h, a.neg(), {-1, -2, -3, -4}, Shape{2, 2});
+    expect_tensor(h, gpu->abs(a.neg().unwrap()), {1, 2, 3, 4}, Shape{2, 2});
+    expect_tensor(h, a.sum({}), {10}, Shape{});
+    expect_tensor(h, a.sum({0}), {4, 6}, Shape{2});
+    expect_tensor(h, gpu->max(a, {1}), {2, 4}, Shape{2});
+    CHECK(a.sum({2}).unwrap_err().kind == Error::Kind::IndexOutOfBounds);
+    CHECK(a.add(gpu->from_vec_f32({1, 2, 3}, Shape{3}).unwrap()).unwrap_err().kind == Error::Kind::BroadcastIncompatible);
+    // fused linear-layer forms: relu(a.b + bias), then an accumulation on top of it
+    Tensor bias = gpu->from_vec_f32({-30, 0}, Shape{2}).unwrap();
+    auto fused = gpu->matmul_fused(a, b, &bias, OXM_ACT_RELU);
+    expect_tensor(h, fused, {0, 22, 13, 50}, Shape{2, 2});
+    Tensor acc = fused.unwrap();
+    expect_tensor(h, gpu->matmul_fused(a, b, nullptr, OXM_ACT_NONE, &acc), {19, 44, 56, 100}, Shape{2, 2});
     unregister_all();
   }
   std::printf("%s: %d checks, %d failed\n", mode.c_str(), g_checks, g_failed);
