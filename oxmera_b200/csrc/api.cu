@@ -469,11 +469,15 @@ constexpr int kMaxChainKb = 3 * 1024 / 32;
 //     contraction blocks at the shape's measured rate, or its epilogue when the
 //     contraction is too short to hide it;
 //   - the unique bytes over HBM bandwidth (reads and writes at their own rates).
-// A product with one or two rows (or columns) of tiles streams every stage from
-// HBM with all CTAs in step; a stage then takes ~0.35 us whatever its size
-// (measured: [1..128, 8192] x [8192, 8192] takes 45.7 us at every tile width and
-// CTA count), so such products want a split contraction: fewer steps per CTA
-// and several slabs of the long operand in flight at once.
+// One CTA cannot finish a contraction block faster than ~0.3 us whatever the
+// tile's width (measured on a single L2-resident tile, K = 8192: 128 x 64 takes
+// 41 us, 128 x 256 43 us; spreading the block's four tcgen05.mma over
+// independent accumulators changed nothing, so it is the issuing thread's
+// ~120 clocks per tcgen05 instruction, not a dependency).  At 256 columns that
+// equals the tensor pipe's own time; narrower tiles leave the pipe idle.  So
+// products too skinny to fill the SMs with 256-wide tiles get a split
+// contraction rather than narrow tiles: [1..128, 8192] x [8192, 8192] takes
+// 45.7 us unsplit at every tile width and 31 us split four ways.
 TileChoice choose_tiles(const oxm_ctx *ctx, const Problem &P, bool tf32, int32_t num_kb, int min_b_rows) {
   struct Cand { int bn, pair; double us_per_kb, us_epilogue; };
   // Microseconds per pipeline stage of one tile at the ~1.45 GHz the power cap
@@ -509,8 +513,7 @@ TileChoice choose_tiles(const oxm_ctx *ctx, const Problem &P, bool tf32, int32_t
     const int tm = kTileM * (c.pair ? 2 : 1);
     const int64_t tiles = ((P.M + tm - 1) / tm) * ((P.N + c.bn - 1) / c.bn) * P.nbatch;
     const int64_t slots = c.pair ? ctx->num_sms / 2 : ctx->num_sms;
-    const bool streaming = (P.M + tm - 1) / tm <= 2 || (P.N + c.bn - 1) / c.bn <= 2;
-    const double kb_us = std::max(c.us_per_kb, streaming ? 0.35 : 0.0);
+    const double kb_us = std::max(c.us_per_kb, 0.30);
     for (int m : mult) {
       const int32_t splits = min_splits * m;
       if (m > 1 && (ctx->opt_split_k == 0 || num_kb / splits < 16)) break;

@@ -105,9 +105,13 @@ struct WaitCtx {
 };
 
 // Wait for `parity` of `bar` with a time bound.  Returns false when the CTA is
-// aborting (either this wait expired or another one did).
+// aborting (either this wait expired or another one did).  The clock is only
+// consulted after a few hundred failed polls: reading %globaltimer costs a
+// sizeable fraction of a microsecond, which a wait that data in flight is
+// about to satisfy must not pay.
 __device__ __forceinline__ bool bounded_wait(uint32_t bar, uint32_t parity, const WaitCtx &w) {
-  if (ptx::mbar_try_wait(bar, parity)) return true;
+  for (int i = 0; i < 512; ++i)
+    if (ptx::mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = ptx::globaltimer_ns();
   for (;;) {
     for (int i = 0; i < 64; ++i)
