@@ -254,6 +254,16 @@ int oxm_launch_counts(oxm_ctx *ctx, int64_t counts[4]);
 /* Name of the compute kernel the last matmul on this context selected. */
 const char *oxm_last_kernel(oxm_ctx *ctx);
 
+/* The decisions oxm_batched_matmul would take for these views on a GPU of
+ * `num_sms` SMs with default options; runs on the host alone (no context, no
+ * GPU; storage pointers are only inspected for alignment).  No counterpart in
+ * the reference: it exists so that the planner can be tested where there is
+ * no GPU.  plan[0] kernel (0 nothing to launch, 1 FFMA, 2 tcgen05), plan[1]
+ * tile width, plan[2] CTA pairs, plan[3] contraction chains (split-K factor),
+ * plan[4] / plan[5] whether A / B is packed first (1) or read in place (0).
+ * Validation errors are those of oxm_batched_matmul. */
+int oxm_plan_matmul(const oxm_view *a, const oxm_view *b, const oxm_view *out, int num_sms, int32_t plan[6]);
+
 #ifdef __cplusplus
 }
 #endif

@@ -19,7 +19,7 @@ EXPORTS = [
     "oxm_matmul", "oxm_batched_matmul", "oxm_batched_matmul_host", "oxm_contiguous",
     "oxm_matmul_f32_noalloc", "oxm_matmul_fused", "oxm_unary", "oxm_binary", "oxm_reduce",
     "oxm_event_create", "oxm_event_destroy", "oxm_event_record", "oxm_event_elapsed_ms", "oxm_stream_handle", "oxm_fill", "oxm_selftest_bounded_wait",
-    "oxm_set_option", "oxm_get_option", "oxm_launch_counts", "oxm_last_kernel",
+    "oxm_set_option", "oxm_get_option", "oxm_launch_counts", "oxm_last_kernel", "oxm_plan_matmul",
 ]
 
 OK, SHAPE_MISMATCH, BROADCAST_INCOMPATIBLE, DTYPE_MISMATCH, UNSUPPORTED_DTYPE = 0, 1, 2, 3, 4
@@ -123,6 +123,7 @@ def load() -> C.CDLL:
         "oxm_get_option": ([p, C.c_char_p, C.POINTER(i64)], i),
         "oxm_launch_counts": ([p, C.POINTER(i64)], i),
         "oxm_last_kernel": ([p], C.c_char_p),
+        "oxm_plan_matmul": ([PV, PV, PV, i, C.POINTER(C.c_int32)], i),
     }
     for name, (argtypes, restype) in sig.items():
         fn = getattr(lib, name)  # AttributeError if the library lacks a declared symbol

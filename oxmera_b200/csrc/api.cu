@@ -537,6 +537,13 @@ TileChoice choose_tiles(const oxm_ctx *ctx, const Problem &P, bool tf32, int32_t
   return best;
 }
 
+// Where the FFMA kernel and the tensor-core path cross on this GPU (the f32 path has two pack
+// launches in front of its GEMM).
+bool wants_tensor_cores(const Problem &P) {
+  const double flops = 2.0 * (double)P.M * (double)P.N * (double)P.K * (double)P.nbatch;
+  return P.K > 0 && flops >= (P.elt == 4 ? 3.0e7 : 8.0e6);
+}
+
 int launch_tcgen05(oxm_ctx *ctx, const Problem &P) {
   if (P.nbd > kMaxBatchDims) return fail(OXM_NOT_IMPLEMENTED, "matmul is not implemented for %d batch dims", P.nbd);
   if (P.M >= (1ll << 31) || P.N >= (1ll << 31) || P.K >= (1ll << 29) || P.nbatch >= (1ll << 31))
@@ -711,13 +718,39 @@ int run_matmul(oxm_ctx *ctx, const oxm_view *a, const oxm_view *b, const oxm_vie
   CUDA_TRY(cudaSetDevice(ctx->device));
   // Small products and empty contractions go to the FFMA kernel; the rest to
   // the tensor cores.  Both are GPU kernels; there is no host path.
-  const double flops = 2.0 * (double)P.M * (double)P.N * (double)P.K * (double)P.nbatch;
   bool use_tc;
   if (ctx->opt_kernel == 1) use_tc = false;
   else if (ctx->opt_kernel == 2) use_tc = P.K > 0;
-  else use_tc = P.K > 0 && flops >= (P.elt == 4 ? 3.0e7 : 8.0e6);
+  else use_tc = wants_tensor_cores(P);
   return use_tc ? launch_tcgen05(ctx, P) : launch_simt(ctx, P);
 }
+
+}  // namespace
+
+// The decisions run_matmul would take for these views with default options, without touching a GPU.
+extern "C" int oxm_plan_matmul(const oxm_view *a, const oxm_view *b, const oxm_view *out, int num_sms, int32_t plan[6]) {
+  if (!a || !b || !out || !plan || num_sms < 2) return fail(OXM_INVALID_ARGUMENT, "plan_matmul: null argument or fewer than 2 SMs");
+  oxm_ctx fake;
+  fake.device = a->device;
+  fake.num_sms = num_sms;
+  int st = validate(&fake, a, b, out, true, false);
+  if (st) return st;
+  const Problem P = normalise(a, b, out);
+  for (int i = 0; i < 6; ++i) plan[i] = 0;
+  if (P.M == 0 || P.N == 0 || P.nbatch == 0) return OXM_OK;  // nothing to launch
+  if (!wants_tensor_cores(P)) { plan[0] = 1; return OXM_OK; }
+  const bool tf32 = P.elt == 4;
+  Staged sa{}, sb{};
+  const bool a_direct = stage_direct(P, false, sa), b_direct = stage_direct(P, true, sb);
+  const int64_t Kst = tf32 ? 3 * ((P.K + 31) / 32 * 32) : P.K;
+  const int bk = kStageKBytes / P.elt;
+  const TileChoice c = choose_tiles(&fake, P, tf32, (int32_t)((Kst + bk - 1) / bk), (P.elt == 1 && b_direct && sb.mn_major) ? 128 : 0);
+  plan[0] = 2; plan[1] = c.bn; plan[2] = c.pair; plan[3] = c.splits;
+  plan[4] = a_direct ? 0 : 1; plan[5] = b_direct ? 0 : 1;
+  return OXM_OK;
+}
+
+namespace {
 
 int check_status(oxm_ctx *ctx) {
   CUDA_TRY(cudaMemcpyAsync(ctx->status_host, ctx->status_dev, sizeof(uint32_t), cudaMemcpyDeviceToHost, ctx->stream));
