@@ -241,6 +241,12 @@ int oxm_selftest_bounded_wait(oxm_ctx *ctx, int64_t limit_ms);
  *   "tma_store"   1 (default) write results with bulk tensor stores when the
  *                 output allows it, 0 always use plain strided stores
  *   "group_m"     0 auto, else the number of tile rows walked together
+ *   "stream_k"    -1 auto, 0 whole tiles only, 1 share the last tiles out by
+ *                 contraction block whenever the tile count does not divide
+ *                 by the SM count ("split_k" 0 also turns this off: one
+ *                 accumulation chain per output element).  Auto uses it only
+ *                 where whole waves of ordinary tiles run beside the
+ *                 shared-out ones and the model sees more than 12 us saved
  *   "wait_limit_ms"  bound of every device-side wait (default 2000, or the
  *                 environment variable OXM_WAIT_LIMIT_MS at context creation)
  * Unknown keys or values are OXM_INVALID_ARGUMENT. */
@@ -260,9 +266,11 @@ const char *oxm_last_kernel(oxm_ctx *ctx);
  * the reference: it exists so that the planner can be tested where there is
  * no GPU.  plan[0] kernel (0 nothing to launch, 1 FFMA, 2 tcgen05), plan[1]
  * tile width, plan[2] CTA pairs, plan[3] contraction chains (split-K factor),
- * plan[4] / plan[5] whether A / B is packed first (1) or read in place (0).
+ * plan[4] / plan[5] whether A / B is packed first (1) or read in place (0),
+ * plan[6] how many of the last tiles are shared out by contraction block
+ * (stream-K; 0 = whole tiles only), plan[7] reserved (0).
  * Validation errors are those of oxm_batched_matmul. */
-int oxm_plan_matmul(const oxm_view *a, const oxm_view *b, const oxm_view *out, int num_sms, int32_t plan[6]);
+int oxm_plan_matmul(const oxm_view *a, const oxm_view *b, const oxm_view *out, int num_sms, int32_t plan[8]);
 
 #ifdef __cplusplus
 }

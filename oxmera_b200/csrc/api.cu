@@ -47,6 +47,8 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t
                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
+constexpr size_t kSkFlagWords = 256 * 8;  // up to 256 SMs, 8 epilogue warps each
+
 struct Workspace {
   void *ptr = nullptr;
   size_t bytes = 0;
@@ -60,6 +62,8 @@ struct oxm_ctx {
   cudaStream_t stream = nullptr;
   uint32_t *status_dev = nullptr;   // device status word written by kernels
   uint32_t *status_host = nullptr;  // pinned mirror
+  uint32_t *sk_flags = nullptr;     // stream-K publication counters, one per (run, CTA of the pair, epilogue warp)
+  uint32_t sk_epoch = 0;            // launch counter the flags are compared against
   EncodeTiledFn encode = nullptr;
   std::mutex mu;
   std::mutex host_mu;  // serialises calls that use the host staging buffers
@@ -68,7 +72,7 @@ struct oxm_ctx {
   cudaStream_t copy_in = nullptr, copy_out = nullptr;  // host entry point: copies overlapped with compute
   cudaEvent_t pipe_events[2 * 16 + 1] = {};
   // options
-  int64_t opt_kernel = 0, opt_tile_n = 0, opt_cta_pair = -1, opt_wait_limit_ms = 2000, opt_group_m = 0, opt_tma_store = 1, opt_split_k = -1, opt_host_chunks = 0;
+  int64_t opt_kernel = 0, opt_tile_n = 0, opt_cta_pair = -1, opt_wait_limit_ms = 2000, opt_group_m = 0, opt_tma_store = 1, opt_split_k = -1, opt_host_chunks = 0, opt_stream_k = -1;
   int64_t launches[4] = {0, 0, 0, 0};
   char last_kernel[96] = "none";
 };
@@ -457,7 +461,20 @@ bool make_out_map(oxm_ctx *ctx, CUtensorMap *tm, void *ptr, int dtype, int elt, 
 // Tile shape, CTA pairing and split-K factor for one product.
 struct TileChoice {
   int bn, pair, splits;
+  int64_t sk_tiles;  // > 0: that many of the last tiles are shared out by contraction block (stream-K)
 };
+
+// Stream-K applies when the tile count does not divide by the number of CTAs
+// (or pairs): the remainder, plus one whole wave when the remainder is less
+// than half a wave, is cut into equal runs, so that no tile is split more than
+// three ways.  Returns the number of tiles shared out that way, or 0.
+int64_t stream_k_tiles(int64_t tiles, int64_t slots, int32_t num_kb) {
+  const int64_t full = tiles / slots, r = tiles % slots;
+  if (r == 0 || num_kb < 16) return 0;
+  if (r * 2 >= slots) return r;
+  if (full == 0) return 0;  // fewer than half a wave of tiles: a split contraction serves better
+  return slots + r;
+}
 
 // The longest accumulation chain the f32 path allows, in pipeline stages (K = 1024).
 constexpr int kMaxChainKb = 3 * 1024 / 32;
@@ -490,7 +507,7 @@ TileChoice choose_tiles(const oxm_ctx *ctx, const Problem &P, bool tf32, int32_t
   constexpr double kHbmWrite = 4.3e6;   // ... and to it (measured on products that only write)
   const int32_t min_splits = tf32 ? std::max(1, (num_kb + kMaxChainKb - 1) / kMaxChainKb) : 1;
   static const int mult[] = {1, 2, 3, 4, 6, 8, 12, 16, 24, 32, 48, 64};
-  TileChoice best{256, 0, min_splits};
+  TileChoice best{256, 0, min_splits, 0};
   double best_t = 1e300;
   double a_nb = 1, b_nb = 1;  // batches each operand owns (broadcast dims repeat one copy)
   for (int d = 0; d < P.nbd; ++d) {
@@ -526,11 +543,25 @@ TileChoice choose_tiles(const oxm_ctx *ctx, const Problem &P, bool tf32, int32_t
       // short for the previous tile's stores to drain meanwhile
       const double tile_us = c.bn > 256 ? kb * kb_us + c.us_epilogue * (kb < 16 ? 2.0 : 1.0)
                                         : std::max(kb * kb_us + 0.3, c.us_epilogue);
-      const double wave_us = (double)waves * tile_us;
+      double wave_us = (double)waves * tile_us;
+      // Stream-K: every CTA gets the same number of blocks, at the price of one more epilogue and
+      // the hand-over of a partial tile (~12 us), and of CTAs that walk K out of step, so that
+      // tiles sharing an operand panel stop sharing its L2 lines.  Measured: it pays when whole
+      // waves of ordinary tiles run beside the shared-out ones (4096^3: 127 -> 116 us; the weight
+      // gradient of the linear layer: 427 -> 412 us) and loses badly when every tile is shared
+      // out (1024 x 8192 x 8192: 97 -> 125 us).  Automatic only in the first situation.
+      int64_t sk = 0;
+      if (splits == 1 && ctx->opt_stream_k != 0 && ctx->opt_split_k != 0) {
+        sk = stream_k_tiles(tiles, slots, kb);
+        const double even_us = (double)tiles / (double)slots * tile_us + 12.0;
+        const bool whole_waves_beside = tiles - sk >= slots;
+        if (sk > 0 && (ctx->opt_stream_k == 1 || (whole_waves_beside && even_us < wave_us))) wave_us = std::min(wave_us, even_us);
+        else sk = 0;
+      }
       double t = std::max(wave_us, hbm_us) + 0.01 * wave_us;  // the second term orders memory-bound ties
       if (splits > 1) t += 4.0 + slab_bytes * (splits + 1) / 4.0e6;  // launch + traffic of the reduction
       if (splits == min_splits ? t <= best_t : t < best_t) {  // ties go to the narrower, later candidate
-        best_t = t; best = TileChoice{c.bn, c.pair, splits};
+        best_t = t; best = TileChoice{c.bn, c.pair, splits, sk};
       }
     }
   }
@@ -637,6 +668,23 @@ int launch_tcgen05(oxm_ctx *ctx, const Problem &P) {
     p.num_tiles *= p.splits;
   }
 
+  p.dp_tiles = p.num_tiles;
+  p.sk_tiles = 0;
+  if (p.splits == 1 && choice.sk_tiles > 0) {
+    const int64_t slots = pair ? ctx->num_sms / 2 : ctx->num_sms;
+    const size_t ws_bytes = (size_t)slots * (pair ? 2 : 1) * kTileM * bn * sizeof(float);
+    if ((size_t)slots * (pair ? 2 : 1) * 8 <= kSkFlagWords) {
+      int st2 = grow(ctx, ctx->pack_ws[2], ws_bytes);
+      if (st2) return st2;
+      p.sk_tiles = choice.sk_tiles;
+      p.dp_tiles = p.num_tiles - p.sk_tiles;
+      p.sk_ws = static_cast<float *>(ctx->pack_ws[2].ptr);
+      p.sk_flags = ctx->sk_flags;
+      if (++ctx->sk_epoch == 0) ctx->sk_epoch = 1;
+      p.sk_epoch = ctx->sk_epoch;
+    }
+  }
+
   CUtensorMap tmA, tmB, tmC;
   memset(&tmC, 0, sizeof(tmC));
   // Rows the box would fetch beyond the matrix are zero-filled at a cost per
@@ -664,7 +712,8 @@ int launch_tcgen05(oxm_ctx *ctx, const Problem &P) {
   if (ctx->opt_tma_store == 0) p.out_tma = 0;
 
   int grid;
-  if (pair) grid = 2 * (int)std::min<int64_t>(p.num_tiles, ctx->num_sms / 2);
+  if (p.sk_tiles > 0) grid = pair ? 2 * (ctx->num_sms / 2) : ctx->num_sms;  // every run needs its CTA
+  else if (pair) grid = 2 * (int)std::min<int64_t>(p.num_tiles, ctx->num_sms / 2);
   else grid = (int)std::min<int64_t>(p.num_tiles, ctx->num_sms);
 
   st = launch_gemm(ctx, kind, sa.mn_major, sb.mn_major, bn, pair, tmA, tmB, tmC, p, grid);
@@ -728,7 +777,7 @@ int run_matmul(oxm_ctx *ctx, const oxm_view *a, const oxm_view *b, const oxm_vie
 }  // namespace
 
 // The decisions run_matmul would take for these views with default options, without touching a GPU.
-extern "C" int oxm_plan_matmul(const oxm_view *a, const oxm_view *b, const oxm_view *out, int num_sms, int32_t plan[6]) {
+extern "C" int oxm_plan_matmul(const oxm_view *a, const oxm_view *b, const oxm_view *out, int num_sms, int32_t plan[8]) {
   if (!a || !b || !out || !plan || num_sms < 2) return fail(OXM_INVALID_ARGUMENT, "plan_matmul: null argument or fewer than 2 SMs");
   oxm_ctx fake;
   fake.device = a->device;
@@ -736,7 +785,7 @@ extern "C" int oxm_plan_matmul(const oxm_view *a, const oxm_view *b, const oxm_v
   int st = validate(&fake, a, b, out, true, false);
   if (st) return st;
   const Problem P = normalise(a, b, out);
-  for (int i = 0; i < 6; ++i) plan[i] = 0;
+  for (int i = 0; i < 8; ++i) plan[i] = 0;
   if (P.M == 0 || P.N == 0 || P.nbatch == 0) return OXM_OK;  // nothing to launch
   if (!wants_tensor_cores(P)) { plan[0] = 1; return OXM_OK; }
   const bool tf32 = P.elt == 4;
@@ -747,6 +796,7 @@ extern "C" int oxm_plan_matmul(const oxm_view *a, const oxm_view *b, const oxm_v
   const TileChoice c = choose_tiles(&fake, P, tf32, (int32_t)((Kst + bk - 1) / bk), (P.elt == 1 && b_direct && sb.mn_major) ? 128 : 0);
   plan[0] = 2; plan[1] = c.bn; plan[2] = c.pair; plan[3] = c.splits;
   plan[4] = a_direct ? 0 : 1; plan[5] = b_direct ? 0 : 1;
+  plan[6] = (int32_t)c.sk_tiles;
   return OXM_OK;
 }
 
@@ -830,6 +880,8 @@ int oxm_ctx_create(int device_index, oxm_ctx **out) {
   cudaError_t e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking);
   if (e == cudaSuccess) e = cudaMalloc(&ctx->status_dev, sizeof(uint32_t));
   if (e == cudaSuccess) e = cudaMemset(ctx->status_dev, 0, sizeof(uint32_t));
+  if (e == cudaSuccess) e = cudaMalloc(&ctx->sk_flags, kSkFlagWords * sizeof(uint32_t));
+  if (e == cudaSuccess) e = cudaMemset(ctx->sk_flags, 0, kSkFlagWords * sizeof(uint32_t));
   if (e == cudaSuccess) e = cudaHostAlloc(&ctx->status_host, sizeof(uint32_t), cudaHostAllocDefault);
   void *fn = nullptr;
   cudaDriverEntryPointQueryResult qres;
@@ -864,6 +916,7 @@ int oxm_ctx_destroy(oxm_ctx *ctx) {
   if (ctx->copy_in) cudaStreamDestroy(ctx->copy_in);
   if (ctx->copy_out) cudaStreamDestroy(ctx->copy_out);
   if (ctx->status_dev) cudaFree(ctx->status_dev);
+  if (ctx->sk_flags) cudaFree(ctx->sk_flags);
   if (ctx->status_host) cudaFreeHost(ctx->status_host);
   if (ctx->stream) cudaStreamDestroy(ctx->stream);
   delete ctx;
@@ -1576,6 +1629,7 @@ int oxm_set_option(oxm_ctx *ctx, const char *key, int64_t value) {
   else if (!strcmp(key, "cta_pair") && value >= -1 && value <= 1) ctx->opt_cta_pair = value;
   else if (!strcmp(key, "wait_limit_ms") && value >= 1 && value <= 600000) ctx->opt_wait_limit_ms = value;
   else if (!strcmp(key, "group_m") && value >= 0 && value <= 1024) ctx->opt_group_m = value;
+  else if (!strcmp(key, "stream_k") && value >= -1 && value <= 1) ctx->opt_stream_k = value;
   else if (!strcmp(key, "tma_store") && (value == 0 || value == 1)) ctx->opt_tma_store = value;
   else if (!strcmp(key, "split_k") && value >= -1 && value <= 64) ctx->opt_split_k = value;
   else if (!strcmp(key, "host_chunks") && value >= 0 && value <= 16) ctx->opt_host_chunks = value;
@@ -1591,6 +1645,7 @@ int oxm_get_option(oxm_ctx *ctx, const char *key, int64_t *value) {
   else if (!strcmp(key, "cta_pair")) *value = ctx->opt_cta_pair;
   else if (!strcmp(key, "wait_limit_ms")) *value = ctx->opt_wait_limit_ms;
   else if (!strcmp(key, "group_m")) *value = ctx->opt_group_m;
+  else if (!strcmp(key, "stream_k")) *value = ctx->opt_stream_k;
   else if (!strcmp(key, "tma_store")) *value = ctx->opt_tma_store;
   else if (!strcmp(key, "split_k")) *value = ctx->opt_split_k;
   else if (!strcmp(key, "host_chunks")) *value = ctx->opt_host_chunks;
@@ -1773,6 +1828,8 @@ extern "C" int oxm_matmul_f32_noalloc(oxm_ctx *ctx, const oxm_view *a, const oxm
   CUtensorMap tmA, tmB, tmC;
   memset(&tmC, 0, sizeof(tmC));
   p.out_tma = 0;  // plain strided stores: the output may be any view
+  p.dp_tiles = p.num_tiles;  // whole tiles only: stream-K would need a workspace
+  p.sk_tiles = 0;
   p.stage_tx = (uint32_t)(kStageKBytes * (kTileM + bn));
   st = make_map(ctx, &tmA, sa, OXM_F32, 4, kTileM, 32);
   if (st) return st;

@@ -66,6 +66,20 @@ struct GemmParams {
   int32_t splits, kb_per_split;
   int64_t tiles_per_split;
   int64_t split_ostride;  // elements
+  // Stream-K: the last `sk_tiles` tiles are cut into
+  // equal runs of contraction blocks, one run per CTA (or CTA pair), so that a
+  // tile count that does not divide by the SM count still keeps every SM busy
+  // to the end.  A run that starts inside a tile leaves its partial sums in
+  // `sk_ws`; the run holding the tile's first block adds them and writes the
+  // tile.  It evens out the block counts but staggers the CTAs along K, so
+  // tiles that share an operand panel no longer read it at the same time and
+  // L2 hits turn into HBM reads: the host uses it only where whole waves of
+  // ordinary tiles run beside the shared-out ones.
+  int64_t dp_tiles;       // tiles [0, dp_tiles) go round-robin as whole tiles; == num_tiles without stream-K
+  int64_t sk_tiles;       // tiles [dp_tiles, dp_tiles + sk_tiles) are shared out by contraction block
+  float *sk_ws;           // [run][cta of the pair][128][BN] partial sums
+  uint32_t *sk_flags;     // [run][cta of the pair][8 epilogue warps]: the launch counter of the last publication
+  uint32_t sk_epoch;      // this launch's counter value (never 0)
   int32_t group_m;        // tile rows walked together (L2 reuse)
   Epilogue epi;           // applied here unless the contraction is split (then by the reduction)
 };
@@ -166,6 +180,60 @@ __device__ __forceinline__ TileCoord decode_tile(const GemmParams &p, int64_t ti
   return c;
 }
 
+// The sequence of work items of one CTA (or CTA pair): first its run of the
+// stream-K region, then whole tiles round-robin.  Every role of the CTA walks
+// the same sequence.
+struct WorkItem {
+  int64_t tile;
+  int32_t kb0, nkb;  // blocks [kb0, kb0 + nkb) of the tile's own contraction range (-1: take the tile's)
+  int32_t kind;      // 0 whole tile, 1 owner (holds the first block, adds the others' partial sums), 2 contributor
+};
+
+// Run `r` of `runs` over `units` contraction blocks: equal shares, the first `units % runs` one longer.
+__device__ __forceinline__ void sk_run(int64_t units, int64_t runs, int64_t r, int64_t &begin, int64_t &end) {
+  const int64_t base = units / runs, rem = units % runs;
+  begin = r * base + min(r, rem);
+  end = begin + base + (r < rem ? 1 : 0);
+}
+
+struct WorkIter {
+  int64_t u, e;    // stream-K blocks still to do
+  int64_t dp;      // next whole tile
+  int64_t stride;  // CTAs (or pairs) in the grid
+  // Pair `who` takes run (stride - 1 - who): a run's partial sums are then always needed by a
+  // higher-numbered run, i.e. by a lower-numbered CTA, which was launched no later.
+  __device__ __forceinline__ void init(const GemmParams &p, int64_t who, int64_t stride_) {
+    stride = stride_;
+    dp = who;
+    u = e = 0;
+    if (p.sk_tiles > 0) sk_run(p.sk_tiles * p.num_kb, stride, stride - 1 - who, u, e);
+  }
+  __device__ __forceinline__ bool next(const GemmParams &p, WorkItem &w) {
+    if (u < e) {
+      const int64_t t = u / p.num_kb;
+      w.tile = p.dp_tiles + t;
+      w.kb0 = static_cast<int32_t>(u - t * p.num_kb);
+      w.nkb = static_cast<int32_t>(min(static_cast<int64_t>(p.num_kb - w.kb0), e - u));
+      w.kind = w.nkb == p.num_kb ? 0 : (w.kb0 == 0 ? 1 : 2);
+      u += w.nkb;
+      return true;
+    }
+    if (dp < p.dp_tiles) {
+      w.tile = dp;
+      w.kb0 = -1; w.nkb = -1; w.kind = 0;
+      dp += stride;
+      return true;
+    }
+    return false;
+  }
+};
+
+__device__ __forceinline__ TileCoord decode_item(const GemmParams &p, const WorkItem &w) {
+  TileCoord c = decode_tile(p, w.tile);
+  if (w.kb0 >= 0) { c.kb0 = w.kb0; c.nkb = w.nkb; }
+  return c;
+}
+
 template <int BN, int STAGES, int A_MN, int B_MN, int KIND, int PAIR>
 __global__ void __launch_bounds__(gemm_threads(BN), 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -252,8 +320,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     if (lane == 0) {
       uint32_t s = 0, ph = 0;
       bool ok = true;
-      for (int64_t tile = tile_first; ok && tile < p.num_tiles; tile += tile_stride) {
-        const TileCoord tc = decode_tile(p, tile);
+      WorkIter it;
+      WorkItem wi;
+      it.init(p, tile_first, tile_stride);
+      while (ok && it.next(p, wi)) {
+        const TileCoord tc = decode_item(p, wi);
         const int32_t m0 = tc.m_blk * TM + static_cast<int32_t>(cta_rank) * kTileM;
         const int32_t n0 = tc.n_blk * BN + static_cast<int32_t>(cta_rank) * SUBC;  // + sub * SUBN per sub-tile
         for (int32_t kb = 0; kb < tc.nkb; ++kb) {
@@ -323,9 +394,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       constexpr uint32_t B_ADV = (B_MN ? MMA_K * kStageKBytes : kMmaKBytes) >> 4;
       uint32_t s = 0, ph = 0, as = 0, aph = 0;
       bool ok = true;
-      for (int64_t tile = tile_first; ok && tile < p.num_tiles; tile += tile_stride) {
-        const int32_t split = static_cast<int32_t>(tile / p.tiles_per_split);
-        const int32_t nkb = min(p.kb_per_split, p.num_kb - split * p.kb_per_split);
+      WorkIter it;
+      WorkItem wi;
+      it.init(p, tile_first, tile_stride);
+      while (ok && it.next(p, wi)) {
+        int32_t nkb = wi.nkb;
+        if (nkb < 0) {
+          const int32_t split = static_cast<int32_t>(wi.tile / p.tiles_per_split);
+          nkb = min(p.kb_per_split, p.num_kb - split * p.kb_per_split);
+        }
         if (!bounded_wait(tempty_bar(as), aph ^ 1u, wc)) break;
         ptx::tc_fence_after();
         const uint32_t d_tmem = tmem_base + as * BN;
@@ -370,12 +447,47 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     const uint32_t stage_smem = base + L::kStagingOffset + (warp - 2u) * L::kStagingTile;
     const int esz = p.out_dtype == 0 ? 4 : (p.out_dtype >= 8 ? 1 : 2);
     uint32_t as = 0, aph = 0;
-    for (int64_t tile = tile_first; tile < p.num_tiles; tile += tile_stride) {
-      const TileCoord tc = decode_tile(p, tile);
+    WorkIter it;
+    WorkItem wi;
+    it.init(p, tile_first, tile_stride);
+    const int64_t my_run = tile_stride - 1 - tile_first;  // this CTA's (pair's) stream-K run
+    constexpr int CPT = PAIR ? 2 : 1;
+    while (it.next(p, wi)) {
+      const TileCoord tc = decode_item(p, wi);
       // tcgen05.ld is warp-collective: leave the loop as a whole warp or not at all.
       const bool ready = bounded_wait(tfull_bar(as), aph, wc);
       if (!__all_sync(0xffffffffu, ready)) break;
       ptx::tc_fence_after();
+      // Stream-K: where this warp's part of a run's partial sums lives, and how many later runs
+      // hold the rest of an owned tile.
+      const int64_t sk_warp_elems = static_cast<int64_t>(kTileM) * BN;
+      float *sk_mine = p.sk_ws + (my_run * CPT + cta_rank) * sk_warp_elems;
+      int sk_others = 0;
+      if (wi.kind == 1) {
+        int32_t left = p.num_kb - wi.nkb;
+        bool arrived = true;
+        for (int64_t r = my_run + 1; left > 0 && r < tile_stride; ++r, ++sk_others) {
+          int64_t rb, re;
+          sk_run(p.sk_tiles * p.num_kb, tile_stride, r, rb, re);
+          left -= static_cast<int32_t>(min(re - rb, static_cast<int64_t>(left)));
+          // wait (bounded) until run r's warp of the same rows and columns has published its sums
+          const uint32_t *flag = p.sk_flags + (r * CPT + cta_rank) * 8 + (warp - 2u);
+          if (arrived && ptx::ld_acquire_gpu(flag) != p.sk_epoch) {
+            const uint64_t t0 = ptx::globaltimer_ns();
+            while (ptx::ld_acquire_gpu(flag) != p.sk_epoch) {
+              if (*wc.abort_flag) { arrived = false; break; }
+              if (ptx::globaltimer_ns() - t0 > wc.limit_ns) {
+                *wc.abort_flag = 1;
+                atomicCAS(wc.status, 0u, kStatusTimeout);
+                arrived = false;
+                break;
+              }
+              __nanosleep(200);
+            }
+          }
+        }
+        if (!__all_sync(0xffffffffu, arrived)) break;
+      }
       const int32_t row = tc.m_blk * TM + static_cast<int32_t>(cta_rank) * kTileM + static_cast<int32_t>(q * 32u + lane);
       const bool row_ok = row < p.M;
       uint8_t *rowp = static_cast<uint8_t *>(p.out) + (tc.o_off + static_cast<int64_t>(row) * p.out_rs) * esz;
@@ -464,6 +576,37 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             else ptx::mbar_arrive(tempty_bar(as));
           }
         }
+        if (wi.kind == 2) {
+          // contributor: this run started inside the tile; leave the raw sums for the tile's owner.
+          // The hand-over area is private to the two warps involved (same rows, same columns,
+          // same registers), so it is laid out by register: every store is 512 contiguous bytes.
+          uint4 *dst = reinterpret_cast<uint4 *>(sk_mine + static_cast<int64_t>(warp - 2u) * (32 * GROUP_COLS)) + lane;
+#pragma unroll
+          for (int i = 0; i < NLD; ++i) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              dst[((c * NLD + i) * 8 + j) * 32] = make_uint4(v[i][4 * j], v[i][4 * j + 1], v[i][4 * j + 2], v[i][4 * j + 3]);
+          }
+          continue;
+        }
+        if (wi.kind == 1) {
+          // owner: add the later runs' sums of these columns, in run order
+          for (int o = 0; o < sk_others; ++o) {
+            const float4 *src = reinterpret_cast<const float4 *>(p.sk_ws + ((my_run + 1 + o) * CPT + cta_rank) * sk_warp_elems +
+                                                                 static_cast<int64_t>(warp - 2u) * (32 * GROUP_COLS)) + lane;
+#pragma unroll
+            for (int i = 0; i < NLD; ++i) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                const float4 t = __ldcg(src + ((c * NLD + i) * 8 + j) * 32);
+                v[i][4 * j] = __float_as_uint(__uint_as_float(v[i][4 * j]) + t.x);
+                v[i][4 * j + 1] = __float_as_uint(__uint_as_float(v[i][4 * j + 1]) + t.y);
+                v[i][4 * j + 2] = __float_as_uint(__uint_as_float(v[i][4 * j + 2]) + t.z);
+                v[i][4 * j + 3] = __float_as_uint(__uint_as_float(v[i][4 * j + 3]) + t.w);
+              }
+            }
+          }
+        }
         const int32_t colb = col_base + c * BATCH;
         if (p.epi.any) {
           // bias, activation and accumulation on the fp32 sums, before rounding
@@ -516,6 +659,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 #pragma unroll
           for (int i = 0; i < NLD; ++i) store_chunk(v[i], colb + i * 32);
         }
+      }
+      if (wi.kind == 2) {
+        // publish: the sums above are visible to whoever reads this launch's counter here
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) ptx::st_release_gpu(p.sk_flags + (my_run * CPT + cta_rank) * 8 + (warp - 2u), p.sk_epoch);
       }
       if (++as == ACC) { as = 0; aph ^= 1u; }
     }

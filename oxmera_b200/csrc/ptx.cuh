@@ -26,6 +26,16 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
   return t;
 }
 
+// A flag another CTA of this GPU reads or writes: release / acquire at GPU scope.
+__device__ __forceinline__ void st_release_gpu(uint32_t *addr, uint32_t v) {
+  asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t *addr) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
+  return v;
+}
+
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
   asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));

@@ -55,6 +55,7 @@ def set_kernel(backend, name, tile_n=0, pair=-1):
     backend.set_option("tile_n", tile_n)
     backend.set_option("cta_pair", pair)
     backend.set_option("split_k", -1)
+    backend.set_option("stream_k", -1)
 
 
 @pytest.fixture(autouse=True)
@@ -307,6 +308,43 @@ def test_skinny_products(backend, oracle, dtype, b_t):
             assert "tcgen05" in backend.last_kernel(), backend.last_kernel()
         err = rel_err(to_f64(got.to_host(), dtype), oracle_ref(oracle, ha, hb, dtype))
         assert err <= TOL[dtype], ((m, n, k), err, backend.last_kernel())
+
+
+@pytest.mark.parametrize("dtype", [DType.BF16, DType.F32], ids=lambda d: d.name)
+def test_stream_k_shares_the_last_tiles_out_by_contraction_block(backend, oracle, dtype):
+    """Tile counts that do not divide by the SM count: the remainder (plus a
+    wave when it is small) is cut into equal runs of contraction blocks; runs
+    that start inside a tile hand their partial sums to the run that holds the
+    tile's first block.  Forced on here for every tile shape, with ragged
+    edges, and twice in a row (the hand-over flags carry a launch counter)."""
+    cases = [(64, 0, (1280, 650, 1024)),     # 110 tiles on 148 CTAs: all of them shared out
+             (128, 0, (1536, 1800, 1100)),   # 180 tiles: one wave and 32 more -> 180 shared out
+             (256, 1, (1536, 2048, 1024)),   # 48 pair tiles on 74 pairs
+             (512, 1, (2000, 3072, 1024)),   # 48 pair tiles of 256 x 512, one accumulator
+             (256, 0, (1024, 5120, 2048))]   # 160 tiles, 1-CTA 128 x 256
+    for tile_n, pair, (m, n, k) in cases:
+        if dtype == DType.F32 and k > 1024:
+            k = 1024  # longer f32 contractions are split into chains, which excludes stream-K
+        a, b = fill(oracle, (m, k), dtype, 61, 0), fill(oracle, (k, n), dtype, 61, 1)
+        ta, tb = Tensor.from_host(a, a.shape, dtype, backend), Tensor.from_host(b, b.shape, dtype, backend)
+        ref = oracle_ref(oracle, a, b, dtype)
+        set_kernel(backend, "tcgen05", tile_n=tile_n, pair=pair)
+        backend.set_option("stream_k", 0)
+        whole = backend.matmul(ta, tb).to_host()
+        backend.set_option("stream_k", 1)
+        try:
+            for _ in range(2):
+                got = backend.matmul(ta, tb).to_host()
+                err = rel_err(to_f64(got, dtype), ref)
+                assert err <= TOL[dtype], (tile_n, pair, (m, n, k), err, backend.last_kernel())
+            # the two schedules differ only in where the fp32 chains are cut
+            assert rel_err(to_f64(got, dtype), to_f64(whole, dtype)) <= (5e-5 if dtype == DType.F32 else 1e-2)
+            backend.set_option("tma_store", 0)  # the strided-store epilogue takes the same hand-over
+            got2 = backend.matmul(ta, tb).to_host()
+            assert np.array_equal(got, got2)
+        finally:
+            backend.set_option("tma_store", 1)
+            backend.set_option("stream_k", 0)
 
 
 def test_expired_device_wait_is_reported_and_survivable(backend):

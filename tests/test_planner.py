@@ -34,16 +34,16 @@ def plan(a, b, out_dtype=None, sms=148):
         y = lb[len(lb) - 1 - i] if i < len(lb) else 1
         lead.insert(0, max(x, y))
     out = view(out_dtype if out_dtype is not None else a.dtype, lead + [a.shape[a.ndim - 2], b.shape[b.ndim - 1]])
-    res = (C.c_int32 * 6)()
+    res = (C.c_int32 * 8)()
     st = capi.load().oxm_plan_matmul(C.byref(a), C.byref(b), C.byref(out), sms, res)
-    return st, dict(kernel=res[0], tile_n=res[1], pair=res[2], splits=res[3], pack_a=res[4], pack_b=res[5])
+    return st, dict(kernel=res[0], tile_n=res[1], pair=res[2], splits=res[3], pack_a=res[4], pack_b=res[5], stream_k=res[6])
 
 
 def test_the_five_configurations():
     bf, f32 = DType.BF16, DType.F32
     # c3: square, B column-major -> the widest pair tile, operands read in place
     st, p = plan(view(bf, [8192, 8192]), t(view(bf, [8192, 8192])))
-    assert st == 0 and p == dict(kernel=TCGEN05, tile_n=512, pair=1, splits=1, pack_a=0, pack_b=0)
+    assert st == 0 and {k: p[k] for k in ('kernel', 'tile_n', 'pair', 'splits', 'pack_a', 'pack_b')} == dict(kernel=TCGEN05, tile_n=512, pair=1, splits=1, pack_a=0, pack_b=0)
     # c4: 32 x [2048, 4096] . [4096, 11008]: 11008 is 43 tiles of 256 but 21.5 of 512
     st, p = plan(view(bf, [32, 2048, 4096]), view(bf, [4096, 11008]))
     assert st == 0 and (p["kernel"], p["tile_n"], p["pair"], p["splits"], p["pack_a"], p["pack_b"]) == (TCGEN05, 256, 1, 1, 0, 0)
@@ -52,7 +52,7 @@ def test_the_five_configurations():
     assert st == 0 and p["kernel"] == TCGEN05 and p["pair"] == 1 and p["splits"] == 1 and p["pack_a"] == p["pack_b"] == 0
     # c2: f32 goes through the TF32 split, which always packs; K = 1024 is one accumulation chain
     st, p = plan(t(view(f32, [8, 1, 1024, 512])), view(f32, [1, 16, 1024, 768]))
-    assert st == 0 and p == dict(kernel=TCGEN05, tile_n=256, pair=1, splits=1, pack_a=1, pack_b=1)
+    assert st == 0 and {k: p[k] for k in ('kernel', 'tile_n', 'pair', 'splits', 'pack_a', 'pack_b')} == dict(kernel=TCGEN05, tile_n=256, pair=1, splits=1, pack_a=1, pack_b=1)
     # c1: small f32 product, still past the crossover with the FFMA kernel
     st, p = plan(view(f32, [256, 512]), view(f32, [512, 384]))
     assert st == 0 and p["kernel"] == TCGEN05
@@ -107,6 +107,6 @@ def test_planner_validates_like_the_product():
     assert st == 3  # DTypeMismatch
     st, p = plan(view(bf, [0, 5]), view(bf, [5, 7]))
     assert st == 0 and p["kernel"] == 0
-    res = (C.c_int32 * 6)()
+    res = (C.c_int32 * 8)()
     a = view(bf, [4, 4])
     assert capi.load().oxm_plan_matmul(C.byref(a), C.byref(a), C.byref(a), 1, res) == 12  # InvalidArgument
