@@ -110,3 +110,22 @@ def test_planner_validates_like_the_product():
     res = (C.c_int32 * 8)()
     a = view(bf, [4, 4])
     assert capi.load().oxm_plan_matmul(C.byref(a), C.byref(a), C.byref(a), 1, res) == 12  # InvalidArgument
+
+
+def test_stream_k_only_beside_whole_waves():
+    bf = DType.BF16
+    # 512 tiles on 74 pairs = 6.92 waves: too little to gain
+    _, p = plan(view(bf, [8192, 8192]), t(view(bf, [8192, 8192])))
+    assert p["stream_k"] == 0
+    # the 8-GPU shard of the same product: 64 tiles, all of them would be shared out
+    _, p = plan(view(bf, [1024, 8192]), t(view(bf, [8192, 8192])))
+    assert p["stream_k"] == 0 and p["tile_n"] == 512
+    # the linear layer's weight gradient: 128 tiles of 256 x 512 = one wave and 54 more
+    _, p = plan(t(view(bf, [16384, 4096])), view(bf, [16384, 4096]))
+    assert (p["tile_n"], p["stream_k"]) == (512, 54)
+    # 4096^3: 256 tiles of 256 x 256 = 3 waves and 34 more -> the last wave and the remainder
+    _, p = plan(view(bf, [4096, 4096]), t(view(bf, [4096, 4096])))
+    assert (p["tile_n"], p["stream_k"]) == (256, 74 + 34)
+    # long f32 contractions are cut into chains instead
+    _, p = plan(view(DType.F32, [4096, 4096]), view(DType.F32, [4096, 4096]))
+    assert p["splits"] > 1 and p["stream_k"] == 0
