@@ -1315,6 +1315,7 @@ unsigned ew_plan_tiles(const oxm_ctx *ctx, EwParams &p, bool binary, int esz) {
   const int64_t R = p.shape[p.tile_r], C = p.shape[p.ndim - 1];
   const int64_t T = esz >= 8 ? 32 : 64;  // EwTile<T>
   const int64_t tiles = ((R + T - 1) / T) * ((C + T - 1) / T) * (p.n / (R * C));
+  if (tiles >= (1ll << 31)) { p.tile_r = -1; return 0; }  // the kernel counts tiles in 32 bits
   return (unsigned)std::min<int64_t>(tiles, (int64_t)ctx->num_sms * 16);
 }
 

@@ -203,7 +203,7 @@ __global__ void __launch_bounds__(256) ew_rows_kernel(const EwParams p) {
 template <typename T> struct EwTile { static constexpr int value = sizeof(T) >= 8 ? 32 : 64; };
 
 template <typename T, int MODE, bool A_TURN, bool B_TURN>
-__global__ void __launch_bounds__(256) ew_tile_kernel(const EwParams p) {
+__global__ void __launch_bounds__(256, (sizeof(T) >= 8 || MODE == 1) ? 4 : 6) ew_tile_kernel(const EwParams p) {
   using C = typename EwTraits<T>::C;
   constexpr int TILE = EwTile<T>::value, STEP = 256 / TILE, ITERS = TILE / STEP;
   __shared__ T sa[A_TURN ? TILE : 1][TILE + 1], sb[B_TURN ? TILE : 1][TILE + 1];
@@ -211,14 +211,17 @@ __global__ void __launch_bounds__(256) ew_tile_kernel(const EwParams p) {
   T *out = static_cast<T *>(p.out);
   const int nd = p.ndim - 1, rd = p.tile_r;
   const int64_t R = p.shape[rd], Cn = p.shape[nd];
-  const int64_t tiles_c = (Cn + TILE - 1) / TILE, tiles_r = (R + TILE - 1) / TILE;
-  const int64_t ntiles = tiles_c * tiles_r * (p.n / (R * Cn));
+  // tile counts fit 32 bits (the host checks): 64-bit divisions would cost more than the tile's own work
+  const uint32_t tiles_c = static_cast<uint32_t>((Cn + TILE - 1) / TILE), tiles_r = static_cast<uint32_t>((R + TILE - 1) / TILE);
+  const uint32_t per_batch = tiles_c * tiles_r;
+  const uint32_t ntiles = per_batch * static_cast<uint32_t>(p.n / (R * Cn));
   const int64_t asr = p.a_strides[rd], asc = p.a_strides[nd], bsr = p.b_strides[rd], bsc = p.b_strides[nd];
   const int tx = threadIdx.x % TILE, ty = threadIdx.x / TILE;
-  for (int64_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
-    const int64_t y = (tile / tiles_c) % tiles_r, x = tile % tiles_c;
-    const int64_t r0 = ((y + x) % tiles_r) * TILE, c0 = x * TILE;  // consecutive tiles step along a diagonal
-    int64_t t = tile / (tiles_c * tiles_r), ao = p.a_off, bo = p.b_off, oo = 0, os = Cn, osr = 0;
+  for (uint32_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+    const uint32_t batch = tile / per_batch, in_batch = tile - batch * per_batch;
+    const uint32_t y = in_batch / tiles_c, x = in_batch - y * tiles_c;
+    const int64_t r0 = static_cast<int64_t>((y + x) % tiles_r) * TILE, c0 = static_cast<int64_t>(x) * TILE;  // consecutive tiles step along a diagonal
+    int64_t t = batch, ao = p.a_off, bo = p.b_off, oo = 0, os = Cn, osr = 0;
     for (int d = nd - 1; d >= 0; --d) {
       if (d == rd) {
         osr = os;
@@ -232,21 +235,38 @@ __global__ void __launch_bounds__(256) ew_tile_kernel(const EwParams p) {
       os *= p.shape[d];
     }
     // every global load of the tile is issued before the first store: a turned
-    // operand along R into shared memory, any other in the output's own mapping
+    // operand along R into shared memory, any other in the output's own mapping.
+    // Addresses advance by one constant per step; tiles inside the matrix skip the edge tests.
+    const bool inside = r0 + TILE <= R && c0 + TILE <= Cn;
     const int64_t c = c0 + tx;
+    const T *pa_t = a + ao + (r0 + tx) * asr + (c0 + ty) * asc;  // turned mapping: thread x walks R
+    const T *pa_d = a + ao + (r0 + ty) * asr + c * asc;          // direct mapping: thread x walks C
+    const T *pb_t = b + bo + (r0 + tx) * bsr + (c0 + ty) * bsc;
+    const T *pb_d = b + bo + (r0 + ty) * bsr + c * bsc;
     T da[ITERS], db[MODE == 1 ? ITERS : 1];
     {
-      const int64_t r = r0 + tx;
       T va[ITERS], vb[MODE == 1 ? ITERS : 1];
+      if (inside) {
 #pragma unroll
-      for (int i = 0; i < ITERS; ++i) {
-        const int64_t ct = c0 + ty + STEP * i, rd2 = r0 + ty + STEP * i;
-        const bool in_t = r < R && ct < Cn, in_d = rd2 < R && c < Cn;
-        if constexpr (A_TURN) { if (in_t) va[i] = a[ao + r * asr + ct * asc]; }
-        else if (in_d) da[i] = a[ao + rd2 * asr + c * asc];
-        if constexpr (MODE == 1) {
-          if constexpr (B_TURN) { if (in_t) vb[i] = b[bo + r * bsr + ct * bsc]; }
-          else if (in_d) db[i] = b[bo + rd2 * bsr + c * bsc];
+        for (int i = 0; i < ITERS; ++i) {
+          if constexpr (A_TURN) va[i] = pa_t[i * STEP * asc];
+          else da[i] = pa_d[i * STEP * asr];
+          if constexpr (MODE == 1) {
+            if constexpr (B_TURN) vb[i] = pb_t[i * STEP * bsc];
+            else db[i] = pb_d[i * STEP * bsr];
+          }
+        }
+      } else {
+        const bool r_in = r0 + tx < R, c_in = c < Cn;
+#pragma unroll
+        for (int i = 0; i < ITERS; ++i) {
+          const bool in_t = r_in && c0 + ty + STEP * i < Cn, in_d = c_in && r0 + ty + STEP * i < R;
+          if constexpr (A_TURN) { if (in_t) va[i] = pa_t[i * STEP * asc]; }
+          else if (in_d) da[i] = pa_d[i * STEP * asr];
+          if constexpr (MODE == 1) {
+            if constexpr (B_TURN) { if (in_t) vb[i] = pb_t[i * STEP * bsc]; }
+            else if (in_d) db[i] = pb_d[i * STEP * bsr];
+          }
         }
       }
 #pragma unroll
@@ -257,19 +277,19 @@ __global__ void __launch_bounds__(256) ew_tile_kernel(const EwParams p) {
       }
     }
     __syncthreads();
+    T *po = out + oo + (r0 + ty) * osr + c;
 #pragma unroll
     for (int i = 0; i < ITERS; ++i) {
       const int rl = ty + STEP * i;
-      const int64_t r = r0 + rl;
-      if (r < R && c < Cn) {
+      if (inside || (r0 + rl < R && c < Cn)) {
         const T ra = A_TURN ? sa[rl][tx] : da[i];
         if constexpr (MODE == 2) {
-          out[oo + r * osr + c] = ra;
+          po[i * STEP * osr] = ra;
         } else if constexpr (MODE == 1) {
           const T rb = B_TURN ? sb[rl][tx] : db[i];
-          ew_store<T>(out, oo + r * osr + c, binary_apply<C>(p.op, ew_load<T>(&ra, 0), ew_load<T>(&rb, 0)));
+          ew_store<T>(po, i * STEP * osr, binary_apply<C>(p.op, ew_load<T>(&ra, 0), ew_load<T>(&rb, 0)));
         } else {
-          ew_store<T>(out, oo + r * osr + c, unary_apply<C>(p.op, ew_load<T>(&ra, 0)));
+          ew_store<T>(po, i * STEP * osr, unary_apply<C>(p.op, ew_load<T>(&ra, 0)));
         }
       }
     }
@@ -337,6 +357,7 @@ __global__ void __launch_bounds__(256) reduce_row_kernel(const ReduceOpParams p)
       const int64_t nv = (r1 - r0 - head) / V;
       if (static_cast<int64_t>(threadIdx.x) < head) acc = reduce_combine<C>(p.op, acc, ew_load<T>(run, r0 + threadIdx.x));
       const EwVec<T> *vec = reinterpret_cast<const EwVec<T> *>(run + r0 + head);
+#pragma unroll 4
       for (int64_t i = threadIdx.x; i < nv; i += 256) {
         const EwVec<T> x = vec[i];
 #pragma unroll
