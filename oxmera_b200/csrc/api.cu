@@ -1367,6 +1367,7 @@ template <typename T> struct ReduceLauncher {
   static int run(oxm_ctx *ctx, const ReduceOpParams &p, bool row_mode, unsigned blocks_x) {
     const dim3 grid(blocks_x, (unsigned)p.splits, 1);
     if (row_mode) reduce_row_kernel<T><<<grid, 256, 0, ctx->stream>>>(p);
+    else if (p.col_vec) reduce_colv_kernel<T><<<grid, 256, 0, ctx->stream>>>(p);
     else reduce_col_kernel<T><<<grid, 256, 0, ctx->stream>>>(p);
     if (p.splits > 1) {
       const unsigned fb = (unsigned)std::min<int64_t>((p.n_out + 255) / 256, (int64_t)ctx->num_sms * 8);
@@ -1583,7 +1584,14 @@ extern "C" int oxm_reduce(oxm_ctx *ctx, int op, const oxm_view *a, const int32_t
     blocks_x = (unsigned)std::min<int64_t>(p.n_out, 65535 * 16);
     max_splits = (p.n_red + 8191) / 8192;    // at least 8 Ki elements per slice
   } else {
-    blocks_x = (unsigned)std::min<int64_t>((p.n_out + 255) / 256, (int64_t)ctx->num_sms * 16);
+    // one contiguous run of kept elements, everything 16-byte aligned: 16 bytes of outputs per thread
+    const int esz = dtype_size(a->dtype), V = 16 / esz;
+    bool vec = p.nkept == 1 && p.kept_strides[0] == 1 && p.n_out % V == 0 &&
+               (reinterpret_cast<uintptr_t>(p.a) + p.a_off * esz) % 16 == 0 && reinterpret_cast<uintptr_t>(p.out) % 16 == 0;
+    for (int d = 0; vec && d < p.nred; ++d) vec = p.red_strides[d] % V == 0;
+    p.col_vec = vec ? 1 : 0;
+    const int64_t threads = vec ? p.n_out / V : p.n_out;
+    blocks_x = (unsigned)std::min<int64_t>((threads + 255) / 256, (int64_t)ctx->num_sms * 16);
     max_splits = (p.n_red + 63) / 64;        // at least 64 serial steps per thread
   }
   p.splits = (int32_t)std::max<int64_t>(1, std::min<int64_t>({(target + blocks_x - 1) / blocks_x, max_splits, (int64_t)1024}));

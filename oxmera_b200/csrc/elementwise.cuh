@@ -426,6 +426,7 @@ struct ReduceOpParams {
   void *out;       // final output (splits == 1) ...
   void *partial;   // ... or [splits][n_out] partial results in the compute type
   int32_t op, nkept, nred, splits;
+  int32_t col_vec;              // COL mapping with 16 bytes of neighbouring outputs per thread
   int64_t n_out, n_red, chunk;  // chunk: reduced elements per slice
   int64_t kept_shape[kEwMaxDims], kept_strides[kEwMaxDims];
   int64_t red_shape[kEwMaxDims], red_strides[kEwMaxDims];
@@ -511,6 +512,48 @@ __global__ void __launch_bounds__(256) reduce_col_kernel(const ReduceOpParams p)
     }
     if (p.splits == 1) ew_store<T>(static_cast<T *>(p.out), o, acc);
     else static_cast<C *>(p.partial)[blockIdx.y * p.n_out + o] = acc;
+  }
+}
+
+// COL mapping, 16 bytes wide: the kept elements are one contiguous run, so a
+// thread owns 16 / sizeof(T) neighbouring outputs and every load is a full
+// vector (the host checks alignment and that every reduced stride keeps it).
+template <typename T>
+__global__ void __launch_bounds__(256) reduce_colv_kernel(const ReduceOpParams p) {
+  using C = typename EwTraits<T>::C;
+  constexpr int V = 16 / sizeof(T);
+  const T *a = static_cast<const T *>(p.a);
+  const int64_t r0 = blockIdx.y * p.chunk, r1 = min(r0 + p.chunk, p.n_red);
+  const int64_t nvec = p.n_out / V;
+  for (int64_t ov = blockIdx.x * 256ll + threadIdx.x; ov < nvec; ov += static_cast<int64_t>(gridDim.x) * 256) {
+    const T *col = a + p.a_off + ov * V;
+    C acc[V];
+#pragma unroll
+    for (int e = 0; e < V; ++e) acc[e] = reduce_identity<C>(p.op);
+    if (p.nred == 1) {
+      const int64_t rs = p.red_strides[0];
+#pragma unroll 4
+      for (int64_t r = r0; r < r1; ++r) {
+        const EwVec<T> x = *reinterpret_cast<const EwVec<T> *>(col + r * rs);
+#pragma unroll
+        for (int e = 0; e < V; ++e) acc[e] = reduce_combine<C>(p.op, acc[e], ew_load<T>(x.v, e));
+      }
+    } else {
+      for (int64_t r = r0; r < r1; ++r) {
+        const EwVec<T> x = *reinterpret_cast<const EwVec<T> *>(col + unravel(r, p.nred, p.red_shape, p.red_strides));
+#pragma unroll
+        for (int e = 0; e < V; ++e) acc[e] = reduce_combine<C>(p.op, acc[e], ew_load<T>(x.v, e));
+      }
+    }
+    if (p.splits == 1) {
+      EwVec<T> o;
+#pragma unroll
+      for (int e = 0; e < V; ++e) ew_store<T>(o.v, e, acc[e]);
+      reinterpret_cast<EwVec<T> *>(p.out)[ov] = o;
+    } else {
+#pragma unroll
+      for (int e = 0; e < V; ++e) static_cast<C *>(p.partial)[blockIdx.y * p.n_out + ov * V + e] = acc[e];
+    }
   }
 }
 
