@@ -291,10 +291,10 @@ def run_ours(args):
         clocks.get("power_w") and clocks.get("power_limit_w") and clocks["power_w"] >= 0.9 * clocks["power_limit_w"])
     capped = bool(capped)
     # NVML's clock and power readings lag by up to a second on these hosts, so a
-    # region of 50 launches or 50 ms back to back counts as sustained whatever
-    # they say: every such run here measured the capped rate (8-GPU shards of
-    # 0.1 ms per step included).
-    burst = not capped and timed_s < 0.05 and args.steps < 50
+    # region of more than 50 ms of back-to-back launches counts as sustained
+    # whatever they say: a 42 ms region still ran at the uncapped rate here,
+    # regions of 150 ms at the capped one.
+    burst = not capped and timed_s < 0.05
     peak = peaks["bf16_tflops"] if burst else peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"])
     if w.dtype == DType.F32:
         peak = peak / 2.0  # tf32 runs at half the bf16 rate; the 3-term split spends 3 MMA flops per useful one
