@@ -10,12 +10,26 @@ torch.distributed.run) every rank multiplies its own slice of the batch dim
 or of A's rows; there is no exchange step, so the job is timed as the slowest
 rank and `value` is total flops / that time.
 
+Before anything is timed every rank checks its own shard's output: two float64
+checksums over the whole shard (C.1 against A.(B.1), 1^T.C against (1^T.A).B) on
+the host; a failing rank makes the run exit non-zero and `shards_checked` false.
+
 Prints ONE JSON line (rank 0).  Keys beyond the base contract:
-  roofline      the tcgen05 GEMM against the measured cuBLAS bf16 peak
+  roofline      the tcgen05 GEMM against the measured cuBLAS bf16 peak, for the
+                `--steps` region (`value`), plus `repeats` (best and median of
+                further repeats of that region), `sustained` (launches back to
+                back for two seconds and more: TFLOP/s, median SM clock of that
+                leg, cycles per launch = time x clock, fraction of the measured
+                sustained cuBLAS figure) and `cold_l2_ms` (one launch after
+                the L2 has been overwritten)
   cpu_baseline  the CPU oracle (a port of oxmera's naive reference matmul) on
                 a bounded slab of the same workload, all host threads
-  e2e           the same metric through the host-buffer entry point
-                (pinned host -> device, multiply, device -> pinned host)
+  e2e           the same metric with operands starting and the result ending
+                in page-locked host memory: through the host-buffer entry point
+                on one GPU; on several GPUs every rank uploads its rows of A and
+                1/N of a replicated B, the replicas are completed by an NCCL
+                all-gather into each GPU's own memory, and every rank brings
+                its rows of C back
 
 --impl reference times the CPU reference path alone (rank 0 only).
 """
@@ -39,6 +53,8 @@ from oxmera_b200.workloads import WORKLOADS, device_fill, gemm_views, materialis
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the tcgen05 GEMM
 # on each workload, from the ncu captures summarised under profiles/.
+# Valid for the whole product on one GPU only: a shard reads all of B whatever its
+# share of A, so the figure does not scale with the shard and is not reported at N > 1.
 NCU_TRAFFIC_BYTES = {"c3": 971_092_480, "c3f8": 460_873_216}  # the 256x512 pair kernel on c3 (summary of the capture under profiles/)
 
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
@@ -207,6 +223,146 @@ def run_reference(args):
 # ---------------------------------------------------------------------------
 # the GPU arm
 # ---------------------------------------------------------------------------
+def _host_f32(x: np.ndarray, dtype: DType) -> np.ndarray:
+    """Host copy of a device tensor as float32 (bf16 arrives as uint16 bits)."""
+    if dtype == DType.BF16:
+        return (x.astype(np.uint32) << 16).view(np.float32)
+    return x.astype(np.float32)
+
+
+def verify_shard(w, work, oracle_fp8=None) -> dict:
+    """Size-independent check of this rank's outputs, in float64 on the host:
+    for every product C = A.B of the shard, C.1 against A.(B.1) and 1^T.C against
+    (1^T.A).B over the WHOLE shard.  A rank that multiplied the wrong rows, read
+    the wrong operand or skipped a tile fails it.  The budget is the rounding of
+    the stored result summed like sqrt(n) (bf16 / f16), or the f32 path's
+    accumulation bias summed like n."""
+    import itertools
+    worst = 0.0
+    for g, a, b, out in work:
+        ha, hb, ho = a.to_host(), b.to_host(), out.to_host()
+        if w.dtype in (DType.F8E4M3, DType.F8E5M2):
+            ha, hb = oracle_fp8(ha), oracle_fp8(hb)
+        else:
+            ha, hb = _host_f32(ha, w.dtype), _host_f32(hb, w.dtype)
+        ho = _host_f32(ho, w.result_dtype)
+        lead = ho.shape[:-2]
+        m, n = ho.shape[-2:]
+        for bi in (list(itertools.product(*[range(d) for d in lead])) or [()]):
+            def pick(full):
+                nb = full.ndim - 2
+                return tuple(0 if full.shape[j] == 1 else bi[len(lead) - nb + j] for j in range(nb))
+            A, B, Cm = ha[pick(ha)], hb[pick(hb)], ho[bi]
+            rms = float(np.sqrt(np.mean(np.square(Cm, dtype=np.float64)))) + 1e-30
+            if w.result_dtype == DType.F32:
+                budget = lambda count: 1e-5 * rms * count + 1e-9
+            else:
+                budget = lambda count: 6 * 2.0 ** -8 * rms * np.sqrt(count) + 1e-9
+            row_ref = A.astype(np.float64) @ B.sum(axis=1, dtype=np.float64)
+            col_ref = A.sum(axis=0, dtype=np.float64) @ B.astype(np.float64)
+            e_row = float(np.max(np.abs(Cm.sum(axis=1, dtype=np.float64) - row_ref))) / budget(n)
+            e_col = float(np.max(np.abs(Cm.sum(axis=0, dtype=np.float64) - col_ref))) / budget(m)
+            worst = max(worst, e_row, e_col)
+    return {"ok": bool(worst <= 1.0), "worst_over_budget": worst}
+
+
+class _DeviceBytes:
+    """A device buffer of this library, seen by torch as a uint8 tensor
+    (zero copy), so that NCCL can gather into it."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3}
+
+
+def e2e_sharded(be, grp, w, work, tensors, host, steps):
+    """End to end on several GPUs.  Per step and per rank: upload from
+    page-locked host memory this rank's rows of every tensor it only needs rows
+    of, and ITS 1/N of the bytes of every tensor it needs whole (a replicated
+    operand, or one it reads a column window of); complete those with an NCCL
+    all-gather (whole buffers, into each GPU's own memory, before any kernel
+    reads them); multiply; bring this rank's part of every result back.  Every
+    input byte crosses PCIe once per step over the whole job.
+    Returns (ms per step, h2d bytes per rank, d2h bytes per rank)."""
+    import torch
+    import torch.distributed as dist
+    from oxmera_b200.backend import shard_ranges
+    rank, world = grp.rank, grp.world
+    esz = w.dtype.size_in_bytes()
+    from oxmera_b200.workloads import shard_extent
+    # Per base tensor: ("rows", dim) when this rank only ever reads one contiguous block of it (the
+    # sharded dim is the outermost one with extent > 1), "full" when it needs all of it.
+    need = {}
+
+    def want(name, dim, sharded):
+        shape = tensors[name].shape
+        block = sharded and shape[dim] != 1 and all(s == 1 for s in shape[:dim])
+        if not block:
+            need[name] = "full"
+        elif need.get(name) != "full":
+            need[name] = ("rows", dim)
+
+    for g, a, b, out in work:
+        want(g.a, g.shard_dim, True)
+        want(g.b, g.shard_b_dim if g.shard_b_dim is not None else 0, g.shard_b_dim is not None)
+    extent = {}
+    for g, a, b, out in work:
+        n = shard_extent(g, tensors[g.a].shape, tensors[g.b].shape)
+        for name in (g.a, g.b):
+            if need.get(name) != "full":
+                extent[name] = n
+    uploads, gathers, h2d = [], [], 0
+    for name, t in tensors.items():
+        if name not in need:
+            continue
+        flat = host[name].reshape(-1).view(np.uint8)
+        nbytes = flat.size
+        if need[name] == "full":
+            per = (nbytes + world - 1) // world
+            if per * world != nbytes or per % 16:
+                raise RuntimeError(f"{name}: {nbytes} bytes do not split into {world} aligned parts")
+            lo, hi = rank * per, (rank + 1) * per
+            full = torch.as_tensor(_DeviceBytes(t.storage().ptr, nbytes), device=f"cuda:{grp.local_rank}")
+            gathers.append((full, lo, hi))
+        else:
+            dim = need[name][1]
+            rg = shard_ranges(extent[name], world)[rank]
+            unit = nbytes // t.shape[dim]
+            lo, hi = rg.start * unit, rg.stop * unit
+        uploads.append((t.storage().ptr + lo, flat[lo:hi]))
+        h2d += hi - lo
+    outs, d2h = [], 0
+    for g, a, b, out in work:
+        ho = be.pinned_empty(out.shape, host[g.a].dtype)
+        outs.append((a, b, out, ho))
+        d2h += ho.size * esz
+
+    def step():
+        for dst, src in uploads:
+            be._h2d(dst, src.ctypes.data, src.size)
+        be.synchronize()  # my parts are in my HBM
+        for full, lo, hi in gathers:
+            dist.all_gather_into_tensor(full, full[lo:hi])
+        torch.cuda.synchronize(grp.local_rank)  # every replica is complete before a kernel reads it
+        for a, b, out, _ in outs:
+            be.matmul_into(a, b, out, batched=True)
+        for _, _, out, ho in outs:
+            lo_, _hi = out.layout().extent()
+            assert out.layout().is_contiguous()
+            be._d2h(ho.ctypes.data, out.storage().ptr + lo_ * esz, ho.size * esz)  # returns when the bytes have landed
+
+    step()  # warm-up (NCCL channels)
+    grp.barrier()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    ms = (time.perf_counter() - t0) * 1e3
+    grp.barrier()
+    for a, b, out, ho in outs:  # what came back is what the device-resident run produced
+        if not np.array_equal(ho, out.to_host()):
+            raise RuntimeError("end-to-end result differs from the device-resident one")
+    return grp.max_over_ranks(ms) / steps, h2d, d2h
+
+
 def measure_brief(be, grp, w, rank, world, steps=10, warmup=3):
     """Device-timed TFLOP/s of one configuration on this rank's shard (max over
     ranks), with inputs generated on the device and outputs allocated once."""
@@ -254,27 +410,84 @@ def run_ours(args):
         for _, a, b, out in work:
             be.matmul_into(a, b, out, batched=True)
 
+    # ---- every rank checks its own shard before anything is timed ----
+    step()
+    be.synchronize()
+    fp8 = None
+    if w.dtype in (DType.F8E4M3, DType.F8E5M2):
+        from tests.oracle_lib import Oracle
+        _o = Oracle()
+        fp8 = lambda bits: _o.fp8_to_f32(bits, int(w.dtype))
+    check = verify_shard(w, work, fp8)
+    all_ok = grp.min_over_ranks(1.0 if check["ok"] else 0.0) > 0.5
+    worst_check = grp.max_over_ranks(check["worst_over_budget"])
+    if not all_ok:
+        sys.stderr.write(f"rank {rank}: shard check {'passed' if check['ok'] else 'FAILED'} "
+                         f"(worst checksum error / budget = {check['worst_over_budget']:.3g})\n")
+        if rank == 0:
+            print(json.dumps({"metric": "GEMM TFLOP/s", "value": None, "n_gpus": world, "shards_checked": False,
+                              "error": "a rank's output failed its checksums; nothing was timed"}), flush=True)
+        be.close()
+        grp.close()
+        sys.exit(3)
+
+    def timed(n_steps):
+        """n_steps back to back between events, bracketed by barriers and synchronisation.
+        Returns (this rank's ms, max over ranks, wall-clock window)."""
+        be.synchronize()
+        grp.barrier()
+        tm = be.timer()
+        t0 = time.perf_counter()
+        tm.start()
+        for _ in range(n_steps):
+            step()
+        tm.stop()
+        be.synchronize()
+        t1 = time.perf_counter()
+        local_ms = tm.elapsed_ms()
+        grp.barrier()
+        return local_ms, grp.max_over_ranks(local_ms), (t0, t1)
+
     sampler = ClockSampler(local)
     sampler.start()
     for _ in range(max(args.warmup, 3)):
         step()
-    be.synchronize()
-    grp.barrier()
     counts0 = be.launch_counts()
-    timer = be.timer()
-    t_wall0 = time.perf_counter()
-    timer.start()
-    for _ in range(args.steps):
-        step()
-    timer.stop()
-    be.synchronize()
-    t_wall1 = time.perf_counter()
-    ms_local = timer.elapsed_ms()
-    grp.barrier()
+    ms_local, ms, (t_wall0, t_wall1) = timed(args.steps)   # the contract's region: `value`
     counts1 = be.launch_counts()
-    sampler.stop()
-    ms = grp.max_over_ranks(ms_local)
     kernel_name = be.last_kernel()
+    # further repeats of the same region: best and median
+    rep_ms = [ms]
+    for _ in range(max(0, args.repeats - 1)):
+        rep_ms.append(timed(args.steps)[1])
+    # launches back to back for two seconds and more, with the clock samples of this leg only
+    n_sus = int(max(args.steps, min(200000, np.ceil(args.sustained_s * 1e3 / max(min(rep_ms) / args.steps, 1e-3))))) if args.sustained_s > 0 else 0
+    sustained = None
+    if n_sus:
+        sus_local, sus_ms, (s0, s1) = timed(n_sus)
+        sus_clk = sampler.summary(s0 + 0.25 * (s1 - s0), s1)  # the clock has settled by the second quarter
+        sustained = {"launches_per_rank": n_sus * len(work), "seconds": sus_ms * 1e-3, "ms_per_step": sus_ms / n_sus,
+                     "tflops": w.flops() * n_sus / (sus_ms * 1e-3) / 1e12, "sm_mhz_median": sus_clk.get("sm_mhz"),
+                     "power_w": sus_clk.get("power_w"), "reasons": sus_clk.get("reasons"), "samples": sus_clk.get("samples")}
+        if sus_clk.get("sm_mhz"):
+            # the clock-independent figure to compare from run to run: SM cycles one step takes on the slowest rank
+            sustained["cycles_per_step"] = sus_ms / n_sus * 1e-3 * sus_clk["sm_mhz"] * 1e6
+            sustained["cycles_per_launch"] = sustained["cycles_per_step"] / len(work)
+    # one step on a cold L2: a buffer larger than the L2 is overwritten first
+    cold_ms = None
+    if args.cold_l2:
+        flush = Tensor.empty((256 << 20,), DType.U8, be)
+        cold = []
+        for _ in range(3):
+            be._lib.oxm_memset(be._ctx, flush.storage().ptr, 0, 256 << 20)
+            tm = be.timer()
+            tm.start()
+            step()
+            tm.stop()
+            cold.append(tm.elapsed_ms())
+        cold_ms = grp.max_over_ranks(float(np.median(cold)))
+        del flush
+    sampler.stop()
 
     flops_total = w.flops()
     tflops = flops_total * args.steps / (ms * 1e-3) / 1e12
@@ -295,24 +508,35 @@ def run_ours(args):
     # whatever they say: a 42 ms region still ran at the uncapped rate here,
     # regions of 150 ms at the capped one.
     burst = not capped and timed_s < 0.05
-    peak = peaks["bf16_tflops"] if burst else peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"])
-    if w.dtype == DType.F32:
-        peak = peak / 2.0  # tf32 runs at half the bf16 rate; the 3-term split spends 3 MMA flops per useful one
-    if w.dtype in (DType.F8E4M3, DType.F8E5M2):
-        peak = peak * 2.0  # no fp8 figure was measured: twice the measured bf16 rate, as the nominal rates relate
+    scale = 0.5 if w.dtype == DType.F32 else 2.0 if w.dtype in (DType.F8E4M3, DType.F8E5M2) else 1.0
+    # f32: tf32 runs at half the bf16 rate (and the 3-term split spends 3 MMA flops per useful one);
+    # fp8: no figure was measured, twice the measured bf16 rate, as the nominal rates relate
+    peak = (peaks["bf16_tflops"] if burst else peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"])) * scale
     launches = counts1["tcgen05"] - counts0["tcgen05"]
     per_gpu_tflops = shard_flops(w, rank, world) * args.steps / (ms_local * 1e-3) / 1e12
     achieved = grp.min_over_ranks(per_gpu_tflops)  # the slowest GPU's own rate
+    if sustained:
+        sus_per_gpu = sustained["tflops"] / world
+        sustained["tflops_per_gpu"] = sus_per_gpu
+        sustained["frac"] = sus_per_gpu / (peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"]) * scale)
+        sustained["peak"] = peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"]) * scale
+    rep_sorted = sorted(rep_ms)
     roofline = {
         "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-        "traffic": NCU_TRAFFIC_BYTES.get(w.key),
+        "traffic": NCU_TRAFFIC_BYTES.get(w.key) if world == 1 else None,
         "kernel": kernel_name,
         "peak_source": f"{peak_src} cuBLAS bf16 8192^3, {'burst' if burst else 'sustained'} figure "
                        f"(timed region {timed_s:.3f} s, power cap {'active' if capped else 'not seen'})"
                        + ("; halved for tf32" if w.dtype == DType.F32 else ""),
-        "frac_of_burst": achieved / (peaks["bf16_tflops"] / (2.0 if w.dtype == DType.F32 else 1.0)),
+        "frac_of_burst": achieved / (peaks["bf16_tflops"] * scale),
         "avg_launch_ms": ms_local / max(1, launches) if launches else None,
         "frac_of_nominal_2250": achieved / ({DType.F32: 1125.0, DType.F8E4M3: 4500.0, DType.F8E5M2: 4500.0}.get(w.dtype, 2250.0)),
+        "repeats": {"n": len(rep_ms), "steps_each": args.steps, "best_ms_per_step": rep_sorted[0] / args.steps,
+                    "median_ms_per_step": rep_sorted[len(rep_sorted) // 2] / args.steps,
+                    "best_tflops": flops_total * args.steps / (rep_sorted[0] * 1e-3) / 1e12,
+                    "median_tflops": flops_total * args.steps / (rep_sorted[len(rep_sorted) // 2] * 1e-3) / 1e12},
+        "sustained": sustained,
+        "cold_l2_ms": cold_ms,
         "note": None if w.dtype != DType.F32 else "f32 runs as three TF32 MMA terms: the tensor pipe executes 3x the algorithmic flops counted here",
     }
 
@@ -326,15 +550,18 @@ def run_ours(args):
             buf = be.pinned_empty(t.shape, npdt)
             buf[...] = t.to_host()
             host[name] = buf
+    if not args.no_e2e and w.result_dtype == w.dtype and world > 1:
+        e_steps = max(2, min(args.steps, args.e2e_steps))
+        e_ms, h2d, d2h = e2e_sharded(be, grp, w, work, tensors, host, e_steps)
+        e2e = {"value": flops_total / (e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+               "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h), "steps": e_steps, "ms_per_step": e_ms,
+               "note": "per-rank bytes; pinned host memory; each rank uploads its rows and 1/N of every operand it needs whole, "
+                       "an NCCL all-gather completes those in each GPU's own memory, oxm_batched_matmul, oxm_d2h of the rank's rows"}
+    elif not args.no_e2e and w.result_dtype == w.dtype:
         from oxmera_b200.backend import shard_ranges
         hwork, h2d, d2h = [], 0, 0
         for g, a, b, out in work:
             ha, hb = host[g.a], host[g.b]
-            if world > 1:
-                rg = shard_ranges(ha.shape[g.shard_dim], world)[rank]
-                idx = [slice(None)] * ha.ndim
-                idx[g.shard_dim] = slice(rg.start, rg.stop)
-                ha = ha[tuple(idx)]
             if g.a_perm:
                 ha = ha.transpose(g.a_perm)
             if g.b_perm:
@@ -388,6 +615,8 @@ def run_ours(args):
             },
             "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e,
             "gpu_launches": counts1["total"] - counts0["total"],
+            "shards_checked": True, "shard_check": {"ranks": world, "worst_checksum_error_over_budget": worst_check,
+                                                    "what": "per rank, over its whole shard, float64 on the host: C.1 vs A.(B.1) and 1^T.C vs (1^T.A).B"},
             "clocks": clocks,
             "other_configs": others,
             "percent_of_dense_peak": 100.0 * tflops / world / ({DType.F32: 1125.0, DType.F8E4M3: 4500.0, DType.F8E5M2: 4500.0}.get(w.dtype, 2250.0)),
@@ -408,6 +637,9 @@ def main():
     ap.add_argument("--cta-pair", type=int, default=-1, choices=[-1, 0, 1], help="-1 auto, 0 one CTA per tile, 1 CTA pairs")
     ap.add_argument("--tile-n", type=int, default=0, choices=[0, 64, 128, 256, 512])
     ap.add_argument("--group-m", type=int, default=0)
+    ap.add_argument("--repeats", type=int, default=5, help="times the --steps region is measured (the first one is `value`)")
+    ap.add_argument("--sustained-s", type=float, default=2.2, help="length of the back-to-back leg in seconds (0: skip)")
+    ap.add_argument("--no-cold-l2", dest="cold_l2", action="store_false")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-others", action="store_true", help="skip the brief measurement of the other configurations")

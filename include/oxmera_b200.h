@@ -52,7 +52,11 @@ typedef enum {
   OXM_NOT_IMPLEMENTED = 9,
   OXM_CUDA_ERROR = 10,      /* a CUDA runtime / driver call failed */
   OXM_TIMEOUT = 11,         /* a bounded device-side wait expired */
-  OXM_INVALID_ARGUMENT = 12 /* null pointer, bad handle, bad option */
+  OXM_INVALID_ARGUMENT = 12, /* null pointer, bad handle, bad option */
+  OXM_DIVIDE_BY_ZERO = 13    /* integer division met a zero divisor (BinaryOps::div,
+                              * crates/oxmera-ops/src/lib.rs:47-49: "Integer division by zero
+                              * is a typed error"); oxmera's Error is non_exhaustive and has
+                              * no variant for it yet, so the Rust side adds one */
 } oxm_status;
 
 /* A tensor as the backend sees it: oxmera's Layout {shape, strides, offset}
@@ -101,6 +105,14 @@ int oxm_free(oxm_ctx *ctx, void *ptr);
 int oxm_h2d(oxm_ctx *ctx, void *dst_device, const void *src_host, size_t bytes);
 int oxm_d2h(oxm_ctx *ctx, void *dst_host, const void *src_device, size_t bytes);
 int oxm_memset(oxm_ctx *ctx, void *dst_device, int byte, size_t bytes);
+/* Copy between two GPUs of one box: `bytes` from `src_device` (memory of
+ * src_ctx's device) into `dst_device` (memory of dst_ctx's device), ordered on
+ * dst_ctx's stream after everything submitted to src_ctx so far.  This is how a
+ * replicated operand reaches the other GPUs without crossing PCIe again
+ * (placement before launch: kernels only ever read their own GPU's memory).
+ * No counterpart in the reference, whose Storage lives on one Device
+ * (crates/oxmera-tensor/src/storage.rs:12-17) and has no device-to-device copy. */
+int oxm_copy_peer(oxm_ctx *dst_ctx, void *dst_device, oxm_ctx *src_ctx, const void *src_device, size_t bytes);
 int oxm_sync(oxm_ctx *ctx);
 /* Page-locked host staging memory (faster, truly asynchronous copies). */
 int oxm_host_alloc(size_t bytes, void **out);
@@ -122,7 +134,9 @@ int oxm_host_free(void *ptr);
  * leading dims broadcast by NumPy rules
  * (crates/oxmera-core/src/shape.rs:49-55), trailing two dims as above.
  *
- * dtypes: f32 (fp32 result; 3xTF32 tensor-core path or an FFMA tile kernel),
+ * dtypes: f32 (fp32 result; 3xTF32 tensor-core path or an FFMA tile kernel;
+ * infinities and NaNs in the operands propagate as in IEEE arithmetic on
+ * either),
  * bf16 and f16 (fp32 accumulate, result rounded to the operand dtype), and
  * fp8 e4m3 / e5m2 (fp32 accumulate; `out` may be the operands' fp8 type —
  * rounded to nearest even, saturating to the largest finite value — or bf16,
@@ -152,8 +166,13 @@ int oxm_matmul_fused(oxm_ctx *ctx, const oxm_view *a, const oxm_view *b, const o
  * 27-50,61-69) for Device::Cuda.  Inputs are any views; `out` is a fresh
  * row-major contiguous tensor of the result's shape and the operands' dtype
  * (crates/oxmera-ops/src/lib.rs:16-17).  dtypes: f32, f64, bf16, f16 for
- * everything; i32, i64 for neg, abs, add, sub, mul, sum, max.  exp / ln on
- * integers, any op on u8 / bool, and integer div are OXM_UNSUPPORTED_DTYPE.
+ * everything; i32, i64 for neg, abs, add, sub, mul, div, sum, max.  exp / ln
+ * on integers and any op on u8 / bool are OXM_UNSUPPORTED_DTYPE.  Integer div
+ * truncates toward zero (the most negative value / -1 wraps to itself); a zero
+ * divisor anywhere makes the call return OXM_DIVIDE_BY_ZERO, as the trait
+ * asks (crates/oxmera-ops/src/lib.rs:47-49) — for that the integer form waits
+ * for its kernel before returning, unlike every other compute call.  max
+ * propagates NaN.
  * Binary operands broadcast by NumPy rules (crates/oxmera-core/src/shape.rs:
  * 49-55) and must share dtype and device.  oxm_reduce removes `axes` from the
  * shape; naxes = 0 means all axes (a scalar result); a sum over an empty
@@ -232,7 +251,8 @@ int oxm_selftest_bounded_wait(oxm_ctx *ctx, int64_t limit_ms);
 /* Options (key, value):
  *   "kernel"      0 auto, 1 force the SIMT FFMA kernel, 2 force the tcgen05
  *                 kernel (packing operands it cannot address directly)
- *   "tile_n"      0 auto, else 64 / 128 / 256 / 512 (512: CTA pairs only)
+ *   "tile_n"      0 auto, else the tile's width: a multiple of 32 from 64 to 512
+ *                 (288 and wider: CTA pairs only)
  *   "cta_pair"    -1 auto, 0 one CTA per tile, 1 CTA pairs (cta_group::2)
  *   "host_chunks" slices of the host entry point's copy/compute pipeline:
  *                 0 auto (up to 8 for outputs of 16 MiB or more), 1 off, 2..16
@@ -259,6 +279,12 @@ int oxm_get_option(oxm_ctx *ctx, const char *key, int64_t *value);
 int oxm_launch_counts(oxm_ctx *ctx, int64_t counts[4]);
 /* Name of the compute kernel the last matmul on this context selected. */
 const char *oxm_last_kernel(oxm_ctx *ctx);
+/* Device memory as this process sees it, in bytes: stats[0] reserved and
+ * stats[1] in use in the device's stream-ordered pool (what oxm_alloc and the
+ * library's workspaces draw from), stats[2] free and stats[3] total on the
+ * device (cudaMemGetInfo).  No counterpart in the reference; tests use it to
+ * show that a call allocated nothing. */
+int oxm_memory_stats(oxm_ctx *ctx, int64_t stats[4]);
 
 /* The decisions oxm_batched_matmul would take for these views on a GPU of
  * `num_sms` SMs with default options; runs on the host alone (no context, no

@@ -427,7 +427,6 @@ int orc_unary(int op, const orc_view *a, const orc_view *out) {
 int orc_binary(int op, const orc_view *a, const orc_view *b, const orc_view *out) {
   if (a->dtype != b->dtype) return ORC_DTYPE_MISMATCH;
   if (!(is_float_dtype(a->dtype) || is_int_dtype(a->dtype))) return ORC_UNSUPPORTED_DTYPE;
-  if (op == 3 && !is_float_dtype(a->dtype)) return ORC_UNSUPPORTED_DTYPE;
   int64_t shape[ORC_MAX_DIMS];
   int nd = 0;
   int st = orc_broadcast_shapes(a->shape, a->ndim, b->shape, b->ndim, shape, &nd);
@@ -438,17 +437,27 @@ int orc_binary(int op, const orc_view *a, const orc_view *b, const orc_view *out
     if (out->shape[d] != shape[d]) return ORC_SHAPE_MISMATCH;
     n *= shape[d];
   }
+  int zero_divisor = 0;
   for (int64_t i = 0; i < n; ++i) {
     int64_t ao = bcast_offset(a, shape, nd, i), bo = bcast_offset(b, shape, nd, i);
     if (is_int_dtype(a->dtype)) {
-      int64_t x = get_i(a, ao), y = get_i(b, bo);
-      put_i(out, out->offset + i, op == 0 ? x + y : op == 1 ? x - y : x * y);
+      int64_t x = get_i(a, ao), y = get_i(b, bo), r;
+      if (op == 3) {
+        /* crates/oxmera-ops/src/lib.rs:47-49: "Integer division by zero is a typed error".
+         * Truncating division; the most negative value over -1 wraps to itself. */
+        if (y == 0) { zero_divisor = 1; r = 0; }
+        else if (y == -1) r = (int64_t)(0ull - (uint64_t)x);
+        else r = x / y;
+      } else {
+        r = op == 0 ? x + y : op == 1 ? x - y : x * y;
+      }
+      put_i(out, out->offset + i, r);
     } else {
       double x = get_f(a, ao), y = get_f(b, bo);
       put_f(out, out->offset + i, op == 0 ? x + y : op == 1 ? x - y : op == 2 ? x * y : x / y);
     }
   }
-  return ORC_OK;
+  return zero_divisor ? ORC_DIVIDE_BY_ZERO : ORC_OK;
 }
 
 int orc_reduce(int op, const orc_view *a, const int32_t *axes, int naxes, const orc_view *out) {
@@ -482,7 +491,8 @@ int orc_reduce(int op, const orc_view *a, const int32_t *axes, int naxes, const 
         iacc = (r == 0) ? x : (op == 0 ? iacc + x : (x > iacc ? x : iacc));
       } else {
         double x = get_f(a, off);
-        facc = (r == 0) ? x : (op == 0 ? facc + x : (x > facc ? x : facc));
+        /* max propagates NaN (a NaN anywhere in the slice makes the result NaN) */
+        facc = (r == 0) ? x : (op == 0 ? facc + x : (facc != facc ? facc : (x != x ? x : (x > facc ? x : facc))));
       }
     }
     if (is_int_dtype(a->dtype)) put_i(out, out->offset + o, iacc);
@@ -526,6 +536,7 @@ static void *fill_worker(void *arg) {
       v = sqrt(-2.0 * log(u1)) * cos(two_pi * u2) * F->scale;
     }
     float f = (float)v;
+    if (F->dtype == ORC_F64) { ((double *)F->dst)[i] = v; continue; }
     if (F->dtype == ORC_F32) ((float *)F->dst)[i] = f;
     else if (F->dtype == ORC_BF16) ((uint16_t *)F->dst)[i] = orc_f32_to_bf16(f);
     else if (F->dtype == ORC_F16) ((uint16_t *)F->dst)[i] = orc_f32_to_f16(f);
@@ -534,8 +545,11 @@ static void *fill_worker(void *arg) {
   return NULL;
 }
 
-void orc_fill(void *dst, int32_t dtype, int64_t n, uint64_t seed, uint64_t stream,
-              int dist, double scale, int nthreads) {
+int orc_fill(void *dst, int32_t dtype, int64_t n, uint64_t seed, uint64_t stream,
+             int dist, double scale, int nthreads) {
+  if (!(dtype == ORC_F32 || dtype == ORC_F64 || dtype == ORC_BF16 || dtype == ORC_F16 || dtype == ORC_F8E4M3 ||
+        dtype == ORC_F8E5M2))
+    return ORC_UNSUPPORTED_DTYPE; /* writing one byte per element into a wider buffer would leave it uninitialised */
   uint64_t key = splitmix64(splitmix64(seed) ^ splitmix64(stream * 0xD1342543DE82EF95ull + 0x632BE59BD9B4E019ull));
   if (nthreads < 1) nthreads = 1;
   if (nthreads > 256) nthreads = 256;
@@ -549,7 +563,8 @@ void orc_fill(void *dst, int32_t dtype, int64_t n, uint64_t seed, uint64_t strea
     jobs[t].lo = t * per < n ? t * per : n;
     jobs[t].hi = (t + 1) * per < n ? (t + 1) * per : n;
   }
-  if (nthreads == 1) { fill_worker(&jobs[0]); return; }
+  if (nthreads == 1) { fill_worker(&jobs[0]); return ORC_OK; }
   for (int t = 0; t < nthreads; ++t) pthread_create(&th[t], NULL, fill_worker, &jobs[t]);
   for (int t = 0; t < nthreads; ++t) pthread_join(th[t], NULL);
+  return ORC_OK;
 }

@@ -54,7 +54,8 @@ enum {
   ORC_INDEX_OUT_OF_BOUNDS = 6,
   ORC_RANK_MISMATCH = 7,
   ORC_BACKEND_UNAVAILABLE = 8,
-  ORC_NOT_IMPLEMENTED = 9
+  ORC_NOT_IMPLEMENTED = 9,
+  ORC_DIVIDE_BY_ZERO = 13 /* integer div met a zero divisor (crates/oxmera-ops/src/lib.rs:47-49) */
 };
 
 /* A tensor view over host memory: oxmera's Layout plus a storage pointer
@@ -101,8 +102,12 @@ int orc_check_matmul(const orc_view *a, const orc_view *b, const orc_view *out,
  * integer dtypes) and rounded once on store.  `out` is row-major contiguous.
  * unary op: 0 neg, 1 exp, 2 ln, 3 abs.  binary op: 0 add, 1 sub, 2 mul, 3 div,
  * operands broadcast by NumPy rules.  reduce op: 0 sum, 1 max over `axes`
- * (naxes = 0: all axes), ascending index order.  dtypes: f32, f64, i32, i64,
- * bf16, f16 with the same refusals as the device library. */
+ * (naxes = 0: all axes), ascending index order; max propagates NaN.  dtypes:
+ * f32, f64, i32, i64, bf16, f16 with the same refusals as the device library.
+ * Integer div truncates toward zero (the most negative value over -1 wraps to
+ * itself); a zero divisor anywhere returns ORC_DIVIDE_BY_ZERO, with 0 stored
+ * for those elements ("Integer division by zero is a typed error",
+ * crates/oxmera-ops/src/lib.rs:47-49). */
 int orc_unary(int op, const orc_view *a, const orc_view *out);
 int orc_binary(int op, const orc_view *a, const orc_view *b, const orc_view *out);
 int orc_reduce(int op, const orc_view *a, const int32_t *axes, int naxes, const orc_view *out);
@@ -123,9 +128,10 @@ float orc_fp8_to_f32(uint8_t b, int32_t dtype);
 
 /* Counter-based synthetic data: element i of stream (seed, stream) depends
  * only on (seed, stream, i), so any slice can be generated anywhere.
- * dist: 0 = U(-1,1), 1 = N(0,1) * scale.  dtype: f32, bf16 or f16. */
-void orc_fill(void *dst, int32_t dtype, int64_t n, uint64_t seed,
-              uint64_t stream, int dist, double scale, int nthreads);
+ * dist: 0 = U(-1,1), 1 = N(0,1) * scale.  dtype: f32, f64, bf16, f16 or fp8;
+ * any other tag returns ORC_UNSUPPORTED_DTYPE and writes nothing. */
+int orc_fill(void *dst, int32_t dtype, int64_t n, uint64_t seed,
+             uint64_t stream, int dist, double scale, int nthreads);
 
 #ifdef __cplusplus
 }

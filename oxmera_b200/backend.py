@@ -17,7 +17,7 @@ from typing import Dict, List, Sequence
 import numpy as np
 
 from . import capi
-from .core import (BackendFault, BackendUnavailable, BroadcastIncompatible, DType, Device, DeviceMismatch,
+from .core import (BackendFault, BackendUnavailable, BroadcastIncompatible, DType, Device, DeviceMismatch, DivisionByZero,
                    DTypeMismatch, IndexOutOfBounds, Layout, NotImplementedOp, OxmeraError, ShapeMismatch, UnsupportedDType,
                    broadcast_shapes)
 from .tensor import Tensor
@@ -42,6 +42,8 @@ def _raise(status: int, op: str, a: Tensor | None = None, b: Tensor | None = Non
         raise BackendUnavailable(None, detail)
     if status == capi.NOT_IMPLEMENTED:
         raise NotImplementedOp(op, detail)
+    if status == capi.DIVIDE_BY_ZERO:
+        raise DivisionByZero(op, detail)
     raise BackendFault(status, f"{op}: {capi.load().oxm_status_name(status).decode()}: {detail}")
 
 
@@ -261,6 +263,14 @@ class B200Backend:
         self._lib.oxm_launch_counts(self._ctx, arr)
         return {"total": arr[0], "tcgen05": arr[1], "simt": arr[2], "pack": arr[3]}
 
+    def memory_stats(self) -> Dict[str, int]:
+        """Bytes reserved / in use in the device's stream-ordered pool, and free / total on the device."""
+        arr = (C.c_int64 * 4)()
+        st = self._lib.oxm_memory_stats(self._ctx, arr)
+        if st != capi.OK:
+            _raise(st, "memory_stats")
+        return {"pool_reserved": arr[0], "pool_used": arr[1], "device_free": arr[2], "device_total": arr[3]}
+
     def last_kernel(self) -> str:
         return self._lib.oxm_last_kernel(self._ctx).decode()
 
@@ -359,33 +369,77 @@ def shard_plan(a_shape: Sequence[int], b_shape: Sequence[int], parts: int):
 def sharded_matmul_host(backends: Sequence[B200Backend], a: np.ndarray, b: np.ndarray, dtype: DType) -> np.ndarray:
     """Multiply host arrays on several GPUs: each backend gets its slice of
     the batch (or of A's rows) plus whatever it needs of the other operand,
-    one host thread per device; the first typed error is re-raised.  No device
-    reads another device's memory and nothing is reduced."""
+    one host thread per device; the first typed error is re-raised.  Nothing
+    is reduced and no kernel reads another device's memory.
+
+    An operand every device needs whole (B, unless it carries the sharded batch
+    dim) crosses PCIe once, not once per device: each device uploads 1/N of its
+    bytes and fetches the rest from its peers with device-to-device copies
+    into its own memory (`oxm_copy_peer`) before its kernel is launched."""
     parts = len(backends)
     axis, ranges = shard_plan(a.shape, b.shape, parts)
     bshape = broadcast_shapes(a.shape[:-2], b.shape[:-2])
     out = np.empty(tuple(bshape) + (a.shape[-2], b.shape[-1]), dtype=a.dtype)
     errors: List[BaseException] = []
+    lead = len(bshape)
+
+    def cut(x, rg):
+        if axis == "rows":
+            return x
+        pos = x.ndim - 2 - lead  # index of the leading batch dim in x, if it has one
+        if pos < 0 or x.shape[pos] == 1:
+            return x
+        idx = [slice(None)] * x.ndim
+        idx[pos] = slice(rg.start, rg.stop)
+        return x[tuple(idx)]
+
+    def a_part(rg):
+        return a[..., rg.start:rg.stop, :] if axis == "rows" else cut(a, rg)
+
+    esz = dtype.size_in_bytes()
+    b_whole = all(cut(b, rg) is b for rg in ranges)
+    per = b.nbytes // parts if parts else 0
+    share_b = (parts > 1 and b_whole and b.flags["C_CONTIGUOUS"] and b.nbytes % (parts * 16) == 0 and
+               all(len(rg) > 0 for rg in ranges) and all(isinstance(be, B200Backend) for be in backends))
+    b_dev: List[Tensor | None] = [None] * parts
+    gate = threading.Barrier(parts) if share_b else None
 
     def work(rank: int):
         try:
             rg = ranges[rank]
             if len(rg) == 0:
                 return
-            if axis == "batch":
-                lead = len(bshape)
-                def cut(x):
-                    pos = x.ndim - 2 - lead  # index of the leading batch dim in x, if it has one
-                    if pos < 0 or x.shape[pos] == 1:
-                        return x
-                    idx = [slice(None)] * x.ndim
-                    idx[pos] = slice(rg.start, rg.stop)
-                    return x[tuple(idx)]
-                out[rg.start:rg.stop] = backends[rank].matmul_host(cut(a), cut(b), dtype)
+            be = backends[rank]
+            if not share_b:
+                res = be.matmul_host(a_part(rg), cut(b, rg), dtype)
             else:
-                out[..., rg.start:rg.stop, :] = backends[rank].matmul_host(a[..., rg.start:rg.stop, :], b, dtype)
+                try:
+                    tb = Tensor.empty(b.shape, dtype, be)
+                    flat = b.reshape(-1).view(np.uint8)
+                    be._h2d(tb.storage().ptr + rank * per, flat[rank * per:(rank + 1) * per].ctypes.data, per)
+                    b_dev[rank] = tb
+                finally:
+                    gate.wait()  # every device has queued the upload of its part (or failed: see below)
+                if any(t is None for t in b_dev):
+                    raise BackendFault(capi.CUDA_ERROR, "a peer could not stage its part of the shared operand")
+                for q in range(parts):
+                    if q != rank:
+                        st = be._lib.oxm_copy_peer(be._ctx, tb.storage().ptr + q * per, backends[q]._ctx,
+                                                   b_dev[q].storage().ptr + q * per, per)
+                        if st != capi.OK:
+                            _raise(st, "copy_peer")
+                ha = np.ascontiguousarray(a_part(rg))
+                ta = Tensor.from_host(ha, ha.shape, dtype, be)
+                res = be.batched_matmul(ta, tb).to_host()
+                gate.wait()  # nobody frees its copy while a peer may still be reading it
+            if axis == "batch":
+                out[rg.start:rg.stop] = res
+            else:
+                out[..., rg.start:rg.stop, :] = res
         except BaseException as e:  # propagate to the caller's thread
             errors.append(e)
+            if gate is not None:
+                gate.abort()
 
     threads = [threading.Thread(target=work, args=(r,)) for r in range(parts)]
     for t in threads:
@@ -393,5 +447,6 @@ def sharded_matmul_host(backends: Sequence[B200Backend], a: np.ndarray, b: np.nd
     for t in threads:
         t.join()
     if errors:
-        raise errors[0]
+        first = [e for e in errors if not isinstance(e, threading.BrokenBarrierError)]
+        raise (first or errors)[0]
     return out

@@ -54,8 +54,19 @@ def build_library(force: bool = False, verbose: bool = False) -> str:
             sys.stderr.write(res.stderr)
         return obj
 
-    with ThreadPoolExecutor(max_workers=min(len(SOURCES), os.cpu_count() or 1)) as pool:
-        objs = list(pool.map(run, SOURCES))
+    # a translation unit is recompiled when its object is older than the unit itself or any header
+    headers = glob.glob(os.path.join(CSRC, "*.cuh")) + [os.path.join(HERE, "..", "include", "oxmera_b200.h")]
+    newest_header = max(os.path.getmtime(h) for h in headers)
+
+    def fresh(src):
+        obj = compile_command(src)[1]
+        return (not force and os.path.exists(obj) and
+                os.path.getmtime(obj) >= max(newest_header, os.path.getmtime(os.path.join(CSRC, src))))
+
+    todo = [s for s in SOURCES if not fresh(s)]
+    with ThreadPoolExecutor(max_workers=min(max(len(todo), 1), os.cpu_count() or 1)) as pool:
+        list(pool.map(run, todo))
+    objs = [compile_command(s)[1] for s in SOURCES]
     res = subprocess.run(link_command(objs), capture_output=True, text=True)
     if res.returncode != 0:
         raise RuntimeError(f"link failed:\n{res.stdout}\n{res.stderr}")

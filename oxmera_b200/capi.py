@@ -15,16 +15,16 @@ LIB_NAME = "liboxmera_b200.so"
 EXPORTS = [
     "oxm_device_count", "oxm_ctx_create", "oxm_ctx_destroy", "oxm_ctx_device", "oxm_backend_name",
     "oxm_last_error", "oxm_status_name",
-    "oxm_alloc", "oxm_free", "oxm_h2d", "oxm_d2h", "oxm_memset", "oxm_sync", "oxm_host_alloc", "oxm_host_free",
+    "oxm_alloc", "oxm_free", "oxm_h2d", "oxm_d2h", "oxm_memset", "oxm_copy_peer", "oxm_sync", "oxm_host_alloc", "oxm_host_free",
     "oxm_matmul", "oxm_batched_matmul", "oxm_batched_matmul_host", "oxm_contiguous",
     "oxm_matmul_f32_noalloc", "oxm_matmul_fused", "oxm_unary", "oxm_binary", "oxm_reduce",
     "oxm_event_create", "oxm_event_destroy", "oxm_event_record", "oxm_event_elapsed_ms", "oxm_stream_handle", "oxm_fill", "oxm_selftest_bounded_wait",
-    "oxm_set_option", "oxm_get_option", "oxm_launch_counts", "oxm_last_kernel", "oxm_plan_matmul",
+    "oxm_set_option", "oxm_get_option", "oxm_launch_counts", "oxm_last_kernel", "oxm_memory_stats", "oxm_plan_matmul",
 ]
 
 OK, SHAPE_MISMATCH, BROADCAST_INCOMPATIBLE, DTYPE_MISMATCH, UNSUPPORTED_DTYPE = 0, 1, 2, 3, 4
 DEVICE_MISMATCH, INDEX_OUT_OF_BOUNDS, RANK_MISMATCH, BACKEND_UNAVAILABLE, NOT_IMPLEMENTED = 5, 6, 7, 8, 9
-CUDA_ERROR, TIMEOUT, INVALID_ARGUMENT = 10, 11, 12
+CUDA_ERROR, TIMEOUT, INVALID_ARGUMENT, DIVIDE_BY_ZERO = 10, 11, 12, 13
 
 
 class View(C.Structure):
@@ -100,6 +100,7 @@ def load() -> C.CDLL:
         "oxm_h2d": ([p, p, p, sz], i),
         "oxm_d2h": ([p, p, p, sz], i),
         "oxm_memset": ([p, p, i, sz], i),
+        "oxm_copy_peer": ([p, p, p, p, sz], i),
         "oxm_sync": ([p], i),
         "oxm_host_alloc": ([sz, C.POINTER(p)], i),
         "oxm_host_free": ([p], i),
@@ -123,6 +124,7 @@ def load() -> C.CDLL:
         "oxm_get_option": ([p, C.c_char_p, C.POINTER(i64)], i),
         "oxm_launch_counts": ([p, C.POINTER(i64)], i),
         "oxm_last_kernel": ([p], C.c_char_p),
+        "oxm_memory_stats": ([p, C.POINTER(i64)], i),
         "oxm_plan_matmul": ([PV, PV, PV, i, C.POINTER(C.c_int32)], i),
     }
     for name, (argtypes, restype) in sig.items():

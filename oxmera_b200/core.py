@@ -124,6 +124,16 @@ class NotImplementedOp(OxmeraError):
         super().__init__(f"{op} is not implemented for {detail}")
 
 
+class DivisionByZero(OxmeraError):
+    """Integer division met a zero divisor.  BinaryOps::div makes this "a typed
+    error" (crates/oxmera-ops/src/lib.rs:47-49); oxmera's non_exhaustive Error
+    has no variant for it yet, so this is the one the backend adds."""
+
+    def __init__(self, op: str, detail: str | None = None):
+        self.op = op
+        super().__init__(detail or f"integer division by zero in {op}")
+
+
 class BackendFault(OxmeraError):
     """A CUDA call failed or a bounded device-side wait expired.  The Rust
     side would fold this into NotImplemented{op, detail}; it is kept apart

@@ -262,13 +262,30 @@ int launch_simt(oxm_ctx *ctx, const Problem &P) {
     p.bdims[d] = (int32_t)P.bdims[d]; p.a_bs[d] = P.a_bs[d]; p.b_bs[d] = P.b_bs[d]; p.o_bs[d] = P.o_bs[d];
   }
   p.epi = P.epi;
-  const int64_t blocks = (int64_t)p.tiles_m * p.tiles_n * P.nbatch;
+  const int64_t tiles = (int64_t)p.tiles_m * p.tiles_n * P.nbatch;
+  // Too few tiles for the SMs and a contraction worth cutting: a cluster of 2, 4 or 8 CTAs per
+  // tile, each with at least 64 elements of k.
+  int ksplit = 1;
+  if (ctx->opt_split_k != 0)
+    while (ksplit < 8 && tiles * ksplit * 2 <= 4 * (int64_t)ctx->num_sms && P.K / (ksplit * 2) >= 64) ksplit *= 2;
+  p.ksplit = ksplit;
+  p.kchunk = (int32_t)(((P.K + ksplit - 1) / ksplit + 15) / 16 * 16);
+  const int64_t blocks = tiles * ksplit;
   if (blocks > INT32_MAX) return fail(OXM_NOT_IMPLEMENTED, "matmul is not implemented for %lld output tiles", (long long)blocks);
-  if (ts == 64) gemm_simt_kernel<64><<<(unsigned)blocks, 256, 0, ctx->stream>>>(p);
-  else gemm_simt_kernel<32><<<(unsigned)blocks, 256, 0, ctx->stream>>>(p);
-  CUDA_TRY(cudaGetLastError());
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3((unsigned)blocks, 1, 1);
+  cfg.blockDim = dim3(256, 1, 1);
+  cfg.stream = ctx->stream;
+  cudaLaunchAttribute attr[1];
+  if (ksplit > 1) {
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)ksplit; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+  }
+  if (ts == 64) CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_simt_kernel<64>, p));
+  else CUDA_TRY(cudaLaunchKernelEx(&cfg, gemm_simt_kernel<32>, p));
   ctx->launches[0]++; ctx->launches[2]++;
-  snprintf(ctx->last_kernel, sizeof(ctx->last_kernel), "gemm_simt_ffma_%dx%d", ts, ts);
+  snprintf(ctx->last_kernel, sizeof(ctx->last_kernel), "gemm_simt_ffma_%dx%d%s", ts, ts, ksplit > 1 ? "_ksplit" : "");
   return OXM_OK;
 }
 
@@ -431,7 +448,10 @@ int launch_gemm(oxm_ctx *ctx, int kind, bool a_mn, bool b_mn, int bn, int pair, 
                           : kind == 2 ? (a_mn ? launch_gemm_f8_am : launch_gemm_f8_ak)
                                       : (a_mn ? launch_gemm_f16_am : launch_gemm_f16_ak);
   cudaError_t e = fn(l, tmA, tmB, tmC, p, ctx->last_kernel, sizeof(ctx->last_kernel));
-  if (e != cudaSuccess) return fail(OXM_CUDA_ERROR, "launch of %s failed: %s", ctx->last_kernel, cudaGetErrorString(e));
+  if (e != cudaSuccess) {
+    cudaGetLastError();  // a refused launch also parks its error for the next caller of cudaGetLastError: take it away
+    return fail(OXM_CUDA_ERROR, "launch of %s failed: %s", ctx->last_kernel, cudaGetErrorString(e));
+  }
   return OXM_OK;
 }
 
@@ -441,6 +461,10 @@ int launch_gemm(oxm_ctx *ctx, int kind, bool a_mn, bool b_mn, int bn, int pair, 
 bool make_out_map(oxm_ctx *ctx, CUtensorMap *tm, void *ptr, int dtype, int elt, int64_t M, int64_t N, int64_t nb,
                   int64_t rs_elems, int64_t bs_elems) {
   if (reinterpret_cast<uintptr_t>(ptr) % 16) return false;
+  // The engine clips a store box at the tensor's edge, but it writes whole 16-byte units: a row
+  // of, say, one f32 element had the three elements after it overwritten.  Rows that do not end
+  // on a 16-byte boundary therefore take the strided-store epilogue.
+  if ((N * elt) % 16) return false;
   if (M > 1 && (rs_elems <= 0 || (rs_elems * elt) % 16)) return false;
   if (nb > 1 && (bs_elems <= 0 || (bs_elems * elt) % 16)) return false;
   if (nb >= (1ll << 31)) return false;
@@ -460,9 +484,14 @@ bool make_out_map(oxm_ctx *ctx, CUtensorMap *tm, void *ptr, int dtype, int elt, 
 
 // Tile shape, CTA pairing and split-K factor for one product.
 struct TileChoice {
-  int bn, pair, splits;
+  int bn, pair, splits;  // bn: the tile's width, any multiple of 32 up to its kernel's capacity
   int64_t sk_tiles;  // > 0: that many of the last tiles are shared out by contraction block (stream-K)
 };
+
+// The kernel instance (its widest tile) that runs tiles of `bn` columns.
+int tile_class(int bn) { return bn > 256 ? 512 : bn > 128 ? 256 : bn > 64 ? 128 : 64; }
+// Columns per tcgen05.mma: tiles wider than 256 are two MMAs side by side.
+int tile_subn(int bn) { return bn > 256 ? bn / 2 : bn; }
 
 // Stream-K applies when the tile count does not divide by the number of CTAs
 // (or pairs): the remainder, plus one whole wave when the remainder is less
@@ -495,13 +524,15 @@ constexpr int kMaxChainKb = 3 * 1024 / 32;
 // products too skinny to fill the SMs with 256-wide tiles get a split
 // contraction rather than narrow tiles: [1..128, 8192] x [8192, 8192] takes
 // 45.7 us unsplit at every tile width and 31 us split four ways.
-TileChoice choose_tiles(const oxm_ctx *ctx, const Problem &P, bool tf32, int32_t num_kb, int min_b_rows) {
-  struct Cand { int bn, pair; double us_per_kb, us_epilogue; };
-  // Microseconds per pipeline stage of one tile at the ~1.45 GHz the power cap
-  // sustains, and per epilogue.  With two accumulators the epilogue hides
-  // behind the next tile's main loop unless the contraction is short; the
-  // 512-wide tile has one accumulator and always pays it.
-  static const Cand cands[] = {{512, 1, 0.706 / 1.03, 2.0}, {256, 1, 0.353, 3.0}, {256, 0, 0.353 / 0.93, 2.0},
+TileChoice choose_tiles(const oxm_ctx *ctx, const Problem &P, bool tf32, int32_t num_kb, int min_b_rows, bool b_mn) {
+  struct Cand { int cls, pair; double us_per_kb, us_epilogue; };
+  // Microseconds per pipeline stage of one full-width tile at the ~1.45 GHz the
+  // power cap sustains, and per epilogue.  With two accumulators the epilogue
+  // hides behind the next tile's main loop unless the contraction is short; the
+  // 512-wide class has one accumulator, whose first half is handed back after
+  // one round of tensor-memory loads (the rest drains under the next tile's
+  // first MMAs), so it pays a short epilogue always.
+  static const Cand cands[] = {{512, 1, 0.706 / 1.03, 0.7}, {256, 1, 0.353, 3.0}, {256, 0, 0.353 / 0.93, 2.0},
                                {128, 0, 0.177 / 0.75, 1.5}, {128, 1, 0.177 / 0.59, 2.0}, {64, 0, 0.088 / 0.5, 1.0}};
   constexpr double kHbmRead = 6.0e6;    // bytes per microsecond from HBM
   constexpr double kHbmWrite = 4.3e6;   // ... and to it (measured on products that only write)
@@ -516,52 +547,69 @@ TileChoice choose_tiles(const oxm_ctx *ctx, const Problem &P, bool tf32, int32_t
   }
   const double hbm_us = (double)P.nbatch * ((double)P.M * P.N * P.oelt) / kHbmWrite +
                         ((double)P.M * P.K * a_nb + (double)P.N * P.K * b_nb) * P.elt * (tf32 ? 3.0 : 1.0) / kHbmRead;
+  const int forced_class = ctx->opt_tile_n ? tile_class((int)ctx->opt_tile_n) : 0;
   // A forced pairing that no candidate of the forced width has is dropped on the second pass.
   for (int pass = 0; pass < 2 && best_t == 1e300; ++pass)
   for (const Cand &c : cands) {
     // an N-major fp8 B tile is staged in boxes of 128 columns: each CTA must own at least one
-    if ((c.pair ? c.bn / 2 : c.bn) < min_b_rows) continue;
-    if (ctx->opt_tile_n && c.bn != ctx->opt_tile_n && ctx->opt_tile_n >= min_b_rows) continue;
+    if ((c.pair ? c.cls / 2 : c.cls) < min_b_rows) continue;
+    if (forced_class && c.cls != forced_class && ctx->opt_tile_n >= min_b_rows) continue;
     if (pass == 0 && ctx->opt_cta_pair >= 0 && c.pair != ctx->opt_cta_pair) continue;
-    if (!ctx->opt_tile_n) {
-      if (c.pair && P.M <= kTileM) continue;          // nothing for the second CTA to do
-      if (c.bn > std::max(64, min_b_rows) && P.N <= c.bn / 2) continue;  // at least half of the tile is outside the matrix
-    }
     const int tm = kTileM * (c.pair ? 2 : 1);
-    const int64_t tiles = ((P.M + tm - 1) / tm) * ((P.N + c.bn - 1) / c.bn) * P.nbatch;
     const int64_t slots = c.pair ? ctx->num_sms / 2 : ctx->num_sms;
-    const double kb_us = std::max(c.us_per_kb, 0.30);
-    for (int m : mult) {
-      const int32_t splits = min_splits * m;
-      if (m > 1 && (ctx->opt_split_k == 0 || num_kb / splits < 16)) break;
-      if (ctx->opt_split_k > 0 && splits != std::max<int64_t>(min_splits, ctx->opt_split_k)) continue;
-      const double slab_bytes = (double)P.nbatch * P.M * P.N * 4.0;
-      if (splits > 1 && slab_bytes * splits > 2e9) break;
-      const int64_t waves = (tiles * splits + slots - 1) / slots;
-      const int32_t kb = (num_kb + splits - 1) / splits;
-      // one accumulator: the epilogue is exposed, and twice as long when the main loop is too
-      // short for the previous tile's stores to drain meanwhile
-      const double tile_us = c.bn > 256 ? kb * kb_us + c.us_epilogue * (kb < 16 ? 2.0 : 1.0)
-                                        : std::max(kb * kb_us + 0.3, c.us_epilogue);
-      double wave_us = (double)waves * tile_us;
-      // Stream-K: every CTA gets the same number of blocks, at the price of one more epilogue and
-      // the hand-over of a partial tile (~12 us), and of CTAs that walk K out of step, so that
-      // tiles sharing an operand panel stop sharing its L2 lines.  Measured: it pays when whole
-      // waves of ordinary tiles run beside the shared-out ones (4096^3: 127 -> 116 us; the weight
-      // gradient of the linear layer: 427 -> 412 us) and loses badly when every tile is shared
-      // out (1024 x 8192 x 8192: 97 -> 125 us).  Automatic only in the first situation.
-      int64_t sk = 0;
-      if (splits == 1 && ctx->opt_stream_k != 0 && ctx->opt_split_k != 0) {
-        sk = stream_k_tiles(tiles, slots, kb);
-        const double even_us = (double)tiles / (double)slots * tile_us + 12.0;
-        const bool whole_waves_beside = tiles - sk >= slots;
-        if (sk > 0 && (ctx->opt_stream_k == 1 || (whole_waves_beside && even_us < wave_us))) wave_us = std::min(wave_us, even_us);
-        else sk = 0;
+    // Widths of this class: the full width, and narrower ones in steps of 32 columns down to
+    // just above the next class (a tile count that fits the SMs better can beat a wider tile).
+    const int w_lo = c.cls == 64 ? 64 : c.cls / 2 + 32;
+    for (int bn = c.cls; bn >= w_lo; bn -= 32) {
+      if (ctx->opt_tile_n && ctx->opt_tile_n >= min_b_rows) {
+        if (bn != ctx->opt_tile_n) continue;
+      } else {
+        if (c.pair && P.M <= kTileM) continue;          // nothing for the second CTA to do
+        if (bn > std::max(64, min_b_rows) && P.N <= bn / 2) continue;  // at least half of the tile is outside the matrix
+        // narrower widths only where whole tiles of them cover the columns with less waste
+        if (bn != c.cls && c.cls < 512) continue;
       }
-      double t = std::max(wave_us, hbm_us) + 0.01 * wave_us;  // the second term orders memory-bound ties
-      if (splits > 1) t += 4.0 + slab_bytes * (splits + 1) / 4.0e6;  // launch + traffic of the reduction
-      if (splits == min_splits ? t <= best_t : t < best_t) {  // ties go to the narrower, later candidate
-        best_t = t; best = TileChoice{c.bn, c.pair, splits, sk};
+      // An MN-major B is fetched in boxes that start at multiples of a CTA's share of the columns:
+      // the TMA engine wants those starts on 16-byte boundaries.
+      const int subc = tile_subn(bn) / (c.pair ? 2 : 1);
+      if (b_mn && (subc * P.elt) % 16) continue;
+      if ((c.pair ? subc * 2 : subc) % 16) continue;      // the MMA's N extent
+      const int64_t tiles = ((P.M + tm - 1) / tm) * ((P.N + bn - 1) / bn) * P.nbatch;
+      const double width = (double)bn / (double)c.cls;
+      // A narrower tile moves the same A bytes for fewer flops: charge half of the lost width back.
+      const double kb_us = std::max(c.us_per_kb * (width + 0.04 * (1.0 - width)), 0.30);
+      for (int m : mult) {
+        const int32_t splits = min_splits * m;
+        if (m > 1 && (ctx->opt_split_k == 0 || num_kb / splits < 16)) break;
+        if (ctx->opt_split_k > 0 && splits != std::max<int64_t>(min_splits, ctx->opt_split_k)) continue;
+        const double slab_bytes = (double)P.nbatch * P.M * P.N * 4.0;
+        if (splits > 1 && slab_bytes * splits > 2e9) break;
+        const int64_t waves = (tiles * splits + slots - 1) / slots;
+        const int32_t kb = (num_kb + splits - 1) / splits;
+        // one accumulator: the epilogue is exposed, and longer when the main loop is too
+        // short for the previous tile's stores to drain meanwhile
+        const double tile_us = c.cls > 256 ? kb * kb_us + c.us_epilogue * (kb < 16 ? 4.0 : 1.0)
+                                           : std::max(kb * kb_us + 0.3, c.us_epilogue);
+        double wave_us = (double)waves * tile_us;
+        // Stream-K: every CTA gets the same number of blocks, at the price of one more epilogue and
+        // the hand-over of a partial tile (~12 us), and of CTAs that walk K out of step, so that
+        // tiles sharing an operand panel stop sharing its L2 lines.  Measured: it pays when whole
+        // waves of ordinary tiles run beside the shared-out ones (4096^3: 127 -> 116 us; the weight
+        // gradient of the linear layer: 427 -> 412 us) and loses badly when every tile is shared
+        // out (1024 x 8192 x 8192: 97 -> 125 us).  Automatic only in the first situation.
+        int64_t sk = 0;
+        if (splits == 1 && ctx->opt_stream_k != 0 && ctx->opt_split_k != 0) {
+          sk = stream_k_tiles(tiles, slots, kb);
+          const double even_us = (double)tiles / (double)slots * tile_us + 12.0;
+          const bool whole_waves_beside = tiles - sk >= slots;
+          if (sk > 0 && (ctx->opt_stream_k == 1 || (whole_waves_beside && even_us < wave_us))) wave_us = std::min(wave_us, even_us);
+          else sk = 0;
+        }
+        double t = std::max(wave_us, hbm_us) + 0.01 * wave_us;  // the second term orders memory-bound ties
+        if (splits > 1) t += 4.0 + slab_bytes * (splits + 1) / 4.0e6;  // launch + traffic of the reduction
+        if (splits == min_splits ? t <= best_t : t < best_t) {  // ties go to the narrower, later candidate
+          best_t = t; best = TileChoice{bn, c.pair, splits, sk};
+        }
       }
     }
   }
@@ -572,7 +620,7 @@ TileChoice choose_tiles(const oxm_ctx *ctx, const Problem &P, bool tf32, int32_t
 // launches in front of its GEMM).
 bool wants_tensor_cores(const Problem &P) {
   const double flops = 2.0 * (double)P.M * (double)P.N * (double)P.K * (double)P.nbatch;
-  return P.K > 0 && flops >= (P.elt == 4 ? 3.0e7 : 8.0e6);
+  return P.K > 0 && flops >= (P.elt == 4 ? 2.0e8 : 8.0e6);
 }
 
 int launch_tcgen05(oxm_ctx *ctx, const Problem &P) {
@@ -594,12 +642,15 @@ int launch_tcgen05(oxm_ctx *ctx, const Problem &P) {
   const int bk = kStageKBytes / P.elt;
 
   const int32_t num_kb_all = (int32_t)((Kst + bk - 1) / bk);
-  const TileChoice choice = choose_tiles(ctx, P, tf32, num_kb_all, (kind == 2 && sb.mn_major) ? 128 : 0);
+  const TileChoice choice = choose_tiles(ctx, P, tf32, num_kb_all, (kind == 2 && sb.mn_major) ? 128 : 0, sb.mn_major);
   const int bn = choice.bn, pair = choice.pair;
+  const int cls = tile_class(bn), subn = tile_subn(bn);
+  const int subc = pair ? subn / 2 : subn;  // B rows (columns of the product) one CTA stages per MMA
   const int tm = kTileM * (pair ? 2 : 1);
 
   GemmParams p{};
   p.M = (int32_t)P.M; p.N = (int32_t)P.N; p.K = (int32_t)Kst;
+  p.bn = bn; p.subn = subn;
   p.tiles_m = (int32_t)((P.M + tm - 1) / tm);
   p.tiles_n = (int32_t)((P.N + bn - 1) / bn);
   p.num_kb = (int32_t)((Kst + bk - 1) / bk);
@@ -622,7 +673,7 @@ int launch_tcgen05(oxm_ctx *ctx, const Problem &P) {
   // format codes of the instruction descriptor: f16 0 / bf16 1 / tf32 2; in the f8f6f4 kind e4m3 0 / e5m2 1
   const uint32_t fmt = tf32 ? 2u : (P.dtype == OXM_BF16 || P.dtype == OXM_F8E5M2) ? 1u : 0u;
   p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((sa.mn_major ? 1u : 0u) << 15) | ((sb.mn_major ? 1u : 0u) << 16) |
-            ((uint32_t)(std::min(bn, 256) >> 3) << 17) | ((uint32_t)(tm >> 4) << 24);
+            ((uint32_t)(subn >> 3) << 17) | ((uint32_t)(tm >> 4) << 24);
   p.status = ctx->status_dev;
   p.wait_limit_ns = (uint64_t)ctx->opt_wait_limit_ms * 1000000ull;
   p.splits = 1;
@@ -672,7 +723,7 @@ int launch_tcgen05(oxm_ctx *ctx, const Problem &P) {
   p.sk_tiles = 0;
   if (p.splits == 1 && choice.sk_tiles > 0) {
     const int64_t slots = pair ? ctx->num_sms / 2 : ctx->num_sms;
-    const size_t ws_bytes = (size_t)slots * (pair ? 2 : 1) * kTileM * bn * sizeof(float);
+    const size_t ws_bytes = (size_t)slots * (pair ? 2 : 1) * kTileM * cls * sizeof(float);  // the kernel spaces runs by its widest tile
     if ((size_t)slots * (pair ? 2 : 1) * 8 <= kSkFlagWords) {
       int st2 = grow(ctx, ctx->pack_ws[2], ws_bytes);
       if (st2) return st2;
@@ -692,10 +743,14 @@ int launch_tcgen05(oxm_ctx *ctx, const Problem &P) {
   // tile's other rows keep whatever shared memory held and feed accumulator
   // rows that are never stored.
   const int a_box_rows = (!pair && !sa.mn_major && P.M < kTileM) ? (int)((P.M + 7) / 8 * 8) : kTileM;
-  p.stage_tx = (uint32_t)(kStageKBytes * (a_box_rows + bn));
+  // Bytes one CTA's loads deliver per stage: its A rows, and per MMA its share of B, which an
+  // MN-major B brings in whole boxes of `boxw` columns.
+  const int boxw = kStageKBytes / P.elt;
+  const int b_cols = sb.mn_major ? (subc + boxw - 1) / boxw * boxw : subc;
+  p.stage_tx = (uint32_t)(kStageKBytes * (a_box_rows + (bn > 256 ? 2 : 1) * b_cols));
   int st = make_map(ctx, &tmA, sa, P.dtype, P.elt, a_box_rows, bk);
   if (st) return st;
-  st = make_map(ctx, &tmB, sb, P.dtype, P.elt, pair ? std::min(bn, 256) / 2 : bn, bk);
+  st = make_map(ctx, &tmB, sb, P.dtype, P.elt, subc, bk);
   if (st) return st;
   // The epilogue writes through a bulk tensor store when the output is a
   // row-contiguous, 16-byte-aligned window whose batch dims fold into one stride.
@@ -716,8 +771,12 @@ int launch_tcgen05(oxm_ctx *ctx, const Problem &P) {
   else if (pair) grid = 2 * (int)std::min<int64_t>(p.num_tiles, ctx->num_sms / 2);
   else grid = (int)std::min<int64_t>(p.num_tiles, ctx->num_sms);
 
-  st = launch_gemm(ctx, kind, sa.mn_major, sb.mn_major, bn, pair, tmA, tmB, tmC, p, grid);
+  st = launch_gemm(ctx, kind, sa.mn_major, sb.mn_major, cls, pair, tmA, tmB, tmC, p, grid);
   if (st) return st;
+  if (bn != cls) {  // the instance's name carries its capacity; say what width it ran at
+    const size_t len = strlen(ctx->last_kernel);
+    snprintf(ctx->last_kernel + len, sizeof(ctx->last_kernel) - len, "_w%d", bn);
+  }
   ctx->launches[0]++; ctx->launches[1]++;
   if (p.splits > 1) {
     const int64_t blocks = std::min<int64_t>((rp.total + 255) / 256, (int64_t)ctx->num_sms * 16);
@@ -793,7 +852,8 @@ extern "C" int oxm_plan_matmul(const oxm_view *a, const oxm_view *b, const oxm_v
   const bool a_direct = stage_direct(P, false, sa), b_direct = stage_direct(P, true, sb);
   const int64_t Kst = tf32 ? 3 * ((P.K + 31) / 32 * 32) : P.K;
   const int bk = kStageKBytes / P.elt;
-  const TileChoice c = choose_tiles(&fake, P, tf32, (int32_t)((Kst + bk - 1) / bk), (P.elt == 1 && b_direct && sb.mn_major) ? 128 : 0);
+  const TileChoice c = choose_tiles(&fake, P, tf32, (int32_t)((Kst + bk - 1) / bk), (P.elt == 1 && b_direct && sb.mn_major) ? 128 : 0,
+                                    b_direct && sb.mn_major);
   plan[0] = 2; plan[1] = c.bn; plan[2] = c.pair; plan[3] = c.splits;
   plan[4] = a_direct ? 0 : 1; plan[5] = b_direct ? 0 : 1;
   plan[6] = (int32_t)c.sk_tiles;
@@ -810,6 +870,8 @@ int check_status(oxm_ctx *ctx) {
     CUDA_TRY(cudaMemsetAsync(ctx->status_dev, 0, sizeof(uint32_t), ctx->stream));
     if (s == OXM_TIMEOUT)
       return fail(OXM_TIMEOUT, "a bounded device-side wait expired in %s; the result of that launch is undefined", ctx->last_kernel);
+    if (s == OXM_DIVIDE_BY_ZERO)
+      return fail(OXM_DIVIDE_BY_ZERO, "integer division by zero in div (the elements with a zero divisor were written as 0)");
     return fail(OXM_CUDA_ERROR, "device-side status %u in %s", s, ctx->last_kernel);
   }
   return OXM_OK;
@@ -840,8 +902,8 @@ const char *oxm_last_error(void) { return g_last_error.c_str(); }
 const char *oxm_status_name(int status) {
   static const char *names[] = {"Ok", "ShapeMismatch", "BroadcastIncompatible", "DTypeMismatch", "UnsupportedDType",
                                 "DeviceMismatch", "IndexOutOfBounds", "RankMismatch", "BackendUnavailable",
-                                "NotImplemented", "CudaError", "Timeout", "InvalidArgument"};
-  return (status >= 0 && status <= 12) ? names[status] : "Unknown";
+                                "NotImplemented", "CudaError", "Timeout", "InvalidArgument", "DivisionByZero"};
+  return (status >= 0 && status <= 13) ? names[status] : "Unknown";
 }
 
 const char *oxm_backend_name(void) { return "b200-tcgen05"; }
@@ -968,6 +1030,32 @@ int oxm_memset(oxm_ctx *ctx, void *dst_device, int byte, size_t bytes) {
   return OXM_OK;
 }
 
+int oxm_copy_peer(oxm_ctx *dst_ctx, void *dst_device, oxm_ctx *src_ctx, const void *src_device, size_t bytes) {
+  if (!dst_ctx || !src_ctx || (bytes && (!dst_device || !src_device))) return fail(OXM_INVALID_ARGUMENT, "oxm_copy_peer: null argument");
+  if (bytes == 0) return OXM_OK;
+  // The copy waits for what the source context has queued so far (its uploads), and runs on the
+  // destination's stream, so the destination's later kernels see the bytes.
+  cudaEvent_t ready = nullptr;
+  CUDA_TRY(cudaSetDevice(src_ctx->device));
+  CUDA_TRY(cudaEventCreateWithFlags(&ready, cudaEventDisableTiming));
+  cudaError_t e = cudaEventRecord(ready, src_ctx->stream);
+  if (e == cudaSuccess) e = cudaSetDevice(dst_ctx->device);
+  if (e == cudaSuccess && dst_ctx->device != src_ctx->device) {
+    // direct copies over NVLink where the pair allows it; without it the runtime stages the copy
+    int can = 0;
+    if (cudaDeviceCanAccessPeer(&can, dst_ctx->device, src_ctx->device) == cudaSuccess && can) {
+      const cudaError_t pe = cudaDeviceEnablePeerAccess(src_ctx->device, 0);
+      if (pe != cudaSuccess) cudaGetLastError();  // already enabled, or refused: the copy works either way
+    }
+  }
+  if (e == cudaSuccess) e = cudaStreamWaitEvent(dst_ctx->stream, ready, 0);
+  if (e == cudaSuccess)
+    e = cudaMemcpyPeerAsync(dst_device, dst_ctx->device, src_device, src_ctx->device, bytes, dst_ctx->stream);
+  cudaEventDestroy(ready);  // released once the work that uses it has completed
+  if (e != cudaSuccess) return fail(OXM_CUDA_ERROR, "oxm_copy_peer failed: %s", cudaGetErrorString(e));
+  return OXM_OK;
+}
+
 int oxm_sync(oxm_ctx *ctx) {
   if (!ctx) return fail(OXM_INVALID_ARGUMENT, "oxm_sync: null context");
   CUDA_TRY(cudaSetDevice(ctx->device));
@@ -1074,16 +1162,27 @@ int oxm_batched_matmul_host(oxm_ctx *ctx, const oxm_view *a, const oxm_view *b, 
     sliced[i] = xd[i] >= 0 && v->strides[xd[i]] > 0 &&
                 (double)v->strides[xd[i]] * (double)v->shape[xd[i]] >= 0.9 * (double)(hi[i] - lo[i] + 1);
   }
-  CUDA_TRY(cudaEventRecord(ev_alloc, ctx->stream));  // staging buffers exist from here on
-  CUDA_TRY(cudaStreamWaitEvent(ctx->copy_in, ev_alloc, 0));
-  CUDA_TRY(cudaStreamWaitEvent(ctx->copy_out, ev_alloc, 0));
-  for (int i = 0; i < 2; ++i)
+  // From here on a failing call must not return past the streams: copies already queued would
+  // keep writing the caller's buffers, and the staging buffers could be freed under them.  The
+  // first error is kept, no further work is queued, and the common tail below drains all three
+  // streams before the error is returned.
+  cudaError_t cuda_err = cudaSuccess;
+  const char *cuda_what = "";
+  auto ok = [&](cudaError_t e, const char *what) {
+    if (e != cudaSuccess && cuda_err == cudaSuccess) { cuda_err = e; cuda_what = what; }
+    return e == cudaSuccess;
+  };
+  ok(cudaEventRecord(ev_alloc, ctx->stream), "cudaEventRecord");  // staging buffers exist from here on
+  ok(cudaStreamWaitEvent(ctx->copy_in, ev_alloc, 0), "cudaStreamWaitEvent");
+  ok(cudaStreamWaitEvent(ctx->copy_out, ev_alloc, 0), "cudaStreamWaitEvent");
+  for (int i = 0; i < 2 && cuda_err == cudaSuccess; ++i)
     if (!sliced[i] && numel[i] > 0)
-      CUDA_TRY(cudaMemcpyAsync(dv[i].base, static_cast<const uint8_t *>(hv[i]->base) + lo[i] * elt,
-                               (size_t)(hi[i] - lo[i] + 1) * elt, cudaMemcpyHostToDevice, ctx->copy_in));
+      ok(cudaMemcpyAsync(dv[i].base, static_cast<const uint8_t *>(hv[i]->base) + lo[i] * elt,
+                         (size_t)(hi[i] - lo[i] + 1) * elt, cudaMemcpyHostToDevice, ctx->copy_in),
+         "copy of an operand to the device");
   const int64_t per = ((lead + chunks - 1) / chunks + unit - 1) / unit * unit;
   int c = 0;
-  for (int64_t i0 = 0; i0 < lead; i0 += per, ++c) {
+  for (int64_t i0 = 0; i0 < lead && st == OXM_OK && cuda_err == cudaSuccess; i0 += per, ++c) {
     const int64_t len = std::min(per, lead - i0);
     oxm_view cv[3] = {dv[0], dv[1], dv[2]};
     for (int i = 0; i < 2; ++i) {
@@ -1097,32 +1196,36 @@ int oxm_batched_matmul_host(oxm_ctx *ctx, const oxm_view *a, const oxm_view *b, 
         int64_t clo, chi, cn;
         view_extent(&hs, &clo, &chi, &cn);
         if (cn > 0)
-          CUDA_TRY(cudaMemcpyAsync(static_cast<uint8_t *>(dv[i].base) + (clo - lo[i]) * elt,
-                                   static_cast<const uint8_t *>(hv[i]->base) + clo * elt, (size_t)(chi - clo + 1) * elt,
-                                   cudaMemcpyHostToDevice, ctx->copy_in));
+          ok(cudaMemcpyAsync(static_cast<uint8_t *>(dv[i].base) + (clo - lo[i]) * elt,
+                             static_cast<const uint8_t *>(hv[i]->base) + clo * elt, (size_t)(chi - clo + 1) * elt,
+                             cudaMemcpyHostToDevice, ctx->copy_in), "copy of an operand slice to the device");
       }
     }
+    if (cuda_err != cudaSuccess) break;
     cv[2].shape[0] = len;
     cv[2].offset += i0 * out->strides[0];
     cudaEvent_t ev_in = ctx->pipe_events[1 + 2 * c], ev_done = ctx->pipe_events[2 + 2 * c];
-    CUDA_TRY(cudaEventRecord(ev_in, ctx->copy_in));
-    CUDA_TRY(cudaStreamWaitEvent(ctx->stream, ev_in, 0));
+    if (!ok(cudaEventRecord(ev_in, ctx->copy_in), "cudaEventRecord") ||
+        !ok(cudaStreamWaitEvent(ctx->stream, ev_in, 0), "cudaStreamWaitEvent")) break;
     st = run_matmul(ctx, &cv[0], &cv[1], &cv[2], true);
     if (st) break;
-    CUDA_TRY(cudaEventRecord(ev_done, ctx->stream));
-    CUDA_TRY(cudaStreamWaitEvent(ctx->copy_out, ev_done, 0));
+    if (!ok(cudaEventRecord(ev_done, ctx->stream), "cudaEventRecord") ||
+        !ok(cudaStreamWaitEvent(ctx->copy_out, ev_done, 0), "cudaStreamWaitEvent")) break;
     const int64_t o0 = (out->offset + i0 * out->strides[0]) * elt;
     const int64_t d0 = (dv[2].offset + i0 * out->strides[0]) * elt;
-    CUDA_TRY(cudaMemcpyAsync(static_cast<uint8_t *>(out->base) + o0, static_cast<uint8_t *>(dv[2].base) + d0,
-                             (size_t)(len * out->strides[0]) * elt, cudaMemcpyDeviceToHost, ctx->copy_out));
+    ok(cudaMemcpyAsync(static_cast<uint8_t *>(out->base) + o0, static_cast<uint8_t *>(dv[2].base) + d0,
+                       (size_t)(len * out->strides[0]) * elt, cudaMemcpyDeviceToHost, ctx->copy_out),
+       "copy of a result slice to the host");
   }
+  const std::string first_detail = g_last_error;  // check_status below may overwrite the message of `st`
   cudaError_t e1 = cudaStreamSynchronize(ctx->copy_in), e2 = cudaStreamSynchronize(ctx->copy_out);
   int st2;
   {
     std::lock_guard<std::mutex> lock(ctx->mu);
-    st2 = check_status(ctx);
+    st2 = check_status(ctx);  // drains the compute stream
   }
-  if (st) return st;
+  if (st) { g_last_error = first_detail; return st; }
+  if (cuda_err != cudaSuccess) return fail(OXM_CUDA_ERROR, "host matmul: %s failed: %s", cuda_what, cudaGetErrorString(cuda_err));
   if (e1 != cudaSuccess || e2 != cudaSuccess)
     return fail(OXM_CUDA_ERROR, "host matmul copy failed: %s", cudaGetErrorString(e1 != cudaSuccess ? e1 : e2));
   return st2;
@@ -1482,7 +1585,7 @@ extern "C" int oxm_binary(oxm_ctx *ctx, int op, const oxm_view *a, const oxm_vie
     return fail(OXM_DEVICE_MISMATCH, "device mismatch: Cuda{index: %d} vs Cuda{index: %d} in %s", a->device, out->device, name);
   if (a->dtype != b->dtype)
     return fail(OXM_DTYPE_MISMATCH, "dtype mismatch: expected %s, got %s in %s", dtype_name(a->dtype), dtype_name(b->dtype), name);
-  if (!is_ew_dtype(a->dtype) || (op == OXM_DIV && !is_float_dtype(a->dtype)))
+  if (!is_ew_dtype(a->dtype))
     return fail(OXM_UNSUPPORTED_DTYPE, "dtype %s is not supported by %s", dtype_name(a->dtype), name);
   // NumPy broadcasting (shape.rs:49-55)
   int nd = std::max(a->ndim, b->ndim);
@@ -1513,6 +1616,17 @@ extern "C" int oxm_binary(oxm_ctx *ctx, int op, const oxm_view *a, const oxm_vie
            (reinterpret_cast<uintptr_t>(p.b) + p.b_off * esz) % 16 == 0 && reinterpret_cast<uintptr_t>(p.out) % 16 == 0) ? 1 : 0;
   std::lock_guard<std::mutex> lock(ctx->mu);
   CUDA_TRY(cudaSetDevice(ctx->device));
+  if (op == OXM_DIV && !is_float_dtype(a->dtype)) {
+    // Integer division reports a zero divisor as a typed error, so it is the one compute call
+    // that waits for its kernel: the status word is read back before returning.
+    const unsigned blocks = (unsigned)std::min<int64_t>((p.n + 255) / 256, (int64_t)ctx->num_sms * 16);
+    if (a->dtype == OXM_I32) int_div_kernel<int32_t><<<blocks, 256, 0, ctx->stream>>>(p, ctx->status_dev);
+    else int_div_kernel<int64_t><<<blocks, 256, 0, ctx->stream>>>(p, ctx->status_dev);
+    CUDA_TRY(cudaGetLastError());
+    ctx->launches[0]++;
+    snprintf(ctx->last_kernel, sizeof(ctx->last_kernel), "binary_%s", name);
+    return check_status(ctx);
+  }
   const unsigned blocks = ew_plan(ctx, p, esz, true);
   dispatch_dtype<BinaryLauncher>(a->dtype, ctx, p, blocks);
   CUDA_TRY(cudaGetLastError());
@@ -1658,7 +1772,7 @@ int oxm_set_option(oxm_ctx *ctx, const char *key, int64_t value) {
   if (!ctx || !key) return fail(OXM_INVALID_ARGUMENT, "oxm_set_option: null argument");
   std::lock_guard<std::mutex> lock(ctx->mu);
   if (!strcmp(key, "kernel") && value >= 0 && value <= 2) ctx->opt_kernel = value;
-  else if (!strcmp(key, "tile_n") && (value == 0 || value == 64 || value == 128 || value == 256 || value == 512)) ctx->opt_tile_n = value;
+  else if (!strcmp(key, "tile_n") && (value == 0 || (value >= 64 && value <= 512 && value % 32 == 0))) ctx->opt_tile_n = value;
   else if (!strcmp(key, "cta_pair") && value >= -1 && value <= 1) ctx->opt_cta_pair = value;
   else if (!strcmp(key, "wait_limit_ms") && value >= 1 && value <= 600000) ctx->opt_wait_limit_ms = value;
   else if (!strcmp(key, "group_m") && value >= 0 && value <= 1024) ctx->opt_group_m = value;
@@ -1694,6 +1808,20 @@ int oxm_launch_counts(oxm_ctx *ctx, int64_t counts[4]) {
 }
 
 const char *oxm_last_kernel(oxm_ctx *ctx) { return ctx ? ctx->last_kernel : "none"; }
+
+int oxm_memory_stats(oxm_ctx *ctx, int64_t stats[4]) {
+  if (!ctx || !stats) return fail(OXM_INVALID_ARGUMENT, "oxm_memory_stats: null argument");
+  CUDA_TRY(cudaSetDevice(ctx->device));
+  cudaMemPool_t pool;
+  CUDA_TRY(cudaDeviceGetDefaultMemPool(&pool, ctx->device));
+  uint64_t reserved = 0, used = 0;
+  CUDA_TRY(cudaMemPoolGetAttribute(pool, cudaMemPoolAttrReservedMemCurrent, &reserved));
+  CUDA_TRY(cudaMemPoolGetAttribute(pool, cudaMemPoolAttrUsedMemCurrent, &used));
+  size_t free_b = 0, total_b = 0;
+  CUDA_TRY(cudaMemGetInfo(&free_b, &total_b));
+  stats[0] = (int64_t)reserved; stats[1] = (int64_t)used; stats[2] = (int64_t)free_b; stats[3] = (int64_t)total_b;
+  return OXM_OK;
+}
 
 }  // extern "C"
 
@@ -1823,6 +1951,7 @@ extern "C" int oxm_matmul_f32_noalloc(oxm_ctx *ctx, const oxm_view *a, const oxm
   const int tm = kTileM * (pair ? 2 : 1);
   GemmParams p{};
   p.M = (int32_t)P.M; p.N = (int32_t)P.N; p.K = (int32_t)(3 * Kp);
+  p.bn = bn; p.subn = bn;
   p.tiles_m = (int32_t)((P.M + tm - 1) / tm);
   p.tiles_n = (int32_t)((P.N + bn - 1) / bn);
   p.num_kb = num_kb;
@@ -1863,7 +1992,7 @@ extern "C" int oxm_matmul_f32_noalloc(oxm_ctx *ctx, const oxm_view *a, const oxm
   p.out_tma = 0;  // plain strided stores: the output may be any view
   p.dp_tiles = p.num_tiles;  // whole tiles only: stream-K would need a workspace
   p.sk_tiles = 0;
-  p.stage_tx = (uint32_t)(kStageKBytes * (kTileM + bn));
+  p.stage_tx = (uint32_t)(kStageKBytes * (kTileM + (pair ? bn / 2 : bn)));  // per CTA
   st = make_map(ctx, &tmA, sa, OXM_F32, 4, kTileM, 32);
   if (st) return st;
   st = make_map(ctx, &tmB, sb, OXM_F32, 4, pair ? bn / 2 : bn, 32);

@@ -84,9 +84,8 @@ template <> __device__ __forceinline__ int64_t unary_apply<int64_t>(int op, int6
 }
 
 template <typename C> __device__ __forceinline__ C binary_apply(int op, C x, C y) {
-  return op == 0 ? x + y : op == 1 ? x - y : op == 2 ? x * y : x / y;  // integer div is refused on the host
+  return op == 0 ? x + y : op == 1 ? x - y : op == 2 ? x * y : x / y;  // integer div has its own kernel
 }
-
 // 16 bytes of T, moved with one vector load / store.
 template <typename T> struct alignas(16) EwVec { T v[16 / sizeof(T)]; };
 
@@ -142,6 +141,31 @@ __global__ void __launch_bounds__(256) binary_kernel(const EwParams p) {
     ew_offsets(p, i, ao, bo);
     ew_store<T>(out, i, binary_apply<C>(p.op, ew_load<T>(a, ao), ew_load<T>(b, bo)));
   }
+}
+
+// Integer division (BinaryOps::div on i32 / i64): truncates toward zero; the
+// most negative value divided by -1 wraps to itself, as two's-complement
+// negation does.  A zero divisor is a typed error for the caller: the thread
+// that meets one stores 0 for that element and records kStatusDivideByZero in
+// the context's status word, which the host reads before the call returns.
+constexpr uint32_t kStatusDivideByZero = 13;  // OXM_DIVIDE_BY_ZERO
+
+template <typename T>
+__global__ void __launch_bounds__(256) int_div_kernel(const EwParams p, uint32_t *status) {
+  const T *a = static_cast<const T *>(p.a), *b = static_cast<const T *>(p.b);
+  T *out = static_cast<T *>(p.out);
+  bool zero_seen = false;
+  for (int64_t i = blockIdx.x * 256ll + threadIdx.x; i < p.n; i += static_cast<int64_t>(gridDim.x) * 256) {
+    int64_t ao, bo;
+    ew_offsets(p, i, ao, bo);
+    const int64_t x = static_cast<int64_t>(a[ao]), y = static_cast<int64_t>(b[bo]);
+    int64_t r = 0;
+    if (y == 0) zero_seen = true;
+    else if (y == -1) r = static_cast<int64_t>(0ull - static_cast<uint64_t>(x));
+    else r = x / y;
+    out[i] = static_cast<T>(r);
+  }
+  if (zero_seen) atomicCAS(status, 0u, kStatusDivideByZero);
 }
 
 // Strided or broadcast operands with a long innermost dim: one CTA per row.
@@ -433,7 +457,9 @@ struct ReduceOpParams {
   int64_t a_off;
 };
 
-template <typename C> __device__ __forceinline__ C reduce_combine(int op, C x, C y) { return op == 0 ? x + y : (y > x ? y : x); }
+// max propagates NaN: once either side is NaN the result stays NaN, whatever the order of combination.
+template <typename C> __device__ __forceinline__ C reduce_max(C x, C y) { return x != x ? x : (y != y ? y : (y > x ? y : x)); }
+template <typename C> __device__ __forceinline__ C reduce_combine(int op, C x, C y) { return op == 0 ? x + y : reduce_max<C>(x, y); }
 
 template <typename C> __device__ __forceinline__ C reduce_identity(int op);
 template <> __device__ __forceinline__ float reduce_identity<float>(int op) { return op == 0 ? 0.0f : -INFINITY; }

@@ -43,6 +43,8 @@ constexpr uint32_t kStatusTimeout = 11;  // OXM_TIMEOUT
 
 struct GemmParams {
   int32_t M, N, K;           // K counts elements of the staged operands
+  int32_t bn;                // tile width in columns: a multiple of 32, at most the kernel's BN
+  int32_t subn;              // columns per tcgen05.mma (bn, or bn / 2 for tiles wider than 256)
   int32_t tiles_m, tiles_n;  // tiles_m counts (kTileM * ctas-per-tile)-row blocks
   int32_t num_kb;            // contraction blocks per tile
   int32_t nbatch;
@@ -58,7 +60,7 @@ struct GemmParams {
   int32_t out_vec;         // rows may be written with 16-byte stores
   int32_t out_tma;         // the output is described by the store tensor map
   uint32_t idesc;
-  uint32_t stage_tx;       // bytes one CTA's loads of one stage deliver (1-CTA kernels: the A box may be shorter than the tile)
+  uint32_t stage_tx;       // bytes one CTA's loads of one stage deliver (the boxes follow the tile's width; a short A gets a short box)
   uint32_t *status;
   uint64_t wait_limit_ns;
   // Split-K: the contraction is cut into `splits` chains of `kb_per_split`
@@ -248,15 +250,25 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   constexpr int MMAS = kStageKBytes / kMmaKBytes;
   constexpr int MMA_K = kMmaKBytes / ELT;  // contraction elements per tcgen05.mma
   constexpr int TM = kTileM * (PAIR ? 2 : 1);
-  // A tile wider than 256 columns is NSUB MMAs of SUBN columns side by side in
+  // BN is the widest tile this instance can hold; the tile's actual width p.bn
+  // may be any multiple of 32 up to it (the shared-memory slots and the tensor
+  // memory columns keep BN's spacing, the TMA boxes and the MMAs follow p.bn).
+  // A tile wider than 256 columns is two MMAs of p.subn columns side by side in
   // tensor memory.  Two accumulators (epilogue overlapped with the next main
   // loop) while they fit the 512 columns, one otherwise.
-  constexpr int NSUB = BN > 256 ? BN / 256 : 1;
-  constexpr int SUBN = BN / NSUB;
-  constexpr int SUBC = PAIR ? SUBN / 2 : SUBN;  // B rows one CTA stages per sub-tile
-  constexpr int ACC = (2 * BN <= 512) ? 2 : 1;
+  constexpr bool WIDE = BN > 256;
+  constexpr int NSUB = WIDE ? 2 : 1;
+  constexpr int SUBC_CAP = (BN / NSUB) / (PAIR ? 2 : 1);  // B rows one CTA can stage per sub-tile
+  constexpr int ACC = WIDE ? 1 : 2;
   constexpr int EPI_GROUPS = gemm_epi_groups(BN);
-  constexpr int GROUP_COLS = BN / EPI_GROUPS;  // accumulator columns one epilogue warp drains
+  constexpr int CH = BN >= 128 ? 4 : 2;   // 32-column chunks an epilogue warp drains per wait
+  constexpr int NPH = WIDE ? 2 : 1;       // drain phases per tile
+  static_assert(NPH * EPI_GROUPS * CH * 32 == BN, "the epilogue warps cover the widest tile exactly");
+  // The one-accumulator tile starts the next tile's MMAs on the first sub-tile
+  // alone, for PRO contraction blocks, as soon as the columns below 256 have
+  // been read out; the second sub-tile follows once the rest is out.  Each
+  // column still sees its products in ascending k, so no bit changes.
+  constexpr int PRO = WIDE ? STAGES - 1 : 0;
   constexpr uint32_t TMEM_COLS = (ACC * BN <= 128) ? 128 : (ACC * BN <= 256) ? 256 : 512;
 
   extern __shared__ uint8_t smem_raw[];
@@ -268,6 +280,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   auto full_bar = [&](int s) { return bars + 8u * s; };
   auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
   auto tfull_bar = [&](int a) { return bars + 8u * (2 * STAGES + a); };
+  // two accumulators: one "drained" barrier each; one accumulator: [0] columns below 256, [1] the rest
   auto tempty_bar = [&](int a) { return bars + 8u * (2 * STAGES + 2 + a); };
   const uint32_t teardown_bar = bars + 8u * (2 * STAGES + 4);
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(base_ptr + L::kBarOffset + L::kNumBars * 8);
@@ -277,6 +290,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   const uint32_t lane = threadIdx.x & 31;
   const uint32_t cta_rank = PAIR ? ptx::cluster_ctarank() : 0u;
   const bool leader = cta_rank == 0;
+  const int32_t bn = p.bn;
+  const int32_t subn = p.subn;
+  const int32_t subc = PAIR ? (subn >> 1) : subn;  // B rows this CTA stages per sub-tile
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -323,10 +339,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       WorkIter it;
       WorkItem wi;
       it.init(p, tile_first, tile_stride);
+      const int32_t b_boxes = (subc + BOXW - 1) / BOXW;  // MN-major B: boxes of BOXW columns per sub-tile
       while (ok && it.next(p, wi)) {
         const TileCoord tc = decode_item(p, wi);
         const int32_t m0 = tc.m_blk * TM + static_cast<int32_t>(cta_rank) * kTileM;
-        const int32_t n0 = tc.n_blk * BN + static_cast<int32_t>(cta_rank) * SUBC;  // + sub * SUBN per sub-tile
+        const int32_t n0 = tc.n_blk * bn + static_cast<int32_t>(cta_rank) * subc;  // + sub * subn per sub-tile
         for (int32_t kb = 0; kb < tc.nkb; ++kb) {
           if (!bounded_wait(empty_bar(s), ph ^ 1u, wc)) { ok = false; break; }
           const uint32_t sa = base + s * L::kStageBytes;
@@ -335,7 +352,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           if constexpr (PAIR) {
             // The leader's barrier collects the bytes of both CTAs' loads.
             const uint32_t fb = ptx::mapa_shared(full_bar(s), 0);
-            if (leader) ptx::mbar_arrive_expect_tx(full_bar(s), 2u * L::kStageBytes);
+            if (leader) ptx::mbar_arrive_expect_tx(full_bar(s), 2u * p.stage_tx);
             if constexpr (A_MN) {
 #pragma unroll
               for (int j = 0; j < kTileM / BOXW; ++j)
@@ -345,11 +362,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             }
 #pragma unroll
             for (int sub = 0; sub < NSUB; ++sub) {
-              const uint32_t sbs = sb + sub * (SUBC * kStageKBytes);
-              const int32_t ns = n0 + sub * SUBN;
+              const uint32_t sbs = sb + sub * (SUBC_CAP * kStageKBytes);
+              const int32_t ns = n0 + sub * subn;
               if constexpr (B_MN) {
-#pragma unroll
-                for (int j = 0; j < SUBC / BOXW; ++j)
+                for (int j = 0; j < b_boxes; ++j)
                   ptx::tma_load_3d_pair(sbs + j * (BK * kStageKBytes), &tmB, fb, ns + j * BOXW, k0, tc.b_batch);
               } else {
                 ptx::tma_load_3d_pair(sbs, &tmB, fb, k0, ns, tc.b_batch);
@@ -366,8 +382,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
               ptx::tma_load_3d(sa, &tmA, fb, k0, m0, tc.a_batch);
             }
             if constexpr (B_MN) {
-#pragma unroll
-              for (int j = 0; j < SUBC / BOXW; ++j)
+              for (int j = 0; j < b_boxes; ++j)
                 ptx::tma_load_3d(sb + j * (BK * kStageKBytes), &tmB, fb, n0 + j * BOXW, k0, tc.b_batch);
             } else {
               ptx::tma_load_3d(sb, &tmB, fb, k0, n0, tc.b_batch);
@@ -392,38 +407,78 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       constexpr uint32_t B_LBO = B_MN ? BK * kStageKBytes : 16;
       constexpr uint32_t A_ADV = (A_MN ? MMA_K * kStageKBytes : kMmaKBytes) >> 4;
       constexpr uint32_t B_ADV = (B_MN ? MMA_K * kStageKBytes : kMmaKBytes) >> 4;
+      constexpr uint32_t B_SUB = (SUBC_CAP * kStageKBytes) >> 4;  // descriptor distance between the sub-tiles' slots
       uint32_t s = 0, ph = 0, as = 0, aph = 0;
       bool ok = true;
       WorkIter it;
       WorkItem wi;
       it.init(p, tile_first, tile_stride);
+      // The four MMAs of one contraction block for sub-tile `sub`, from stage `st`.
+      auto issue = [&](uint32_t st, int sub, uint32_t d_tmem, int32_t kb) {
+        const uint32_t sa = base + st * L::kStageBytes;
+        const uint32_t sb = sa + L::kABytes;
+        const uint64_t adesc = make_smem_desc(sa, A_LBO, 1024);
+        const uint64_t bdesc = make_smem_desc(sb, B_LBO, 1024) + static_cast<uint64_t>(sub * B_SUB);
+#pragma unroll
+        for (int j = 0; j < MMAS; ++j)
+          ptx::umma<PAIR, KIND>(d_tmem + sub * subn, adesc + static_cast<uint64_t>(j * A_ADV),
+                                bdesc + static_cast<uint64_t>(j * B_ADV), p.idesc, (kb | j) != 0 ? 1u : 0u);
+      };
+      auto release_stage = [&](uint32_t st) {
+        if constexpr (PAIR) ptx::umma_commit_pair(empty_bar(st), 3);
+        else ptx::umma_commit(empty_bar(st));
+      };
       while (ok && it.next(p, wi)) {
         int32_t nkb = wi.nkb;
         if (nkb < 0) {
           const int32_t split = static_cast<int32_t>(wi.tile / p.tiles_per_split);
           nkb = min(p.kb_per_split, p.num_kb - split * p.kb_per_split);
         }
-        if (!bounded_wait(tempty_bar(as), aph ^ 1u, wc)) break;
+        if (!bounded_wait(tempty_bar(WIDE ? 0 : as), aph ^ 1u, wc)) break;
         ptx::tc_fence_after();
         const uint32_t d_tmem = tmem_base + as * BN;
-        for (int32_t kb = 0; kb < nkb; ++kb) {
+        int32_t kb = 0;
+        if constexpr (WIDE) {
+          // The first sub-tile's columns are free: run it ahead for up to PRO blocks
+          // while the epilogue warps finish reading the second sub-tile's.
+          const int32_t pro = min(PRO, nkb);
+          uint32_t s2 = s, ph2 = ph;
+          for (int32_t k2 = 0; k2 < pro; ++k2) {
+            if (!bounded_wait(full_bar(s2), ph2, wc)) { ok = false; break; }
+            ptx::tc_fence_after();
+            issue(s2, 0, d_tmem, k2);
+            if (++s2 == STAGES) { s2 = 0; ph2 ^= 1u; }
+          }
+          if (!ok) break;
+          if (!bounded_wait(tempty_bar(1), aph ^ 1u, wc)) break;
+          ptx::tc_fence_after();
+          for (int32_t k2 = 0; k2 < pro; ++k2) {
+            issue(s, 1, d_tmem, k2);
+            release_stage(s);
+            if (++s == STAGES) { s = 0; ph ^= 1u; }
+          }
+          kb = pro;
+        }
+        for (; kb < nkb; ++kb) {
           if (!bounded_wait(full_bar(s), ph, wc)) { ok = false; break; }
           ptx::tc_fence_after();
-          const uint32_t sa = base + s * L::kStageBytes;
-          const uint32_t sb = sa + L::kABytes;
-          const uint64_t adesc = make_smem_desc(sa, A_LBO, 1024);
-          const uint64_t bdesc = make_smem_desc(sb, B_LBO, 1024);
+          if constexpr (WIDE) {
+            // sub-tiles side by side, k step by k step: both reuse the A slice while it is hot
+            const uint32_t sa = base + s * L::kStageBytes;
+            const uint32_t sb = sa + L::kABytes;
+            const uint64_t adesc = make_smem_desc(sa, A_LBO, 1024);
+            const uint64_t bdesc = make_smem_desc(sb, B_LBO, 1024);
 #pragma unroll
-          for (int j = 0; j < MMAS; ++j) {
+            for (int j = 0; j < MMAS; ++j) {
 #pragma unroll
-            for (int sub = 0; sub < NSUB; ++sub) {
-              ptx::umma<PAIR, KIND>(d_tmem + sub * SUBN, adesc + static_cast<uint64_t>(j * A_ADV),
-                                    bdesc + static_cast<uint64_t>(j * B_ADV + sub * ((SUBC * kStageKBytes) >> 4)),
-                                    p.idesc, (kb | j) != 0 ? 1u : 0u);
+              for (int sub = 0; sub < NSUB; ++sub)
+                ptx::umma<PAIR, KIND>(d_tmem + sub * subn, adesc + static_cast<uint64_t>(j * A_ADV),
+                                      bdesc + static_cast<uint64_t>(j * B_ADV + sub * B_SUB), p.idesc, (kb | j) != 0 ? 1u : 0u);
             }
+          } else {
+            issue(s, 0, d_tmem, kb);
           }
-          if constexpr (PAIR) ptx::umma_commit_pair(empty_bar(s), 3);
-          else ptx::umma_commit(empty_bar(s));
+          release_stage(s);
           if (++s == STAGES) { s = 0; ph ^= 1u; }
         }
         if (!ok) break;
@@ -443,15 +498,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     __syncwarp();
   } else {
     // ---------------- epilogue: TMEM -> registers -> global ----------------
+    const uint32_t ew = warp - 2u;
     const uint32_t q = warp & 3u;  // the TMEM lane quarter this warp may read
-    const uint32_t stage_smem = base + L::kStagingOffset + (warp - 2u) * L::kStagingTile;
+    const uint32_t grp = ew >> 2;  // which share of the columns this warp drains
+    const uint32_t stage_smem = base + L::kStagingOffset + ew * L::kStagingTile;
     const int esz = p.out_dtype == 0 ? 4 : (p.out_dtype >= 8 ? 1 : 2);
+    const int32_t nchunks = bn >> 5;  // 32-column chunks of a tile
     uint32_t as = 0, aph = 0;
     WorkIter it;
     WorkItem wi;
     it.init(p, tile_first, tile_stride);
     const int64_t my_run = tile_stride - 1 - tile_first;  // this CTA's (pair's) stream-K run
     constexpr int CPT = PAIR ? 2 : 1;
+    constexpr int WARP_COLS = NPH * CH * 32;  // columns one warp drains from the widest tile
     while (it.next(p, wi)) {
       const TileCoord tc = decode_item(p, wi);
       // tcgen05.ld is warp-collective: leave the loop as a whole warp or not at all.
@@ -471,7 +530,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           sk_run(p.sk_tiles * p.num_kb, tile_stride, r, rb, re);
           left -= static_cast<int32_t>(min(re - rb, static_cast<int64_t>(left)));
           // wait (bounded) until run r's warp of the same rows and columns has published its sums
-          const uint32_t *flag = p.sk_flags + (r * CPT + cta_rank) * 8 + (warp - 2u);
+          const uint32_t *flag = p.sk_flags + (r * CPT + cta_rank) * 8 + ew;
           if (arrived && ptx::ld_acquire_gpu(flag) != p.sk_epoch) {
             const uint64_t t0 = ptx::globaltimer_ns();
             while (ptx::ld_acquire_gpu(flag) != p.sk_epoch) {
@@ -535,9 +594,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           }
         }
       };
-      const int32_t gcol = static_cast<int32_t>((warp - 2u) >> 2) * GROUP_COLS;  // this warp's first column
-      const uint32_t t_acc = tmem_base + as * BN + gcol + ((q * 32u) << 16);
-      const int32_t col_base = tc.n_blk * BN + gcol;
+      const uint32_t t_row = tmem_base + as * BN + ((q * 32u) << 16);
+      const int32_t tile_col0 = tc.n_blk * bn;
       const int32_t row0 = row - static_cast<int32_t>(lane);  // first of this warp's 32 rows
       // One 128-byte-wide chunk of the warp's 32 rows: staged in shared memory in
       // the 128-byte swizzle (16-byte piece j of row r lands at piece j ^ (r & 7)),
@@ -559,33 +617,36 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           ptx::bulk_commit_group();
         }
       };
-      constexpr int BATCH = GROUP_COLS % 128 == 0 ? 128 : 64;  // columns drained per wait
-      constexpr int NLD = BATCH / 32;
 #pragma unroll 1
-      for (int c = 0; c < GROUP_COLS / BATCH; ++c) {
-        uint32_t v[NLD][32];
+      for (int dp = 0; dp < NPH; ++dp) {
+        // this warp's chunks of the phase: [ch0, ch0 + CH), those below nchunks exist
+        const int32_t ch0 = dp * (CH * EPI_GROUPS) + static_cast<int32_t>(grp) * CH;
+        uint32_t v[CH][32];
 #pragma unroll
-        for (int i = 0; i < NLD; ++i) ptx::tmem_ld_32x32(t_acc + c * BATCH + i * 32, v[i]);
+        for (int i = 0; i < CH; ++i)
+          if (ch0 + i < nchunks) ptx::tmem_ld_32x32(t_row + static_cast<uint32_t>((ch0 + i) * 32), v[i]);
         ptx::tmem_ld_wait();
-        if (c == GROUP_COLS / BATCH - 1) {
-          // The accumulator now lives in registers: hand it back before converting and storing.
+        if (WIDE || dp == NPH - 1) {
+          // These columns now live in registers: hand them back before converting and storing.
           ptx::tc_fence_before();
           __syncwarp();
           if (lane == 0) {
-            if constexpr (PAIR) ptx::mbar_arrive_cluster(ptx::mapa_shared(tempty_bar(as), 0));
-            else ptx::mbar_arrive(tempty_bar(as));
+            const uint32_t bar = tempty_bar(WIDE ? dp : static_cast<int>(as));
+            if constexpr (PAIR) ptx::mbar_arrive_cluster(ptx::mapa_shared(bar, 0));
+            else ptx::mbar_arrive(bar);
           }
         }
         if (wi.kind == 2) {
           // contributor: this run started inside the tile; leave the raw sums for the tile's owner.
           // The hand-over area is private to the two warps involved (same rows, same columns,
           // same registers), so it is laid out by register: every store is 512 contiguous bytes.
-          uint4 *dst = reinterpret_cast<uint4 *>(sk_mine + static_cast<int64_t>(warp - 2u) * (32 * GROUP_COLS)) + lane;
+          uint4 *dst = reinterpret_cast<uint4 *>(sk_mine + static_cast<int64_t>(ew) * (32 * WARP_COLS)) + lane;
 #pragma unroll
-          for (int i = 0; i < NLD; ++i) {
+          for (int i = 0; i < CH; ++i) {
+            if (ch0 + i >= nchunks) continue;
 #pragma unroll
             for (int j = 0; j < 8; ++j)
-              dst[((c * NLD + i) * 8 + j) * 32] = make_uint4(v[i][4 * j], v[i][4 * j + 1], v[i][4 * j + 2], v[i][4 * j + 3]);
+              dst[((dp * CH + i) * 8 + j) * 32] = make_uint4(v[i][4 * j], v[i][4 * j + 1], v[i][4 * j + 2], v[i][4 * j + 3]);
           }
           continue;
         }
@@ -593,12 +654,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           // owner: add the later runs' sums of these columns, in run order
           for (int o = 0; o < sk_others; ++o) {
             const float4 *src = reinterpret_cast<const float4 *>(p.sk_ws + ((my_run + 1 + o) * CPT + cta_rank) * sk_warp_elems +
-                                                                 static_cast<int64_t>(warp - 2u) * (32 * GROUP_COLS)) + lane;
+                                                                 static_cast<int64_t>(ew) * (32 * WARP_COLS)) + lane;
 #pragma unroll
-            for (int i = 0; i < NLD; ++i) {
+            for (int i = 0; i < CH; ++i) {
+              if (ch0 + i >= nchunks) continue;
 #pragma unroll
               for (int j = 0; j < 8; ++j) {
-                const float4 t = __ldcg(src + ((c * NLD + i) * 8 + j) * 32);
+                const float4 t = __ldcg(src + ((dp * CH + i) * 8 + j) * 32);
                 v[i][4 * j] = __float_as_uint(__uint_as_float(v[i][4 * j]) + t.x);
                 v[i][4 * j + 1] = __float_as_uint(__uint_as_float(v[i][4 * j + 1]) + t.y);
                 v[i][4 * j + 2] = __float_as_uint(__uint_as_float(v[i][4 * j + 2]) + t.z);
@@ -607,11 +669,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             }
           }
         }
-        const int32_t colb = col_base + c * BATCH;
+        const int32_t colb = tile_col0 + ch0 * 32;
         if (p.epi.any) {
           // bias, activation and accumulation on the fp32 sums, before rounding
 #pragma unroll
-          for (int i = 0; i < NLD; ++i) {
+          for (int i = 0; i < CH; ++i) {
+            if (ch0 + i >= nchunks) continue;
 #pragma unroll
             for (int e = 0; e < 32; ++e) {
               const int32_t col = colb + i * 32 + e;
@@ -625,7 +688,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         if (p.out_tma) {
           if constexpr (KIND == 1) {
 #pragma unroll
-            for (int i = 0; i < NLD; ++i) {
+            for (int i = 0; i < CH; ++i) {
+              if (ch0 + i >= nchunks) continue;
               uint4 piece[8];
 #pragma unroll
               for (int j = 0; j < 8; ++j) piece[j] = make_uint4(v[i][4 * j], v[i][4 * j + 1], v[i][4 * j + 2], v[i][4 * j + 3]);
@@ -633,7 +697,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             }
           } else {
 #pragma unroll
-            for (int i = 0; i < NLD / 2; ++i) {
+            for (int i = 0; i < CH / 2; ++i) {
+              if (ch0 + 2 * i >= nchunks) continue;
+              if (ch0 + 2 * i + 1 >= nchunks) {
+                // the tile's last chunk has no partner to fill a 128-byte box with
+                store_chunk(v[2 * i], colb + i * 64);
+                continue;
+              }
               uint4 piece[8];
 #pragma unroll
               for (int j = 0; j < 8; ++j) {
@@ -657,14 +727,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           }
         } else {
 #pragma unroll
-          for (int i = 0; i < NLD; ++i) store_chunk(v[i], colb + i * 32);
+          for (int i = 0; i < CH; ++i)
+            if (ch0 + i < nchunks) store_chunk(v[i], colb + i * 32);
         }
       }
       if (wi.kind == 2) {
         // publish: the sums above are visible to whoever reads this launch's counter here
         __threadfence();
         __syncwarp();
-        if (lane == 0) ptx::st_release_gpu(p.sk_flags + (my_run * CPT + cta_rank) * 8 + (warp - 2u), p.sk_epoch);
+        if (lane == 0) ptx::st_release_gpu(p.sk_flags + (my_run * CPT + cta_rank) * 8 + ew, p.sk_epoch);
       }
       if (++as == ACC) { as = 0; aph ^= 1u; }
     }

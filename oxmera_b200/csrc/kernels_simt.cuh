@@ -37,6 +37,17 @@ __global__ void bounded_wait_selftest_kernel(uint32_t *status, uint64_t limit_ns
 // walked in ascending k in blocks of 16.  Reads A, B and writes
 // C through signed element strides, so transposed / narrowed / flipped views
 // and broadcast batch dims need no preparation.
+//
+// The loads of the next four blocks are in flight while a block is multiplied
+// (they wait in registers until the shared-memory tiles are free again), so a
+// CTA pays the latency of global memory once, not once per block.
+//
+// Products with too few tiles to fill the GPU split the contraction over the
+// `ksplit` CTAs of a thread-block cluster (the CTAs of one cluster are
+// consecutive blocks of the grid).  Each adds up its own range of k; the
+// partial tiles meet in the first CTA's registers through distributed shared
+// memory, always in rank order, so the result does not depend on timing.
+// With ksplit = 1 every output element is one fp32 chain in ascending k.
 // ---------------------------------------------------------------------------
 struct SimtParams {
   const void *a, *b;
@@ -44,6 +55,7 @@ struct SimtParams {
   int32_t dtype, out_dtype;
   int32_t M, N, K;
   int32_t tiles_m, tiles_n;
+  int32_t ksplit, kchunk;            // CTAs per tile along k (the cluster size); k elements per CTA, a multiple of 16
   int64_t a_off, b_off, o_off;       // elements
   int64_t a_rs, a_cs, b_rs, b_cs, o_rs, o_cs;
   int32_t nbd;
@@ -59,8 +71,10 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const SimtParams p) {
   constexpr int BK = 16, TT = TS / 16, PER_THREAD = TS * BK / 256;
   __shared__ float As[BK][TS + 4];
   __shared__ float Bs[BK][TS + 4];
+  __shared__ float red[TS][TS + 1];  // a CTA's partial tile, read by the first CTA of its cluster
 
-  const int64_t tile = blockIdx.x;
+  const int32_t krank = p.ksplit > 1 ? static_cast<int32_t>(blockIdx.x % p.ksplit) : 0;
+  const int64_t tile = p.ksplit > 1 ? blockIdx.x / p.ksplit : blockIdx.x;
   const int32_t tpb = p.tiles_m * p.tiles_n;
   int32_t batch = static_cast<int32_t>(tile / tpb);
   const int32_t t = static_cast<int32_t>(tile % tpb);
@@ -74,6 +88,8 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const SimtParams p) {
     b_off += idx * p.b_bs[d];
     o_off += idx * p.o_bs[d];
   }
+  const int32_t k_begin = krank * p.kchunk;
+  const int32_t k_end = min(p.K, k_begin + p.kchunk);
 
   const int tx = threadIdx.x & 15;  // column group
   const int ty = threadIdx.x >> 4;  // row group
@@ -83,43 +99,86 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const SimtParams p) {
 #pragma unroll
     for (int j = 0; j < TT; ++j) acc[i][j] = 0.f;
 
-  for (int32_t k0 = 0; k0 < p.K; k0 += BK) {
-    // TS x 16 elements of A and 16 x TS of B
+  // This thread's elements of a TS x 16 block of A and a 16 x TS block of B;
+  // the faster-varying thread index follows the operand's unit stride.
+  // PF blocks are in flight at any time: the loads of block i + PF are issued
+  // as soon as block i has moved from registers to shared memory.
+  constexpr int PF = 4;
+  const bool a_kfast = p.a_cs == 1, b_kfast = p.b_rs == 1;
+  float ra[PF][PER_THREAD], rb[PF][PER_THREAD];
+  auto fetch = [&](float (&fa)[PER_THREAD], float (&fb)[PER_THREAD], int32_t k0) {
 #pragma unroll
     for (int r = 0; r < PER_THREAD; ++r) {
       const int e = threadIdx.x + r * 256;
       {
-        // A: make the faster-varying thread index follow A's unit stride.
-        int mm, kk;
-        if (p.a_cs == 1) { kk = e & 15; mm = e >> 4; } else { mm = e % TS; kk = e / TS; }
+        const int mm = a_kfast ? (e >> 4) : (e % TS), kk = a_kfast ? (e & 15) : (e / TS);
         const int32_t gm = m0 + mm, gk = k0 + kk;
-        float v = 0.f;
-        if (gm < p.M && gk < p.K) v = load_elem(p.a, p.dtype, a_off + gm * p.a_rs + gk * p.a_cs);
-        As[kk][mm] = v;
+        fa[r] = (gm < p.M && gk < k_end) ? load_elem(p.a, p.dtype, a_off + gm * p.a_rs + gk * p.a_cs) : 0.f;
       }
       {
-        int nn, kk;
-        if (p.b_rs == 1) { kk = e & 15; nn = e >> 4; } else { nn = e % TS; kk = e / TS; }
+        const int nn = b_kfast ? (e >> 4) : (e % TS), kk = b_kfast ? (e & 15) : (e / TS);
         const int32_t gn = n0 + nn, gk = k0 + kk;
-        float v = 0.f;
-        if (gn < p.N && gk < p.K) v = load_elem(p.b, p.dtype, b_off + gk * p.b_rs + gn * p.b_cs);
-        Bs[kk][nn] = v;
+        fb[r] = (gn < p.N && gk < k_end) ? load_elem(p.b, p.dtype, b_off + gk * p.b_rs + gn * p.b_cs) : 0.f;
       }
     }
-    __syncthreads();
+  };
 #pragma unroll
-    for (int kk = 0; kk < BK; ++kk) {
-      float av[TT], bv[TT];
+  for (int f = 0; f < PF; ++f)
+    if (k_begin + f * BK < k_end) fetch(ra[f], rb[f], k_begin + f * BK);
+  for (int32_t kg = k_begin; kg < k_end; kg += PF * BK) {
 #pragma unroll
-      for (int i = 0; i < TT; ++i) av[i] = As[kk][ty * TT + i];
+    for (int f = 0; f < PF; ++f) {
+      const int32_t k0 = kg + f * BK;
+      if (k0 >= k_end) break;
 #pragma unroll
-      for (int j = 0; j < TT; ++j) bv[j] = Bs[kk][tx * TT + j];
+      for (int r = 0; r < PER_THREAD; ++r) {
+        const int e = threadIdx.x + r * 256;
+        As[a_kfast ? (e & 15) : (e / TS)][a_kfast ? (e >> 4) : (e % TS)] = ra[f][r];
+        Bs[b_kfast ? (e & 15) : (e / TS)][b_kfast ? (e >> 4) : (e % TS)] = rb[f][r];
+      }
+      __syncthreads();
+      if (k0 + PF * BK < k_end) fetch(ra[f], rb[f], k0 + PF * BK);
+#pragma unroll
+      for (int kk = 0; kk < BK; ++kk) {
+        float av[TT], bv[TT];
+#pragma unroll
+        for (int i = 0; i < TT; ++i) av[i] = As[kk][ty * TT + i];
+#pragma unroll
+        for (int j = 0; j < TT; ++j) bv[j] = Bs[kk][tx * TT + j];
+#pragma unroll
+        for (int i = 0; i < TT; ++i)
+#pragma unroll
+          for (int j = 0; j < TT; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+      }
+      __syncthreads();
+    }
+  }
+
+  if (p.ksplit > 1) {
+    if (krank != 0) {
 #pragma unroll
       for (int i = 0; i < TT; ++i)
 #pragma unroll
-        for (int j = 0; j < TT; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+        for (int j = 0; j < TT; ++j) red[ty * TT + i][tx * TT + j] = acc[i][j];
     }
-    __syncthreads();
+    ptx::cluster_arrive();
+    ptx::cluster_wait();  // every CTA's partial tile is in its shared memory
+    if (krank == 0) {
+      for (int r = 1; r < p.ksplit; ++r) {
+#pragma unroll
+        for (int i = 0; i < TT; ++i)
+#pragma unroll
+          for (int j = 0; j < TT; ++j) {
+            const uint32_t remote = ptx::mapa_shared(ptx::smem_u32(&red[ty * TT + i][tx * TT + j]), static_cast<uint32_t>(r));
+            float v;
+            asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+            acc[i][j] += v;
+          }
+      }
+    }
+    ptx::cluster_arrive();
+    ptx::cluster_wait();  // nobody leaves while its shared memory may still be read
+    if (krank != 0) return;
   }
 
 #pragma unroll
@@ -146,7 +205,8 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const SimtParams p) {
 // mode 1: f32 -> three TF32 terms per 32-wide K block, laid out so that one
 //         ordinary TF32 GEMM over the tripled K computes the 3xTF32 product:
 //           A side: [hi | hi | lo]      B side: [hi | lo | hi]
-//         hi = tf32(x) (round to nearest), lo = tf32(x - hi).
+//         hi = tf32(x) (round to nearest), lo = tf32(x - hi).  An infinity
+//         or NaN is written as [x | 0 | 0] on both sides.
 // A 32x32 tile goes through shared memory so that both the read and the write
 // are coalesced whichever of (row, k) is the source's unit stride.
 // ---------------------------------------------------------------------------
@@ -221,12 +281,19 @@ __global__ void __launch_bounds__(256) pack_kernel(const PackParams p) {
         hi = xv;
         lo = 0.f;
       }
+      float second = (p.mode == 1) ? hi : lo, third = (p.mode == 1) ? lo : hi;
+      // An infinity or NaN must meet its partner exactly once, as in IEEE
+      // arithmetic: it goes into the first block alone, where it multiplies the
+      // partner's leading term (inf * 2 = inf, inf * 0 = NaN), and the blocks
+      // that would pair it with a correction term (inf * 0 = NaN, or an
+      // infinity of the other sign) hold zero.
+      if (!isfinite(xv)) second = third = 0.f;
       // k0 is a multiple of 32, so this tile is exactly one 32-wide K block.
       const int64_t o = dst_batch + static_cast<int64_t>(gr) * p.dst_row_elems + 3ll * k0 + kk;
       float *d = static_cast<float *>(p.dst);
       d[o] = hi;
-      d[o + 32] = (p.mode == 1) ? hi : lo;
-      d[o + 64] = (p.mode == 1) ? lo : hi;
+      d[o + 32] = second;
+      d[o + 64] = third;
     }
   }
 }

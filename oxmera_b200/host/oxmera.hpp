@@ -106,7 +106,10 @@ class Strides {
 struct Error {
   enum class Kind {
     ShapeMismatch = 1, BroadcastIncompatible, DTypeMismatch, UnsupportedDType, DeviceMismatch,
-    IndexOutOfBounds, RankMismatch, BackendUnavailable, NotImplemented
+    IndexOutOfBounds, RankMismatch, BackendUnavailable, NotImplemented,
+    // BinaryOps::div: "Integer division by zero is a typed error" (crates/oxmera-ops/src/lib.rs:47-49);
+    // the reference's non_exhaustive enum has no variant for it yet.
+    DivisionByZero = 13
   } kind;
   Shape expected, got;        // ShapeMismatch; BroadcastIncompatible uses them as lhs, rhs; IndexOutOfBounds: got = shape
   std::vector<size_t> index;  // IndexOutOfBounds
@@ -129,6 +132,7 @@ struct Error {
         return "rank mismatch: index of rank " + std::to_string(index_rank) + " against shape of rank " + std::to_string(shape_rank);
       case Kind::BackendUnavailable:
         return !detail.empty() ? detail : "no backend available for device " + lhs_device.debug();
+      case Kind::DivisionByZero: return "integer division by zero in " + op;
       default: return op + " is not implemented for " + detail;
     }
   }
@@ -666,7 +670,7 @@ class B200Backend : public Backend {
   // backend conditions fold into NotImplemented{op, detail}.
   static Error from_status(int st, const char *op, Device lhs, Device rhs) {
     Error e{Error::Kind::NotImplemented};
-    if (st >= 1 && st <= 9) e.kind = static_cast<Error::Kind>(st);
+    if ((st >= 1 && st <= 9) || st == OXM_DIVIDE_BY_ZERO) e.kind = static_cast<Error::Kind>(st);
     e.op = op;
     e.detail = oxm_last_error();
     e.lhs_device = lhs; e.rhs_device = rhs;

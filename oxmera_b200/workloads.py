@@ -32,8 +32,9 @@ class GemmSpec:
     a_perm: Optional[Tuple[int, ...]]
     b: str
     b_perm: Optional[Tuple[int, ...]]
-    # The dim of A's BASE tensor (before a_perm) that shards across GPUs: the
-    # batch dim, or the dim that becomes the M rows.  K never shards.
+    # The dim of A's BASE tensor (before a_perm) that shards across GPUs: a
+    # batch dim, or the dim that becomes the M rows.  K never shards.  When A
+    # has extent 1 there (it broadcasts over that batch dim) only B is cut.
     shard_dim: int
     shard_b_dim: Optional[int] = None  # B's matching base dim when B carries the same batch dim
 
@@ -94,7 +95,9 @@ WORKLOADS: Dict[str, Workload] = {
         "c2", "f32 broadcast-batched: [8,1,1024,512] transposed view . [1,16,1024,768] -> [8,16,512,768], N(0,1)/32, seed 1",
         DType.F32, 1,
         (_t("T", (8, 1, 1024, 512), "normal", 1.0 / 32.0, 0), _t("B", (1, 16, 1024, 768), "normal", 1.0 / 32.0, 1)),
-        (GemmSpec("C", "T", (0, 1, 3, 2), "B", None, 0),)),
+        # of the two batch dims the second is cut: every GPU then needs all of T (16 MiB) and 1/N of B
+        # (48 MiB in all) rather than 1/N of T and all of B
+        (GemmSpec("C", "T", (0, 1, 3, 2), "B", None, 1, 1),)),
     "c3": Workload(
         "c3", "bf16 8192^3, A row-major, B column-major, N(0,1)/sqrt(8192), fp32 accumulate, bf16 out, seed 2",
         DType.BF16, 2,
@@ -148,10 +151,12 @@ def gemm_views(w: Workload, g: GemmSpec, tensors: Dict[str, Tensor], rank: int =
     Returns (a_view, b_view, row_or_batch_range)."""
     from .backend import shard_ranges
     a, b = tensors[g.a], tensors[g.b]
-    rg = range(0, a.shape[g.shard_dim])
+    total = shard_extent(g, a.shape, b.shape)
+    rg = range(0, total)
     if world > 1:
-        rg = shard_ranges(a.shape[g.shard_dim], world)[rank]
-        a = a.narrow(g.shard_dim, rg.start, len(rg))
+        rg = shard_ranges(total, world)[rank]
+        if a.shape[g.shard_dim] != 1:
+            a = a.narrow(g.shard_dim, rg.start, len(rg))
         if g.shard_b_dim is not None and b.shape[g.shard_b_dim] != 1:
             b = b.narrow(g.shard_b_dim, rg.start, len(rg))
     if g.a_perm:
@@ -161,12 +166,32 @@ def gemm_views(w: Workload, g: GemmSpec, tensors: Dict[str, Tensor], rank: int =
     return a, b, rg
 
 
+def shard_extent(g: GemmSpec, a_shape: Sequence[int], b_shape: Sequence[int]) -> int:
+    """How many units (batch entries or rows) product `g` shards over: the
+    extent of the sharded dim in whichever base tensor carries it."""
+    n = a_shape[g.shard_dim]
+    if g.shard_b_dim is not None:
+        n = max(n, b_shape[g.shard_b_dim])
+    return n
+
+
+def shard_axis(w: Workload, g: GemmSpec) -> int:
+    """The axis of product `g`'s output along which the ranks' shards lie side by side."""
+    a_shape, b_shape, o_shape = w.gemm_shapes(g)
+    a_base = w.spec(g.a).shape
+    if a_base[g.shard_dim] != 1 or g.shard_b_dim is None:
+        pos = list(g.a_perm).index(g.shard_dim) if g.a_perm else g.shard_dim
+        return pos + (len(o_shape) - len(a_shape))
+    pos = list(g.b_perm).index(g.shard_b_dim) if g.b_perm else g.shard_b_dim
+    return pos + (len(o_shape) - len(b_shape))
+
+
 def shard_flops(w: Workload, rank: int, world: int) -> int:
     from .backend import shard_ranges
     total = 0
     for g in w.gemms:
         a, b, o = w.gemm_shapes(g)
-        full = w.spec(g.a).shape[g.shard_dim]
+        full = shard_extent(g, w.spec(g.a).shape, w.spec(g.b).shape)
         part = len(shard_ranges(full, world)[rank])
         total += 2 * numel(o) * a[-1] * part // full
     return total

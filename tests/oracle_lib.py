@@ -66,7 +66,7 @@ class Oracle:
         self.lib.orc_f32_to_fp8.argtypes = [C.c_float, C.c_int32]; self.lib.orc_f32_to_fp8.restype = C.c_uint8
         self.lib.orc_fp8_to_f32.argtypes = [C.c_uint8, C.c_int32]; self.lib.orc_fp8_to_f32.restype = C.c_float
         self.lib.orc_fill.argtypes = [C.c_void_p, C.c_int32, C.c_int64, C.c_uint64, C.c_uint64, C.c_int, C.c_double, C.c_int]
-        self.lib.orc_fill.restype = None
+        self.lib.orc_fill.restype = C.c_int
         self.threads = os.cpu_count() or 1
 
     def matmul(self, a: np.ndarray, b: np.ndarray, tag: int, acc: int = ACC_NATIVE, out_tag: int | None = None,
@@ -134,7 +134,8 @@ class Oracle:
     def fill(self, shape, tag: int, seed: int, stream: int, dist: str, scale: float = 1.0) -> np.ndarray:
         """Seeded synthetic data: dist 'uniform' = U(-1,1), 'normal' = N(0,1)*scale."""
         out = np.empty(shape, dtype=_NP[tag])
-        self.lib.orc_fill(out.ctypes.data, tag, out.size, seed, stream, 0 if dist == "uniform" else 1, scale, self.threads)
+        st = self.lib.orc_fill(out.ctypes.data, tag, out.size, seed, stream, 0 if dist == "uniform" else 1, scale, self.threads)
+        assert st == 0, f"orc_fill refuses dtype tag {tag}"
         return out
 
     def fp8_to_f32(self, bits: np.ndarray, tag: int) -> np.ndarray:

@@ -22,6 +22,22 @@ def test_header_and_binding_agree():
     assert header_symbols() == sorted(capi.EXPORTS)
 
 
+def test_rust_binding_declares_exactly_the_header():
+    """rust/oxmera-b200/src/ffi.rs cannot be compiled here (no Rust toolchain),
+    but its `extern "C"` block must name exactly the functions the header
+    declares, and its status and dtype constants must carry the header's values."""
+    text = open(os.path.join(ROOT, "rust", "oxmera-b200", "src", "ffi.rs")).read()
+    block = text[text.index('extern "C" {'):]
+    assert sorted(set(re.findall(r"pub fn (oxm_[a-z0-9_]+)\s*\(", block))) == header_symbols()
+    header = open(os.path.join(ROOT, "include", "oxmera_b200.h")).read()
+    for name, value in re.findall(r"\b(OXM_[A-Z0-9_]+)\s*=\s*(\d+)", header):
+        m = re.search(r"pub const %s: \w+ = (\d+);" % name, text)
+        assert m and int(m.group(1)) == int(value), name
+    lib_rs = open(os.path.join(ROOT, "rust", "oxmera-b200", "src", "lib.rs")).read()
+    for trait in ("UnaryOps", "BinaryOps", "MatmulOps", "ReduceOps", "Backend"):
+        assert f"impl {trait} for B200Backend" in lib_rs, trait
+
+
 def test_library_exports_every_declared_symbol():
     lib = capi.load()
     for name in header_symbols():

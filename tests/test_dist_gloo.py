@@ -67,13 +67,12 @@ def _rank_main(rank, world, port, out_dir):
 def test_two_gloo_ranks_tile_the_unsharded_result(tmp_path):
     world = 2
     mp.spawn(_rank_main, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
-    from oxmera_b200.workloads import WORKLOADS
+    from oxmera_b200.workloads import WORKLOADS, shard_axis
     for key in ("c3", "c4", "c5", "c2"):
         for gi, g in enumerate(WORKLOADS[key].gemms):
             whole = np.load(tmp_path / f"{key}_{gi}_whole.npy")
             parts = [np.load(tmp_path / f"{key}_{gi}_rank{r}.npy") for r in range(world)]
-            axis = 0 if whole.ndim > 2 else whole.ndim - 2
-            assert np.array_equal(np.concatenate(parts, axis=axis), whole), (key, g.name)
+            assert np.array_equal(np.concatenate(parts, axis=shard_axis(WORKLOADS[key], g)), whole), (key, g.name)
 
 
 def test_shard_ranges_and_plan():

@@ -17,7 +17,7 @@ import pytest
 
 import oxmera_b200 as ox
 from oxmera_b200 import DType, Tensor
-from oxmera_b200.workloads import WORKLOADS, gemm_views, materialise, scaled
+from oxmera_b200.workloads import WORKLOADS, gemm_views, materialise, scaled, shard_axis
 from tests.test_gpu_parity import TAG, TOL, oracle_ref, rel_err, to_f64
 
 pytestmark = pytest.mark.gpu
@@ -153,8 +153,7 @@ def test_shards_reassemble_to_the_whole(backend, oracle, key):
                 for rank in range(world):
                     sa, sb, rg = gemm_views(w, g, dev, rank, world)
                     parts.append(backend.batched_matmul(sa, sb).to_host())
-                axis = 0 if len(whole.shape) > 2 else whole.ndim - 2
-                assert np.array_equal(np.concatenate(parts, axis=axis), whole), (w.key, g.name, world)
+                assert np.array_equal(np.concatenate(parts, axis=shard_axis(w, g)), whole), (w.key, g.name, world)
     finally:
         backend.set_option("kernel", 0)
         backend.set_option("split_k", -1)

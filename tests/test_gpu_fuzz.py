@@ -1,12 +1,14 @@
 """Seeded random products through the C ABI against the oracle: random
 extents (tile tails in M, N and K), random operand majors, windows with odd
-offsets, flips, broadcast batch dims, every tile width and both kernels.
+offsets, flips, broadcast batch dims, tile widths of every kernel instance
+and both kernels, each output inside guard bands that must stay untouched.
 The cases are drawn from a fixed seed, so a failure names a reproducible
 case index."""
 import numpy as np
 import pytest
 
 from oxmera_b200 import DType, Tensor
+from tests.guard import guarded_matmul
 from tests.test_gpu_parity import TOL, fill, oracle_ref, rel_err, set_kernel, to_f64
 
 pytestmark = pytest.mark.gpu
@@ -51,11 +53,13 @@ def test_random_products(backend, oracle, dtype):
         va, vta = va[..., :kk], vta.narrow(va.ndim - 1, 0, kk)
         vb, vtb = vb[..., :kk, :], vtb.narrow(vb.ndim - 2, 0, kk)
         kernel = ["auto", "simt", "tcgen05", "tcgen05"][int(rng.integers(0, 4))]
-        tile_n = int(rng.choice([0, 64, 128, 256, 512])) if kernel == "tcgen05" else 0
+        tile_n = int(rng.choice([0, 64, 96, 128, 192, 256, 320, 480, 512])) if kernel == "tcgen05" else 0
         set_kernel(backend, kernel, tile_n=tile_n)
         backend.set_option("split_k", int(rng.choice([-1, 0, 2])) if kernel == "tcgen05" and dtype != DType.F32 else -1)
-        got = backend.batched_matmul(vta, vtb) if batch else backend.matmul(vta, vtb)
+        # every output sits inside guard bands; the layout (fresh contiguous, aligned or odd window) rotates
+        layout, aligned = [("flat", True), ("window", True), ("window", False), ("flat", False)][case % 4]
+        got = guarded_matmul(backend, vta, vtb, batched=bool(batch), layout=layout, aligned=aligned)
         ref = oracle_ref(oracle, va, vb, dtype)
         assert got.shape == ref.shape, (case, got.shape, ref.shape)
-        err = rel_err(to_f64(got.to_host(), dtype), ref)
+        err = rel_err(to_f64(got, dtype), ref)
         assert err <= TOL[dtype], (case, va.shape, vb.shape, kernel, tile_n, err, backend.last_kernel())

@@ -84,11 +84,13 @@ def test_unary_ops(backend, oracle, dtype):
 
 @pytest.mark.parametrize("dtype", FLOATS + INTS, ids=lambda d: d.name)
 def test_binary_ops_broadcast(backend, oracle, dtype):
-    fns = [backend.add, backend.sub, backend.mul] + ([backend.div] if dtype in FLOATS else [])
+    fns = [backend.add, backend.sub, backend.mul, backend.div]  # the integer test data has no zero divisors: see below
     cases = [((64, 33), (64, 33)), ((2, 3), (3,)), ((2, 1), (1, 3)), ((), (2, 3)), ((4, 1, 5), (3, 1)), ((130, 1, 17), (1, 9, 1)),
              ((2, 0), (1, 1))]
     for ls, rs in cases:
         a, b = host(oracle, ls, dtype, 20), host(oracle, rs, dtype, 21, positive=dtype in FLOATS)
+        if dtype in INTS:
+            b = np.where(b == 0, 7, b).astype(b.dtype)
         ta, tb = Tensor.from_host(a, ls, dtype, backend), Tensor.from_host(b, rs, dtype, backend)
         for op, fn in enumerate(fns):
             out = fn(ta, tb)
@@ -100,9 +102,44 @@ def test_binary_ops_broadcast(backend, oracle, dtype):
     ta, tb = Tensor.from_host(a, a.shape, dtype, backend), Tensor.from_host(b, b.shape, dtype, backend)
     got = ta.add(tb.permute([1, 0]).flip(0))
     assert_close(got.to_host(), oracle.binary(0, a, b.T[::-1], TAGS[dtype])[1], dtype, ulps=1)
-    if dtype in INTS:
-        with pytest.raises(ox.UnsupportedDType):
-            backend.div(ta, ta)
+
+
+@pytest.mark.parametrize("dtype", INTS, ids=lambda d: d.name)
+def test_integer_division_by_zero_is_a_typed_error(backend, oracle, dtype):
+    """BinaryOps::div (crates/oxmera-ops/src/lib.rs:47-49): truncating division;
+    a zero divisor anywhere surfaces as DivisionByZero from the call itself, on
+    a healthy kernel, and the context keeps working."""
+    npdt = NPDT[dtype]
+    a = np.array([[7, -7, 9, -9], [0, 100, -100, 5]], npdt)
+    b = np.array([2, -2, 4, 3], npdt)
+    ta, tb = Tensor.from_host(a, a.shape, dtype, backend), Tensor.from_host(b, b.shape, dtype, backend)
+    assert backend.div(ta, tb).to_host().tolist() == [[3, 3, 2, -3], [0, -50, -25, 1]]
+    lo = np.iinfo(npdt).min
+    edge = Tensor.from_host(np.array([lo, lo + 1], npdt), (2,), dtype, backend)
+    minus = Tensor.from_host(np.array([-1, -1], npdt), (2,), dtype, backend)
+    assert backend.div(edge, minus).to_host().tolist() == oracle.binary(3, np.array([lo, lo + 1], npdt), np.array([-1, -1], npdt), TAGS[dtype])[1].tolist()
+    # a large, strided, broadcast case against the oracle, then the same with one zero planted
+    h = host(oracle, (300, 70), dtype, 50)
+    d = np.where(host(oracle, (70,), dtype, 51) == 0, 3, host(oracle, (70,), dtype, 51)).astype(npdt)
+    th, td = Tensor.from_host(h, h.shape, dtype, backend), Tensor.from_host(d, d.shape, dtype, backend)
+    st, ref = oracle.binary(3, h.T[:, ::-1], d[:, None], TAGS[dtype])
+    assert st == 0
+    assert np.array_equal(backend.div(th.permute([1, 0]).flip(1), td.reshape((70, 1))).to_host(), ref)
+    d[41] = 0
+    tz = Tensor.from_host(d, d.shape, dtype, backend)
+    assert oracle.binary(3, h, d, TAGS[dtype])[0] == 13
+    with pytest.raises(ox.DivisionByZero) as e:
+        backend.div(th, tz)
+    assert "div" in str(e.value)
+    backend.synchronize()  # the error was consumed by the failing call; nothing is left pending
+    assert backend.div(ta, tb).to_host().tolist() == [[3, 3, 2, -3], [0, -50, -25, 1]]
+
+
+def test_float_division_follows_ieee(backend):
+    a = Tensor.from_host(np.array([1.0, -1.0, 0.0, 6.0], np.float32), (4,), DType.F32, backend)
+    z = Tensor.from_host(np.array([0.0, 0.0, 0.0, 3.0], np.float32), (4,), DType.F32, backend)
+    got = backend.div(a, z).to_host()
+    assert np.isposinf(got[0]) and np.isneginf(got[1]) and np.isnan(got[2]) and got[3] == 2.0
 
 
 def test_binary_errors(backend):
@@ -138,6 +175,20 @@ def test_reductions(backend, oracle, dtype):
                     else:
                         exact = as_f64(hv, dtype).sum(axis=tuple(axes) if axes else None)
                         assert rel_err(as_f64(out.to_host(), dtype), np.asarray(exact)) <= tol[dtype], (shape, axes)
+    if dtype in FLOATS:
+        # max propagates NaN wherever it sits in the slice, through every thread mapping
+        for shape, axes in (((5, 3000), [1]), ((3000, 5), [0]), ((40, 4096), [0]), ((64, 64), [])):
+            h = host(oracle, shape, dtype, 31)
+            flat = h.reshape(-1)
+            for pos in (0, flat.size // 2, flat.size - 1):
+                hh = flat.copy()
+                hh[pos] = 0x7FC0 if dtype == DType.BF16 else np.nan
+                hh = hh.reshape(shape)
+                got = as_f64(backend.max(Tensor.from_host(hh, shape, dtype, backend), axes).to_host(), dtype)
+                st, ref = oracle.reduce(1, hh, axes, TAGS[dtype])
+                ref = as_f64(ref, dtype)
+                assert st == 0 and np.array_equal(np.isnan(got), np.isnan(ref)) and np.isnan(ref).sum() == 1, (shape, axes, pos)
+                assert np.array_equal(got[~np.isnan(got)], ref[~np.isnan(ref)])
     e = Tensor.from_host(np.zeros((3, 0), np.float32), (3, 0), DType.F32, backend)
     assert backend.sum(e, [1]).to_host().tolist() == [0.0, 0.0, 0.0]
     with pytest.raises(ox.NotImplementedOp):

@@ -13,6 +13,7 @@ import pytest
 
 import oxmera_b200 as ox
 from oxmera_b200 import DType, Tensor
+from tests.guard import Guarded, guarded_matmul
 from tests.oracle_lib import ACC_F64, ACC_NATIVE, BF16, F16, F32
 
 pytestmark = pytest.mark.gpu
@@ -147,9 +148,14 @@ def test_shape_sweep(backend, oracle, kernel, dtype):
     for i, (m, n, k) in enumerate(SHAPES):
         a = fill(oracle, (m, k), dtype, 100 + i, 0)
         b = fill(oracle, (k, n), dtype, 100 + i, 1)
-        got = backend.matmul(Tensor.from_host(a, a.shape, dtype, backend), Tensor.from_host(b, b.shape, dtype, backend))
-        err = rel_err(to_f64(got.to_host(), dtype), oracle_ref(oracle, a, b, dtype))
+        ta, tb = Tensor.from_host(a, a.shape, dtype, backend), Tensor.from_host(b, b.shape, dtype, backend)
+        got = backend.matmul(ta, tb).to_host()
+        err = rel_err(to_f64(got, dtype), oracle_ref(oracle, a, b, dtype))
         assert err <= TOL[dtype], (kernel, dtype.name, (m, n, k), err, backend.last_kernel())
+        # the same product into outputs with guard bands: nothing outside the output may be written,
+        # whichever epilogue the output's alignment selects, and not a bit of the result may change
+        for layout, aligned in (("flat", True), ("window", True), ("window", False)):
+            assert np.array_equal(guarded_matmul(backend, ta, tb, layout=layout, aligned=aligned), got), (kernel, (m, n, k), layout, aligned)
 
 
 @pytest.mark.parametrize("dtype", [DType.BF16, DType.F16, DType.F32], ids=lambda d: d.name)
@@ -225,15 +231,33 @@ def test_broadcast_batch_dims(backend, oracle, kernel, dtype):
         assert err <= TOL[dtype], (ashape, bshape, err, backend.last_kernel())
 
 
-@pytest.mark.parametrize("tile_n", [64, 128, 256, 512])
+@pytest.mark.parametrize("tile_n", [64, 96, 128, 160, 224, 256, 288, 320, 384, 416, 448, 480, 512])
 @pytest.mark.parametrize("dtype", [DType.BF16, DType.F32], ids=lambda d: d.name)
 def test_tile_widths(backend, oracle, tile_n, dtype):
-    set_kernel(backend, "tcgen05", tile_n=tile_n)
+    """Every kernel instance at its full width and at narrower widths (any
+    multiple of 32 columns), with a B operand of either major, ragged edges in
+    M and N, and guard bands around the output."""
     m, n, k = 384, 1100, 448
-    a, b = fill(oracle, (m, k), dtype, 31, 0), fill(oracle, (k, n), dtype, 31, 1)
-    got = backend.matmul(Tensor.from_host(a, a.shape, dtype, backend), Tensor.from_host(b, b.shape, dtype, backend))
-    assert f"bn{tile_n}" in backend.last_kernel()
-    assert rel_err(to_f64(got.to_host(), dtype), oracle_ref(oracle, a, b, dtype)) <= TOL[dtype]
+    cls = 512 if tile_n > 256 else 256 if tile_n > 128 else 128 if tile_n > 64 else 64
+    a = fill(oracle, (m, k), dtype, 31, 0)
+    ta = Tensor.from_host(a, a.shape, dtype, backend)
+    for b_t in (0, 1):
+        set_kernel(backend, "tcgen05", tile_n=tile_n)
+        backend.set_option("split_k", 0)  # one chain per element at every width, so that widths can be compared bit for bit
+        hb = fill(oracle, (n, k) if b_t else (k, n), dtype, 31, 1)
+        b = hb.T if b_t else hb
+        tb = Tensor.from_host(hb, hb.shape, dtype, backend)
+        tb = tb.permute([1, 0]) if b_t else tb
+        got = backend.matmul(ta, tb).to_host()
+        name = backend.last_kernel()
+        assert f"bn{cls}_" in name and (tile_n == cls or name.endswith(f"_w{tile_n}")), name
+        assert rel_err(to_f64(got, dtype), oracle_ref(oracle, a, b, dtype)) <= TOL[dtype], (tile_n, b_t, name)
+        for aligned in (True, False):
+            assert np.array_equal(guarded_matmul(backend, ta, tb, aligned=aligned), got), (tile_n, b_t, aligned)
+        # the width changes which tile an element falls in, never the chain of products behind it
+        set_kernel(backend, "tcgen05", tile_n=cls)
+        backend.set_option("split_k", 0)
+        assert np.array_equal(backend.matmul(ta, tb).to_host(), got), (tile_n, b_t)
 
 
 def test_long_f32_contractions_keep_their_accuracy(backend, oracle):
@@ -253,6 +277,35 @@ def test_long_f32_contractions_keep_their_accuracy(backend, oracle):
         err = rel_err(got.to_host(), oracle_ref(oracle, a, b, DType.F32))
         print(f"f32 K={ashape[-1]}: error {err:.3e}")
         assert err <= 5e-5, (ashape, bshape, err)
+
+
+@pytest.mark.parametrize("kernel", ["simt", "tcgen05", "auto"])
+def test_f32_infinities_and_nans_follow_ieee_on_every_path(backend, kernel):
+    """inf * 2 = inf, inf * 0 = NaN, inf - inf = NaN, NaN poisons its row and
+    column, whichever kernel computes the product: the FFMA kernel does this by
+    construction; the 3xTF32 split has to keep an infinity from meeting a
+    correction term (inf * 0).  Small-integer data, so finite outputs are exact."""
+    set_kernel(backend, kernel)
+    rng = np.random.default_rng(17)
+    for (m, n, k), at, bt in (((70, 50, 96), 0, 0), ((260, 300, 1500), 1, 1), ((512, 768, 2048), 1, 0)):
+        a = rng.integers(-3, 4, size=(m, k)).astype(np.float32)
+        b = rng.integers(-3, 4, size=(k, n)).astype(np.float32)
+        a[3, 10], a[5, 20], a[9, 30], a[m - 1, k - 1] = np.inf, -np.inf, np.nan, -np.inf
+        b[40, 7], b[41, 8], b[k - 1, n - 1] = np.inf, np.nan, np.inf
+        a[11, 40] = np.inf  # meets b[40, 7] = inf in output (11, 7): inf * inf = inf
+        with np.errstate(invalid="ignore"):
+            ref = a.astype(np.float64) @ b.astype(np.float64)
+        sa = np.ascontiguousarray(a.T) if at else a
+        sb = np.ascontiguousarray(b.T) if bt else b
+        ta, tb = Tensor.from_host(sa, sa.shape, DType.F32, backend), Tensor.from_host(sb, sb.shape, DType.F32, backend)
+        ta = ta.permute([1, 0]) if at else ta
+        tb = tb.permute([1, 0]) if bt else tb
+        x = backend.matmul(ta, tb).to_host()
+        where = (kernel, (m, n, k), backend.last_kernel())
+        assert np.array_equal(np.isnan(x), np.isnan(ref)), where
+        assert np.array_equal(np.isposinf(x), np.isposinf(ref)) and np.array_equal(np.isneginf(x), np.isneginf(ref)), where
+        fin = np.isfinite(ref)
+        assert np.array_equal(x[fin], ref[fin].astype(np.float32)), where
 
 
 @pytest.mark.parametrize("dtype", [DType.BF16, DType.F16], ids=lambda d: d.name)
@@ -304,7 +357,7 @@ def test_skinny_products(backend, oracle, dtype, b_t):
         if b_t:
             hb, tb = hb.T, tb.permute([1, 0])
         got = backend.matmul(ta, tb)
-        if 2 * m * n * k >= 3e7:
+        if 2 * m * n * k >= (2e8 if dtype == DType.F32 else 8e6):  # where the FFMA kernel hands over to the tensor cores
             assert "tcgen05" in backend.last_kernel(), backend.last_kernel()
         err = rel_err(to_f64(got.to_host(), dtype), oracle_ref(oracle, ha, hb, dtype))
         assert err <= TOL[dtype], ((m, n, k), err, backend.last_kernel())
@@ -321,6 +374,7 @@ def test_stream_k_shares_the_last_tiles_out_by_contraction_block(backend, oracle
              (128, 0, (1536, 1800, 1100)),   # 180 tiles: one wave and 32 more -> 180 shared out
              (256, 1, (1536, 2048, 1024)),   # 48 pair tiles on 74 pairs
              (512, 1, (2000, 3072, 1024)),   # 48 pair tiles of 256 x 512, one accumulator
+             (480, 1, (2000, 3072, 1024)),   # 56 pair tiles of 256 x 480: the same instance, narrower
              (256, 0, (1024, 5120, 2048))]   # 160 tiles, 1-CTA 128 x 256
     for tile_n, pair, (m, n, k) in cases:
         if dtype == DType.F32 and k > 1024:
@@ -333,8 +387,8 @@ def test_stream_k_shares_the_last_tiles_out_by_contraction_block(backend, oracle
         whole = backend.matmul(ta, tb).to_host()
         backend.set_option("stream_k", 1)
         try:
-            for _ in range(2):
-                got = backend.matmul(ta, tb).to_host()
+            for rep in range(2):
+                got = guarded_matmul(backend, ta, tb, layout="flat" if rep else "window")
                 err = rel_err(to_f64(got, dtype), ref)
                 assert err <= TOL[dtype], (tile_n, pair, (m, n, k), err, backend.last_kernel())
             # the two schedules differ only in where the fp32 chains are cut
@@ -392,16 +446,17 @@ def test_output_written_through_its_own_strides(backend, oracle):
     """A shard writes its rows into a window of the parent output."""
     a, b = fill(oracle, (192, 96), DType.BF16, 61, 0), fill(oracle, (96, 160), DType.BF16, 61, 1)
     ta, tb = Tensor.from_host(a, a.shape, DType.BF16, backend), Tensor.from_host(b, b.shape, DType.BF16, backend)
-    parent = Tensor.from_host(np.zeros((192, 160), np.uint16), (192, 160), DType.BF16, backend)
     for kernel in ("simt", "tcgen05"):
         set_kernel(backend, kernel)
-        for r0, r1 in ((0, 64), (64, 192)):
-            backend.matmul_into(ta.narrow(0, r0, r1 - r0), tb, parent.narrow(0, r0, r1 - r0), batched=False)
-        assert rel_err(to_f64(parent.to_host(), DType.BF16), oracle_ref(oracle, a, b, DType.BF16)) <= 1e-2
-    # a transposed output view (column stride != 1)
-    out_t = Tensor.empty((160, 192), DType.BF16, backend).permute([1, 0])
-    backend.matmul_into(ta, tb, out_t, batched=False)
-    assert rel_err(to_f64(out_t.to_host(), DType.BF16), oracle_ref(oracle, a, b, DType.BF16)) <= 1e-2
+        for aligned in (True, False):
+            g = Guarded(backend, (192, 160), DType.BF16, "window", aligned)  # the parent, itself inside guard bands
+            for r0, r1 in ((0, 64), (64, 192)):
+                backend.matmul_into(ta.narrow(0, r0, r1 - r0), tb, g.view.narrow(0, r0, r1 - r0), batched=False)
+            assert rel_err(to_f64(g.result(), DType.BF16), oracle_ref(oracle, a, b, DType.BF16)) <= 1e-2
+        # a transposed output view (column stride != 1)
+        g = Guarded(backend, (160, 192), DType.BF16, "window")
+        backend.matmul_into(ta, tb, g.view.permute([1, 0]), batched=False)
+        assert rel_err(to_f64(g.result().T, DType.BF16), oracle_ref(oracle, a, b, DType.BF16)) <= 1e-2
 
 
 def test_host_entry_point(backend, oracle):

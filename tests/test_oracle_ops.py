@@ -34,7 +34,42 @@ def test_binary_broadcasts_like_numpy(oracle):
     assert oracle.binary(0, np.zeros((2, 3)), np.zeros((2, 4)), F64)[0] == 2  # BroadcastIncompatible
     i = np.arange(12, dtype=np.int32).reshape(3, 4)
     assert oracle.binary(2, i, i[:1], I32)[1].tolist() == (i * i[:1]).tolist()
-    assert oracle.binary(3, i, i, I32)[0] == 4  # integer division is refused
+
+
+def test_integer_division_and_its_typed_zero_error(oracle):
+    # crates/oxmera-ops/src/lib.rs:47-49: "Integer division by zero is a typed error"
+    for tag, dt in ((I32, np.int32), (I64, np.int64)):
+        a = np.array([[7, -7, 9, -9], [0, 100, -100, 5]], dt)
+        b = np.array([2, -2, 4, 3], dt)
+        st, c = oracle.binary(3, a, b, tag)
+        assert st == 0 and c.tolist() == [[3, 3, 2, -3], [0, -50, -25, 1]]  # truncation toward zero
+        lo = np.iinfo(dt).min
+        st, c = oracle.binary(3, np.array([lo, lo + 1], dt), np.array([-1, -1], dt), tag)
+        assert st == 0 and c.tolist() == [lo, -(lo + 1)]  # the most negative value over -1 wraps
+        st, c = oracle.binary(3, a, np.array([2, 0, 4, 3], dt), tag)
+        assert st == 13 and c[:, 1].tolist() == [0, 0] and c[:, 0].tolist() == [3, 0]  # DivisionByZero; others still computed
+    st, c = oracle.binary(3, np.array([1.0, -1.0, 0.0], np.float32), np.zeros(3, np.float32), F32)
+    assert st == 0 and np.isposinf(c[0]) and np.isneginf(c[1]) and np.isnan(c[2])  # float division follows IEEE-754
+
+
+def test_max_propagates_nan(oracle):
+    x = oracle.fill((4, 6), F32, 5, 0, "normal")
+    for pos in (0, 3, 5):
+        y = x.copy()
+        y[1, pos] = np.nan
+        st, c = oracle.reduce(1, y, [1], F32)
+        assert st == 0 and np.isnan(c[1]) and not np.isnan(c[[0, 2, 3]]).any()
+        assert np.array_equal(c[[0, 2, 3]], y[[0, 2, 3]].max(axis=1))
+    st, c = oracle.reduce(1, np.full((2, 3), np.nan, np.float32), [], F32)
+    assert st == 0 and np.isnan(c)
+
+
+def test_fill_covers_f64_and_refuses_what_it_cannot_write(oracle):
+    x = oracle.fill((1000,), F64, 9, 0, "normal")
+    assert x.dtype == np.float64 and np.isfinite(x).all() and 0.8 < x.std() < 1.2
+    assert np.array_equal(x.astype(np.float32), oracle.fill((1000,), F32, 9, 0, "normal"))  # the same stream, rounded
+    with pytest.raises(AssertionError):
+        oracle.fill((4,), I32, 9, 0, "normal")
 
 
 @pytest.mark.parametrize("tag", [F32, F64, BF16, F16, I32, I64])
