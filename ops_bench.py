@@ -1,7 +1,7 @@
 """Throughput of the HBM-bound operators (unary, binary, reductions,
 contiguous() of a transposed view) against the measured copy bandwidth.
 
-    python -m oxmera_b200.ops_bench [--rows R --cols C] [--reps N] [--only NAME]
+    python ops_bench.py [--rows R --cols C] [--reps N] [--only NAME]
 
 Prints one JSON line per case: algorithmic bytes (every input element read
 once, every output element written once), CUDA-event time per launch and the
@@ -12,12 +12,15 @@ from __future__ import annotations
 import argparse
 import json
 import os
+import sys
 
-from . import B200Backend, DType, Tensor
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+from oxmera_b200 import B200Backend, DType, Tensor  # noqa: E402
 
 
 def _peak_gbs() -> float:
-    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "MEASURED_PEAKS.json")
     try:
         return float(json.load(open(path))["hbm_gbs"])
     except Exception:

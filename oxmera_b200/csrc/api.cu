@@ -443,7 +443,9 @@ int make_map(oxm_ctx *ctx, CUtensorMap *tm, const Staged &s, int dtype, int elt,
 // Launch one instance of the tensor-core GEMM (defined in the gemm_*.cu units).
 int launch_gemm(oxm_ctx *ctx, int kind, bool a_mn, bool b_mn, int bn, int pair, const CUtensorMap &tmA, const CUtensorMap &tmB,
                 const CUtensorMap &tmC, const GemmParams &p, int grid) {
-  const GemmLaunch l{bn, pair, b_mn, grid, ctx->stream};
+  // whole tiles with a 16-bit result: the wide tile's register-packed epilogue
+  const bool packed = bn == 512 && kind != 1 && p.sk_tiles == 0 && (p.out_dtype == OXM_BF16 || p.out_dtype == OXM_F16);
+  const GemmLaunch l{bn, pair, packed, b_mn, grid, ctx->stream};
   const GemmLaunchFn fn = kind == 1 ? launch_gemm_tf32
                           : kind == 2 ? (a_mn ? launch_gemm_f8_am : launch_gemm_f8_ak)
                                       : (a_mn ? launch_gemm_f16_am : launch_gemm_f16_ak);

@@ -13,7 +13,8 @@
 namespace oxm {
 
 struct GemmLaunch {
-  int bn, pair;      // tile width; CTA pairs
+  int bn, pair;      // the instance's widest tile; CTA pairs
+  bool packed;       // bn = 512: the epilogue that packs its share into registers before storing (16-bit results, whole tiles)
   bool b_mn;         // B is MN-major (A's major is fixed per translation unit)
   int grid;
   cudaStream_t stream;
@@ -33,11 +34,11 @@ OXM_DECLARE_GEMM_LAUNCH(launch_gemm_f8_ak)    // fp8, A K-major
 OXM_DECLARE_GEMM_LAUNCH(launch_gemm_f8_am)    // fp8, A M-major
 OXM_DECLARE_GEMM_LAUNCH(launch_gemm_tf32)     // f32 as 3xTF32, packed K-major operands
 
-template <int BN, int STAGES, int A_MN, int B_MN, int KIND, int PAIR>
+template <int BN, int STAGES, int A_MN, int B_MN, int KIND, int PAIR, int PACKED = 0>
 cudaError_t launch_instance(const GemmLaunch &l, const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap &tmC,
                             const GemmParams &p, char *name, size_t name_len) {
   using L = GemmSmem<BN, STAGES, PAIR>;
-  auto kern = gemm_tcgen05_kernel<BN, STAGES, A_MN, B_MN, KIND, PAIR>;
+  auto kern = gemm_tcgen05_kernel<BN, STAGES, A_MN, B_MN, KIND, PAIR, PACKED>;
   static_assert(L::kDynamic <= 232448, "shared memory budget of one SM");
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic);
   if (e != cudaSuccess) return e;
@@ -52,8 +53,8 @@ cudaError_t launch_instance(const GemmLaunch &l, const CUtensorMap &tmA, const C
     attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr; cfg.numAttrs = 1;
   }
-  snprintf(name, name_len, "gemm_tcgen05_%s_bn%d_s%d_%c%c_%s", KIND == 1 ? "tf32x3" : KIND == 2 ? "f8" : "f16", BN, STAGES,
-           A_MN ? 'm' : 'k', B_MN ? 'n' : 'k', PAIR ? "pair" : "1cta");
+  snprintf(name, name_len, "gemm_tcgen05_%s_bn%d_s%d_%c%c_%s%s", KIND == 1 ? "tf32x3" : KIND == 2 ? "f8" : "f16", BN, STAGES,
+           A_MN ? 'm' : 'k', B_MN ? 'n' : 'k', PAIR ? "pair" : "1cta", PACKED ? "_pk" : "");
   return cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmC, p);
 }
 
@@ -62,7 +63,12 @@ template <int A_MN, int B_MN, int KIND>
 cudaError_t launch_shape(const GemmLaunch &l, const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap &tmC,
                          const GemmParams &p, char *name, size_t name_len) {
   if (l.pair) {
-    if (l.bn == 512) return launch_instance<512, 4, A_MN, B_MN, KIND, 1>(l, tmA, tmB, tmC, p, name, name_len);
+    if (l.bn == 512) {
+      if constexpr (KIND != 1) {
+        if (l.packed) return launch_instance<512, 4, A_MN, B_MN, KIND, 1, 1>(l, tmA, tmB, tmC, p, name, name_len);
+      }
+      return launch_instance<512, 4, A_MN, B_MN, KIND, 1>(l, tmA, tmB, tmC, p, name, name_len);
+    }
     if (l.bn == 256) return launch_instance<256, 6, A_MN, B_MN, KIND, 1>(l, tmA, tmB, tmC, p, name, name_len);
     return launch_instance<128, 8, A_MN, B_MN, KIND, 1>(l, tmA, tmB, tmC, p, name, name_len);
   }

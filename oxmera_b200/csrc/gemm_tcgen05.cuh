@@ -37,8 +37,13 @@ constexpr int kMmaKBytes = 32;     // contraction bytes per tcgen05.mma
 // columns: the per-warp chain tensor memory -> registers -> staging -> bulk
 // store is latency bound, so a second group halves the time per tile, which
 // shows wherever the epilogue is exposed (one accumulator, or short contractions).
+// With two groups the CTA is three warpgroups - {TMA, MMA, two idle warps} and
+// the two epilogue groups - so that the first can hand most of its registers
+// to the other two (setmaxnreg): an epilogue warp then holds a whole 256-column
+// share of an accumulator in registers at once.
 __host__ __device__ constexpr int gemm_epi_groups(int bn) { return bn >= 256 ? 2 : 1; }
-__host__ __device__ constexpr int gemm_threads(int bn) { return 64 + 128 * gemm_epi_groups(bn); }
+__host__ __device__ constexpr int gemm_threads(int bn) { return gemm_epi_groups(bn) == 2 ? 384 : 192; }
+constexpr int kProducerRegs = 56, kEpilogueRegs = 224;  // 128 x 56 + 256 x 224 = 64512 of the SM's 65536
 constexpr uint32_t kStatusTimeout = 11;  // OXM_TIMEOUT
 
 struct GemmParams {
@@ -236,13 +241,17 @@ __device__ __forceinline__ TileCoord decode_item(const GemmParams &p, const Work
   return c;
 }
 
-template <int BN, int STAGES, int A_MN, int B_MN, int KIND, int PAIR>
+// PACKED (the one-accumulator tile with a 16-bit result, whole tiles only): the epilogue packs its
+// share of the accumulator into registers and hands the accumulator back before it stores anything.
+// The two epilogues live in separate instances: compiled into one, each costs the other registers.
+template <int BN, int STAGES, int A_MN, int B_MN, int KIND, int PAIR, int PACKED = 0>
 __global__ void __launch_bounds__(gemm_threads(BN), 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
   static_assert(!(KIND == 1 && (A_MN || B_MN)), "the tf32 path stages K-major operands only");
   static_assert(BN % 64 == 0 && BN >= 64 && BN <= 512, "tile width");
   static_assert(BN <= 256 || PAIR, "tiles wider than one MMA need the CTA pair");
+  static_assert(!PACKED || (BN > 256 && KIND != 1), "the packed drain is the wide tile's, for 16-bit results");
   using L = GemmSmem<BN, STAGES, PAIR>;
   constexpr int ELT = KIND == 1 ? 4 : KIND == 2 ? 1 : 2;  // operand bytes per element
   constexpr int BK = kStageKBytes / ELT;   // contraction elements per stage
@@ -270,6 +279,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   // column still sees its products in ascending k, so no bit changes.
   constexpr int PRO = WIDE ? STAGES - 1 : 0;
   constexpr uint32_t TMEM_COLS = (ACC * BN <= 128) ? 128 : (ACC * BN <= 256) ? 256 : 512;
+  constexpr uint32_t EPI_WARP0 = EPI_GROUPS == 2 ? 4 : 2;  // first epilogue warp
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = ptx::smem_u32(smem_raw);
@@ -326,11 +336,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   }
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-
   WaitCtx wc{abort_flag, p.status, p.wait_limit_ns};
   const int64_t tile_stride = PAIR ? (gridDim.x >> 1) : gridDim.x;
   const int64_t tile_first = PAIR ? (blockIdx.x >> 1) : blockIdx.x;
 
+  if (warp < EPI_WARP0) {
+  // Registers move from the warpgroup of the two single-thread roles to the epilogue warpgroups.
+  if constexpr (EPI_GROUPS == 2) ptx::setmaxnreg_dec<kProducerRegs>();
   if (warp == 0) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
@@ -496,9 +508,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       }
     }
     __syncwarp();
+  }
   } else {
     // ---------------- epilogue: TMEM -> registers -> global ----------------
-    const uint32_t ew = warp - 2u;
+    if constexpr (EPI_GROUPS == 2) ptx::setmaxnreg_inc<kEpilogueRegs>();
+    const uint32_t ew = warp - EPI_WARP0;
     const uint32_t q = warp & 3u;  // the TMEM lane quarter this warp may read
     const uint32_t grp = ew >> 2;  // which share of the columns this warp drains
     const uint32_t stage_smem = base + L::kStagingOffset + ew * L::kStagingTile;
@@ -617,6 +631,105 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           ptx::bulk_commit_group();
         }
       };
+      // The one-accumulator tile with a 16-bit result: this warp's whole share of the accumulator
+      // (up to 256 columns) is rounded and packed into 128 registers, the accumulator is handed
+      // back, and only then does anything get stored - the next tile's main loop never waits for a
+      // store (one staged bulk store takes microseconds; four of them per warp used to sit between
+      // two tiles).
+      if constexpr (PACKED) {
+        {
+          uint32_t pk[NPH][CH][16];
+#pragma unroll
+          for (int dp = 0; dp < NPH; ++dp) {
+            const int32_t ch0 = dp * (CH * EPI_GROUPS) + static_cast<int32_t>(grp) * CH;
+            // two chunks (64 columns) per round of tensor-memory loads: 64 registers of raw sums
+            // beside the up to 128 packed ones
+#pragma unroll
+            for (int r = 0; r < CH / 2; ++r) {
+              uint32_t v[2][32];
+#pragma unroll
+              for (int i = 0; i < 2; ++i)
+                if (ch0 + 2 * r + i < nchunks) ptx::tmem_ld_32x32(t_row + static_cast<uint32_t>((ch0 + 2 * r + i) * 32), v[i]);
+              ptx::tmem_ld_wait();
+              if (p.epi.any) {
+                const int32_t colb = tile_col0 + (ch0 + 2 * r) * 32;
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                  if (ch0 + 2 * r + i >= nchunks) continue;
+#pragma unroll
+                  for (int e = 0; e < 32; ++e) {
+                    const int32_t col = colb + i * 32 + e;
+                    if (row_ok && col < p.N) {
+                      const int64_t idx = tc.o_off + static_cast<int64_t>(row) * p.out_rs + static_cast<int64_t>(col) * p.out_cs;
+                      v[i][e] = __float_as_uint(apply_epilogue(p.epi, __uint_as_float(v[i][e]), col, p.out, p.out_dtype, idx));
+                    }
+                  }
+                }
+              }
+#pragma unroll
+              for (int i = 0; i < 2; ++i) {
+#pragma unroll
+                for (int e = 0; e < 16; ++e) {
+                  const float lo = __uint_as_float(v[i][2 * e]), hi = __uint_as_float(v[i][2 * e + 1]);
+                  if (p.out_dtype == 6) {
+                    __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi);
+                    pk[dp][2 * r + i][e] = *reinterpret_cast<uint32_t *>(&t);
+                  } else {
+                    __half2 t = __floats2half2_rn(lo, hi);
+                    pk[dp][2 * r + i][e] = *reinterpret_cast<uint32_t *>(&t);
+                  }
+                }
+              }
+            }
+          }
+          ptx::tc_fence_before();
+          __syncwarp();
+          if (lane == 0) {
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+              if constexpr (PAIR) ptx::mbar_arrive_cluster(ptx::mapa_shared(tempty_bar(half), 0));
+              else ptx::mbar_arrive(tempty_bar(half));
+            }
+          }
+          // One packed 32-column chunk of this thread's row through plain stores (no partner chunk to
+          // fill a store box with, or an output the bulk store cannot describe).
+          auto store_packed = [&](const uint32_t (&h)[16], int32_t col0) {
+            if (!row_ok || col0 >= p.N) return;
+            if (p.out_vec && col0 + 32 <= p.N) {
+              uint4 *dst = reinterpret_cast<uint4 *>(rowp + static_cast<int64_t>(col0) * 2);
+#pragma unroll
+              for (int i = 0; i < 4; ++i) dst[i] = make_uint4(h[4 * i], h[4 * i + 1], h[4 * i + 2], h[4 * i + 3]);
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (col0 + i < p.N)
+                  reinterpret_cast<uint16_t *>(rowp)[static_cast<int64_t>(col0 + i) * p.out_cs] =
+                      static_cast<uint16_t>(h[i >> 1] >> (16 * (i & 1)));
+            }
+          };
+#pragma unroll
+          for (int dp = 0; dp < NPH; ++dp) {
+            const int32_t ch0 = dp * (CH * EPI_GROUPS) + static_cast<int32_t>(grp) * CH;
+#pragma unroll
+            for (int i = 0; i < CH / 2; ++i) {
+              const int32_t c = ch0 + 2 * i, col = tile_col0 + c * 32;
+              if (c >= nchunks) continue;
+              if (p.out_tma && c + 1 < nchunks) {
+                uint4 piece[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                  const uint32_t *src = j < 4 ? &pk[dp][2 * i][4 * j] : &pk[dp][2 * i + 1][4 * (j - 4)];
+                  piece[j] = make_uint4(src[0], src[1], src[2], src[3]);
+                }
+                emit(piece, col);
+              } else {
+                store_packed(pk[dp][2 * i], col);
+                if (c + 1 < nchunks) store_packed(pk[dp][2 * i + 1], col + 32);
+              }
+            }
+          }
+        }
+      } else {
 #pragma unroll 1
       for (int dp = 0; dp < NPH; ++dp) {
         // this warp's chunks of the phase: [ch0, ch0 + CH), those below nchunks exist
@@ -731,6 +844,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             if (ch0 + i < nchunks) store_chunk(v[i], colb + i * 32);
         }
       }
+      }  // two-phase drain
       if (wi.kind == 2) {
         // publish: the sums above are visible to whoever reads this launch's counter here
         __threadfence();

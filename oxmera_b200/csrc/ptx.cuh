@@ -135,6 +135,18 @@ __device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bul
 // Until the issuing thread's earlier bulk stores have finished READING shared memory.
 __device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 
+// ---- registers ---------------------------------------------------------------
+// Give up / take registers for the rest of the kernel; executed by all four warps
+// of a warpgroup together.  A CTA's warpgroups trade registers this way so that
+// the few threads that only issue copies and MMAs do not hold what the epilogue
+// warps need.
+template <int N> __device__ __forceinline__ void setmaxnreg_dec() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N> __device__ __forceinline__ void setmaxnreg_inc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+
 // ---- tcgen05 ---------------------------------------------------------------
 
 template <int PAIR>
