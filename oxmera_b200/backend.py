@@ -95,6 +95,24 @@ class B200Backend:
             _raise(st, "batched_matmul" if batched else "matmul", lhs, rhs)
         return out
 
+    def prepare_matmul(self, lhs: Tensor, rhs: Tensor, out: Tensor, batched: bool = True):
+        """The same call as `matmul_into` with the three `oxm_view` structs built
+        once: returns a function of no arguments that submits the product.  A
+        loop that multiplies the same tensors again and again (a benchmark, a
+        training step) then pays the C call alone, not the marshalling of the
+        views - which for a product of a few microseconds is most of the time."""
+        fn = self._lib.oxm_batched_matmul if batched else self._lib.oxm_matmul
+        va, vb, vo = lhs._view(), rhs._view(), out._view()
+        pa, pb, po, ctx = C.byref(va), C.byref(vb), C.byref(vo), self._ctx
+        keep = (va, vb, vo, lhs, rhs, out)  # the structs and the storages stay alive with the closure
+
+        def submit(_keep=keep):
+            st = fn(ctx, pa, pb, po)
+            if st != capi.OK:
+                _raise(st, "batched_matmul" if batched else "matmul", lhs, rhs)
+
+        return submit
+
     def matmul_fused(self, lhs: Tensor, rhs: Tensor, bias: Tensor | None = None, activation: str = "none",
                      accumulate_into: Tensor | None = None) -> Tensor:
         """act(lhs . rhs + bias), optionally added into an existing tensor

@@ -526,7 +526,8 @@ constexpr int kMaxChainKb = 3 * 1024 / 32;
 // products too skinny to fill the SMs with 256-wide tiles get a split
 // contraction rather than narrow tiles: [1..128, 8192] x [8192, 8192] takes
 // 45.7 us unsplit at every tile width and 31 us split four ways.
-TileChoice choose_tiles(const oxm_ctx *ctx, const Problem &P, bool tf32, int32_t num_kb, int min_b_rows, bool b_mn) {
+TileChoice choose_tiles(const oxm_ctx *ctx, const Problem &P, bool tf32, int32_t num_kb, int min_b_rows, bool b_mn,
+                        bool a_mn = false) {
   struct Cand { int cls, pair; double us_per_kb, us_epilogue; };
   // Microseconds per pipeline stage of one full-width tile at the ~1.45 GHz the
   // power cap sustains, and per epilogue.  With two accumulators the epilogue
@@ -570,6 +571,9 @@ TileChoice choose_tiles(const oxm_ctx *ctx, const Problem &P, bool tf32, int32_t
         if (bn > std::max(64, min_b_rows) && P.N <= bn / 2) continue;  // at least half of the tile is outside the matrix
         // narrower widths only where whole tiles of them cover the columns with less waste
         if (bn != c.cls && c.cls < 512) continue;
+        // An MN-major B arrives in whole boxes of 128 bytes of columns: a narrower tile loads the
+        // same boxes as the full one and only saves tensor time, which measured as no gain at all.
+        if (bn != c.cls && b_mn) continue;
       }
       // An MN-major B is fetched in boxes that start at multiples of a CTA's share of the columns:
       // the TMA engine wants those starts on 16-byte boundaries.
@@ -579,7 +583,10 @@ TileChoice choose_tiles(const oxm_ctx *ctx, const Problem &P, bool tf32, int32_t
       const int64_t tiles = ((P.M + tm - 1) / tm) * ((P.N + bn - 1) / bn) * P.nbatch;
       const double width = (double)bn / (double)c.cls;
       // A narrower tile moves the same A bytes for fewer flops: charge half of the lost width back.
-      const double kb_us = std::max(c.us_per_kb * (width + 0.04 * (1.0 - width)), 0.30);
+      // With both operands MN-major (a weight gradient) the 256-wide pair tile measured 15 % slower
+      // per block than with K-major ones (0.51 against 0.44 us), the 512-wide one the same.
+      const double major = (a_mn && b_mn && c.cls <= 256) ? 1.15 : 1.0;
+      const double kb_us = std::max(c.us_per_kb * major * (width + 0.04 * (1.0 - width)), 0.30);
       for (int m : mult) {
         const int32_t splits = min_splits * m;
         if (m > 1 && (ctx->opt_split_k == 0 || num_kb / splits < 16)) break;
@@ -602,7 +609,10 @@ TileChoice choose_tiles(const oxm_ctx *ctx, const Problem &P, bool tf32, int32_t
         int64_t sk = 0;
         if (splits == 1 && ctx->opt_stream_k != 0 && ctx->opt_split_k != 0) {
           sk = stream_k_tiles(tiles, slots, kb);
-          const double even_us = (double)tiles / (double)slots * tile_us + 12.0;
+          // (the one-accumulator tile shares work out with its two-phase epilogue, which keeps the
+          // accumulator for about 7 us per tile; whole tiles get the register-packed one)
+          const double sk_tile_us = c.cls > 256 ? kb * kb_us + 7.0 : tile_us;
+          const double even_us = (double)tiles / (double)slots * sk_tile_us + 12.0;
           const bool whole_waves_beside = tiles - sk >= slots;
           if (sk > 0 && (ctx->opt_stream_k == 1 || (whole_waves_beside && even_us < wave_us))) wave_us = std::min(wave_us, even_us);
           else sk = 0;
@@ -644,7 +654,7 @@ int launch_tcgen05(oxm_ctx *ctx, const Problem &P) {
   const int bk = kStageKBytes / P.elt;
 
   const int32_t num_kb_all = (int32_t)((Kst + bk - 1) / bk);
-  const TileChoice choice = choose_tiles(ctx, P, tf32, num_kb_all, (kind == 2 && sb.mn_major) ? 128 : 0, sb.mn_major);
+  const TileChoice choice = choose_tiles(ctx, P, tf32, num_kb_all, (kind == 2 && sb.mn_major) ? 128 : 0, sb.mn_major, sa.mn_major);
   const int bn = choice.bn, pair = choice.pair;
   const int cls = tile_class(bn), subn = tile_subn(bn);
   const int subc = pair ? subn / 2 : subn;  // B rows (columns of the product) one CTA stages per MMA
@@ -855,7 +865,7 @@ extern "C" int oxm_plan_matmul(const oxm_view *a, const oxm_view *b, const oxm_v
   const int64_t Kst = tf32 ? 3 * ((P.K + 31) / 32 * 32) : P.K;
   const int bk = kStageKBytes / P.elt;
   const TileChoice c = choose_tiles(&fake, P, tf32, (int32_t)((Kst + bk - 1) / bk), (P.elt == 1 && b_direct && sb.mn_major) ? 128 : 0,
-                                    b_direct && sb.mn_major);
+                                    b_direct && sb.mn_major, a_direct && sa.mn_major);
   plan[0] = 2; plan[1] = c.bn; plan[2] = c.pair; plan[3] = c.splits;
   plan[4] = a_direct ? 0 : 1; plan[5] = b_direct ? 0 : 1;
   plan[6] = (int32_t)c.sk_tiles;

@@ -639,23 +639,24 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       if constexpr (PACKED) {
         {
           uint32_t pk[NPH][CH][16];
+          constexpr int RC = 2;  // four at once would not fit beside the packed half
 #pragma unroll
           for (int dp = 0; dp < NPH; ++dp) {
             const int32_t ch0 = dp * (CH * EPI_GROUPS) + static_cast<int32_t>(grp) * CH;
-            // two chunks (64 columns) per round of tensor-memory loads: 64 registers of raw sums
-            // beside the up to 128 packed ones
+            // RC chunks (32 columns each) per round of tensor-memory loads: 32 RC registers of raw
+            // sums beside the up to 128 packed ones
 #pragma unroll
-            for (int r = 0; r < CH / 2; ++r) {
-              uint32_t v[2][32];
+            for (int r = 0; r < CH / RC; ++r) {
+              uint32_t v[RC][32];
 #pragma unroll
-              for (int i = 0; i < 2; ++i)
-                if (ch0 + 2 * r + i < nchunks) ptx::tmem_ld_32x32(t_row + static_cast<uint32_t>((ch0 + 2 * r + i) * 32), v[i]);
+              for (int i = 0; i < RC; ++i)
+                if (ch0 + RC * r + i < nchunks) ptx::tmem_ld_32x32(t_row + static_cast<uint32_t>((ch0 + RC * r + i) * 32), v[i]);
               ptx::tmem_ld_wait();
               if (p.epi.any) {
-                const int32_t colb = tile_col0 + (ch0 + 2 * r) * 32;
+                const int32_t colb = tile_col0 + (ch0 + RC * r) * 32;
 #pragma unroll
-                for (int i = 0; i < 2; ++i) {
-                  if (ch0 + 2 * r + i >= nchunks) continue;
+                for (int i = 0; i < RC; ++i) {
+                  if (ch0 + RC * r + i >= nchunks) continue;
 #pragma unroll
                   for (int e = 0; e < 32; ++e) {
                     const int32_t col = colb + i * 32 + e;
@@ -667,28 +668,28 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 }
               }
 #pragma unroll
-              for (int i = 0; i < 2; ++i) {
+              for (int i = 0; i < RC; ++i) {
 #pragma unroll
                 for (int e = 0; e < 16; ++e) {
                   const float lo = __uint_as_float(v[i][2 * e]), hi = __uint_as_float(v[i][2 * e + 1]);
                   if (p.out_dtype == 6) {
                     __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi);
-                    pk[dp][2 * r + i][e] = *reinterpret_cast<uint32_t *>(&t);
+                    pk[dp][RC * r + i][e] = *reinterpret_cast<uint32_t *>(&t);
                   } else {
                     __half2 t = __floats2half2_rn(lo, hi);
-                    pk[dp][2 * r + i][e] = *reinterpret_cast<uint32_t *>(&t);
+                    pk[dp][RC * r + i][e] = *reinterpret_cast<uint32_t *>(&t);
                   }
                 }
               }
             }
-          }
-          ptx::tc_fence_before();
-          __syncwarp();
-          if (lane == 0) {
-#pragma unroll
-            for (int half = 0; half < 2; ++half) {
-              if constexpr (PAIR) ptx::mbar_arrive_cluster(ptx::mapa_shared(tempty_bar(half), 0));
-              else ptx::mbar_arrive(tempty_bar(half));
+            // This half of the accumulator (phase 0: the columns below 256, which hold the first
+            // sub-tile) is in registers: hand it back.  The MMA warp starts the next tile on the
+            // first sub-tile while the second half is still being read out here.
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+              if constexpr (PAIR) ptx::mbar_arrive_cluster(ptx::mapa_shared(tempty_bar(dp), 0));
+              else ptx::mbar_arrive(tempty_bar(dp));
             }
           }
           // One packed 32-column chunk of this thread's row through plain stores (no partner chunk to

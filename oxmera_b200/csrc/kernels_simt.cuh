@@ -38,7 +38,7 @@ __global__ void bounded_wait_selftest_kernel(uint32_t *status, uint64_t limit_ns
 // C through signed element strides, so transposed / narrowed / flipped views
 // and broadcast batch dims need no preparation.
 //
-// The loads of the next four blocks are in flight while a block is multiplied
+// The loads of the next two blocks are in flight while a block is multiplied
 // (they wait in registers until the shared-memory tiles are free again), so a
 // CTA pays the latency of global memory once, not once per block.
 //
@@ -102,8 +102,10 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const SimtParams p) {
   // This thread's elements of a TS x 16 block of A and a 16 x TS block of B;
   // the faster-varying thread index follows the operand's unit stride.
   // PF blocks are in flight at any time: the loads of block i + PF are issued
-  // as soon as block i has moved from registers to shared memory.
-  constexpr int PF = 4;
+  // as soon as block i has moved from registers to shared memory.  (Four in
+  // flight measured slower than two: the extra registers cost more than the
+  // deeper queue gains.)
+  constexpr int PF = 2;
   const bool a_kfast = p.a_cs == 1, b_kfast = p.b_rs == 1;
   float ra[PF][PER_THREAD], rb[PF][PER_THREAD];
   auto fetch = [&](float (&fa)[PER_THREAD], float (&fb)[PER_THREAD], int32_t k0) {

@@ -41,21 +41,50 @@ def plan(a, b, out_dtype=None, sms=148):
 
 def test_the_five_configurations():
     bf, f32 = DType.BF16, DType.F32
-    # c3: square, B column-major -> the widest pair tile, operands read in place
+    # c3: square, B column-major -> the widest pair tile (512 tiles = 6.92 waves of 74 pairs), operands read in place
     st, p = plan(view(bf, [8192, 8192]), t(view(bf, [8192, 8192])))
     assert st == 0 and {k: p[k] for k in ('kernel', 'tile_n', 'pair', 'splits', 'pack_a', 'pack_b')} == dict(kernel=TCGEN05, tile_n=512, pair=1, splits=1, pack_a=0, pack_b=0)
-    # c4: 32 x [2048, 4096] . [4096, 11008]: 11008 is 43 tiles of 256 but 21.5 of 512
+    # c4: 32 x [2048, 4096] . [4096, 11008]: 11008 is 43 tiles of 256 but 21.5 of 512, and W is N-major, so no
+    # narrower width of the wide tile would load less: 256 x 256 pairs
     st, p = plan(view(bf, [32, 2048, 4096]), view(bf, [4096, 11008]))
     assert st == 0 and (p["kernel"], p["tile_n"], p["pair"], p["splits"], p["pack_a"], p["pack_b"]) == (TCGEN05, 256, 1, 1, 0, 0)
-    # c5's weight gradient: dY^T . X, both operands M- / N-major views
+    # c5: forward and input gradient are 512 wide tiles; the weight gradient dY^T . X has both operands
+    # M- / N-major views and 128 tiles: the wide tile, the last tiles shared out by contraction block
+    st, p = plan(view(bf, [16384, 4096]), t(view(bf, [4096, 4096])))
+    assert st == 0 and (p["tile_n"], p["pair"], p["stream_k"]) == (512, 1, 0)
     st, p = plan(t(view(bf, [16384, 4096])), view(bf, [16384, 4096]))
-    assert st == 0 and p["kernel"] == TCGEN05 and p["pair"] == 1 and p["splits"] == 1 and p["pack_a"] == p["pack_b"] == 0
+    assert st == 0 and p["kernel"] == TCGEN05 and (p["tile_n"], p["pair"], p["splits"]) == (512, 1, 1) and p["pack_a"] == p["pack_b"] == 0
     # c2: f32 goes through the TF32 split, which always packs; K = 1024 is one accumulation chain
     st, p = plan(t(view(f32, [8, 1, 1024, 512])), view(f32, [1, 16, 1024, 768]))
-    assert st == 0 and {k: p[k] for k in ('kernel', 'tile_n', 'pair', 'splits', 'pack_a', 'pack_b')} == dict(kernel=TCGEN05, tile_n=256, pair=1, splits=1, pack_a=1, pack_b=1)
-    # c1: small f32 product, still past the crossover with the FFMA kernel
+    assert st == 0 and {k: p[k] for k in ('kernel', 'pair', 'splits', 'pack_a', 'pack_b')} == dict(kernel=TCGEN05, pair=1, splits=1, pack_a=1, pack_b=1)
+    assert p["tile_n"] == 384  # 768 columns are two tiles of 384: no half-empty tile as with 512
+    # c1: a small f32 product: one launch of the FFMA kernel (its contraction split over a cluster)
     st, p = plan(view(f32, [256, 512]), view(f32, [512, 384]))
-    assert st == 0 and p["kernel"] == TCGEN05
+    assert st == 0 and p["kernel"] == FFMA
+
+
+def test_the_shards_of_an_8_gpu_run():
+    """The M-row shards of c3 and the batch shards of c4: tile widths that are
+    not powers of two fit the 74 CTA pairs where 512 columns leave a tenth of
+    them idle."""
+    bf = DType.BF16
+    b = t(view(bf, [8192, 8192]))
+    # 1024 rows: 4 x 16 tiles of 512 use 64 of 74 pairs; 4 x 18 tiles of 480 use 72, each 6 % shorter
+    st, p = plan(view(bf, [1024, 8192]), b)
+    assert st == 0 and (p["tile_n"], p["pair"], p["splits"], p["stream_k"]) == (480, 1, 1, 0)
+    # 2048 rows: 8 x 18 = 144 tiles of 480 are two nearly full waves
+    st, p = plan(view(bf, [2048, 8192]), b)
+    assert st == 0 and (p["tile_n"], p["pair"], p["splits"]) == (480, 1, 1)
+    # 4096 rows: 512 tiles of 256 x 256 are 6.92 waves, as for the whole product with the wide tile
+    st, p = plan(view(bf, [4096, 8192]), b)
+    assert st == 0 and (p["tile_n"], p["pair"], p["splits"]) == (256, 1, 1)
+    # c4 on 8 GPUs: 4 batch entries per GPU
+    st, p = plan(view(bf, [4, 2048, 4096]), view(bf, [4096, 11008]))
+    assert st == 0 and (p["tile_n"], p["pair"], p["splits"]) == (256, 1, 1)
+    # any multiple of 32 columns can be forced; an N-major B never gets a narrowed wide tile on its own
+    for n in (2048, 3000, 11008):
+        st, p = plan(view(bf, [4096, 4096]), view(bf, [4096, n]))
+        assert st == 0 and p["tile_n"] in (64, 128, 256, 512), (n, p)
 
 
 def test_long_f32_contractions_are_cut_into_chains():
@@ -117,15 +146,12 @@ def test_stream_k_only_beside_whole_waves():
     # 512 tiles on 74 pairs = 6.92 waves: too little to gain
     _, p = plan(view(bf, [8192, 8192]), t(view(bf, [8192, 8192])))
     assert p["stream_k"] == 0
-    # the 8-GPU shard of the same product: 64 tiles, all of them would be shared out
+    # the 8-GPU shard of the same product: all of its tiles would be shared out
     _, p = plan(view(bf, [1024, 8192]), t(view(bf, [8192, 8192])))
-    assert p["stream_k"] == 0 and p["tile_n"] == 512
+    assert p["stream_k"] == 0
     # the linear layer's weight gradient: 128 tiles of 256 x 512 = one wave and 54 more
     _, p = plan(t(view(bf, [16384, 4096])), view(bf, [16384, 4096]))
     assert (p["tile_n"], p["stream_k"]) == (512, 54)
-    # 4096^3: 256 tiles of 256 x 256 = 3 waves and 34 more -> the last wave and the remainder
-    _, p = plan(view(bf, [4096, 4096]), t(view(bf, [4096, 4096])))
-    assert (p["tile_n"], p["stream_k"]) == (256, 74 + 34)
     # long f32 contractions are cut into chains instead
     _, p = plan(view(DType.F32, [4096, 4096]), view(DType.F32, [4096, 4096]))
     assert p["splits"] > 1 and p["stream_k"] == 0
