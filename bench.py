@@ -55,7 +55,12 @@ from oxmera_b200.workloads import WORKLOADS, device_fill, gemm_views, materialis
 # on each workload, from the ncu captures summarised under profiles/.
 # Valid for the whole product on one GPU only: a shard reads all of B whatever its
 # share of A, so the figure does not scale with the shard and is not reported at N > 1.
-NCU_TRAFFIC_BYTES = {"c3": 971_092_480, "c3f8": 460_873_216}  # the 256x512 pair kernel on c3 (summary of the capture under profiles/)
+NCU_TRAFFIC_BYTES = {
+    "c3": 972_272_896,     # the 256 x 512 pair kernel (gemm_tcgen05_pair512_c3_bf16_8192.md)
+    "c3f8": 460_873_216,   # gemm_tcgen05_f8_c3f8_8192.md
+    "c2": 1_324_522_280,   # the tf32x3 GEMM alone; the two pack launches add 161 MB (gemm_tcgen05_tf32x3_c2.md)
+    "c5": 2_121_017_088 // 3,  # mean of the three launches of a step (gemm_tcgen05_c5_linear_fwd_bwd.md)
+}
 
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
@@ -133,7 +138,9 @@ class ClockSampler(threading.Thread):
         window = [s for s in self.samples if t0 <= s[0] <= t1]
         label = "timed region"
         if len(window) < 3:
-            window, label = self.samples, "warm-up + timed region"
+            # too short to be sampled: everything up to its end (and the one reading that follows),
+            # never the longer legs that run after it
+            window, label = [s for s in self.samples if s[0] <= t1 + 0.1] or self.samples, "warm-up + timed region"
         names = {0x2: "applications_clocks_setting", 0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x10: "sync_boost",
                  0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown", 0x80: "hw_power_brake_slowdown",
                  0x100: "display_clock_setting"}
@@ -228,6 +235,24 @@ def _host_f32(x: np.ndarray, dtype: DType) -> np.ndarray:
     if dtype == DType.BF16:
         return (x.astype(np.uint32) << 16).view(np.float32)
     return x.astype(np.float32)
+
+
+def decode_fp8(bits: np.ndarray, dtype: DType) -> np.ndarray:
+    """OCP 8-bit floats to float32 through a 256-entry table: e4m3 (bias 7, no
+    infinities, S.1111.111 = NaN) and e5m2 (bias 15, IEEE-like)."""
+    e_bits, m_bits, bias = (4, 3, 7) if dtype == DType.F8E4M3 else (5, 2, 15)
+    table = np.empty(256, np.float32)
+    for v in range(256):
+        sign = -1.0 if v & 0x80 else 1.0
+        e, m = (v >> m_bits) & ((1 << e_bits) - 1), v & ((1 << m_bits) - 1)
+        if e == 0:
+            x = m * 2.0 ** (1 - bias - m_bits)
+        elif dtype == DType.F8E4M3:
+            x = float("nan") if (e == 15 and m == 7) else (1 + m / 8.0) * 2.0 ** (e - bias)
+        else:
+            x = (float("inf") if m == 0 else float("nan")) if e == 31 else (1 + m / 4.0) * 2.0 ** (e - bias)
+        table[v] = sign * x
+    return table[np.asarray(bits, np.uint8)]
 
 
 def verify_shard(w, work, oracle_fp8=None) -> dict:
@@ -394,6 +419,10 @@ def run_ours(args):
     grp = init_from_env("nccl")
     rank, world, local = grp.rank, grp.world, grp.local_rank
     w = WORKLOADS[args.workload]
+    # --shard-of N on one GPU: the work rank 0 of an N-GPU run would get, timed alone
+    # (a cheap look at one shard's tiling; every figure of the line then counts that shard only)
+    srank, sworld = (0, args.shard_of) if (world == 1 and args.shard_of > 1) else (rank, world)
+    alone = sworld != world
     be = B200Backend(local)
     be.set_option("cta_pair", args.cta_pair)
     be.set_option("tile_n", args.tile_n)
@@ -401,7 +430,7 @@ def run_ours(args):
     tensors = materialise(w, device_fill(be))
     work = []
     for g in w.gemms:
-        a, b, rg = gemm_views(w, g, tensors, rank, world)
+        a, b, rg = gemm_views(w, g, tensors, srank, sworld)
         oshape = tuple(broadcast_shapes(a.shape[:-2], b.shape[:-2])) + (a.shape[-2], b.shape[-1])
         out = Tensor.empty(oshape, w.result_dtype, be)  # pooled: allocated once, outside the timed region
         work.append((g, a, b, out))
@@ -418,9 +447,7 @@ def run_ours(args):
     be.synchronize()
     fp8 = None
     if w.dtype in (DType.F8E4M3, DType.F8E5M2):
-        from tests.oracle_lib import Oracle
-        _o = Oracle()
-        fp8 = lambda bits: _o.fp8_to_f32(bits, int(w.dtype))
+        fp8 = lambda bits: decode_fp8(bits, w.dtype)
     check = verify_shard(w, work, fp8)
     all_ok = grp.min_over_ranks(1.0 if check["ok"] else 0.0) > 0.5
     worst_check = grp.max_over_ranks(check["worst_over_budget"])
@@ -451,6 +478,7 @@ def run_ours(args):
         grp.barrier()
         return local_ms, grp.max_over_ranks(local_ms), (t0, t1)
 
+    job_flops = shard_flops(w, srank, sworld) if alone else w.flops()
     sampler = ClockSampler(local)
     sampler.start()
     for _ in range(max(args.warmup, 3)):
@@ -470,7 +498,7 @@ def run_ours(args):
         sus_local, sus_ms, (s0, s1) = timed(n_sus)
         sus_clk = sampler.summary(s0 + 0.25 * (s1 - s0), s1)  # the clock has settled by the second quarter
         sustained = {"launches_per_rank": n_sus * len(work), "seconds": sus_ms * 1e-3, "ms_per_step": sus_ms / n_sus,
-                     "tflops": w.flops() * n_sus / (sus_ms * 1e-3) / 1e12, "sm_mhz_median": sus_clk.get("sm_mhz"),
+                     "tflops": job_flops * n_sus / (sus_ms * 1e-3) / 1e12, "sm_mhz_median": sus_clk.get("sm_mhz"),
                      "power_w": sus_clk.get("power_w"), "reasons": sus_clk.get("reasons"), "samples": sus_clk.get("samples")}
         if sus_clk.get("sm_mhz"):
             # the clock-independent figure to compare from run to run: SM cycles one step takes on the slowest rank
@@ -492,7 +520,7 @@ def run_ours(args):
         del flush
     sampler.stop()
 
-    flops_total = w.flops()
+    flops_total = job_flops
     tflops = flops_total * args.steps / (ms * 1e-3) / 1e12
     peaks, peak_src = load_peaks()
     timed_s = ms * 1e-3
@@ -516,7 +544,7 @@ def run_ours(args):
     # fp8: no figure was measured, twice the measured bf16 rate, as the nominal rates relate
     peak = (peaks["bf16_tflops"] if burst else peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"])) * scale
     launches = counts1["tcgen05"] - counts0["tcgen05"]
-    per_gpu_tflops = shard_flops(w, rank, world) * args.steps / (ms_local * 1e-3) / 1e12
+    per_gpu_tflops = shard_flops(w, srank, sworld) * args.steps / (ms_local * 1e-3) / 1e12
     achieved = grp.min_over_ranks(per_gpu_tflops)  # the slowest GPU's own rate
     if sustained:
         sus_per_gpu = sustained["tflops"] / world
@@ -526,7 +554,7 @@ def run_ours(args):
     rep_sorted = sorted(rep_ms)
     roofline = {
         "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-        "traffic": NCU_TRAFFIC_BYTES.get(w.key) if world == 1 else None,
+        "traffic": NCU_TRAFFIC_BYTES.get(w.key) if sworld == 1 else None,
         "kernel": kernel_name,
         "peak_source": f"{peak_src} cuBLAS bf16 8192^3, {'burst' if burst else 'sustained'} figure "
                        f"(timed region {timed_s:.3f} s, power cap {'active' if capped else 'not seen'})"
@@ -553,6 +581,8 @@ def run_ours(args):
             buf = be.pinned_empty(t.shape, npdt)
             buf[...] = t.to_host()
             host[name] = buf
+    if alone:
+        args.no_e2e = args.no_cpu = args.no_others = True
     if not args.no_e2e and w.result_dtype == w.dtype and world > 1:
         e_steps = max(2, min(args.steps, args.e2e_steps))
         e_ms, h2d, d2h = e2e_sharded(be, grp, w, work, tensors, host, e_steps)
@@ -612,7 +642,7 @@ def run_ours(args):
             "scaling": "strong", "vs_baseline": None, "dtype": w.dtype.name.lower(), "data": "synthetic",
             "config": {
                 "workload": f"{w.key}: {w.title}",
-                "sharding": "none" if world == 1 else f"{'batch' if len(w.gemm_shapes(w.gemms[0])[2]) > 2 else 'M-row blocks'} over {world} GPUs, no collective",
+                "sharding": f"rank 0's shard of a {sworld}-GPU run, alone on one GPU" if alone else "none" if world == 1 else f"{'batch' if len(w.gemm_shapes(w.gemms[0])[2]) > 2 else 'M-row blocks'} over {world} GPUs, no collective",
                 "l2": "inputs + output exceed the 126 MB L2" if w.algorithmic_bytes() > 126e6 else "working set fits L2 (latency-bound config)",
                 "accumulate": "fp32", "flops_per_step": flops_total, "algorithmic_bytes_per_step": w.algorithmic_bytes(),
             },
@@ -638,7 +668,8 @@ def main():
     ap.add_argument("--workload", default="c3", choices=sorted(WORKLOADS))
     ap.add_argument("--e2e-steps", type=int, default=10)
     ap.add_argument("--cta-pair", type=int, default=-1, choices=[-1, 0, 1], help="-1 auto, 0 one CTA per tile, 1 CTA pairs")
-    ap.add_argument("--tile-n", type=int, default=0, choices=[0, 64, 128, 256, 512])
+    ap.add_argument("--tile-n", type=int, default=0, help="0 auto, else a multiple of 32 from 64 to 512")
+    ap.add_argument("--shard-of", type=int, default=0, help="on one GPU: time only the shard rank 0 of an N-GPU run gets")
     ap.add_argument("--group-m", type=int, default=0)
     ap.add_argument("--repeats", type=int, default=5, help="times the --steps region is measured (the first one is `value`)")
     ap.add_argument("--sustained-s", type=float, default=2.2, help="length of the back-to-back leg in seconds (0: skip)")

@@ -161,6 +161,26 @@ typedef struct {
 } oxm_epilogue;
 int oxm_matmul_fused(oxm_ctx *ctx, const oxm_view *a, const oxm_view *b, const oxm_view *out, const oxm_epilogue *ep);
 
+/* Block-scaled fp8 product (the OCP Microscaling format MXFP8):
+ *   out[i, j] = sum over blocks kb of
+ *               2^(a_scale[i, kb] - 127) * 2^(b_scale[kb, j] - 127) *
+ *               sum over the block's 32 k of a[i, k] * b[k, j],
+ * accumulated in fp32.  `a` and `b` are F8E4M3 or F8E5M2 views (the same
+ * type), shaped and broadcast as for oxm_batched_matmul, with a contraction
+ * length that is a multiple of 32; `a_scale` and `b_scale` are U8 views of
+ * E8M0 exponents with their operand's shape except that the contraction dim
+ * is divided by 32 ([.., M, K/32] and [.., K/32, N]); a scale byte of 255 is
+ * NaN.  `out` is BF16, F16, F32 or the operands' type.  Operands the tensor
+ * core cannot read in place (contraction dim not contiguous, odd pitches) are
+ * packed first; the scales are always regrouped on the device into the
+ * 512-byte atoms the tensor core reads, a pass over K/32 bytes per operand
+ * row.  oxmera's DType stops at the 8-bit integer types
+ * (crates/oxmera-core/src/dtype.rs:9-23) and no crate of it has a quantised
+ * product: this entry point has no counterpart in the reference and stands
+ * beside oxm_matmul_fused as the backend half such an op would call. */
+int oxm_matmul_mx(oxm_ctx *ctx, const oxm_view *a, const oxm_view *a_scale, const oxm_view *b, const oxm_view *b_scale,
+                  const oxm_view *out);
+
 /* ---- the other op families of Backend --------------------------------------
  * Stand behind UnaryOps, BinaryOps and ReduceOps (crates/oxmera-ops/src/lib.rs:
  * 27-50,61-69) for Device::Cuda.  Inputs are any views; `out` is a fresh
@@ -267,6 +287,7 @@ int oxm_selftest_bounded_wait(oxm_ctx *ctx, int64_t limit_ms);
  *                 accumulation chain per output element).  Auto uses it only
  *                 where whole waves of ordinary tiles run beside the
  *                 shared-out ones and the model sees more than 12 us saved
+ *   "simt_tile"   0 auto, 32 or 64: the FFMA kernel's tile edge
  *   "wait_limit_ms"  bound of every device-side wait (default 2000, or the
  *                 environment variable OXM_WAIT_LIMIT_MS at context creation)
  * Unknown keys or values are OXM_INVALID_ARGUMENT. */

@@ -358,6 +358,62 @@ static int run_matmul(const orc_view *a, const orc_view *b, const orc_view *out,
   return ORC_OK;
 }
 
+/* The block-scaled fp8 product (OCP Microscaling Formats specification v1.0,
+ * MXFP8: 32 elements share one E8M0 scale 2^(e - 127), e = 255 is NaN).  The
+ * reference has no quantised product (its DType stops at U8 / Bool,
+ * crates/oxmera-core/src/dtype.rs:9-22), so this restates the published
+ * definition: per output element, in double,
+ *   sum over blocks kb of  sa[i, kb] * sb[kb, j] * (sum over the block's 32 k of a[i, k] * b[k, j]).
+ * Scales are U8 views shaped like their operand with the contraction dim / 32;
+ * batch dims broadcast as in orc_batched_matmul.  out is F32 or F64. */
+static double e8m0(uint8_t e) { return e == 255 ? (double)bits_f32(0x7fc00000u) : ldexp(1.0, (int)e - 127); }
+
+int orc_matmul_mx(const orc_view *a, const orc_view *a_scale, const orc_view *b, const orc_view *b_scale, const orc_view *out) {
+  int st = orc_check_matmul(a, b, out, 1);
+  if (st != ORC_OK) return st;
+  if (a->dtype != ORC_F8E4M3 && a->dtype != ORC_F8E5M2) return ORC_UNSUPPORTED_DTYPE;
+  if (out->dtype != ORC_F32 && out->dtype != ORC_F64) return ORC_UNSUPPORTED_DTYPE;
+  const int an = a->ndim, bn = b->ndim, on = out->ndim;
+  const int64_t m = a->shape[an - 2], k = a->shape[an - 1], n = b->shape[bn - 1];
+  if (k % 32) return ORC_SHAPE_MISMATCH;
+  if (a_scale->dtype != 4 || b_scale->dtype != 4) return ORC_DTYPE_MISMATCH; /* U8 */
+  if (a_scale->ndim != an || b_scale->ndim != bn) return ORC_SHAPE_MISMATCH;
+  for (int i = 0; i < an; ++i)
+    if (a_scale->shape[i] != (i == an - 1 ? k / 32 : a->shape[i])) return ORC_SHAPE_MISMATCH;
+  for (int i = 0; i < bn; ++i)
+    if (b_scale->shape[i] != (i == bn - 2 ? k / 32 : b->shape[i])) return ORC_SHAPE_MISMATCH;
+  const int bnd = on - 2;
+  int64_t nbatch = 1;
+  for (int d = 0; d < bnd; ++d) nbatch *= out->shape[d];
+  for (int64_t bi = 0; bi < nbatch; ++bi) {
+    int64_t a_off = a->offset, b_off = b->offset, o_off = out->offset, sa_off = a_scale->offset, sb_off = b_scale->offset;
+    int64_t rem = bi;
+    for (int d = bnd - 1; d >= 0; --d) {
+      const int64_t idx = rem % out->shape[d];
+      rem /= out->shape[d];
+      const int ad = d - (bnd - (an - 2)), bd = d - (bnd - (bn - 2));
+      if (ad >= 0 && a->shape[ad] != 1) { a_off += idx * a->strides[ad]; sa_off += idx * a_scale->strides[ad]; }
+      if (bd >= 0 && b->shape[bd] != 1) { b_off += idx * b->strides[bd]; sb_off += idx * b_scale->strides[bd]; }
+      o_off += idx * out->strides[d];
+    }
+    for (int64_t i = 0; i < m; ++i)
+      for (int64_t j = 0; j < n; ++j) {
+        double acc = 0.0;
+        for (int64_t kb = 0; kb < k / 32; ++kb) {
+          double blk = 0.0;
+          for (int64_t kk = kb * 32; kk < kb * 32 + 32; ++kk)
+            blk += (double)orc_fp8_to_f32(((const uint8_t *)a->base)[a_off + i * a->strides[an - 2] + kk * a->strides[an - 1]], a->dtype) *
+                   (double)orc_fp8_to_f32(((const uint8_t *)b->base)[b_off + kk * b->strides[bn - 2] + j * b->strides[bn - 1]], b->dtype);
+          const double sa = e8m0(((const uint8_t *)a_scale->base)[sa_off + i * a_scale->strides[an - 2] + kb * a_scale->strides[an - 1]]);
+          const double sb = e8m0(((const uint8_t *)b_scale->base)[sb_off + kb * b_scale->strides[bn - 2] + j * b_scale->strides[bn - 1]]);
+          acc += sa * sb * blk;
+        }
+        store_from_f64(out->base, out->dtype, o_off + i * out->strides[on - 2] + j * out->strides[on - 1], acc);
+      }
+  }
+  return ORC_OK;
+}
+
 int orc_matmul(const orc_view *a, const orc_view *b, const orc_view *out, int acc_mode, int nthreads) {
   return run_matmul(a, b, out, acc_mode, nthreads, 0, NULL);
 }

@@ -93,6 +93,13 @@ int orc_batched_matmul(const orc_view *a, const orc_view *b,
 int orc_matmul_fused(const orc_view *a, const orc_view *b, const orc_view *out, const orc_view *bias, int act,
                      int accumulate, int acc_mode, int nthreads);
 
+/* The block-scaled fp8 product (OCP Microscaling Formats v1.0, MXFP8): fp8
+ * operands, one E8M0 scale (a U8: 2^(e - 127), 255 = NaN) per 32 contraction
+ * elements of every row of A ([.., M, K/32]) and column of B ([.., K/32, N]);
+ * every output element is summed in double.  No counterpart in the reference. */
+int orc_matmul_mx(const orc_view *a, const orc_view *a_scale, const orc_view *b, const orc_view *b_scale,
+                  const orc_view *out);
+
 /* Validation only: the status orc_matmul / orc_batched_matmul would return. */
 int orc_check_matmul(const orc_view *a, const orc_view *b, const orc_view *out,
                      int batched);

@@ -134,6 +134,26 @@ class B200Backend:
             _raise(st, "matmul_fused", lhs, rhs)
         return out
 
+    def matmul_mx(self, lhs: Tensor, lhs_scale: Tensor, rhs: Tensor, rhs_scale: Tensor,
+                  out_dtype: DType = DType.BF16) -> Tensor:
+        """The block-scaled fp8 product (MXFP8): lhs and rhs are fp8 tensors,
+        lhs_scale [.., M, K/32] and rhs_scale [.., K/32, N] hold one E8M0
+        exponent (a U8) per 32 contraction elements of every row of lhs and
+        column of rhs.  Shapes broadcast as in batched_matmul; the result is
+        a fresh tensor of `out_dtype`."""
+        bshape = broadcast_shapes(lhs.shape[:-2], rhs.shape[:-2]) if lhs.ndim >= 2 and rhs.ndim >= 2 else ()
+        rows = lhs.shape[-2] if lhs.ndim >= 2 else 0
+        cols = rhs.shape[-1] if rhs.ndim >= 1 else 0
+        out = Tensor.empty(tuple(bshape) + (rows, cols), out_dtype, self)
+        self.matmul_mx_into(lhs, lhs_scale, rhs, rhs_scale, out)
+        return out
+
+    def matmul_mx_into(self, lhs: Tensor, lhs_scale: Tensor, rhs: Tensor, rhs_scale: Tensor, out: Tensor) -> None:
+        st = self._lib.oxm_matmul_mx(self._ctx, C.byref(lhs._view()), C.byref(lhs_scale._view()), C.byref(rhs._view()),
+                                     C.byref(rhs_scale._view()), C.byref(out._view()))
+        if st != capi.OK:
+            _raise(st, "matmul_mx", lhs, rhs)
+
     def _mm(self, lhs: Tensor, rhs: Tensor, batched: bool) -> Tensor:
         op = "batched_matmul" if batched else "matmul"
         for t in (lhs, rhs):

@@ -17,7 +17,7 @@ EXPORTS = [
     "oxm_last_error", "oxm_status_name",
     "oxm_alloc", "oxm_free", "oxm_h2d", "oxm_d2h", "oxm_memset", "oxm_copy_peer", "oxm_sync", "oxm_host_alloc", "oxm_host_free",
     "oxm_matmul", "oxm_batched_matmul", "oxm_batched_matmul_host", "oxm_contiguous",
-    "oxm_matmul_f32_noalloc", "oxm_matmul_fused", "oxm_unary", "oxm_binary", "oxm_reduce",
+    "oxm_matmul_f32_noalloc", "oxm_matmul_fused", "oxm_matmul_mx", "oxm_unary", "oxm_binary", "oxm_reduce",
     "oxm_event_create", "oxm_event_destroy", "oxm_event_record", "oxm_event_elapsed_ms", "oxm_stream_handle", "oxm_fill", "oxm_selftest_bounded_wait",
     "oxm_set_option", "oxm_get_option", "oxm_launch_counts", "oxm_last_kernel", "oxm_memory_stats", "oxm_plan_matmul",
 ]
@@ -112,6 +112,7 @@ def load() -> C.CDLL:
         "oxm_binary": ([p, i, PV, PV, PV], i),
         "oxm_reduce": ([p, i, PV, C.POINTER(C.c_int32), i, PV], i),
         "oxm_matmul_fused": ([p, PV, PV, PV, C.POINTER(Epilogue)], i),
+        "oxm_matmul_mx": ([p, PV, PV, PV, PV, PV], i),
         "oxm_matmul_f32_noalloc": ([p, PV, PV, PV], i),
         "oxm_event_create": ([p, C.POINTER(p)], i),
         "oxm_event_destroy": ([p], i),

@@ -67,12 +67,12 @@ struct oxm_ctx {
   EncodeTiledFn encode = nullptr;
   std::mutex mu;
   std::mutex host_mu;  // serialises calls that use the host staging buffers
-  Workspace pack_ws[3];  // packed A, packed B, split-K partial sums
+  Workspace pack_ws[5];  // packed A, packed B, split-K partial sums, scale atoms of A and of B (block-scaled products)
   Workspace host_stage[3];
   cudaStream_t copy_in = nullptr, copy_out = nullptr;  // host entry point: copies overlapped with compute
   cudaEvent_t pipe_events[2 * 16 + 1] = {};
   // options
-  int64_t opt_kernel = 0, opt_tile_n = 0, opt_cta_pair = -1, opt_wait_limit_ms = 2000, opt_group_m = 0, opt_tma_store = 1, opt_split_k = -1, opt_host_chunks = 0, opt_stream_k = -1;
+  int64_t opt_kernel = 0, opt_tile_n = 0, opt_cta_pair = -1, opt_wait_limit_ms = 2000, opt_group_m = 0, opt_tma_store = 1, opt_split_k = -1, opt_host_chunks = 0, opt_stream_k = -1, opt_simt_tile = 0;
   int64_t launches[4] = {0, 0, 0, 0};
   char last_kernel[96] = "none";
 };
@@ -190,7 +190,9 @@ struct Problem {
   Epilogue epi;
 };
 
-Problem normalise(const oxm_view *a, const oxm_view *b, const oxm_view *out) {
+// `merge` = false keeps every batch dim of extent > 1 as it is (the block-scaled product walks
+// its scale views by the same dims).
+Problem normalise(const oxm_view *a, const oxm_view *b, const oxm_view *out, bool merge = true) {
   Problem P{};
   P.dtype = a->dtype;
   P.elt = dtype_size(a->dtype);
@@ -220,7 +222,7 @@ Problem normalise(const oxm_view *a, const oxm_view *b, const oxm_view *out) {
   // Merge neighbours that every tensor walks with one stride.
   int w = 0;
   for (int d = 0; d < n; ++d) {
-    if (w > 0 && as[w - 1] == as[d] * dims[d] && bs[w - 1] == bs[d] * dims[d] && os[w - 1] == os[d] * dims[d]) {
+    if (merge && w > 0 && as[w - 1] == as[d] * dims[d] && bs[w - 1] == bs[d] * dims[d] && os[w - 1] == os[d] * dims[d]) {
       dims[w - 1] *= dims[d];
       as[w - 1] = as[d]; bs[w - 1] = bs[d]; os[w - 1] = os[d];
     } else {
@@ -229,7 +231,7 @@ Problem normalise(const oxm_view *a, const oxm_view *b, const oxm_view *out) {
     }
   }
   // A single batch dim over a shared B folds into M: one tall GEMM.
-  if (w == 1 && bs[0] == 0 && as[0] == P.M * P.a_rs && os[0] == P.M * P.o_rs && P.M > 0) {
+  if (merge && w == 1 && bs[0] == 0 && as[0] == P.M * P.a_rs && os[0] == P.M * P.o_rs && P.M > 0) {
     P.M *= dims[0];
     w = 0;
   }
@@ -253,7 +255,8 @@ int launch_simt(oxm_ctx *ctx, const Problem &P) {
   p.dtype = P.dtype; p.out_dtype = P.out_dtype;
   p.M = (int32_t)P.M; p.N = (int32_t)P.N; p.K = (int32_t)P.K;
   // 64-wide tiles, or 32-wide ones when those would leave most SMs idle
-  const int ts = (((P.M + 63) / 64) * ((P.N + 63) / 64) * P.nbatch < 2 * (int64_t)ctx->num_sms) ? 32 : 64;
+  int ts = (((P.M + 63) / 64) * ((P.N + 63) / 64) * P.nbatch < 2 * (int64_t)ctx->num_sms) ? 32 : 64;
+  if (ctx->opt_simt_tile == 32 || ctx->opt_simt_tile == 64) ts = (int)ctx->opt_simt_tile;
   p.tiles_m = (int32_t)((P.M + ts - 1) / ts); p.tiles_n = (int32_t)((P.N + ts - 1) / ts);
   p.a_off = P.a_off; p.b_off = P.b_off; p.o_off = P.o_off;
   p.a_rs = P.a_rs; p.a_cs = P.a_ks; p.b_rs = P.b_ks; p.b_cs = P.b_rs; p.o_rs = P.o_rs; p.o_cs = P.o_cs;
@@ -268,6 +271,8 @@ int launch_simt(oxm_ctx *ctx, const Problem &P) {
   int ksplit = 1;
   if (ctx->opt_split_k != 0)
     while (ksplit < 8 && tiles * ksplit * 2 <= 4 * (int64_t)ctx->num_sms && P.K / (ksplit * 2) >= 64) ksplit *= 2;
+  if (ctx->opt_split_k == 2 || ctx->opt_split_k == 4 || ctx->opt_split_k == 8)  // forced: a cluster of that many CTAs per tile
+    ksplit = (int)std::min<int64_t>(ctx->opt_split_k, std::max<int64_t>(1, P.K / 16));
   p.ksplit = ksplit;
   p.kchunk = (int32_t)(((P.K + ksplit - 1) / ksplit + 15) / 16 * 16);
   const int64_t blocks = tiles * ksplit;
@@ -440,13 +445,38 @@ int make_map(oxm_ctx *ctx, CUtensorMap *tm, const Staged &s, int dtype, int elt,
   return OXM_OK;
 }
 
+// Fill the kernel's batch-dim arrays.  The tiles enumerate batch entries with the last listed dim
+// fastest; listed last is the dim along which the fewest operand bytes change from one entry to
+// the next (a broadcast operand changes none), so tiles in flight at the same time share the
+// larger operand in L2.  `o_bstride` = the output's element stride per dim (the caller's), and the
+// store map's batch coordinate counts entries in the output's own (row-major) order.
+void fill_batch_dims(GemmParams &p, const Problem &P, const Staged &sa, const Staged &sb, const int64_t *o_bstride) {
+  int order[kMaxBatchDims];
+  for (int d = 0; d < P.nbd; ++d) order[d] = d;
+  const double a_entry = (double)sa.rows * (double)sa.K, b_entry = (double)sb.rows * (double)sb.K;
+  auto changing = [&](int d) { return (sa.bmul[d] ? a_entry : 0.0) + (sb.bmul[d] ? b_entry : 0.0); };
+  std::stable_sort(order, order + P.nbd, [&](int x, int y) { return changing(x) > changing(y); });
+  int64_t row_major[kMaxBatchDims];
+  int64_t run = 1;
+  for (int d = P.nbd - 1; d >= 0; --d) { row_major[d] = run; run *= P.bdims[d]; }
+  for (int i = 0; i < P.nbd; ++i) {
+    const int d = order[i];
+    p.bdims[i] = (int32_t)P.bdims[d];
+    p.a_bmul[i] = sa.bmul[d];
+    p.b_bmul[i] = sb.bmul[d];
+    p.o_bmul[i] = (int32_t)row_major[d];
+    p.o_bstride[i] = o_bstride[d];
+  }
+}
+
 // Launch one instance of the tensor-core GEMM (defined in the gemm_*.cu units).
 int launch_gemm(oxm_ctx *ctx, int kind, bool a_mn, bool b_mn, int bn, int pair, const CUtensorMap &tmA, const CUtensorMap &tmB,
-                const CUtensorMap &tmC, const GemmParams &p, int grid) {
+                const CUtensorMap &tmC, const GemmParams &p, int grid, const CUtensorMap *sf = nullptr) {
   // whole tiles with a 16-bit result: the wide tile's register-packed epilogue
   const bool packed = bn == 512 && kind != 1 && p.sk_tiles == 0 && (p.out_dtype == OXM_BF16 || p.out_dtype == OXM_F16);
-  const GemmLaunch l{bn, pair, packed, b_mn, grid, ctx->stream};
+  const GemmLaunch l{bn, pair, packed, b_mn, grid, ctx->stream, sf};
   const GemmLaunchFn fn = kind == 1 ? launch_gemm_tf32
+                          : kind == 3 ? launch_gemm_mx
                           : kind == 2 ? (a_mn ? launch_gemm_f8_am : launch_gemm_f8_ak)
                                       : (a_mn ? launch_gemm_f16_am : launch_gemm_f16_ak);
   cudaError_t e = fn(l, tmA, tmB, tmC, p, ctx->last_kernel, sizeof(ctx->last_kernel));
@@ -671,11 +701,9 @@ int launch_tcgen05(oxm_ctx *ctx, const Problem &P) {
   p.nbd = P.nbd;
   bool vec = P.o_cs == 1 && !is_fp8(P.out_dtype) && (reinterpret_cast<uintptr_t>(P.o) + P.o_off * P.oelt) % 16 == 0 &&
              (P.o_rs * P.oelt) % 16 == 0;
+  int64_t obs[kMaxBatchDims] = {0};  // the output's (or the partial-sum workspace's) stride per batch dim
   for (int d = 0; d < P.nbd; ++d) {
-    p.bdims[d] = (int32_t)P.bdims[d];
-    p.a_bmul[d] = sa.bmul[d];
-    p.b_bmul[d] = sb.bmul[d];
-    p.o_bstride[d] = P.o_bs[d];
+    obs[d] = P.o_bs[d];
     if ((P.o_bs[d] * P.oelt) % 16) vec = false;
   }
   p.out = static_cast<uint8_t *>(P.o) + P.o_off * P.oelt;
@@ -720,7 +748,7 @@ int launch_tcgen05(oxm_ctx *ctx, const Problem &P) {
     for (int d = P.nbd - 1; d >= 0; --d) {
       rp.bdims[d] = (int32_t)P.bdims[d];
       rp.o_bs[d] = P.o_bs[d];
-      p.o_bstride[d] = dense;
+      obs[d] = dense;
       dense *= P.bdims[d];
     }
     p.out = ctx->pack_ws[2].ptr;
@@ -730,6 +758,8 @@ int launch_tcgen05(oxm_ctx *ctx, const Problem &P) {
     p.split_ostride = slab;
     p.num_tiles *= p.splits;
   }
+
+  fill_batch_dims(p, P, sa, sb, obs);
 
   p.dp_tiles = p.num_tiles;
   p.sk_tiles = 0;
@@ -797,6 +827,208 @@ int launch_tcgen05(oxm_ctx *ctx, const Problem &P) {
     ctx->launches[0]++; ctx->launches[3]++;
   }
   return OXM_OK;
+}
+
+// ---------------------------------------------------------------------------
+// block-scaled fp8 product (MX): C = (A * 2^(sa - 127)) . (B * 2^(sb - 127)),
+// one E8M0 scale per 32 contraction elements of every row of A and column of B
+// ---------------------------------------------------------------------------
+
+// Regroup one operand's scale view into atoms in workspace `slot` and describe them to the TMA
+// engine as {128 words, stages, batch x row groups}.
+int stage_scale_atoms(oxm_ctx *ctx, const Problem &P, bool is_b, const oxm_view *sv, const int64_t *sv_bs, int slot,
+                      CUtensorMap *tm, int32_t *row_groups) {
+  const int64_t rows = is_b ? P.N : P.M, kblocks = P.K / 32;
+  SfParams sp{};
+  sp.src = static_cast<const uint8_t *>(sv->base);
+  sp.src_off = sv->offset;
+  sp.src_rs = sv->strides[sv->ndim - (is_b ? 1 : 2)];
+  sp.src_ks = sv->strides[sv->ndim - (is_b ? 2 : 1)];
+  sp.rows = (int32_t)rows; sp.kblocks = (int32_t)kblocks;
+  sp.row_groups = (int32_t)((rows + 127) / 128);
+  sp.stages = (int32_t)((kblocks + 3) / 4);
+  const int64_t *obs = is_b ? P.b_bs : P.a_bs;
+  int64_t nb = 1;
+  sp.nbd = 0;
+  for (int d = 0; d < P.nbd; ++d) {
+    if (obs[d] == 0) continue;  // the operand repeats over this dim, and so do its scales
+    sp.bdims[sp.nbd] = (int32_t)P.bdims[d];
+    sp.src_bs[sp.nbd] = sv_bs[d];
+    sp.nbd++;
+    nb *= P.bdims[d];
+  }
+  const int64_t atoms = nb * sp.row_groups * sp.stages;
+  if (nb * sp.row_groups >= (1ll << 31) || atoms >= (1ll << 40)) return fail(OXM_NOT_IMPLEMENTED, "matmul_mx is not implemented for %lld scale atoms", (long long)atoms);
+  sp.total_words = atoms * 128;
+  int st = grow(ctx, ctx->pack_ws[slot], (size_t)atoms * kSfAtomBytes);
+  if (st) return st;
+  sp.dst = static_cast<uint32_t *>(ctx->pack_ws[slot].ptr);
+  const int64_t blocks = std::min<int64_t>((sp.total_words + 255) / 256, (int64_t)ctx->num_sms * 32);
+  mx_scale_atoms_kernel<<<(unsigned)blocks, 256, 0, ctx->stream>>>(sp);
+  CUDA_TRY(cudaGetLastError());
+  ctx->launches[0]++; ctx->launches[3]++;
+  cuuint64_t dims[3] = {128, (cuuint64_t)sp.stages, (cuuint64_t)(nb * sp.row_groups)};
+  cuuint64_t strides[2] = {(cuuint64_t)kSfAtomBytes, (cuuint64_t)kSfAtomBytes * (cuuint64_t)sp.stages};
+  cuuint32_t box[3] = {128, 1, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = ctx->encode(tm, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, sp.dst, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                           CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(OXM_CUDA_ERROR, "cuTensorMapEncodeTiled failed (%d) for the scale atoms", (int)r);
+  *row_groups = sp.row_groups;
+  return OXM_OK;
+}
+
+int launch_mx(oxm_ctx *ctx, const Problem &P, const oxm_view *a_scale, const int64_t *sa_bs, const oxm_view *b_scale,
+              const int64_t *sb_bs) {
+  if (P.nbd > kMaxBatchDims) return fail(OXM_NOT_IMPLEMENTED, "matmul_mx is not implemented for %d batch dims", P.nbd);
+  if (P.M >= (1ll << 31) || P.N >= (1ll << 31) || P.K >= (1ll << 29) || P.nbatch >= (1ll << 31))
+    return fail(OXM_NOT_IMPLEMENTED, "matmul_mx is not implemented for extents above 2^31");
+  // operands: K-major for the tensor core, in place where the TMA engine can address them
+  Staged sa{}, sb{};
+  if (!stage_direct(P, false, sa) || sa.mn_major) {
+    int st = stage_packed(ctx, P, false, 0, sa);
+    if (st) return st;
+  }
+  if (!stage_direct(P, true, sb) || sb.mn_major) {
+    int st = stage_packed(ctx, P, true, 1, sb);
+    if (st) return st;
+  }
+  CUtensorMap sf[2];
+  int32_t sf_mb = 0, sf_nb = 0;
+  int st = stage_scale_atoms(ctx, P, false, a_scale, sa_bs, 3, &sf[0], &sf_mb);
+  if (st) return st;
+  st = stage_scale_atoms(ctx, P, true, b_scale, sb_bs, 4, &sf[1], &sf_nb);
+  if (st) return st;
+
+  // The wide pair tile, 256 or 384 columns (whole 128-column scale atoms; the 32 columns of
+  // tensor memory above 480 hold the scales): whichever leaves fewer idle pair-waves.
+  const int tm = 2 * kTileM;
+  const int64_t tiles_m = (P.M + tm - 1) / tm, slots = std::max(1, ctx->num_sms / 2);
+  auto cost = [&](int w) {
+    const int64_t tiles = tiles_m * ((P.N + w - 1) / w) * P.nbatch;
+    return (double)((tiles + slots - 1) / slots) * (w + 24);  // a tile's time grows with its width, plus its drain
+  };
+  int bn = (P.N <= 256 || cost(256) < cost(384)) ? 256 : 384;
+  if (ctx->opt_tile_n == 256 || ctx->opt_tile_n == 384) bn = (int)ctx->opt_tile_n;
+  const int subn = bn / 2, subc = subn / 2;
+  const int bk = kStageKBytes;  // one byte per element
+
+  GemmParams p{};
+  p.M = (int32_t)P.M; p.N = (int32_t)P.N; p.K = (int32_t)P.K;
+  p.bn = bn; p.subn = subn;
+  p.tiles_m = (int32_t)tiles_m;
+  p.tiles_n = (int32_t)((P.N + bn - 1) / bn);
+  p.num_kb = (int32_t)((P.K + bk - 1) / bk);
+  p.nbatch = (int32_t)P.nbatch;
+  p.num_tiles = (int64_t)p.tiles_m * p.tiles_n * P.nbatch;
+  p.nbd = P.nbd;
+  bool vec = P.o_cs == 1 && !is_fp8(P.out_dtype) && (reinterpret_cast<uintptr_t>(P.o) + P.o_off * P.oelt) % 16 == 0 &&
+             (P.o_rs * P.oelt) % 16 == 0;
+  for (int d = 0; d < P.nbd; ++d)
+    if ((P.o_bs[d] * P.oelt) % 16) vec = false;
+  fill_batch_dims(p, P, sa, sb, P.o_bs);
+  p.out = static_cast<uint8_t *>(P.o) + P.o_off * P.oelt;
+  p.out_rs = P.o_rs; p.out_cs = P.o_cs;
+  p.out_dtype = P.out_dtype;
+  p.out_vec = vec ? 1 : 0;
+  // block-scaled instruction descriptor: operand formats e4m3 0 / e5m2 1, E8M0 scales, N and M
+  // of one MMA; the kernel adds each contraction block's scale ids
+  const uint32_t fmt = P.dtype == OXM_F8E5M2 ? 1u : 0u;
+  p.idesc = (fmt << 7) | (fmt << 10) | ((uint32_t)(subn >> 3) << 17) | (1u << 23) | ((uint32_t)(tm >> 4) << 24);
+  p.status = ctx->status_dev;
+  p.wait_limit_ns = (uint64_t)ctx->opt_wait_limit_ms * 1000000ull;
+  p.splits = 1;
+  p.kb_per_split = p.num_kb;
+  p.tiles_per_split = p.num_tiles;
+  p.dp_tiles = p.num_tiles;
+  p.group_m = ctx->opt_group_m > 0 ? (int32_t)ctx->opt_group_m : 16;
+  p.epi = P.epi;
+  p.sf_mb = sf_mb; p.sf_nb = sf_nb;
+  p.stage_tx = (uint32_t)(kStageKBytes * (kTileM + 2 * subc) + kSfAtomBytes * (1 + bn / 128));
+
+  CUtensorMap tmA, tmB, tmC;
+  memset(&tmC, 0, sizeof(tmC));
+  st = make_map(ctx, &tmA, sa, P.dtype, 1, kTileM, bk);
+  if (st) return st;
+  st = make_map(ctx, &tmB, sb, P.dtype, 1, subc, bk);
+  if (st) return st;
+  if ((P.o_cs == 1 || P.N == 1) && (P.out_dtype == OXM_BF16 || P.out_dtype == OXM_F16)) {
+    bool fold = true;
+    for (int d = 0; d + 1 < P.nbd; ++d) fold = fold && P.o_bs[d] == P.o_bs[d + 1] * P.bdims[d + 1];
+    p.out_tma = fold && make_out_map(ctx, &tmC, p.out, P.out_dtype, P.oelt, P.M, P.N, P.nbatch, P.o_rs,
+                                     P.nbd ? P.o_bs[P.nbd - 1] : 0) ? 1 : 0;
+  }
+  if (ctx->opt_tma_store == 0) p.out_tma = 0;
+  const int grid = 2 * (int)std::min<int64_t>(p.num_tiles, slots);
+  st = launch_gemm(ctx, 3, false, false, 512, 1, tmA, tmB, tmC, p, grid, sf);
+  if (st) return st;
+  const size_t len = strlen(ctx->last_kernel);
+  snprintf(ctx->last_kernel + len, sizeof(ctx->last_kernel) - len, "_w%d", bn);
+  ctx->launches[0]++; ctx->launches[1]++;
+  return OXM_OK;
+}
+
+// The scale view of one operand: u8 (E8M0), the operand's shape with the contraction dim divided
+// by 32.  Fills the view's stride for every batch dim of the normalised problem.
+int check_scale_view(const oxm_ctx *ctx, const char *which, const oxm_view *operand, const oxm_view *sv, bool is_b,
+                     const oxm_view *out, const Problem &P, int64_t *sv_bs) {
+  if (sv->dtype != OXM_U8)
+    return fail(OXM_DTYPE_MISMATCH, "dtype mismatch: expected U8, got %s in matmul_mx (%s: E8M0 scales are bytes)", dtype_name(sv->dtype), which);
+  if (sv->device != ctx->device)
+    return fail(OXM_DEVICE_MISMATCH, "device mismatch: Cuda{index: %d} vs Cuda{index: %d} in matmul_mx (%s)", ctx->device, sv->device, which);
+  bool ok = sv->ndim == operand->ndim;
+  const int kd = operand->ndim - (is_b ? 2 : 1);  // the contraction dim
+  std::string exp = "[";
+  for (int i = 0; i < operand->ndim; ++i) {
+    const int64_t e = i == kd ? operand->shape[i] / 32 : operand->shape[i];
+    if (ok && sv->shape[i] != e) ok = false;
+    exp += (i ? ", " : "") + std::to_string(e);
+  }
+  exp += "]";
+  if (!ok) return fail(OXM_SHAPE_MISMATCH, "shape mismatch: expected %s, got %s in matmul_mx (%s)", exp.c_str(), shape_str(sv).c_str(), which);
+  int64_t numel = 1;
+  for (int i = 0; i < sv->ndim; ++i) numel *= sv->shape[i];
+  if (numel > 0 && !sv->base) return fail(OXM_INVALID_ARGUMENT, "matmul_mx: %s with null storage", which);
+  // strides over the problem's batch dims, in normalise()'s order (extent-1 dims dropped)
+  const int nbd = out->ndim - 2;
+  const int64_t *obs = is_b ? P.b_bs : P.a_bs;
+  int n = 0;
+  for (int d = 0; d < nbd; ++d) {
+    if (out->shape[d] == 1) continue;
+    const int od = d - (nbd - (operand->ndim - 2));
+    sv_bs[n] = (od >= 0 && sv->shape[od] != 1) ? sv->strides[od] : 0;
+    if ((obs[n] == 0) != (sv_bs[n] == 0))
+      return fail(OXM_INVALID_ARGUMENT, "matmul_mx: %s must repeat over batch dim %d exactly where its operand does", which, d);
+    ++n;
+  }
+  return OXM_OK;
+}
+
+int run_matmul_mx(oxm_ctx *ctx, const oxm_view *a, const oxm_view *a_scale, const oxm_view *b, const oxm_view *b_scale,
+                  const oxm_view *out) {
+  if (!a_scale || !b_scale) return fail(OXM_INVALID_ARGUMENT, "matmul_mx: null argument");
+  int st = validate(ctx, a, b, out, true, false);
+  if (st) return st;
+  if (!is_fp8(a->dtype)) return fail(OXM_UNSUPPORTED_DTYPE, "dtype %s is not supported by matmul_mx (F8E4M3 or F8E5M2 operands)", dtype_name(a->dtype));
+  const int64_t K = a->shape[a->ndim - 1];
+  if (K % 32)
+    return fail(OXM_SHAPE_MISMATCH, "shape mismatch: expected a contraction length that is a multiple of 32, got %lld in matmul_mx", (long long)K);
+  for (const oxm_view *v : {a, b, out}) {
+    int64_t numel = 1;
+    for (int i = 0; i < v->ndim; ++i) numel *= v->shape[i];
+    if (numel > 0 && v->base == nullptr) return fail(OXM_INVALID_ARGUMENT, "matmul_mx: view with null storage");
+  }
+  Problem P = normalise(a, b, out, false);
+  int64_t sa_bs[OXM_MAX_DIMS] = {0}, sb_bs[OXM_MAX_DIMS] = {0};
+  st = check_scale_view(ctx, "a_scale", a, a_scale, false, out, P, sa_bs);
+  if (st) return st;
+  st = check_scale_view(ctx, "b_scale", b, b_scale, true, out, P, sb_bs);
+  if (st) return st;
+  if (P.M == 0 || P.N == 0 || P.nbatch == 0) return OXM_OK;
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  CUDA_TRY(cudaSetDevice(ctx->device));
+  if (K == 0) return launch_simt(ctx, P);  // an empty contraction: zeros, written by the FFMA kernel's store path
+  return launch_mx(ctx, P, a_scale, sa_bs, b_scale, sb_bs);
 }
 
 int run_matmul(oxm_ctx *ctx, const oxm_view *a, const oxm_view *b, const oxm_view *out, bool batched,
@@ -1093,6 +1325,11 @@ int oxm_matmul(oxm_ctx *ctx, const oxm_view *a, const oxm_view *b, const oxm_vie
 
 int oxm_batched_matmul(oxm_ctx *ctx, const oxm_view *a, const oxm_view *b, const oxm_view *out) {
   return run_matmul(ctx, a, b, out, true);
+}
+
+int oxm_matmul_mx(oxm_ctx *ctx, const oxm_view *a, const oxm_view *a_scale, const oxm_view *b, const oxm_view *b_scale,
+                  const oxm_view *out) {
+  return run_matmul_mx(ctx, a, a_scale, b, b_scale, out);
 }
 
 int oxm_matmul_fused(oxm_ctx *ctx, const oxm_view *a, const oxm_view *b, const oxm_view *out, const oxm_epilogue *ep) {
@@ -1792,6 +2029,7 @@ int oxm_set_option(oxm_ctx *ctx, const char *key, int64_t value) {
   else if (!strcmp(key, "tma_store") && (value == 0 || value == 1)) ctx->opt_tma_store = value;
   else if (!strcmp(key, "split_k") && value >= -1 && value <= 64) ctx->opt_split_k = value;
   else if (!strcmp(key, "host_chunks") && value >= 0 && value <= 16) ctx->opt_host_chunks = value;
+  else if (!strcmp(key, "simt_tile") && (value == 0 || value == 32 || value == 64)) ctx->opt_simt_tile = value;
   else return fail(OXM_INVALID_ARGUMENT, "oxm_set_option: unknown option or value: %s = %lld", key, (long long)value);
   return OXM_OK;
 }
@@ -1808,6 +2046,7 @@ int oxm_get_option(oxm_ctx *ctx, const char *key, int64_t *value) {
   else if (!strcmp(key, "tma_store")) *value = ctx->opt_tma_store;
   else if (!strcmp(key, "split_k")) *value = ctx->opt_split_k;
   else if (!strcmp(key, "host_chunks")) *value = ctx->opt_host_chunks;
+  else if (!strcmp(key, "simt_tile")) *value = ctx->opt_simt_tile;
   else return fail(OXM_INVALID_ARGUMENT, "oxm_get_option: unknown option: %s", key);
   return OXM_OK;
 }

@@ -18,6 +18,7 @@ struct GemmLaunch {
   bool b_mn;         // B is MN-major (A's major is fixed per translation unit)
   int grid;
   cudaStream_t stream;
+  const CUtensorMap *sf = nullptr;  // block-scaled kind: the maps of A's and B's scale atoms
 };
 
 // Launches the instance named by `l`; writes its name into `name`.
@@ -33,11 +34,12 @@ OXM_DECLARE_GEMM_LAUNCH(launch_gemm_f16_am)   // bf16 / f16, A M-major
 OXM_DECLARE_GEMM_LAUNCH(launch_gemm_f8_ak)    // fp8, A K-major
 OXM_DECLARE_GEMM_LAUNCH(launch_gemm_f8_am)    // fp8, A M-major
 OXM_DECLARE_GEMM_LAUNCH(launch_gemm_tf32)     // f32 as 3xTF32, packed K-major operands
+OXM_DECLARE_GEMM_LAUNCH(launch_gemm_mx)       // block-scaled fp8 (MX), K-major operands, wide pair tile
 
 template <int BN, int STAGES, int A_MN, int B_MN, int KIND, int PAIR, int PACKED = 0>
 cudaError_t launch_instance(const GemmLaunch &l, const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap &tmC,
                             const GemmParams &p, char *name, size_t name_len) {
-  using L = GemmSmem<BN, STAGES, PAIR>;
+  using L = GemmSmem<BN, STAGES, PAIR, KIND == 3>;
   auto kern = gemm_tcgen05_kernel<BN, STAGES, A_MN, B_MN, KIND, PAIR, PACKED>;
   static_assert(L::kDynamic <= 232448, "shared memory budget of one SM");
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic);
@@ -53,9 +55,15 @@ cudaError_t launch_instance(const GemmLaunch &l, const CUtensorMap &tmA, const C
     attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr; cfg.numAttrs = 1;
   }
-  snprintf(name, name_len, "gemm_tcgen05_%s_bn%d_s%d_%c%c_%s%s", KIND == 1 ? "tf32x3" : KIND == 2 ? "f8" : "f16", BN, STAGES,
-           A_MN ? 'm' : 'k', B_MN ? 'n' : 'k', PAIR ? "pair" : "1cta", PACKED ? "_pk" : "");
-  return cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmC, p);
+  snprintf(name, name_len, "gemm_tcgen05_%s_bn%d_s%d_%c%c_%s%s", KIND == 1 ? "tf32x3" : KIND == 2 ? "f8" : KIND == 3 ? "mxf8" : "f16",
+           BN, STAGES, A_MN ? 'm' : 'k', B_MN ? 'n' : 'k', PAIR ? "pair" : "1cta", PACKED ? "_pk" : "");
+  SfMaps<KIND == 3> sfm{};
+  if constexpr (KIND == 3) {
+    if (!l.sf) return cudaErrorInvalidValue;
+    sfm.a = l.sf[0];
+    sfm.b = l.sf[1];
+  }
+  return cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmC, p, sfm);
 }
 
 // Tile shapes and their pipeline depths (every one fills 192 KiB of shared memory).

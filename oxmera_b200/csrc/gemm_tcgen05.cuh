@@ -13,7 +13,11 @@
 //     (row/column dim contiguous): the transposed views of a linear layer's
 //     backward need no copy;
 //   - PAIR = 1 runs cta_group::2: two CTAs of a cluster share one 256-row tile,
-//     each staging its own A rows and its own half of B (no multicast).
+//     each staging its own A rows and its own half of B (no multicast);
+//   - KIND = 3 is the block-scaled fp8 product (MX: one E8M0 scale per 32
+//     contraction elements of every operand row): the scales travel beside the
+//     operands, 512 bytes per 128 rows and stage, and the MMA warp copies them
+//     into spare tensor-memory columns ahead of each stage's MMAs.
 //
 // Every wait is bounded.  When a bound expires the waiter records
 // OXM_TIMEOUT in the status word, raises the CTA's abort flag, and every role
@@ -56,8 +60,11 @@ struct GemmParams {
   int64_t num_tiles;
   int32_t nbd;               // output batch dims
   int32_t bdims[kMaxBatchDims];
-  int32_t a_bmul[kMaxBatchDims];  // output batch index -> operand batch coordinate
+  // The batch dims in the order the tiles walk them (last one fastest): the host puts last the dim
+  // along which the fewest operand bytes change, so that tiles in flight share the larger operand.
+  int32_t a_bmul[kMaxBatchDims];  // batch index -> operand batch coordinate
   int32_t b_bmul[kMaxBatchDims];
+  int32_t o_bmul[kMaxBatchDims];  // batch index -> batch coordinate of the store tensor map
   int64_t o_bstride[kMaxBatchDims];  // elements
   void *out;
   int64_t out_rs, out_cs;  // elements
@@ -88,12 +95,25 @@ struct GemmParams {
   uint32_t *sk_flags;     // [run][cta of the pair][8 epilogue warps]: the launch counter of the last publication
   uint32_t sk_epoch;      // this launch's counter value (never 0)
   int32_t group_m;        // tile rows walked together (L2 reuse)
+  int32_t sf_mb, sf_nb;   // block-scaled kind: 128-row scale atoms per batch entry of A and of B
   Epilogue epi;           // applied here unless the contraction is split (then by the reduction)
 };
 
-template <int BN, int STAGES, int PAIR>
+// Scales of the block-scaled kind, per stage: one 512-byte atom for this CTA's
+// 128 rows of A, then one per 128 columns of the tile (at most 384) for B.
+constexpr int kSfAtomBytes = 512;
+constexpr int kMxMaxBN = 384;
+constexpr int kSfStageBytes = kSfAtomBytes * (1 + kMxMaxBN / 128);
+constexpr int kSfTmemCols = 16;  // 4 columns for A's scales + up to 12 for B's; two such sets sit at the top of tensor memory
+
+// Tensor maps of the scale arrays: present only in the block-scaled instances.
+template <int MX> struct SfMaps {};
+template <> struct SfMaps<1> { CUtensorMap a, b; };
+
+template <int BN, int STAGES, int PAIR, int MX = 0>
 struct GemmSmem {
-  static constexpr int kBNC = PAIR ? BN / 2 : BN;  // B rows staged by one CTA
+  // B rows staged by one CTA (the block-scaled tile is at most 384 columns wide: two sub-tiles of 96 rows per CTA)
+  static constexpr int kBNC = MX ? kMxMaxBN / 2 : PAIR ? BN / 2 : BN;
   static constexpr int kABytes = kTileM * kStageKBytes;
   static constexpr int kBBytes = kBNC * kStageKBytes;
   static constexpr int kStageBytes = kABytes + kBBytes;
@@ -101,7 +121,9 @@ struct GemmSmem {
   static constexpr int kStagingOffset = STAGES * kStageBytes;
   static constexpr int kStagingTile = 32 * kStageKBytes;
   static constexpr int kStagingBytes = 4 * gemm_epi_groups(BN) * kStagingTile;
-  static constexpr int kBarOffset = kStagingOffset + kStagingBytes;
+  static constexpr int kSfOffset = kStagingOffset + kStagingBytes;
+  static constexpr int kSfStage = MX ? kSfStageBytes : 0;
+  static constexpr int kBarOffset = kSfOffset + STAGES * kSfStage;
   // full[STAGES] empty[STAGES] tmem_full[2] tmem_empty[2] teardown, then two u32 slots
   static constexpr int kNumBars = 2 * STAGES + 5;
   static constexpr int kTotal = kBarOffset + kNumBars * 8 + 16;
@@ -116,6 +138,17 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_
   d |= static_cast<uint64_t>(sbo_bytes >> 4) << 32;
   d |= 1ull << 46;  // descriptor version of this architecture
   d |= 2ull << 61;  // 128-byte swizzle
+  return d;
+}
+
+// Descriptor of one scale atom for the shared -> tensor memory copy: 32 rows of
+// 16 bytes, dense, no swizzle (groups of 8 rows 128 bytes apart).
+__device__ __forceinline__ uint64_t make_sf_desc(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>(16u >> 4) << 16;
+  d |= static_cast<uint64_t>(128u >> 4) << 32;
+  d |= 1ull << 46;
   return d;
 }
 
@@ -163,7 +196,7 @@ __device__ __forceinline__ TileCoord decode_tile(const GemmParams &p, int64_t ti
   const int32_t tpb = p.tiles_m * p.tiles_n;
   int32_t batch = static_cast<int32_t>(tile / tpb);
   const int32_t t = static_cast<int32_t>(tile - static_cast<int64_t>(batch) * tpb);
-  c.o_batch = split * p.nbatch + batch;
+  c.o_batch = split * p.nbatch;
   // Walk GROUP_M tile rows at a time so that concurrently resident CTAs share
   // A and B panels in L2.
   const int32_t GROUP_M = p.group_m;
@@ -182,6 +215,7 @@ __device__ __forceinline__ TileCoord decode_tile(const GemmParams &p, int64_t ti
     batch /= p.bdims[d];
     c.a_batch += idx * p.a_bmul[d];
     c.b_batch += idx * p.b_bmul[d];
+    c.o_batch += idx * p.o_bmul[d];
     c.o_off += static_cast<int64_t>(idx) * p.o_bstride[d];
   }
   return c;
@@ -247,13 +281,16 @@ __device__ __forceinline__ TileCoord decode_item(const GemmParams &p, const Work
 template <int BN, int STAGES, int A_MN, int B_MN, int KIND, int PAIR, int PACKED = 0>
 __global__ void __launch_bounds__(gemm_threads(BN), 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                    const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
+                    const __grid_constant__ CUtensorMap tmC, const GemmParams p,
+                    const __grid_constant__ SfMaps<KIND == 3> sfm) {
+  constexpr bool MX = KIND == 3;
   static_assert(!(KIND == 1 && (A_MN || B_MN)), "the tf32 path stages K-major operands only");
+  static_assert(!MX || (BN == 512 && PAIR && !A_MN && !B_MN), "the block-scaled kind: wide pair tile, K-major operands");
   static_assert(BN % 64 == 0 && BN >= 64 && BN <= 512, "tile width");
   static_assert(BN <= 256 || PAIR, "tiles wider than one MMA need the CTA pair");
   static_assert(!PACKED || (BN > 256 && KIND != 1), "the packed drain is the wide tile's, for 16-bit results");
-  using L = GemmSmem<BN, STAGES, PAIR>;
-  constexpr int ELT = KIND == 1 ? 4 : KIND == 2 ? 1 : 2;  // operand bytes per element
+  using L = GemmSmem<BN, STAGES, PAIR, MX>;
+  constexpr int ELT = KIND == 1 ? 4 : KIND >= 2 ? 1 : 2;  // operand bytes per element
   constexpr int BK = kStageKBytes / ELT;   // contraction elements per stage
   constexpr int BOXW = kStageKBytes / ELT; // elements along MN in one MN-major box
   constexpr int MMAS = kStageKBytes / kMmaKBytes;
@@ -267,7 +304,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   // loop) while they fit the 512 columns, one otherwise.
   constexpr bool WIDE = BN > 256;
   constexpr int NSUB = WIDE ? 2 : 1;
-  constexpr int SUBC_CAP = (BN / NSUB) / (PAIR ? 2 : 1);  // B rows one CTA can stage per sub-tile
+  constexpr int SUBC_CAP = MX ? kMxMaxBN / 4 : (BN / NSUB) / (PAIR ? 2 : 1);  // B rows one CTA can stage per sub-tile
   constexpr int ACC = WIDE ? 1 : 2;
   constexpr int EPI_GROUPS = gemm_epi_groups(BN);
   constexpr int CH = BN >= 128 ? 4 : 2;   // 32-column chunks an epilogue warp drains per wait
@@ -322,6 +359,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     ptx::prefetch_tensormap(&tmA);
     ptx::prefetch_tensormap(&tmB);
     if (p.out_tma) ptx::prefetch_tensormap(&tmC);
+    if constexpr (MX) {
+      ptx::prefetch_tensormap(&sfm.a);
+      ptx::prefetch_tensormap(&sfm.b);
+    }
   }
   if (warp == 1) {
     ptx::tmem_alloc<PAIR>(ptx::smem_u32(tmem_slot), TMEM_COLS);
@@ -383,6 +424,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 ptx::tma_load_3d_pair(sbs, &tmB, fb, k0, ns, tc.b_batch);
               }
             }
+            if constexpr (MX) {
+              // this stage's scales: the atom of this CTA's 128 rows of A, and those of ALL the tile's
+              // columns (each CTA of the pair multiplies its rows by every column)
+              const uint32_t sf = base + L::kSfOffset + s * L::kSfStage;
+              const int32_t ks = tc.kb0 + kb;
+              ptx::tma_load_3d_pair(sf, &sfm.a, fb, 0, ks, tc.a_batch * p.sf_mb + (m0 >> 7));
+              const int32_t nb0 = tc.b_batch * p.sf_nb + ((tc.n_blk * bn) >> 7);
+              for (int32_t g = 0; g < (bn >> 7); ++g)
+                ptx::tma_load_3d_pair(sf + kSfAtomBytes * (1 + g), &sfm.b, fb, 0, ks, nb0 + g);
+            }
           } else {
             const uint32_t fb = full_bar(s);
             ptx::mbar_arrive_expect_tx(fb, p.stage_tx);
@@ -426,15 +477,35 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       WorkItem wi;
       it.init(p, tile_first, tile_stride);
       // The four MMAs of one contraction block for sub-tile `sub`, from stage `st`.
+      // Block-scaled kind: stage `st`'s scales go from shared memory to the top columns of tensor
+      // memory (two sets, taken in turn by stage), in order with the MMAs issued around them.
+      // Returns the set's first column: A's scales there, B's from four columns on.
+      auto stage_scales = [&](uint32_t st) -> uint32_t {
+        const uint32_t set = tmem_base + static_cast<uint32_t>(BN - 2 * kSfTmemCols) + (st & 1u) * kSfTmemCols;
+        const uint32_t sf = base + L::kSfOffset + st * L::kSfStage;
+        ptx::tmem_cp_32x128b_x4<PAIR>(set, make_sf_desc(sf));
+        for (int32_t g = 0; g < (bn >> 7); ++g)
+          ptx::tmem_cp_32x128b_x4<PAIR>(set + 4u + 4u * g, make_sf_desc(sf + kSfAtomBytes * (1 + g)));
+        return set;
+      };
       auto issue = [&](uint32_t st, int sub, uint32_t d_tmem, int32_t kb) {
         const uint32_t sa = base + st * L::kStageBytes;
         const uint32_t sb = sa + L::kABytes;
         const uint64_t adesc = make_smem_desc(sa, A_LBO, 1024);
         const uint64_t bdesc = make_smem_desc(sb, B_LBO, 1024) + static_cast<uint64_t>(sub * B_SUB);
+        if constexpr (MX) {
+          const uint32_t set = stage_scales(st);
 #pragma unroll
-        for (int j = 0; j < MMAS; ++j)
-          ptx::umma<PAIR, KIND>(d_tmem + sub * subn, adesc + static_cast<uint64_t>(j * A_ADV),
-                                bdesc + static_cast<uint64_t>(j * B_ADV), p.idesc, (kb | j) != 0 ? 1u : 0u);
+          for (int j = 0; j < MMAS; ++j)  // contraction block j of the stage: scale byte j of either operand
+            ptx::umma_mx<PAIR>(d_tmem + sub * subn, adesc + static_cast<uint64_t>(j * A_ADV), bdesc + static_cast<uint64_t>(j * B_ADV),
+                               p.idesc | (static_cast<uint32_t>(j) << 4) | (static_cast<uint32_t>(j) << 29), set,
+                               set + 4u + static_cast<uint32_t>(sub * (subn >> 5)), (kb | j) != 0 ? 1u : 0u);
+        } else {
+#pragma unroll
+          for (int j = 0; j < MMAS; ++j)
+            ptx::umma<PAIR, KIND>(d_tmem + sub * subn, adesc + static_cast<uint64_t>(j * A_ADV),
+                                  bdesc + static_cast<uint64_t>(j * B_ADV), p.idesc, (kb | j) != 0 ? 1u : 0u);
+        }
       };
       auto release_stage = [&](uint32_t st) {
         if constexpr (PAIR) ptx::umma_commit_pair(empty_bar(st), 3);
@@ -480,12 +551,25 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             const uint32_t sb = sa + L::kABytes;
             const uint64_t adesc = make_smem_desc(sa, A_LBO, 1024);
             const uint64_t bdesc = make_smem_desc(sb, B_LBO, 1024);
+            if constexpr (MX) {
+              const uint32_t set = stage_scales(s);
+#pragma unroll
+              for (int j = 0; j < MMAS; ++j) {
+#pragma unroll
+                for (int sub = 0; sub < NSUB; ++sub)
+                  ptx::umma_mx<PAIR>(d_tmem + sub * subn, adesc + static_cast<uint64_t>(j * A_ADV),
+                                     bdesc + static_cast<uint64_t>(j * B_ADV + sub * B_SUB),
+                                     p.idesc | (static_cast<uint32_t>(j) << 4) | (static_cast<uint32_t>(j) << 29), set,
+                                     set + 4u + static_cast<uint32_t>(sub * (subn >> 5)), (kb | j) != 0 ? 1u : 0u);
+              }
+            } else {
 #pragma unroll
             for (int j = 0; j < MMAS; ++j) {
 #pragma unroll
               for (int sub = 0; sub < NSUB; ++sub)
                 ptx::umma<PAIR, KIND>(d_tmem + sub * subn, adesc + static_cast<uint64_t>(j * A_ADV),
                                       bdesc + static_cast<uint64_t>(j * B_ADV + sub * B_SUB), p.idesc, (kb | j) != 0 ? 1u : 0u);
+            }
             }
           } else {
             issue(s, 0, d_tmem, kb);
@@ -597,7 +681,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             if (col0 + i < p.N) {
               const float f = __uint_as_float(v[i]);
               const int64_t e = static_cast<int64_t>(col0 + i) * p.out_cs;
-              if constexpr (KIND == 2) {
+              if constexpr (KIND >= 2) {
                 store_elem(rowp, p.out_dtype, e, f);  // fp8 operands: the output may be fp8 or wider
               } else {
                 if (p.out_dtype == 0) reinterpret_cast<float *>(rowp)[e] = f;

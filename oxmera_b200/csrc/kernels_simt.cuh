@@ -69,8 +69,9 @@ struct SimtParams {
 template <int TS>
 __global__ void __launch_bounds__(256) gemm_simt_kernel(const SimtParams p) {
   constexpr int BK = 16, TT = TS / 16, PER_THREAD = TS * BK / 256;
-  __shared__ float As[BK][TS + 4];
-  __shared__ float Bs[BK][TS + 4];
+  // rows of TS + 4 floats keep every thread's TT consecutive values 4 TT-byte aligned: one vector load each
+  __shared__ __align__(16) float As[BK][TS + 4];
+  __shared__ __align__(16) float Bs[BK][TS + 4];
   __shared__ float red[TS][TS + 1];  // a CTA's partial tile, read by the first CTA of its cluster
 
   const int32_t krank = p.ksplit > 1 ? static_cast<int32_t>(blockIdx.x % p.ksplit) : 0;
@@ -142,11 +143,20 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const SimtParams p) {
       if (k0 + PF * BK < k_end) fetch(ra[f], rb[f], k0 + PF * BK);
 #pragma unroll
       for (int kk = 0; kk < BK; ++kk) {
+        // With scalar loads the 2 x 2 tile issues one shared-memory load per FMA and the loads,
+        // not the FMAs, set the kernel's time.
         float av[TT], bv[TT];
-#pragma unroll
-        for (int i = 0; i < TT; ++i) av[i] = As[kk][ty * TT + i];
-#pragma unroll
-        for (int j = 0; j < TT; ++j) bv[j] = Bs[kk][tx * TT + j];
+        if constexpr (TT == 4) {
+          const float4 a4 = *reinterpret_cast<const float4 *>(&As[kk][ty * TT]);
+          const float4 b4 = *reinterpret_cast<const float4 *>(&Bs[kk][tx * TT]);
+          av[0] = a4.x; av[1] = a4.y; av[2] = a4.z; av[3] = a4.w;
+          bv[0] = b4.x; bv[1] = b4.y; bv[2] = b4.z; bv[3] = b4.w;
+        } else {
+          const float2 a2 = *reinterpret_cast<const float2 *>(&As[kk][ty * TT]);
+          const float2 b2 = *reinterpret_cast<const float2 *>(&Bs[kk][tx * TT]);
+          av[0] = a2.x; av[1] = a2.y;
+          bv[0] = b2.x; bv[1] = b2.y;
+        }
 #pragma unroll
         for (int i = 0; i < TT; ++i)
 #pragma unroll
@@ -225,6 +235,53 @@ struct PackParams {
   int64_t src_bs[kSimtMaxBatchDims];
   int32_t tiles_r, tiles_k;
 };
+
+// ---------------------------------------------------------------------------
+// Scale atoms of the block-scaled product.  The E8M0 scales of one operand
+// (a view: row r, contraction block kb, any strides, broadcast batch dims left
+// out) are regrouped into the 512-byte atoms the tensor core's scale copy
+// takes: atom (batch, r / 128, kb / 4) holds, at byte (r % 32) * 16 +
+// (r % 128) / 32 * 4 + kb % 4, the scale of row r and block kb.  Atoms are
+// ordered [batch][row group][stage]; positions beyond the operand hold 0x7F
+// (2^0), which only ever multiplies the zeros the loads fill in there.
+// ---------------------------------------------------------------------------
+struct SfParams {
+  const uint8_t *src;
+  uint32_t *dst;
+  int64_t src_off, src_rs, src_ks;
+  int32_t rows, kblocks;   // extents of the view
+  int32_t row_groups, stages;  // ceil(rows / 128), ceil(kblocks / 4)
+  int32_t nbd;
+  int32_t bdims[kSimtMaxBatchDims];
+  int64_t src_bs[kSimtMaxBatchDims];
+  int64_t total_words;
+};
+
+__global__ void __launch_bounds__(256) mx_scale_atoms_kernel(const SfParams p) {
+  for (int64_t w = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; w < p.total_words;
+       w += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int32_t within = static_cast<int32_t>(w & 127);
+    int64_t atom = w >> 7;
+    const int32_t stage = static_cast<int32_t>(atom % p.stages);
+    atom /= p.stages;
+    const int32_t rg = static_cast<int32_t>(atom % p.row_groups);
+    int64_t batch = atom / p.row_groups;
+    const int32_t r = rg * 128 + (within & 3) * 32 + (within >> 2);
+    int64_t off = p.src_off;
+    for (int d = p.nbd - 1; d >= 0; --d) {
+      off += (batch % p.bdims[d]) * p.src_bs[d];
+      batch /= p.bdims[d];
+    }
+    uint32_t word = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int32_t kb = stage * 4 + i;
+      const uint32_t byte = (r < p.rows && kb < p.kblocks) ? p.src[off + static_cast<int64_t>(r) * p.src_rs + static_cast<int64_t>(kb) * p.src_ks] : 0x7Fu;
+      word |= byte << (8 * i);
+    }
+    p.dst[w] = word;
+  }
+}
 
 __device__ __forceinline__ float tf32_round(float x) {
   uint32_t u;

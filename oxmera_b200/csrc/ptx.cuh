@@ -198,6 +198,39 @@ __device__ __forceinline__ void umma(uint32_t d_tmem, uint64_t a_desc, uint64_t 
 }
 #undef OXM_UMMA
 
+// Block-scaled form (kind::mxf8f6f4, one E8M0 scale per 32 contraction elements
+// of each operand row): D[tmem] (+)= (A * 2^(sfa-127)) * (B * 2^(sfb-127)).  The
+// scales are read from tensor memory: 32-bit column c of lane (r % 32) holds, one
+// byte per contraction block, the scales of operand row r + 32 * c; the
+// descriptor's scale ids say which byte this instruction takes.
+template <int PAIR>
+__device__ __forceinline__ void umma_mx(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                        uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+  if constexpr (PAIR) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+                 ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem) : "memory");
+  } else {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+                 ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem) : "memory");
+  }
+}
+
+// Shared memory -> tensor memory: 32 rows of 16 bytes (described by `src_desc`,
+// a matrix descriptor without swizzle) go to lanes 0..31 of four consecutive
+// 32-bit columns starting at `dst_tmem`, and the same to lanes 32..63, 64..95 and
+// 96..127.  Runs in order with the MMAs the same thread issues.  In the pair form
+// each CTA of the pair copies from its own shared memory to its own tensor memory.
+template <int PAIR>
+__device__ __forceinline__ void tmem_cp_32x128b_x4(uint32_t dst_tmem, uint64_t src_desc) {
+  if constexpr (PAIR) {
+    asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(dst_tmem), "l"(src_desc) : "memory");
+  } else {
+    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(dst_tmem), "l"(src_desc) : "memory");
+  }
+}
+
 // Arrive on `bar` (this CTA) once every MMA issued so far by this thread has finished.
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");

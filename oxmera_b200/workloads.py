@@ -51,7 +51,7 @@ class Workload:
 
     @property
     def result_dtype(self) -> DType:
-        return self.out_dtype or self.dtype
+        return self.dtype if self.out_dtype is None else self.out_dtype
 
     def spec(self, name: str) -> TensorSpec:
         return next(t for t in self.tensors if t.name == name)

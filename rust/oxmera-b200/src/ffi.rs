@@ -113,6 +113,7 @@ extern "C" {
     pub fn oxm_matmul(ctx: *mut oxm_ctx, a: *const oxm_view, b: *const oxm_view, out: *const oxm_view) -> c_int;
     pub fn oxm_batched_matmul(ctx: *mut oxm_ctx, a: *const oxm_view, b: *const oxm_view, out: *const oxm_view) -> c_int;
     pub fn oxm_matmul_fused(ctx: *mut oxm_ctx, a: *const oxm_view, b: *const oxm_view, out: *const oxm_view, ep: *const oxm_epilogue) -> c_int;
+    pub fn oxm_matmul_mx(ctx: *mut oxm_ctx, a: *const oxm_view, a_scale: *const oxm_view, b: *const oxm_view, b_scale: *const oxm_view, out: *const oxm_view) -> c_int;
     pub fn oxm_unary(ctx: *mut oxm_ctx, op: c_int, a: *const oxm_view, out: *const oxm_view) -> c_int;
     pub fn oxm_binary(ctx: *mut oxm_ctx, op: c_int, a: *const oxm_view, b: *const oxm_view, out: *const oxm_view) -> c_int;
     pub fn oxm_reduce(ctx: *mut oxm_ctx, op: c_int, a: *const oxm_view, axes: *const i32, naxes: c_int, out: *const oxm_view) -> c_int;

@@ -249,6 +249,30 @@ impl B200Backend {
         Ok(out)
     }
 
+    /// The block-scaled fp8 product (MXFP8): `lhs_scale` `[.., M, K/32]` and
+    /// `rhs_scale` `[.., K/32, N]` are U8 tensors of E8M0 exponents, one per 32
+    /// contraction elements of every row of `lhs` and column of `rhs`.
+    pub fn matmul_mx(&self, lhs: &Tensor, lhs_scale: &Tensor, rhs: &Tensor, rhs_scale: &Tensor, out_dtype: DType) -> Result<Tensor> {
+        let op = "matmul_mx";
+        let (a, b) = (self.view(lhs, op)?, self.view(rhs, op)?);
+        let (sa, sb) = (self.view(lhs_scale, op)?, self.view(rhs_scale, op)?);
+        let (ld, rd) = (lhs.shape().dims(), rhs.shape().dims());
+        if ld.len() < 2 || rd.len() < 2 {
+            return Err(Error::ShapeMismatch { expected: lhs.shape().clone(), got: rhs.shape().clone(), op });
+        }
+        let lead = broadcast_shapes(&Shape::new(ld[..ld.len() - 2].to_vec()), &Shape::new(rd[..rd.len() - 2].to_vec()))?;
+        let mut dims = lead.dims().to_vec();
+        dims.push(ld[ld.len() - 2]);
+        dims.push(rd[rd.len() - 1]);
+        let out = self.empty(Shape::new(dims), out_dtype)?;
+        let o = self.view(&out, op)?;
+        let st = unsafe { ffi::oxm_matmul_mx(self.raw(), &a, &sa, &b, &sb, &o) };
+        if st != ffi::OXM_OK {
+            return Err(self.fail(st, op, Some(lhs), Some(rhs)));
+        }
+        Ok(out)
+    }
+
     /// `act(lhs . rhs + bias)`, optionally added into `accumulate_into`
     /// (gradient accumulation), in one kernel.
     pub fn matmul_fused(&self, lhs: &Tensor, rhs: &Tensor, bias: Option<&Tensor>, activation: i32, accumulate_into: Option<&Tensor>) -> Result<Tensor> {

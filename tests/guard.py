@@ -100,7 +100,7 @@ def guarded_matmul(backend, a: Tensor, b: Tensor, batched: bool | None = None, l
     if batched is None:
         batched = not (len(a.shape) == 2 and len(b.shape) == 2)
     shape = tuple(broadcast_shapes(a.shape[:-2], b.shape[:-2])) + (a.shape[-2], b.shape[-1])
-    g = Guarded(backend, shape, out_dtype or a.dtype, layout, aligned)
+    g = Guarded(backend, shape, a.dtype if out_dtype is None else out_dtype, layout, aligned)  # DType.F32 is 0: no `or`
     if call is not None:
         call(g.view)
     else:

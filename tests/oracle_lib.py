@@ -15,8 +15,9 @@ F32, F64, BF16, F16 = 0, 1, 6, 7
 F8E4M3, F8E5M2 = 8, 9
 ACC_NATIVE, ACC_F64 = 0, 1
 I32, I64 = 2, 3
+U8 = 4
 _NP = {F32: np.float32, F64: np.float64, I32: np.int32, I64: np.int64, BF16: np.uint16, F16: np.float16,
-       F8E4M3: np.uint8, F8E5M2: np.uint8}
+       F8E4M3: np.uint8, F8E5M2: np.uint8, U8: np.uint8}
 _SIZE = {F32: 4, F64: 8, 2: 4, 3: 8, 4: 1, 5: 1, BF16: 2, F16: 2, F8E4M3: 1, F8E5M2: 1}
 
 
@@ -54,6 +55,7 @@ class Oracle:
         self.lib.orc_batched_matmul.argtypes = [PV, PV, PV, C.c_int, C.c_int]
         self.lib.orc_check_matmul.argtypes = [PV, PV, PV, C.c_int]
         self.lib.orc_matmul_fused.argtypes = [PV, PV, PV, PV, C.c_int, C.c_int, C.c_int, C.c_int]
+        self.lib.orc_matmul_mx.argtypes = [PV, PV, PV, PV, PV]
         self.lib.orc_unary.argtypes = [C.c_int, PV, PV]
         self.lib.orc_binary.argtypes = [C.c_int, PV, PV, PV]
         self.lib.orc_reduce.argtypes = [C.c_int, PV, C.POINTER(C.c_int32), C.c_int, PV]
@@ -100,6 +102,15 @@ class Oracle:
         vbias = _view(bias, tag) if bias is not None else None
         st = self.lib.orc_matmul_fused(C.byref(va), C.byref(vb), C.byref(vo), C.byref(vbias) if vbias is not None else None,
                                        act, 1 if prev is not None else 0, acc, nthreads or self.threads)
+        return st, out
+
+    def matmul_mx(self, a, a_scale, b, b_scale, tag):
+        """The block-scaled fp8 product in double: a, b fp8 bytes; a_scale
+        [.., M, K/32] and b_scale [.., K/32, N] E8M0 bytes."""
+        lead = np.broadcast_shapes(a.shape[:-2], b.shape[:-2])
+        out = np.zeros(tuple(lead) + (a.shape[-2], b.shape[-1]), dtype=np.float64)
+        va, vsa, vb, vsb, vo = _view(a, tag), _view(a_scale, U8), _view(b, tag), _view(b_scale, U8), _view(out, F64)
+        st = self.lib.orc_matmul_mx(C.byref(va), C.byref(vsa), C.byref(vb), C.byref(vsb), C.byref(vo))
         return st, out
 
     def unary(self, op: int, a: np.ndarray, tag: int):
