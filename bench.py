@@ -49,7 +49,7 @@ sys.path.insert(0, ROOT)
 
 from oxmera_b200 import B200Backend, DType, Tensor, broadcast_shapes  # noqa: E402
 from oxmera_b200.dist import init_from_env  # noqa: E402
-from oxmera_b200.workloads import WORKLOADS, device_fill, gemm_views, materialise, shard_flops  # noqa: E402
+from oxmera_b200.workloads import WORKLOADS, device_fill, gemm_views, materialise, mx_scales, shard_flops  # noqa: E402
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the tcgen05 GEMM
 # on each workload, from the ncu captures summarised under profiles/.
@@ -168,7 +168,7 @@ def cpu_reference(workload_key: str, steps: int, warmup: int, target_s: float = 
     tag = {DType.F32: F32, DType.BF16: BF16, DType.F16: F16, DType.F8E4M3: 8, DType.F8E5M2: 9}
     w = WORKLOADS[workload_key]
     o = Oracle()
-    cores = o.threads
+    cores = 1 if w.mx else o.threads  # the block-scaled port is a plain single-threaded loop
     # a first guess of the slab from a tiny probe of the first product
     slabs = []
     for g in w.gemms:
@@ -184,6 +184,13 @@ def cpu_reference(workload_key: str, steps: int, warmup: int, target_s: float = 
         inputs = [o.fill((rows, k), tag[w.dtype], w.seed, sa.stream, sa.dist, sa.scale) for _, k, _, sa, _ in slabs]
         flops, t0 = 0, time.perf_counter()  # data generation stays outside the timed part
         for (g, k, n, sa, b_view), a_rows in zip(slabs, inputs):
+            if w.mx:
+                rng = np.random.default_rng(rows)
+                st, _ = o.matmul_mx(a_rows, rng.integers(124, 131, size=(rows, k // 32), dtype=np.uint8), b_view,
+                                    rng.integers(124, 131, size=(k // 32, n), dtype=np.uint8), tag[w.dtype])
+                assert st == 0
+                flops += 2 * rows * k * n
+                continue
             st, _ = o.matmul(a_rows, b_view, tag[w.dtype], acc=ACC_NATIVE, nthreads=cores)
             assert st == 0
             flops += 2 * rows * k * n
@@ -255,7 +262,7 @@ def decode_fp8(bits: np.ndarray, dtype: DType) -> np.ndarray:
     return table[np.asarray(bits, np.uint8)]
 
 
-def verify_shard(w, work, oracle_fp8=None) -> dict:
+def verify_shard(w, work, oracle_fp8=None, scales=None) -> dict:
     """Size-independent check of this rank's outputs, in float64 on the host:
     for every product C = A.B of the shard, C.1 against A.(B.1) and 1^T.C against
     (1^T.A).B over the WHOLE shard.  A rank that multiplied the wrong rows, read
@@ -268,6 +275,10 @@ def verify_shard(w, work, oracle_fp8=None) -> dict:
         ha, hb, ho = a.to_host(), b.to_host(), out.to_host()
         if w.dtype in (DType.F8E4M3, DType.F8E5M2):
             ha, hb = oracle_fp8(ha), oracle_fp8(hb)
+            if scales is not None:  # block-scaled: every 32 of K carry a power of two
+                sa, sb = scales[work.index((g, a, b, out))]
+                ha = ha * np.repeat(np.ldexp(np.float32(1), sa.to_host().astype(np.int32) - 127), 32, axis=-1)
+                hb = hb * np.repeat(np.ldexp(np.float32(1), sb.to_host().astype(np.int32) - 127), 32, axis=-2)
         else:
             ha, hb = _host_f32(ha, w.dtype), _host_f32(hb, w.dtype)
         ho = _host_f32(ho, w.result_dtype)
@@ -397,7 +408,12 @@ def measure_brief(be, grp, w, rank, world, steps=10, warmup=3):
         a, b, _ = gemm_views(w, g, tensors, rank, world)
         oshape = tuple(broadcast_shapes(a.shape[:-2], b.shape[:-2])) + (a.shape[-2], b.shape[-1])
         work.append((a, b, Tensor.empty(oshape, w.result_dtype, be)))
-    calls = [be.prepare_matmul(a, b, out, batched=True) for a, b, out in work]  # views marshalled once
+    if w.mx:
+        sc = mx_scales(w, be)
+        calls = [be.prepare_matmul_mx(a, sa, b, sb, out)
+                 for (a, b, out), (sa, sb) in zip(work, [gemm_views(w, g, sc, rank, world)[:2] for g in w.gemms])]
+    else:
+        calls = [be.prepare_matmul(a, b, out, batched=True) for a, b, out in work]  # views marshalled once
     for _ in range(warmup):
         for call in calls:
             call()
@@ -436,7 +452,13 @@ def run_ours(args):
         work.append((g, a, b, out))
     be.synchronize()
 
-    calls = [be.prepare_matmul(a, b, out, batched=True) for _, a, b, out in work]  # views marshalled once
+    scales = None
+    if w.mx:
+        sc = mx_scales(w, be)
+        scales = [gemm_views(w, g, sc, srank, sworld)[:2] for g in w.gemms]
+        calls = [be.prepare_matmul_mx(a, sa, b, sb, out) for (_, a, b, out), (sa, sb) in zip(work, scales)]
+    else:
+        calls = [be.prepare_matmul(a, b, out, batched=True) for _, a, b, out in work]  # views marshalled once
 
     def step():
         for call in calls:
@@ -448,7 +470,7 @@ def run_ours(args):
     fp8 = None
     if w.dtype in (DType.F8E4M3, DType.F8E5M2):
         fp8 = lambda bits: decode_fp8(bits, w.dtype)
-    check = verify_shard(w, work, fp8)
+    check = verify_shard(w, work, fp8, scales)
     all_ok = grp.min_over_ranks(1.0 if check["ok"] else 0.0) > 0.5
     worst_check = grp.max_over_ranks(check["worst_over_budget"])
     if not all_ok:
@@ -625,7 +647,7 @@ def run_ours(args):
         others = {}
         for opt, val in (("cta_pair", -1), ("tile_n", 0), ("group_m", 0)):
             be.set_option(opt, val)  # the library's own choices, whatever the main run forced
-        for key in ("c1", "c2", "c4", "c5"):
+        for key in ("c1", "c2", "c4", "c5", "c3f8", "c3mx"):
             if key == w.key:
                 continue
             others[key] = measure_brief(be, grp, WORKLOADS[key], rank, world)

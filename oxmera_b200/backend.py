@@ -141,12 +141,27 @@ class B200Backend:
         exponent (a U8) per 32 contraction elements of every row of lhs and
         column of rhs.  Shapes broadcast as in batched_matmul; the result is
         a fresh tensor of `out_dtype`."""
-        bshape = broadcast_shapes(lhs.shape[:-2], rhs.shape[:-2]) if lhs.ndim >= 2 and rhs.ndim >= 2 else ()
-        rows = lhs.shape[-2] if lhs.ndim >= 2 else 0
-        cols = rhs.shape[-1] if rhs.ndim >= 1 else 0
+        if len(lhs.shape) < 2 or len(rhs.shape) < 2:
+            raise ShapeMismatch(lhs.shape, rhs.shape, "matmul_mx", "expected operands of rank >= 2")
+        bshape = broadcast_shapes(lhs.shape[:-2], rhs.shape[:-2])
+        rows, cols = lhs.shape[-2], rhs.shape[-1]
         out = Tensor.empty(tuple(bshape) + (rows, cols), out_dtype, self)
         self.matmul_mx_into(lhs, lhs_scale, rhs, rhs_scale, out)
         return out
+
+    def prepare_matmul_mx(self, lhs: Tensor, lhs_scale: Tensor, rhs: Tensor, rhs_scale: Tensor, out: Tensor):
+        """`matmul_mx_into` with the views marshalled once (see prepare_matmul)."""
+        views = [t._view() for t in (lhs, lhs_scale, rhs, rhs_scale, out)]
+        ptrs = [C.byref(v) for v in views]
+        fn, ctx = self._lib.oxm_matmul_mx, self._ctx
+        keep = (views, lhs, lhs_scale, rhs, rhs_scale, out)
+
+        def submit(_keep=keep):
+            st = fn(ctx, *ptrs)
+            if st != capi.OK:
+                _raise(st, "matmul_mx", lhs, rhs)
+
+        return submit
 
     def matmul_mx_into(self, lhs: Tensor, lhs_scale: Tensor, rhs: Tensor, rhs_scale: Tensor, out: Tensor) -> None:
         st = self._lib.oxm_matmul_mx(self._ctx, C.byref(lhs._view()), C.byref(lhs_scale._view()), C.byref(rhs._view()),

@@ -254,8 +254,10 @@ int launch_simt(oxm_ctx *ctx, const Problem &P) {
   p.a = P.a; p.b = P.b; p.out = P.o;
   p.dtype = P.dtype; p.out_dtype = P.out_dtype;
   p.M = (int32_t)P.M; p.N = (int32_t)P.N; p.K = (int32_t)P.K;
-  // 64-wide tiles, or 32-wide ones when those would leave most SMs idle
-  int ts = (((P.M + 63) / 64) * ((P.N + 63) / 64) * P.nbatch < 2 * (int64_t)ctx->num_sms) ? 32 : 64;
+  // 64-wide tiles wherever they can occupy half of the SMs, alone or with the contraction of
+  // each tile split over a cluster of up to 8 CTAs; 32-wide tiles for outputs smaller than that.
+  const int64_t tiles64 = ((P.M + 63) / 64) * ((P.N + 63) / 64) * P.nbatch;
+  int ts = tiles64 * 8 >= ctx->num_sms / 2 ? 64 : 32;
   if (ctx->opt_simt_tile == 32 || ctx->opt_simt_tile == 64) ts = (int)ctx->opt_simt_tile;
   p.tiles_m = (int32_t)((P.M + ts - 1) / ts); p.tiles_n = (int32_t)((P.N + ts - 1) / ts);
   p.a_off = P.a_off; p.b_off = P.b_off; p.o_off = P.o_off;
@@ -267,10 +269,12 @@ int launch_simt(oxm_ctx *ctx, const Problem &P) {
   p.epi = P.epi;
   const int64_t tiles = (int64_t)p.tiles_m * p.tiles_n * P.nbatch;
   // Too few tiles for the SMs and a contraction worth cutting: a cluster of 2, 4 or 8 CTAs per
-  // tile, each with at least 64 elements of k.
+  // tile - as many as still fit the GPU in one wave (two CTAs per SM) with at least one staged
+  // block of k each (2048 / ts elements).  Measured on a 256 x 512 x 384 f32 product: 64-wide
+  // tiles in clusters of 8 take 14.4 us, clusters of 4 18.5, 32-wide tiles 16.4 at best.
   int ksplit = 1;
   if (ctx->opt_split_k != 0)
-    while (ksplit < 8 && tiles * ksplit * 2 <= 4 * (int64_t)ctx->num_sms && P.K / (ksplit * 2) >= 64) ksplit *= 2;
+    while (ksplit < 8 && tiles * ksplit * 2 <= 2 * (int64_t)ctx->num_sms && P.K / (ksplit * 2) >= 2048 / ts) ksplit *= 2;
   if (ctx->opt_split_k == 2 || ctx->opt_split_k == 4 || ctx->opt_split_k == 8)  // forced: a cluster of that many CTAs per tile
     ksplit = (int)std::min<int64_t>(ctx->opt_split_k, std::max<int64_t>(1, P.K / 16));
   p.ksplit = ksplit;
@@ -900,17 +904,30 @@ int launch_mx(oxm_ctx *ctx, const Problem &P, const oxm_view *a_scale, const int
   st = stage_scale_atoms(ctx, P, true, b_scale, sb_bs, 4, &sf[1], &sf_nb);
   if (st) return st;
 
-  // The wide pair tile, 256 or 384 columns (whole 128-column scale atoms; the 32 columns of
-  // tensor memory above 480 hold the scales): whichever leaves fewer idle pair-waves.
+  // Tile widths of this kind: the MMA takes B's scales from the tensor-memory column its address
+  // names, one column per 32 columns of B, and that address must be even: a tile that starts 32
+  // or 96 columns into a 128-column scale atom, or a second sub-tile that starts an odd number of
+  // 32-column groups after the first (width 320), is refused by the hardware with "misaligned
+  // address" (seen on widths 160, 224 and 320; 128, 192, 256 and 384 run).  A tile's columns may
+  // touch at most three atoms.  So: 128 or 192 columns for the two-accumulator tile, 256 or 384
+  // for the one-accumulator tile (two MMAs side by side, which read every A stage twice).
+  // Whichever leaves the fewest idle pair-waves wins.
   const int tm = 2 * kTileM;
   const int64_t tiles_m = (P.M + tm - 1) / tm, slots = std::max(1, ctx->num_sms / 2);
+  // Per column of tile width the four shapes measured (8192^3, TFLOP/s): 384: 2175, 256: 1705,
+  // 192: 1655, 128: 1288 - the wider the tile, the fewer scale copies and MMA instructions per flop.
   auto cost = [&](int w) {
     const int64_t tiles = tiles_m * ((P.N + w - 1) / w) * P.nbatch;
-    return (double)((tiles + slots - 1) / slots) * (w + 24);  // a tile's time grows with its width, plus its drain
+    const double per_col = w == 384 ? 1.0 : w == 256 ? 1.28 : w == 192 ? 1.31 : 1.69;
+    return (double)((tiles + slots - 1) / slots) * (w * per_col + 24);  // a tile's time grows with its width, plus its drain
   };
-  int bn = (P.N <= 256 || cost(256) < cost(384)) ? 256 : 384;
-  if (ctx->opt_tile_n == 256 || ctx->opt_tile_n == 384) bn = (int)ctx->opt_tile_n;
-  const int subn = bn / 2, subc = subn / 2;
+  int bn = 384;
+  for (int w : {256, 192, 128})
+    if (cost(w) < cost(bn) * 0.97) bn = w;
+  if (ctx->opt_tile_n == 128 || ctx->opt_tile_n == 192 || ctx->opt_tile_n == 256 || ctx->opt_tile_n == 384) bn = (int)ctx->opt_tile_n;
+  const int cls = bn > 192 ? 512 : 256;
+  const int nsub = cls == 512 ? 2 : 1;
+  const int subn = bn / nsub, subc = subn / 2;
   const int bk = kStageKBytes;  // one byte per element
 
   GemmParams p{};
@@ -941,10 +958,11 @@ int launch_mx(oxm_ctx *ctx, const Problem &P, const oxm_view *a_scale, const int
   p.kb_per_split = p.num_kb;
   p.tiles_per_split = p.num_tiles;
   p.dp_tiles = p.num_tiles;
-  p.group_m = ctx->opt_group_m > 0 ? (int32_t)ctx->opt_group_m : 16;
+  p.group_m = ctx->opt_group_m > 0 ? (int32_t)ctx->opt_group_m : (cls == 512 ? 16 : 8);
   p.epi = P.epi;
   p.sf_mb = sf_mb; p.sf_nb = sf_nb;
-  p.stage_tx = (uint32_t)(kStageKBytes * (kTileM + 2 * subc) + kSfAtomBytes * (1 + bn / 128));
+  // per CTA and stage: its A rows, its share of B, the atom of its rows' scales (the kernel adds B's scale atoms per tile)
+  p.stage_tx = (uint32_t)(kStageKBytes * (kTileM + nsub * subc) + kSfAtomBytes);
 
   CUtensorMap tmA, tmB, tmC;
   memset(&tmC, 0, sizeof(tmC));
@@ -960,7 +978,7 @@ int launch_mx(oxm_ctx *ctx, const Problem &P, const oxm_view *a_scale, const int
   }
   if (ctx->opt_tma_store == 0) p.out_tma = 0;
   const int grid = 2 * (int)std::min<int64_t>(p.num_tiles, slots);
-  st = launch_gemm(ctx, 3, false, false, 512, 1, tmA, tmB, tmC, p, grid, sf);
+  st = launch_gemm(ctx, 3, false, false, cls, 1, tmA, tmB, tmC, p, grid, sf);
   if (st) return st;
   const size_t len = strlen(ctx->last_kernel);
   snprintf(ctx->last_kernel + len, sizeof(ctx->last_kernel) - len, "_w%d", bn);

@@ -100,11 +100,22 @@ struct GemmParams {
 };
 
 // Scales of the block-scaled kind, per stage: one 512-byte atom for this CTA's
-// 128 rows of A, then one per 128 columns of the tile (at most 384) for B.
+// 128 rows of A, then the atoms (128 columns each, aligned to 128 in the
+// matrix) that cover the tile's columns of B: at most three.  Tiles are 128,
+// 192, 256 or 384 columns wide, so a tile (and the second sub-tile of a wide
+// one) starts 0 or 64 columns into an atom and the MMA's scale address is that
+// of the atom's first or third column (an odd column offset is refused by the
+// hardware as a misaligned address).
 constexpr int kSfAtomBytes = 512;
-constexpr int kMxMaxBN = 384;
-constexpr int kSfStageBytes = kSfAtomBytes * (1 + kMxMaxBN / 128);
-constexpr int kSfTmemCols = 16;  // 4 columns for A's scales + up to 12 for B's; two such sets sit at the top of tensor memory
+constexpr int kSfMaxBAtoms = 3;
+constexpr int kSfStageBytes = kSfAtomBytes * (1 + kSfMaxBAtoms);
+constexpr int kSfTmemCols = 16;  // 4 columns for A's scales + 12 for B's: one set
+constexpr int kSfSets = 2;       // sets of scale columns at the top of tensor memory (480..511), taken in turn by stage
+// B rows one CTA of the pair stages per sub-tile in the block-scaled instances: 96.  The
+// two-accumulator tile is at most 192 columns wide (its accumulators sit at columns 0 and 256 of
+// tensor memory), the one-accumulator tile at most 384 (two sub-tiles of 192); both leave columns
+// 480..511 to the scales.
+__host__ __device__ constexpr int mx_subc_cap(int) { return 96; }
 
 // Tensor maps of the scale arrays: present only in the block-scaled instances.
 template <int MX> struct SfMaps {};
@@ -112,8 +123,8 @@ template <> struct SfMaps<1> { CUtensorMap a, b; };
 
 template <int BN, int STAGES, int PAIR, int MX = 0>
 struct GemmSmem {
-  // B rows staged by one CTA (the block-scaled tile is at most 384 columns wide: two sub-tiles of 96 rows per CTA)
-  static constexpr int kBNC = MX ? kMxMaxBN / 2 : PAIR ? BN / 2 : BN;
+  // B rows staged by one CTA
+  static constexpr int kBNC = MX ? mx_subc_cap(BN) * (BN > 256 ? 2 : 1) : PAIR ? BN / 2 : BN;
   static constexpr int kABytes = kTileM * kStageKBytes;
   static constexpr int kBBytes = kBNC * kStageKBytes;
   static constexpr int kStageBytes = kABytes + kBBytes;
@@ -285,7 +296,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     const __grid_constant__ SfMaps<KIND == 3> sfm) {
   constexpr bool MX = KIND == 3;
   static_assert(!(KIND == 1 && (A_MN || B_MN)), "the tf32 path stages K-major operands only");
-  static_assert(!MX || (BN == 512 && PAIR && !A_MN && !B_MN), "the block-scaled kind: wide pair tile, K-major operands");
+  static_assert(!MX || ((BN == 512 || BN == 256) && PAIR && !A_MN && !B_MN), "the block-scaled kind: pair tiles, K-major operands");
   static_assert(BN % 64 == 0 && BN >= 64 && BN <= 512, "tile width");
   static_assert(BN <= 256 || PAIR, "tiles wider than one MMA need the CTA pair");
   static_assert(!PACKED || (BN > 256 && KIND != 1), "the packed drain is the wide tile's, for 16-bit results");
@@ -304,7 +315,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   // loop) while they fit the 512 columns, one otherwise.
   constexpr bool WIDE = BN > 256;
   constexpr int NSUB = WIDE ? 2 : 1;
-  constexpr int SUBC_CAP = MX ? kMxMaxBN / 4 : (BN / NSUB) / (PAIR ? 2 : 1);  // B rows one CTA can stage per sub-tile
+  constexpr int SUBC_CAP = MX ? mx_subc_cap(BN) : (BN / NSUB) / (PAIR ? 2 : 1);  // B rows one CTA can stage per sub-tile
+  // block-scaled kind: the two sets of scale columns, 480..511, above every accumulator (two of
+  // at most 192 columns at 0 and 256, or one of at most 384)
+  constexpr uint32_t SF_COL0 = 512 - kSfSets * kSfTmemCols;
+  constexpr uint32_t SF_SET = kSfTmemCols;
   constexpr int ACC = WIDE ? 1 : 2;
   constexpr int EPI_GROUPS = gemm_epi_groups(BN);
   constexpr int CH = BN >= 128 ? 4 : 2;   // 32-column chunks an epilogue warp drains per wait
@@ -405,7 +420,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           if constexpr (PAIR) {
             // The leader's barrier collects the bytes of both CTAs' loads.
             const uint32_t fb = ptx::mapa_shared(full_bar(s), 0);
-            if (leader) ptx::mbar_arrive_expect_tx(full_bar(s), 2u * p.stage_tx);
+            // (block-scaled kind: plus the atoms of B's scales this tile's columns touch)
+            const int32_t sfb_atoms = MX ? (((tc.n_blk * bn) & 127) + bn + 127) >> 7 : 0;
+            if (leader) ptx::mbar_arrive_expect_tx(full_bar(s), 2u * (p.stage_tx + static_cast<uint32_t>(sfb_atoms) * kSfAtomBytes));
             if constexpr (A_MN) {
 #pragma unroll
               for (int j = 0; j < kTileM / BOXW; ++j)
@@ -431,7 +448,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
               const int32_t ks = tc.kb0 + kb;
               ptx::tma_load_3d_pair(sf, &sfm.a, fb, 0, ks, tc.a_batch * p.sf_mb + (m0 >> 7));
               const int32_t nb0 = tc.b_batch * p.sf_nb + ((tc.n_blk * bn) >> 7);
-              for (int32_t g = 0; g < (bn >> 7); ++g)
+              for (int32_t g = 0; g < sfb_atoms; ++g)
                 ptx::tma_load_3d_pair(sf + kSfAtomBytes * (1 + g), &sfm.b, fb, 0, ks, nb0 + g);
             }
           } else {
@@ -476,18 +493,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       WorkIter it;
       WorkItem wi;
       it.init(p, tile_first, tile_stride);
-      // The four MMAs of one contraction block for sub-tile `sub`, from stage `st`.
-      // Block-scaled kind: stage `st`'s scales go from shared memory to the top columns of tensor
-      // memory (two sets, taken in turn by stage), in order with the MMAs issued around them.
-      // Returns the set's first column: A's scales there, B's from four columns on.
+      // Block-scaled kind: stage `st`'s scales go from shared memory to one of the two sets of
+      // scale columns of tensor memory (taken in turn, so that a copy never waits for the MMAs of
+      // the stage before it, which read the other set), in order with the MMAs issued around
+      // them.  Returns the set's first column: A's scales there, B's from four columns on.
+      int32_t sfb_atoms = 0;    // atoms of B's scales the current tile's columns touch
+      uint32_t sfb_first = 0;   // the tile's first column within the first atom, in 32-column groups
       auto stage_scales = [&](uint32_t st) -> uint32_t {
-        const uint32_t set = tmem_base + static_cast<uint32_t>(BN - 2 * kSfTmemCols) + (st & 1u) * kSfTmemCols;
+        const uint32_t set = tmem_base + SF_COL0 + (st & 1u) * SF_SET;
         const uint32_t sf = base + L::kSfOffset + st * L::kSfStage;
         ptx::tmem_cp_32x128b_x4<PAIR>(set, make_sf_desc(sf));
-        for (int32_t g = 0; g < (bn >> 7); ++g)
+        for (int32_t g = 0; g < sfb_atoms; ++g)
           ptx::tmem_cp_32x128b_x4<PAIR>(set + 4u + 4u * g, make_sf_desc(sf + kSfAtomBytes * (1 + g)));
         return set;
       };
+      // The four MMAs of one contraction block for sub-tile `sub`, from stage `st`.
       auto issue = [&](uint32_t st, int sub, uint32_t d_tmem, int32_t kb) {
         const uint32_t sa = base + st * L::kStageBytes;
         const uint32_t sb = sa + L::kABytes;
@@ -499,7 +519,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           for (int j = 0; j < MMAS; ++j)  // contraction block j of the stage: scale byte j of either operand
             ptx::umma_mx<PAIR>(d_tmem + sub * subn, adesc + static_cast<uint64_t>(j * A_ADV), bdesc + static_cast<uint64_t>(j * B_ADV),
                                p.idesc | (static_cast<uint32_t>(j) << 4) | (static_cast<uint32_t>(j) << 29), set,
-                               set + 4u + static_cast<uint32_t>(sub * (subn >> 5)), (kb | j) != 0 ? 1u : 0u);
+                               set + 4u + sfb_first + static_cast<uint32_t>(sub * (subn >> 5)), (kb | j) != 0 ? 1u : 0u);
         } else {
 #pragma unroll
           for (int j = 0; j < MMAS; ++j)
@@ -516,6 +536,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         if (nkb < 0) {
           const int32_t split = static_cast<int32_t>(wi.tile / p.tiles_per_split);
           nkb = min(p.kb_per_split, p.num_kb - split * p.kb_per_split);
+        }
+        if constexpr (MX) {
+          const int32_t tile_n0 = decode_item(p, wi).n_blk * bn;
+          sfb_atoms = ((tile_n0 & 127) + bn + 127) >> 7;
+          sfb_first = static_cast<uint32_t>((tile_n0 & 127) >> 5);
         }
         if (!bounded_wait(tempty_bar(WIDE ? 0 : as), aph ^ 1u, wc)) break;
         ptx::tc_fence_after();
@@ -560,7 +585,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                   ptx::umma_mx<PAIR>(d_tmem + sub * subn, adesc + static_cast<uint64_t>(j * A_ADV),
                                      bdesc + static_cast<uint64_t>(j * B_ADV + sub * B_SUB),
                                      p.idesc | (static_cast<uint32_t>(j) << 4) | (static_cast<uint32_t>(j) << 29), set,
-                                     set + 4u + static_cast<uint32_t>(sub * (subn >> 5)), (kb | j) != 0 ? 1u : 0u);
+                                     set + 4u + sfb_first + static_cast<uint32_t>(sub * (subn >> 5)), (kb | j) != 0 ? 1u : 0u);
               }
             } else {
 #pragma unroll

@@ -66,13 +66,27 @@ struct SimtParams {
 
 // TS x TS output tile per 256-thread CTA (TS = 64: 4 x 4 per thread; TS = 32:
 // 2 x 2 per thread, for products with too few 64-wide tiles to fill the GPU).
+//
+// The contraction is staged in blocks of BK = 2048 / TS elements (64 for the
+// small tile): one block is 8 elements of each operand per thread, fetched into
+// registers while the previous block is being multiplied, so a CTA that owns
+// 128 elements of k (the usual share when a cluster splits the contraction)
+// synchronises four times in all.  Per thread, the addresses of its 8 elements
+// differ by a constant, so the loop adds one stride per block and no index is
+// rebuilt.  Every output element accumulates its products in ascending k, and a
+// cluster's partial tiles are added in rank order: the result does not depend
+// on the tile size or on who does the adding.
 template <int TS>
 __global__ void __launch_bounds__(256) gemm_simt_kernel(const SimtParams p) {
-  constexpr int BK = 16, TT = TS / 16, PER_THREAD = TS * BK / 256;
-  // rows of TS + 4 floats keep every thread's TT consecutive values 4 TT-byte aligned: one vector load each
-  __shared__ __align__(16) float As[BK][TS + 4];
-  __shared__ __align__(16) float Bs[BK][TS + 4];
-  __shared__ float red[TS][TS + 1];  // a CTA's partial tile, read by the first CTA of its cluster
+  constexpr int BK = 2048 / TS, TT = TS / 16, PER_THREAD = 8;
+  static_assert(TS * BK == 256 * PER_THREAD, "eight elements of each operand per thread and block");
+  // Row pitch: a multiple of the vector load's width that is not a multiple of 32 banks (a
+  // k-fastest operand is written one column at a time: 2 floats of padding keep that to two-way
+  // conflicts for the small tile, 4 floats to four-way for the large one).
+  constexpr int PITCH = TS + (TT == 4 ? 4 : 2);
+  __shared__ __align__(16) float As[BK][PITCH];
+  __shared__ __align__(16) float Bs[BK][PITCH];
+  __shared__ __align__(16) float red[TS][PITCH];  // a CTA's partial tile, read by the other CTAs of its cluster
 
   const int32_t krank = p.ksplit > 1 ? static_cast<int32_t>(blockIdx.x % p.ksplit) : 0;
   const int64_t tile = p.ksplit > 1 ? blockIdx.x / p.ksplit : blockIdx.x;
@@ -100,97 +114,101 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const SimtParams p) {
 #pragma unroll
     for (int j = 0; j < TT; ++j) acc[i][j] = 0.f;
 
-  // This thread's elements of a TS x 16 block of A and a 16 x TS block of B;
-  // the faster-varying thread index follows the operand's unit stride.
-  // PF blocks are in flight at any time: the loads of block i + PF are issued
-  // as soon as block i has moved from registers to shared memory.  (Four in
-  // flight measured slower than two: the extra registers cost more than the
-  // deeper queue gains.)
-  constexpr int PF = 2;
+  // Element r of this thread in a block of A (TS rows x BK of k) is e = tid + 256 r; the faster
+  // index of e follows the operand's unit stride, so a warp reads consecutive addresses.
+  //   k fastest:   row = e / BK = row0 + (256 / BK) r,  k = e % BK = kk0          (the same k for every r)
+  //   row fastest: row = e % TS = row0,                 k = e / TS = kk0 + (256 / TS) r
   const bool a_kfast = p.a_cs == 1, b_kfast = p.b_rs == 1;
-  float ra[PF][PER_THREAD], rb[PF][PER_THREAD];
-  auto fetch = [&](float (&fa)[PER_THREAD], float (&fb)[PER_THREAD], int32_t k0) {
+  const int a_row0 = a_kfast ? threadIdx.x / BK : threadIdx.x % TS, a_kk0 = a_kfast ? threadIdx.x % BK : threadIdx.x / TS;
+  const int b_col0 = b_kfast ? threadIdx.x / BK : threadIdx.x % TS, b_kk0 = b_kfast ? threadIdx.x % BK : threadIdx.x / TS;
+  const int a_drow = a_kfast ? 256 / BK : 0, a_dk = a_kfast ? 0 : 256 / TS;
+  const int b_dcol = b_kfast ? 256 / BK : 0, b_dk = b_kfast ? 0 : 256 / TS;
+  const int64_t a_step = static_cast<int64_t>(a_drow) * p.a_rs + static_cast<int64_t>(a_dk) * p.a_cs;  // from element r to r + 1
+  const int64_t b_step = static_cast<int64_t>(b_dcol) * p.b_cs + static_cast<int64_t>(b_dk) * p.b_rs;
+  int64_t a_idx = a_off + static_cast<int64_t>(m0 + a_row0) * p.a_rs + static_cast<int64_t>(k_begin + a_kk0) * p.a_cs;
+  int64_t b_idx = b_off + static_cast<int64_t>(n0 + b_col0) * p.b_cs + static_cast<int64_t>(k_begin + b_kk0) * p.b_rs;
+  const int64_t a_blk = static_cast<int64_t>(BK) * p.a_cs, b_blk = static_cast<int64_t>(BK) * p.b_rs;  // from block to block
+  const bool f32 = p.dtype == 0;
+
+  float ra[PER_THREAD], rb[PER_THREAD];
+  auto fetch = [&](int32_t k0) {
 #pragma unroll
     for (int r = 0; r < PER_THREAD; ++r) {
-      const int e = threadIdx.x + r * 256;
-      {
-        const int mm = a_kfast ? (e >> 4) : (e % TS), kk = a_kfast ? (e & 15) : (e / TS);
-        const int32_t gm = m0 + mm, gk = k0 + kk;
-        fa[r] = (gm < p.M && gk < k_end) ? load_elem(p.a, p.dtype, a_off + gm * p.a_rs + gk * p.a_cs) : 0.f;
-      }
-      {
-        const int nn = b_kfast ? (e >> 4) : (e % TS), kk = b_kfast ? (e & 15) : (e / TS);
-        const int32_t gn = n0 + nn, gk = k0 + kk;
-        fb[r] = (gn < p.N && gk < k_end) ? load_elem(p.b, p.dtype, b_off + gk * p.b_rs + gn * p.b_cs) : 0.f;
+      const bool a_ok = m0 + a_row0 + r * a_drow < p.M && k0 + a_kk0 + r * a_dk < k_end;
+      const bool b_ok = n0 + b_col0 + r * b_dcol < p.N && k0 + b_kk0 + r * b_dk < k_end;
+      if (f32) {
+        ra[r] = a_ok ? __ldg(static_cast<const float *>(p.a) + a_idx + r * a_step) : 0.f;
+        rb[r] = b_ok ? __ldg(static_cast<const float *>(p.b) + b_idx + r * b_step) : 0.f;
+      } else {
+        ra[r] = a_ok ? load_elem(p.a, p.dtype, a_idx + r * a_step) : 0.f;
+        rb[r] = b_ok ? load_elem(p.b, p.dtype, b_idx + r * b_step) : 0.f;
       }
     }
+    a_idx += a_blk;
+    b_idx += b_blk;
   };
+  if (k_begin < k_end) fetch(k_begin);
+  for (int32_t k0 = k_begin; k0 < k_end; k0 += BK) {
 #pragma unroll
-  for (int f = 0; f < PF; ++f)
-    if (k_begin + f * BK < k_end) fetch(ra[f], rb[f], k_begin + f * BK);
-  for (int32_t kg = k_begin; kg < k_end; kg += PF * BK) {
-#pragma unroll
-    for (int f = 0; f < PF; ++f) {
-      const int32_t k0 = kg + f * BK;
-      if (k0 >= k_end) break;
-#pragma unroll
-      for (int r = 0; r < PER_THREAD; ++r) {
-        const int e = threadIdx.x + r * 256;
-        As[a_kfast ? (e & 15) : (e / TS)][a_kfast ? (e >> 4) : (e % TS)] = ra[f][r];
-        Bs[b_kfast ? (e & 15) : (e / TS)][b_kfast ? (e >> 4) : (e % TS)] = rb[f][r];
-      }
-      __syncthreads();
-      if (k0 + PF * BK < k_end) fetch(ra[f], rb[f], k0 + PF * BK);
-#pragma unroll
-      for (int kk = 0; kk < BK; ++kk) {
-        // With scalar loads the 2 x 2 tile issues one shared-memory load per FMA and the loads,
-        // not the FMAs, set the kernel's time.
-        float av[TT], bv[TT];
-        if constexpr (TT == 4) {
-          const float4 a4 = *reinterpret_cast<const float4 *>(&As[kk][ty * TT]);
-          const float4 b4 = *reinterpret_cast<const float4 *>(&Bs[kk][tx * TT]);
-          av[0] = a4.x; av[1] = a4.y; av[2] = a4.z; av[3] = a4.w;
-          bv[0] = b4.x; bv[1] = b4.y; bv[2] = b4.z; bv[3] = b4.w;
-        } else {
-          const float2 a2 = *reinterpret_cast<const float2 *>(&As[kk][ty * TT]);
-          const float2 b2 = *reinterpret_cast<const float2 *>(&Bs[kk][tx * TT]);
-          av[0] = a2.x; av[1] = a2.y;
-          bv[0] = b2.x; bv[1] = b2.y;
-        }
-#pragma unroll
-        for (int i = 0; i < TT; ++i)
-#pragma unroll
-          for (int j = 0; j < TT; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
-      }
-      __syncthreads();
+    for (int r = 0; r < PER_THREAD; ++r) {
+      As[a_kk0 + r * a_dk][a_row0 + r * a_drow] = ra[r];
+      Bs[b_kk0 + r * b_dk][b_col0 + r * b_dcol] = rb[r];
     }
-  }
-
-  if (p.ksplit > 1) {
-    if (krank != 0) {
+    __syncthreads();
+    if (k0 + BK < k_end) fetch(k0 + BK);  // in flight while this block is multiplied
+    const int kmax = min(BK, k_end - k0);  // rows beyond it hold zeros or the previous block: skipped
+#pragma unroll 8
+    for (int kk = 0; kk < kmax; ++kk) {
+      // one vector load per operand: with scalar loads the 2 x 2 tile issues a load per FMA
+      float av[TT], bv[TT];
+      if constexpr (TT == 4) {
+        const float4 a4 = *reinterpret_cast<const float4 *>(&As[kk][ty * TT]);
+        const float4 b4 = *reinterpret_cast<const float4 *>(&Bs[kk][tx * TT]);
+        av[0] = a4.x; av[1] = a4.y; av[2] = a4.z; av[3] = a4.w;
+        bv[0] = b4.x; bv[1] = b4.y; bv[2] = b4.z; bv[3] = b4.w;
+      } else {
+        const float2 a2 = *reinterpret_cast<const float2 *>(&As[kk][ty * TT]);
+        const float2 b2 = *reinterpret_cast<const float2 *>(&Bs[kk][tx * TT]);
+        av[0] = a2.x; av[1] = a2.y;
+        bv[0] = b2.x; bv[1] = b2.y;
+      }
 #pragma unroll
       for (int i = 0; i < TT; ++i)
 #pragma unroll
-        for (int j = 0; j < TT; ++j) red[ty * TT + i][tx * TT + j] = acc[i][j];
+        for (int j = 0; j < TT; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
     }
+    __syncthreads();
+  }
+
+  if (p.ksplit > 1) {
+    // Every CTA of the cluster leaves its partial tile in its own shared memory; CTA r then adds
+    // up and stores the rows r, r + ksplit, ... of the tile, taking the partial sums in rank
+    // order (its own included) so that the result is the one a single adder would produce.
+#pragma unroll
+    for (int i = 0; i < TT; ++i)
+#pragma unroll
+      for (int j = 0; j < TT; ++j) red[ty * TT + i][tx * TT + j] = acc[i][j];
     ptx::cluster_arrive();
-    ptx::cluster_wait();  // every CTA's partial tile is in its shared memory
-    if (krank == 0) {
-      for (int r = 1; r < p.ksplit; ++r) {
-#pragma unroll
-        for (int i = 0; i < TT; ++i)
-#pragma unroll
-          for (int j = 0; j < TT; ++j) {
-            const uint32_t remote = ptx::mapa_shared(ptx::smem_u32(&red[ty * TT + i][tx * TT + j]), static_cast<uint32_t>(r));
-            float v;
-            asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
-            acc[i][j] += v;
-          }
+    ptx::cluster_wait();
+    for (int e = threadIdx.x; e < TS * TS; e += 256) {
+      const int row = e / TS, col = e % TS;
+      if (row % p.ksplit != krank) continue;
+      const int32_t gm = m0 + row, gn = n0 + col;
+      if (gm >= p.M || gn >= p.N) continue;
+      float sum = 0.f;
+      const uint32_t local = ptx::smem_u32(&red[row][col]);
+      for (int r = 0; r < p.ksplit; ++r) {
+        float v;
+        asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(ptx::mapa_shared(local, static_cast<uint32_t>(r))) : "memory");
+        sum = r == 0 ? v : sum + v;
       }
+      const int64_t idx = o_off + gm * p.o_rs + gn * p.o_cs;
+      if (p.epi.any) sum = apply_epilogue(p.epi, sum, gn, p.out, p.out_dtype, idx);
+      store_elem(p.out, p.out_dtype, idx, sum);
     }
     ptx::cluster_arrive();
     ptx::cluster_wait();  // nobody leaves while its shared memory may still be read
-    if (krank != 0) return;
+    return;
   }
 
 #pragma unroll

@@ -48,6 +48,7 @@ class Workload:
     tensors: Tuple[TensorSpec, ...]
     gemms: Tuple[GemmSpec, ...]
     out_dtype: Optional[DType] = None  # fp8 products may be kept wider than their operands
+    mx: bool = False  # block-scaled: every base tensor (contraction dim last) comes with E8M0 scales, one per 32 of K
 
     @property
     def result_dtype(self) -> DType:
@@ -125,13 +126,34 @@ WORKLOADS: Dict[str, Workload] = {
 }
 
 
+WORKLOADS["c3mx"] = Workload(
+    "c3mx", "MXFP8: fp8 e4m3 8192^3 with one E8M0 scale per 32 of K (exponents 124..130), A row-major, B column-major, "
+            "N(0,1), fp32 accumulate, bf16 out, seed 2",
+    DType.F8E4M3, 2,
+    (_t("A", (8192, 8192), "normal", 1.0, 0), _t("Bt", (8192, 8192), "normal", 1.0, 1)),
+    (GemmSpec("C", "A", None, "Bt", (1, 0), 0),), DType.BF16, mx=True)
+
+
+def mx_scales(w: Workload, backend) -> Dict[str, Tensor]:
+    """The E8M0 scale tensor of every base tensor of a block-scaled workload
+    (shape: the tensor's with its last dim / 32), seeded, generated on the
+    host: exponents 124..130, i.e. scales 1/8 .. 8."""
+    import numpy as np
+    out = {}
+    for t in w.tensors:
+        shape = tuple(t.shape[:-1]) + (t.shape[-1] // 32,)
+        host = np.random.default_rng(1000 * w.seed + t.stream).integers(124, 131, size=shape, dtype=np.uint8)
+        out[t.name] = Tensor.from_host(host, shape, DType.U8, backend)
+    return out
+
+
 def scaled(w: Workload, factor: int) -> Workload:
     """The same workload with every extent above 64 divided by `factor`
     (tests: oracle-sized versions of the large configurations)."""
     shr = lambda s: tuple(max(64, d // factor) if d > 64 else d for d in s)
     return Workload(w.key + f"/{factor}", w.title + f" (extents / {factor})", w.dtype, w.seed,
                     tuple(TensorSpec(t.name, shr(t.shape), t.dist, t.scale, t.stream) for t in w.tensors), w.gemms,
-                    w.out_dtype)
+                    w.out_dtype, w.mx)
 
 
 Fill = Callable[[TensorSpec, DType, int], Tensor]
