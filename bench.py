@@ -82,6 +82,7 @@ class ClockSampler(threading.Thread):
         self.samples = []  # (t, sm_mhz, reasons)
         self.max_mhz = None
         self._halt = threading.Event()
+        self._pause = threading.Event()
         self.ok = False
         try:
             import pynvml
@@ -114,6 +115,9 @@ class ClockSampler(threading.Thread):
             return
         nv = self.nv
         while not self._halt.is_set():
+            if self._pause.is_set():
+                time.sleep(0.01)
+                continue
             try:
                 mhz = nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)
                 try:
@@ -131,6 +135,14 @@ class ClockSampler(threading.Thread):
 
     def stop(self):
         self._halt.set()
+
+    def pause(self):
+        """Stop sampling for a while: the sampling thread competes with a launch-bound Python loop
+        for the interpreter (a 14 us-per-launch loop measured 21 us beside it)."""
+        self._pause.set()
+
+    def resume(self):
+        self._pause.clear()
 
     def summary(self, t0: float, t1: float):
         if not self.ok:
@@ -513,6 +525,29 @@ def run_ours(args):
     rep_ms = [ms]
     for _ in range(max(0, args.repeats - 1)):
         rep_ms.append(timed(args.steps)[1])
+    # ---- the other configurations, briefly, so one run shows them all ----
+    # After the burst regions and a two-second pause, before the seconds-long leg below: ten
+    # launches each on a GPU that is neither cold nor at its power cap.  The order matters on a
+    # 1 kW part: right after the sustained leg the same ten launches of c5 read 1250-1270 TFLOP/s
+    # instead of 1480-1540, and right after the c3 bursts (no pause) the latency-bound c1 reads
+    # 21 us per launch instead of 14-15.
+    others = None
+    if alone:
+        args.no_e2e = args.no_cpu = args.no_others = True
+    if not args.no_others:
+        others = {}
+        sampler.pause()
+        time.sleep(2.0)
+        for opt, val in (("cta_pair", -1), ("tile_n", 0), ("group_m", 0)):
+            be.set_option(opt, val)  # the library's own choices, whatever the main run forced
+        for key in ("c1", "c2", "c4", "c5", "c3f8", "c3mx"):
+            if key == w.key:
+                continue
+            others[key] = measure_brief(be, grp, WORKLOADS[key], rank, world)
+        for opt, val in (("cta_pair", args.cta_pair), ("tile_n", args.tile_n), ("group_m", args.group_m)):
+            be.set_option(opt, val)
+        sampler.resume()
+
     # launches back to back for two seconds and more, with the clock samples of this leg only
     n_sus = int(max(args.steps, min(200000, np.ceil(args.sustained_s * 1e3 / max(min(rep_ms) / args.steps, 1e-3))))) if args.sustained_s > 0 else 0
     sustained = None
@@ -603,8 +638,6 @@ def run_ours(args):
             buf = be.pinned_empty(t.shape, npdt)
             buf[...] = t.to_host()
             host[name] = buf
-    if alone:
-        args.no_e2e = args.no_cpu = args.no_others = True
     if not args.no_e2e and w.result_dtype == w.dtype and world > 1:
         e_steps = max(2, min(args.steps, args.e2e_steps))
         e_ms, h2d, d2h = e2e_sharded(be, grp, w, work, tensors, host, e_steps)
@@ -640,17 +673,6 @@ def run_ours(args):
                "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h), "steps": e_steps,
                "ms_per_step": e_ms / e_steps,
                "note": "per-rank bytes; pinned host memory; oxm_batched_matmul_host per product"}
-
-    # ---- the other configurations, briefly, so one run shows all five ----
-    others = None
-    if not args.no_others:
-        others = {}
-        for opt, val in (("cta_pair", -1), ("tile_n", 0), ("group_m", 0)):
-            be.set_option(opt, val)  # the library's own choices, whatever the main run forced
-        for key in ("c1", "c2", "c4", "c5", "c3f8", "c3mx"):
-            if key == w.key:
-                continue
-            others[key] = measure_brief(be, grp, WORKLOADS[key], rank, world)
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu:

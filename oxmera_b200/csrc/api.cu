@@ -839,9 +839,10 @@ int launch_tcgen05(oxm_ctx *ctx, const Problem &P) {
 // ---------------------------------------------------------------------------
 
 // Regroup one operand's scale view into atoms in workspace `slot` and describe them to the TMA
-// engine as {128 words, stages, batch x row groups}.
+// engine as {128 words, row groups, stages, batch}; a load takes one atom (A) or three
+// neighbouring row groups' atoms (B: all that a tile's columns can touch).
 int stage_scale_atoms(oxm_ctx *ctx, const Problem &P, bool is_b, const oxm_view *sv, const int64_t *sv_bs, int slot,
-                      CUtensorMap *tm, int32_t *row_groups) {
+                      CUtensorMap *tm) {
   const int64_t rows = is_b ? P.N : P.M, kblocks = P.K / 32;
   SfParams sp{};
   sp.src = static_cast<const uint8_t *>(sv->base);
@@ -871,14 +872,14 @@ int stage_scale_atoms(oxm_ctx *ctx, const Problem &P, bool is_b, const oxm_view 
   mx_scale_atoms_kernel<<<(unsigned)blocks, 256, 0, ctx->stream>>>(sp);
   CUDA_TRY(cudaGetLastError());
   ctx->launches[0]++; ctx->launches[3]++;
-  cuuint64_t dims[3] = {128, (cuuint64_t)sp.stages, (cuuint64_t)(nb * sp.row_groups)};
-  cuuint64_t strides[2] = {(cuuint64_t)kSfAtomBytes, (cuuint64_t)kSfAtomBytes * (cuuint64_t)sp.stages};
-  cuuint32_t box[3] = {128, 1, 1};
-  cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = ctx->encode(tm, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, sp.dst, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+  cuuint64_t dims[4] = {128, (cuuint64_t)sp.row_groups, (cuuint64_t)sp.stages, (cuuint64_t)nb};
+  cuuint64_t strides[3] = {(cuuint64_t)kSfAtomBytes, (cuuint64_t)kSfAtomBytes * (cuuint64_t)sp.row_groups,
+                           (cuuint64_t)kSfAtomBytes * (cuuint64_t)sp.row_groups * (cuuint64_t)sp.stages};
+  cuuint32_t box[4] = {128, is_b ? (cuuint32_t)kSfMaxBAtoms : 1u, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = ctx->encode(tm, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, sp.dst, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                            CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(OXM_CUDA_ERROR, "cuTensorMapEncodeTiled failed (%d) for the scale atoms", (int)r);
-  *row_groups = sp.row_groups;
   return OXM_OK;
 }
 
@@ -898,10 +899,9 @@ int launch_mx(oxm_ctx *ctx, const Problem &P, const oxm_view *a_scale, const int
     if (st) return st;
   }
   CUtensorMap sf[2];
-  int32_t sf_mb = 0, sf_nb = 0;
-  int st = stage_scale_atoms(ctx, P, false, a_scale, sa_bs, 3, &sf[0], &sf_mb);
+  int st = stage_scale_atoms(ctx, P, false, a_scale, sa_bs, 3, &sf[0]);
   if (st) return st;
-  st = stage_scale_atoms(ctx, P, true, b_scale, sb_bs, 4, &sf[1], &sf_nb);
+  st = stage_scale_atoms(ctx, P, true, b_scale, sb_bs, 4, &sf[1]);
   if (st) return st;
 
   // Tile widths of this kind: the MMA takes B's scales from the tensor-memory column its address
@@ -960,9 +960,8 @@ int launch_mx(oxm_ctx *ctx, const Problem &P, const oxm_view *a_scale, const int
   p.dp_tiles = p.num_tiles;
   p.group_m = ctx->opt_group_m > 0 ? (int32_t)ctx->opt_group_m : (cls == 512 ? 16 : 8);
   p.epi = P.epi;
-  p.sf_mb = sf_mb; p.sf_nb = sf_nb;
-  // per CTA and stage: its A rows, its share of B, the atom of its rows' scales (the kernel adds B's scale atoms per tile)
-  p.stage_tx = (uint32_t)(kStageKBytes * (kTileM + nsub * subc) + kSfAtomBytes);
+  // per CTA and stage: its A rows, its share of B, the atom of its rows' scales and three atoms of B's
+  p.stage_tx = (uint32_t)(kStageKBytes * (kTileM + nsub * subc) + kSfAtomBytes * (1 + kSfMaxBAtoms));
 
   CUtensorMap tmA, tmB, tmC;
   memset(&tmC, 0, sizeof(tmC));

@@ -95,7 +95,6 @@ struct GemmParams {
   uint32_t *sk_flags;     // [run][cta of the pair][8 epilogue warps]: the launch counter of the last publication
   uint32_t sk_epoch;      // this launch's counter value (never 0)
   int32_t group_m;        // tile rows walked together (L2 reuse)
-  int32_t sf_mb, sf_nb;   // block-scaled kind: 128-row scale atoms per batch entry of A and of B
   Epilogue epi;           // applied here unless the contraction is split (then by the reduction)
 };
 
@@ -420,9 +419,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           if constexpr (PAIR) {
             // The leader's barrier collects the bytes of both CTAs' loads.
             const uint32_t fb = ptx::mapa_shared(full_bar(s), 0);
-            // (block-scaled kind: plus the atoms of B's scales this tile's columns touch)
-            const int32_t sfb_atoms = MX ? (((tc.n_blk * bn) & 127) + bn + 127) >> 7 : 0;
-            if (leader) ptx::mbar_arrive_expect_tx(full_bar(s), 2u * (p.stage_tx + static_cast<uint32_t>(sfb_atoms) * kSfAtomBytes));
+            // (block-scaled kind: stage_tx counts the scale atoms too, which warp 2 loads)
+            if (leader) ptx::mbar_arrive_expect_tx(full_bar(s), 2u * p.stage_tx);
             if constexpr (A_MN) {
 #pragma unroll
               for (int j = 0; j < kTileM / BOXW; ++j)
@@ -440,16 +438,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
               } else {
                 ptx::tma_load_3d_pair(sbs, &tmB, fb, k0, ns, tc.b_batch);
               }
-            }
-            if constexpr (MX) {
-              // this stage's scales: the atom of this CTA's 128 rows of A, and those of ALL the tile's
-              // columns (each CTA of the pair multiplies its rows by every column)
-              const uint32_t sf = base + L::kSfOffset + s * L::kSfStage;
-              const int32_t ks = tc.kb0 + kb;
-              ptx::tma_load_3d_pair(sf, &sfm.a, fb, 0, ks, tc.a_batch * p.sf_mb + (m0 >> 7));
-              const int32_t nb0 = tc.b_batch * p.sf_nb + ((tc.n_blk * bn) >> 7);
-              for (int32_t g = 0; g < sfb_atoms; ++g)
-                ptx::tma_load_3d_pair(sf + kSfAtomBytes * (1 + g), &sfm.b, fb, 0, ks, nb0 + g);
             }
           } else {
             const uint32_t fb = full_bar(s);
@@ -617,6 +605,42 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       }
     }
     __syncwarp();
+  } else if (MX && warp == 2) {
+    // ---------------- scale producer (block-scaled kind) ----------------
+    // The third warp of the producer warpgroup loads every stage's scale atoms: the atom of this
+    // CTA's 128 rows of A, and the three atoms from the one the tile's first column lies in on
+    // for B (each CTA of the pair multiplies its rows by ALL the tile's columns, so both load
+    // them; atoms beyond the matrix read as zeros).  It walks the same tiles and stages as the
+    // TMA warp and waits on the same "stage empty" barriers; its bytes are counted on the same
+    // "stage full" barrier.  (With these loads on the TMA warp, seven copies per stage from one
+    // thread, the stages arrived too slowly for the tensor pipe.)
+    if constexpr (MX) {
+    if (lane == 0) {
+      uint32_t s = 0, ph = 0;
+      bool ok = true;
+      WorkIter it;
+      WorkItem wi;
+      it.init(p, tile_first, tile_stride);
+      while (ok && it.next(p, wi)) {
+        const TileCoord tc = decode_item(p, wi);
+        const int32_t rg_a = (tc.m_blk * TM + static_cast<int32_t>(cta_rank) * kTileM) >> 7;
+        const int32_t rg_b = (tc.n_blk * bn) >> 7;
+        for (int32_t kb = 0; kb < tc.nkb; ++kb) {
+          if (!bounded_wait(empty_bar(s), ph ^ 1u, wc)) { ok = false; break; }
+          const uint32_t fb = ptx::mapa_shared(full_bar(s), 0);
+          const uint32_t sf = base + L::kSfOffset + s * L::kSfStage;
+          ptx::tma_load_4d_pair(sf, &sfm.a, fb, 0, rg_a, tc.kb0 + kb, tc.a_batch);
+          ptx::tma_load_4d_pair(sf + kSfAtomBytes, &sfm.b, fb, 0, rg_b, tc.kb0 + kb, tc.b_batch);
+          if (++s == STAGES) { s = 0; ph ^= 1u; }
+        }
+      }
+      if (*abort_flag) {
+        const uint64_t t0 = ptx::globaltimer_ns();
+        while (ptx::globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+      }
+    }
+    __syncwarp();
+    }
   }
   } else {
     // ---------------- epilogue: TMEM -> registers -> global ----------------

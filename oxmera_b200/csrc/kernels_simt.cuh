@@ -156,9 +156,10 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const SimtParams p) {
     }
     __syncthreads();
     if (k0 + BK < k_end) fetch(k0 + BK);  // in flight while this block is multiplied
-    const int kmax = min(BK, k_end - k0);  // rows beyond it hold zeros or the previous block: skipped
-#pragma unroll 8
-    for (int kk = 0; kk < kmax; ++kk) {
+    // all BK steps, whatever is left of k: the fetch wrote zeros beyond k_end, and a loop of known
+    // length lets the compiler run the shared-memory loads well ahead of the FMAs that use them
+#pragma unroll
+    for (int kk = 0; kk < BK; ++kk) {
       // one vector load per operand: with scalar loads the 2 x 2 tile issues a load per FMA
       float av[TT], bv[TT];
       if constexpr (TT == 4) {
@@ -195,13 +196,20 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const SimtParams p) {
       if (row % p.ksplit != krank) continue;
       const int32_t gm = m0 + row, gn = n0 + col;
       if (gm >= p.M || gn >= p.N) continue;
-      float sum = 0.f;
+      // all the remote loads first, then the additions: a load followed by the addition that needs
+      // it would hold the next load back for a full trip through distributed shared memory
       const uint32_t local = ptx::smem_u32(&red[row][col]);
-      for (int r = 0; r < p.ksplit; ++r) {
-        float v;
-        asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(ptx::mapa_shared(local, static_cast<uint32_t>(r))) : "memory");
-        sum = r == 0 ? v : sum + v;
+      float v[8];
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        v[r] = 0.f;
+        if (r < p.ksplit)
+          asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v[r]) : "r"(ptx::mapa_shared(local, static_cast<uint32_t>(r))) : "memory");
       }
+      float sum = v[0];
+#pragma unroll
+      for (int r = 1; r < 8; ++r)
+        if (r < p.ksplit) sum += v[r];
       const int64_t idx = o_off + gm * p.o_rs + gn * p.o_cs;
       if (p.epi.any) sum = apply_epilogue(p.epi, sum, gn, p.out, p.out_dtype, idx);
       store_elem(p.out, p.out_dtype, idx, sum);
@@ -260,7 +268,9 @@ struct PackParams {
 // out) are regrouped into the 512-byte atoms the tensor core's scale copy
 // takes: atom (batch, r / 128, kb / 4) holds, at byte (r % 32) * 16 +
 // (r % 128) / 32 * 4 + kb % 4, the scale of row r and block kb.  Atoms are
-// ordered [batch][row group][stage]; positions beyond the operand hold 0x7F
+// ordered [batch][stage][row group] (the atoms of neighbouring row groups at
+// one stage lie side by side: one load fetches all a tile needs); positions
+// beyond the operand hold 0x7F
 // (2^0), which only ever multiplies the zeros the loads fill in there.
 // ---------------------------------------------------------------------------
 struct SfParams {
@@ -280,10 +290,10 @@ __global__ void __launch_bounds__(256) mx_scale_atoms_kernel(const SfParams p) {
        w += static_cast<int64_t>(gridDim.x) * blockDim.x) {
     const int32_t within = static_cast<int32_t>(w & 127);
     int64_t atom = w >> 7;
-    const int32_t stage = static_cast<int32_t>(atom % p.stages);
-    atom /= p.stages;
     const int32_t rg = static_cast<int32_t>(atom % p.row_groups);
-    int64_t batch = atom / p.row_groups;
+    atom /= p.row_groups;
+    const int32_t stage = static_cast<int32_t>(atom % p.stages);
+    int64_t batch = atom / p.stages;
     const int32_t r = rg * 128 + (within & 3) * 32 + (within >> 2);
     int64_t off = p.src_off;
     for (int d = p.nbd - 1; d >= 0; --d) {

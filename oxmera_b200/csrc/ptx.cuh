@@ -124,6 +124,16 @@ __device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap
       : "memory");
 }
 
+// The 4-D form of the pair load (the scale atoms of the block-scaled product: word, row group, stage, batch).
+__device__ __forceinline__ void tma_load_4d_pair(uint32_t dst, const CUtensorMap *tm, uint32_t bar,
+                                                 int32_t c0, int32_t c1, int32_t c2, int32_t c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tm)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+
 // 3-D tiled store from this CTA's shared memory; completion is tracked by the
 // issuing thread's bulk async-group.  The engine clips the box at the tensor's edge.
 __device__ __forceinline__ void tma_store_3d(const CUtensorMap *tm, uint32_t src, int32_t c0, int32_t c1, int32_t c2) {
