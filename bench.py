@@ -429,10 +429,16 @@ def measure_brief(be, grp, w, rank, world, steps=10, warmup=3):
     for _ in range(warmup):
         for call in calls:
             call()
-    # three regions of `steps` steps: under the power cap a region can land in a slower phase of the
-    # clock (c5 alternates between about 1480 and 1340 TFLOP/s from one region to the next)
+    # Three bursts of `steps` steps, each after half a second of idle: the burst regime `value` is
+    # measured in.  On a 1 kW part the clock follows the last ~100 ms of load: back to back with
+    # other work the same ten steps of c5 read 1250-1340 TFLOP/s, after a short idle 1480-1540 (the
+    # sustained regime is reported for the main workload, `roofline.sustained`).
     regions = []
     for _ in range(3):
+        be.synchronize()
+        time.sleep(0.5)
+        for call in calls:  # one step to wake the clocks
+            call()
         be.synchronize()
         grp.barrier()
         timer = be.timer()
@@ -532,12 +538,7 @@ def run_ours(args):
     for _ in range(max(0, args.repeats - 1)):
         rep_ms.append(timed(args.steps)[1])
     # ---- the other configurations, briefly, so one run shows them all ----
-    # Ten launches each, before the seconds-long leg below.  The order matters on a 1 kW part whose
-    # clock follows the last seconds of load: the tensor-bound ones run right after the burst
-    # regions, in the regime `value` was measured in (after the sustained leg, or after a pause,
-    # the same ten launches of c5 read 1250-1340 TFLOP/s instead of 1480-1540); the two
-    # latency-bound f32 ones run after a two-second pause (right after the bursts c1 read 21 us
-    # per launch instead of 14-15, c2 169-215 TFLOP/s instead of 234-241).
+    # Bursts of ten steps each (median of three, see measure_brief), before the seconds-long leg below.
     others = None
     if alone:
         args.no_e2e = args.no_cpu = args.no_others = True
@@ -546,15 +547,10 @@ def run_ours(args):
         sampler.pause()
         for opt, val in (("cta_pair", -1), ("tile_n", 0), ("group_m", 0)):
             be.set_option(opt, val)  # the library's own choices, whatever the main run forced
-        paused = False
-        for key in ("c4", "c5", "c3f8", "c3mx", "c1", "c2"):
+        for key in ("c1", "c2", "c4", "c5", "c3f8", "c3mx"):
             if key == w.key:
                 continue
-            if key in ("c1", "c2") and not paused:
-                time.sleep(2.0)
-                paused = True
             others[key] = measure_brief(be, grp, WORKLOADS[key], rank, world)
-        others = {k: others[k] for k in ("c1", "c2", "c4", "c5", "c3f8", "c3mx") if k in others}
         for opt, val in (("cta_pair", args.cta_pair), ("tile_n", args.tile_n), ("group_m", args.group_m)):
             be.set_option(opt, val)
         sampler.resume()
@@ -602,11 +598,12 @@ def run_ours(args):
         clocks.get("sm_mhz") and clocks.get("sm_max_mhz") and clocks["sm_mhz"] < 0.85 * clocks["sm_max_mhz"]) or (
         clocks.get("power_w") and clocks.get("power_limit_w") and clocks["power_w"] >= 0.9 * clocks["power_limit_w"])
     capped = bool(capped)
-    # NVML's clock and power readings lag by up to a second on these hosts, so a
-    # region of more than 50 ms of back-to-back launches counts as sustained
-    # whatever they say: a 42 ms region still ran at the uncapped rate here,
-    # regions of 150 ms at the capped one.
-    burst = not capped and timed_s < 0.05
+    # NVML's clock and power readings lag by up to a second on these hosts, so the length of the
+    # region decides: under 50 ms of back-to-back launches it is held against the burst figure
+    # (the higher, i.e. stricter, denominator - also when the samples around it show the cap,
+    # which then only says that the GPU was still warm from what ran before); a longer region
+    # ran at the capped rate in every run here and is held against the sustained figure.
+    burst = timed_s < 0.05
     scale = 0.5 if w.dtype == DType.F32 else 2.0 if w.dtype in (DType.F8E4M3, DType.F8E5M2) else 1.0
     # f32: tf32 runs at half the bf16 rate (and the 3-term split spends 3 MMA flops per useful one);
     # fp8: no figure was measured, twice the measured bf16 rate, as the nominal rates relate

@@ -119,6 +119,28 @@ def test_batched_and_broadcast(backend, oracle):
     assert rel_err(fresh.to_host(), ref) <= TOL[DType.F32]
 
 
+@pytest.mark.parametrize("dtype", [DType.F8E4M3, DType.F8E5M2], ids=lambda d: d.name)
+def test_fp8_output_rounds_once(backend, oracle, dtype):
+    """The product kept in the operands' own 8-bit type: one rounding of the
+    fp32 sum, at most one fp8 ulp from the oracle's value, saturated rather
+    than infinite."""
+    m, n, k = 200, 300, 256
+    rng = np.random.default_rng(17)
+    a = oracle.fill((m, k), TAG[dtype], 24, 0, "normal", 0.5)
+    bt = oracle.fill((n, k), TAG[dtype], 24, 1, "normal", 0.5)
+    sa, sbt = scales(rng, (m, k // 32), 124, 128), scales(rng, (n, k // 32), 124, 128)
+    st, ref = oracle.matmul_mx(a, sa, bt.T, sbt.T, TAG[dtype])
+    assert st == 0
+    got = mx(backend, dev(backend, a, dtype), dev(backend, sa, DType.U8), dev(backend, bt, dtype).permute([1, 0]),
+             dev(backend, sbt, DType.U8).permute([1, 0]), dtype)
+    g = oracle.fp8_to_f32(got, TAG[dtype]).astype(np.float64)
+    assert np.all(np.isfinite(g))
+    big = 448.0 if dtype == DType.F8E4M3 else 57344.0
+    rms = float(np.sqrt(np.mean(ref * ref)))
+    ulp = 2.0 ** -3 if dtype == DType.F8E4M3 else 2.0 ** -2
+    assert np.max(np.abs(g - np.clip(ref, -big, big)) / np.maximum(np.abs(ref), rms)) <= ulp
+
+
 def test_nan_scale_poisons_its_row_only(backend):
     m, n, k = 128, 256, 64
     a = np.full((m, k), 0x38, np.uint8)
