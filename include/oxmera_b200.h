@@ -272,12 +272,14 @@ int oxm_selftest_bounded_wait(oxm_ctx *ctx, int64_t limit_ms);
  *   "kernel"      0 auto, 1 force the SIMT FFMA kernel, 2 force the tcgen05
  *                 kernel (packing operands it cannot address directly)
  *   "tile_n"      0 auto, else the tile's width: a multiple of 32 from 64 to 512
- *                 (288 and wider: CTA pairs only)
+ *                 (288 and wider: CTA pairs only).  oxm_matmul_mx takes 128, 192,
+ *                 256 or 384 from it and ignores other values
  *   "cta_pair"    -1 auto, 0 one CTA per tile, 1 CTA pairs (cta_group::2)
  *   "host_chunks" slices of the host entry point's copy/compute pipeline:
  *                 0 auto (up to 8 for outputs of 16 MiB or more), 1 off, 2..16
  *   "split_k"     -1 auto, 0 never split beyond what f32 accuracy needs, else
- *                 the number of contraction chains
+ *                 the number of contraction chains (the FFMA kernel takes 2, 4
+ *                 or 8 from it: CTAs of a cluster per tile)
  *   "tma_store"   1 (default) write results with bulk tensor stores when the
  *                 output allows it, 0 always use plain strided stores
  *   "group_m"     0 auto, else the number of tile rows walked together
