@@ -57,7 +57,8 @@ from oxmera_b200.workloads import WORKLOADS, device_fill, gemm_views, materialis
 # share of A, so the figure does not scale with the shard and is not reported at N > 1.
 NCU_TRAFFIC_BYTES = {
     "c3": 972_272_896,     # the 256 x 512 pair kernel (gemm_tcgen05_pair512_c3_bf16_8192.md)
-    "c3f8": 460_873_216,   # gemm_tcgen05_f8_c3f8_8192.md
+    "c3f8": 446_797_056,   # gemm_tcgen05_mxf8_c3mx_8192.md (the plain fp8 column)
+    "c3mx": 431_382_528,   # gemm_tcgen05_mxf8_c3mx_8192.md
     "c2": 1_324_522_280,   # the tf32x3 GEMM alone; the two pack launches add 161 MB (gemm_tcgen05_tf32x3_c2.md)
     "c5": 2_121_017_088 // 3,  # mean of the three launches of a step (gemm_tcgen05_c5_linear_fwd_bwd.md)
 }
