@@ -31,19 +31,21 @@ namespace oxmera {
 // ---------------------------------------------------------------- core ----
 
 // crates/oxmera-core/src/dtype.rs:9-22, plus the two 16-bit floats the backend adds.
-enum class DType : int32_t { F32 = 0, F64 = 1, I32 = 2, I64 = 3, U8 = 4, Bool = 5, BF16 = 6, F16 = 7 };
+enum class DType : int32_t { F32 = 0, F64 = 1, I32 = 2, I64 = 3, U8 = 4, Bool = 5, BF16 = 6, F16 = 7, F8E4M3 = 8, F8E5M2 = 9 };
 
 inline size_t size_in_bytes(DType d) {
   switch (d) {
     case DType::F32: case DType::I32: return 4;
     case DType::F64: case DType::I64: return 8;
-    case DType::U8: case DType::Bool: return 1;
+    case DType::U8: case DType::Bool: case DType::F8E4M3: case DType::F8E5M2: return 1;
     default: return 2;
   }
 }
-inline bool is_float(DType d) { return d == DType::F32 || d == DType::F64 || d == DType::BF16 || d == DType::F16; }
+inline bool is_float(DType d) {
+  return d == DType::F32 || d == DType::F64 || d == DType::BF16 || d == DType::F16 || d == DType::F8E4M3 || d == DType::F8E5M2;
+}
 inline const char *dtype_name(DType d) {
-  static const char *n[] = {"F32", "F64", "I32", "I64", "U8", "Bool", "BF16", "F16"};
+  static const char *n[] = {"F32", "F64", "I32", "I64", "U8", "Bool", "BF16", "F16", "F8E4M3", "F8E5M2"};
   return n[static_cast<int>(d)];
 }
 
@@ -595,6 +597,34 @@ class B200Backend : public Backend {
     const int st = oxm_matmul_fused(ctx_, &a, &b, &o, &ep);
     if (st != OXM_OK) {
       Error e = from_status(st, "matmul_fused", lhs.device(), rhs.device());
+      e.expected = lhs.shape(); e.got = rhs.shape();
+      return e;
+    }
+    return out;
+  }
+
+  // The block-scaled fp8 product (MXFP8; no counterpart in the reference's traits): fp8 operands,
+  // one E8M0 exponent (a U8) per 32 contraction elements of every row of lhs ([M, K/32]) and
+  // column of rhs ([K/32, N]).
+  Result<Tensor> matmul_mx(const Tensor &lhs, const Tensor &lhs_scale, const Tensor &rhs, const Tensor &rhs_scale, DType out_dtype) {
+    for (const Tensor *t : {&lhs, &lhs_scale, &rhs, &rhs_scale}) {
+      if (!(t->device() == device())) {
+        Error e{Error::Kind::DeviceMismatch};
+        e.lhs_device = t->device(); e.rhs_device = device(); e.op = "matmul_mx";
+        return e;
+      }
+    }
+    if (lhs.shape().ndim() != 2 || rhs.shape().ndim() != 2) {
+      Error e{Error::Kind::NotImplemented};
+      e.op = "matmul_mx"; e.detail = "operands of rank other than 2";
+      return e;
+    }
+    Result<Tensor> out = empty(Shape{lhs.shape().dims()[0], rhs.shape().dims()[1]}, out_dtype);
+    if (out.is_err()) return out;
+    oxm_view a = view(lhs), sa = view(lhs_scale), b = view(rhs), sb = view(rhs_scale), o = view(out.unwrap());
+    const int st = oxm_matmul_mx(ctx_, &a, &sa, &b, &sb, &o);
+    if (st != OXM_OK) {
+      Error e = from_status(st, "matmul_mx", lhs.device(), rhs.device());
       e.expected = lhs.shape(); e.got = rhs.shape();
       return e;
     }

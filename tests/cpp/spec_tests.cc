@@ -322,6 +322,19 @@ int main(int argc, char **argv) {
     expect_tensor(h, fused, {0, 22, 13, 50}, Shape{2, 2});
     Tensor acc = fused.unwrap();
     expect_tensor(h, gpu->matmul_fused(a, b, nullptr, OXM_ACT_NONE, &acc), {19, 44, 56, 100}, Shape{2, 2});
+    // the block-scaled fp8 product: ones (e4m3 0x38) times ones over K = 64, row 1 of A scaled by 2
+    // in its second block, column 2 of B by 1/2 in its first; B is the transposed view of an [N, K] tensor
+    {
+      const size_t M = 2, N = 3, K = 64;
+      std::vector<uint8_t> ones_a(M * K, 0x38), ones_b(N * K, 0x38), sa = {127, 127, 127, 128}, sbt = {127, 127, 127, 127, 126, 127};
+      Tensor ma = gpu->from_host(ones_a.data(), Shape{M, K}, DType::F8E4M3).unwrap();
+      Tensor mbt = gpu->from_host(ones_b.data(), Shape{N, K}, DType::F8E4M3).unwrap();
+      Tensor msa = gpu->from_host(sa.data(), Shape{M, K / 32}, DType::U8).unwrap();
+      Tensor msbt = gpu->from_host(sbt.data(), Shape{N, K / 32}, DType::U8).unwrap();
+      auto prod = gpu->matmul_mx(ma, msa, mbt.permute({1, 0}).unwrap(), msbt.permute({1, 0}).unwrap(), DType::F32);
+      expect_tensor(h, prod, {64, 64, 48, 96, 96, 80}, Shape{M, N});
+      CHECK(gpu->matmul_mx(a, msa, b, msbt, DType::F32).unwrap_err().kind == Error::Kind::UnsupportedDType);
+    }
     unregister_all();
   }
   std::printf("%s: %d checks, %d failed\n", mode.c_str(), g_checks, g_failed);
