@@ -15,7 +15,9 @@ from concurrent.futures import ThreadPoolExecutor
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "build")
-SOURCES = ["api.cu", "gemm_f16_ak.cu", "gemm_f16_am.cu", "gemm_f8_ak.cu", "gemm_f8_am.cu", "gemm_tf32.cu", "gemm_mx.cu"]
+# the longest units first: they decide the wall time of a parallel build
+SOURCES = ["gemm_f16_kk.cu", "gemm_f16_kn.cu", "gemm_f16_mk.cu", "gemm_f16_mn.cu", "gemm_f8_kk.cu", "gemm_f8_kn.cu", "gemm_f8_mk.cu",
+           "gemm_f8_mn.cu", "gemm_tf32.cu", "api.cu", "gemm_mx.cu"]
 OUT = os.path.join(HERE, "liboxmera_b200.so")
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC"]

@@ -481,8 +481,8 @@ int launch_gemm(oxm_ctx *ctx, int kind, bool a_mn, bool b_mn, int bn, int pair, 
   const GemmLaunch l{bn, pair, packed, b_mn, grid, ctx->stream, sf};
   const GemmLaunchFn fn = kind == 1 ? launch_gemm_tf32
                           : kind == 3 ? launch_gemm_mx
-                          : kind == 2 ? (a_mn ? launch_gemm_f8_am : launch_gemm_f8_ak)
-                                      : (a_mn ? launch_gemm_f16_am : launch_gemm_f16_ak);
+                          : kind == 2 ? (a_mn ? (b_mn ? launch_gemm_f8_mn : launch_gemm_f8_mk) : (b_mn ? launch_gemm_f8_kn : launch_gemm_f8_kk))
+                                      : (a_mn ? (b_mn ? launch_gemm_f16_mn : launch_gemm_f16_mk) : (b_mn ? launch_gemm_f16_kn : launch_gemm_f16_kk));
   cudaError_t e = fn(l, tmA, tmB, tmC, p, ctx->last_kernel, sizeof(ctx->last_kernel));
   if (e != cudaSuccess) {
     cudaGetLastError();  // a refused launch also parks its error for the next caller of cudaGetLastError: take it away

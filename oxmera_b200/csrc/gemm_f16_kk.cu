@@ -2,5 +2,5 @@
 #include "gemm_instances.cuh"
 
 namespace oxm {
-OXM_DEFINE_GEMM_LAUNCH(launch_gemm_f8_ak, 0, 2, 1)
+OXM_DEFINE_GEMM_LAUNCH(launch_gemm_f16_kk, 0, 0, 0)
 }  // namespace oxm

@@ -2,5 +2,5 @@
 #include "gemm_instances.cuh"
 
 namespace oxm {
-OXM_DEFINE_GEMM_LAUNCH(launch_gemm_f16_am, 1, 0, 1)
+OXM_DEFINE_GEMM_LAUNCH(launch_gemm_f16_mk, 1, 0, 0)
 }  // namespace oxm

@@ -2,5 +2,5 @@
 #include "gemm_instances.cuh"
 
 namespace oxm {
-OXM_DEFINE_GEMM_LAUNCH(launch_gemm_f8_am, 1, 2, 1)
+OXM_DEFINE_GEMM_LAUNCH(launch_gemm_f8_mk, 1, 0, 2)
 }  // namespace oxm

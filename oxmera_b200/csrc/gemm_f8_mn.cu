@@ -2,5 +2,5 @@
 #include "gemm_instances.cuh"
 
 namespace oxm {
-OXM_DEFINE_GEMM_LAUNCH(launch_gemm_f16_ak, 0, 0, 1)
+OXM_DEFINE_GEMM_LAUNCH(launch_gemm_f8_mn, 1, 1, 2)
 }  // namespace oxm

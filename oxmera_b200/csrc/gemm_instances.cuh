@@ -1,7 +1,7 @@
 // Instantiation and launch of the tensor-core GEMM.  The kernel template has
 // some sixty useful instantiations; they are spread over several translation
-// units (one per operand type and A-operand major) so that they compile in
-// parallel.  Each unit defines one launch function with this signature.
+// units (one per operand type and pair of operand majors) so that they compile
+// in parallel.  Each unit defines one launch function with this signature.
 #pragma once
 
 #include <cuda_runtime.h>
@@ -15,7 +15,7 @@ namespace oxm {
 struct GemmLaunch {
   int bn, pair;      // the instance's widest tile; CTA pairs
   bool packed;       // bn = 512: the epilogue that packs its share into registers before storing (16-bit results, whole tiles)
-  bool b_mn;         // B is MN-major (A's major is fixed per translation unit)
+  bool b_mn;         // B is MN-major (both majors are fixed per translation unit; kept for the record)
   int grid;
   cudaStream_t stream;
   const CUtensorMap *sf = nullptr;  // block-scaled kind: the maps of A's and B's scale atoms
@@ -29,10 +29,14 @@ typedef cudaError_t (*GemmLaunchFn)(const GemmLaunch &l, const CUtensorMap &tmA,
   cudaError_t NAME(const GemmLaunch &l, const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap &tmC, \
                    const GemmParams &p, char *name, size_t name_len);
 
-OXM_DECLARE_GEMM_LAUNCH(launch_gemm_f16_ak)   // bf16 / f16, A K-major
-OXM_DECLARE_GEMM_LAUNCH(launch_gemm_f16_am)   // bf16 / f16, A M-major
-OXM_DECLARE_GEMM_LAUNCH(launch_gemm_f8_ak)    // fp8, A K-major
-OXM_DECLARE_GEMM_LAUNCH(launch_gemm_f8_am)    // fp8, A M-major
+OXM_DECLARE_GEMM_LAUNCH(launch_gemm_f16_kk)   // bf16 / f16, A K-major, B K-major
+OXM_DECLARE_GEMM_LAUNCH(launch_gemm_f16_kn)   // bf16 / f16, A K-major, B N-major
+OXM_DECLARE_GEMM_LAUNCH(launch_gemm_f16_mk)   // bf16 / f16, A M-major, B K-major
+OXM_DECLARE_GEMM_LAUNCH(launch_gemm_f16_mn)   // bf16 / f16, A M-major, B N-major
+OXM_DECLARE_GEMM_LAUNCH(launch_gemm_f8_kk)    // fp8, the same four
+OXM_DECLARE_GEMM_LAUNCH(launch_gemm_f8_kn)
+OXM_DECLARE_GEMM_LAUNCH(launch_gemm_f8_mk)
+OXM_DECLARE_GEMM_LAUNCH(launch_gemm_f8_mn)
 OXM_DECLARE_GEMM_LAUNCH(launch_gemm_tf32)     // f32 as 3xTF32, packed K-major operands
 OXM_DECLARE_GEMM_LAUNCH(launch_gemm_mx)       // block-scaled fp8 (MX), K-major operands, wide pair tile
 
@@ -85,13 +89,10 @@ cudaError_t launch_shape(const GemmLaunch &l, const CUtensorMap &tmA, const CUte
   return launch_instance<64, 8, A_MN, B_MN, KIND, 0>(l, tmA, tmB, tmC, p, name, name_len);
 }
 
-#define OXM_DEFINE_GEMM_LAUNCH(NAME, A_MN, KIND, ALLOW_B_MN)                                               \
+#define OXM_DEFINE_GEMM_LAUNCH(NAME, A_MN, B_MN, KIND)                                                     \
   cudaError_t NAME(const GemmLaunch &l, const CUtensorMap &tmA, const CUtensorMap &tmB, const CUtensorMap &tmC, \
                    const GemmParams &p, char *name, size_t name_len) {                                     \
-    if constexpr (ALLOW_B_MN) {                                                                            \
-      if (l.b_mn) return launch_shape<A_MN, ALLOW_B_MN, KIND>(l, tmA, tmB, tmC, p, name, name_len);        \
-    }                                                                                                      \
-    return launch_shape<A_MN, 0, KIND>(l, tmA, tmB, tmC, p, name, name_len);                               \
+    return launch_shape<A_MN, B_MN, KIND>(l, tmA, tmB, tmC, p, name, name_len);                            \
   }
 
 }  // namespace oxm

@@ -2,5 +2,5 @@
 #include "gemm_instances.cuh"
 
 namespace oxm {
-OXM_DEFINE_GEMM_LAUNCH(launch_gemm_tf32, 0, 1, 0)
+OXM_DEFINE_GEMM_LAUNCH(launch_gemm_tf32, 0, 0, 1)
 }  // namespace oxm

@@ -11,11 +11,16 @@ use std::process::Command;
 
 const SOURCES: &[&str] = &[
     "api.cu",
-    "gemm_f16_ak.cu",
-    "gemm_f16_am.cu",
-    "gemm_f8_ak.cu",
-    "gemm_f8_am.cu",
+    "gemm_f16_kk.cu",
+    "gemm_f16_kn.cu",
+    "gemm_f16_mk.cu",
+    "gemm_f16_mn.cu",
+    "gemm_f8_kk.cu",
+    "gemm_f8_kn.cu",
+    "gemm_f8_mk.cu",
+    "gemm_f8_mn.cu",
     "gemm_tf32.cu",
+    "gemm_mx.cu",
 ];
 const ARCH: &[&str] = &["-gencode", "arch=compute_100a,code=sm_100a"];
 
