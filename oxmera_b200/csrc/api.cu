@@ -1546,7 +1546,8 @@ int oxm_contiguous(oxm_ctx *ctx, const oxm_view *src, const oxm_view *dst) {
     switch (p.elt) {
       case 1: ew_tile_kernel<uint8_t, 2, true, false><<<tb, 256, 0, ctx->stream>>>(e); break;
       case 2:
-        if (e.pairs) ew_tile2_kernel<uint16_t, 2, true, false><<<tb, 256, 0, ctx->stream>>>(e);
+        if (e.quads) ew_reg2_kernel<uint16_t, 2, true, false><<<tb, 256, 0, ctx->stream>>>(e);
+        else if (e.pairs) ew_tile2_kernel<uint16_t, 2, true, false><<<tb, 256, 0, ctx->stream>>>(e);
         else ew_tile_kernel<uint16_t, 2, true, false><<<tb, 256, 0, ctx->stream>>>(e);
         break;
       case 4: ew_tile_kernel<uint32_t, 2, true, false><<<tb, 256, 0, ctx->stream>>>(e); break;
@@ -1646,6 +1647,10 @@ int dispatch_dtype(int dtype, Args &&...args) {
 template <typename T> struct UnaryLauncher {
   static int run(oxm_ctx *ctx, const EwParams &p, unsigned blocks) {
     if constexpr (sizeof(T) == 2) {
+      if (p.tile_r >= 0 && p.quads) {
+        ew_reg2_kernel<T, 0, true, false><<<blocks, 256, 0, ctx->stream>>>(p);
+        return OXM_OK;
+      }
       if (p.tile_r >= 0 && p.pairs) {
         ew_tile2_kernel<T, 0, true, false><<<blocks, 256, 0, ctx->stream>>>(p);
         return OXM_OK;
@@ -1659,6 +1664,14 @@ template <typename T> struct UnaryLauncher {
 };
 template <typename T> struct BinaryLauncher {
   static int run(oxm_ctx *ctx, const EwParams &p, unsigned blocks) {
+    if constexpr (sizeof(T) == 2) {
+      if (p.tile_r >= 0 && p.quads) {
+        if (p.a_turn && p.b_turn) ew_reg2_kernel<T, 1, true, true><<<blocks, 256, 0, ctx->stream>>>(p);
+        else if (p.a_turn) ew_reg2_kernel<T, 1, true, false><<<blocks, 256, 0, ctx->stream>>>(p);
+        else ew_reg2_kernel<T, 1, false, true><<<blocks, 256, 0, ctx->stream>>>(p);
+        return OXM_OK;
+      }
+    }
     // (the pair-access tile kernel measured no faster than this one for two operands)
     if (p.tile_r >= 0) {
       if (p.a_turn && p.b_turn) ew_tile_kernel<T, 1, true, true><<<blocks, 256, 0, ctx->stream>>>(p);
@@ -1696,7 +1709,7 @@ unsigned ew_plan_tiles(const oxm_ctx *ctx, EwParams &p, bool binary, int esz) {
   const int64_t tiles = ((R + T - 1) / T) * ((C + T - 1) / T) * (p.n / (R * C));
   if (tiles >= (1ll << 31)) { p.tile_r = -1; return 0; }  // the kernel counts tiles in 32 bits
   // Pairs: 2-byte elements, even tile extents, every row of every operand starting on a 4-byte boundary.
-  p.pairs = 0;
+  p.pairs = 0; p.quads = 0;
   if (esz == 2 && R % 2 == 0 && C % 2 == 0 && reinterpret_cast<uintptr_t>(p.out) % 4 == 0) {
     const int nd = p.ndim - 1;
     auto pair_ok = [&](const void *base, int64_t off, const int64_t *st, bool turned) {
@@ -1708,6 +1721,17 @@ unsigned ew_plan_tiles(const oxm_ctx *ctx, EwParams &p, bool binary, int esz) {
       return true;
     };
     p.pairs = (pair_ok(p.a, p.a_off, p.a_strides, p.a_turn) && (!binary || pair_ok(p.b, p.b_off, p.b_strides, p.b_turn))) ? 1 : 0;
+    // Quads (the turn in registers): on top of that, the straight operands and the output move 8 bytes
+    // along C: C a multiple of 4, their rows 8-byte aligned.
+    auto quad_ok = [&](const void *base, int64_t off, const int64_t *st, bool turned) {
+      if (turned) return true;  // read in pairs along R: the pair conditions are all it needs
+      if ((reinterpret_cast<uintptr_t>(base) + off * 2) % 8) return false;
+      for (int d = 0; d < nd; ++d)
+        if (st[d] % 4) return false;
+      return true;
+    };
+    p.quads = (p.pairs && C % 4 == 0 && reinterpret_cast<uintptr_t>(p.out) % 8 == 0 && quad_ok(p.a, p.a_off, p.a_strides, p.a_turn) &&
+               (!binary || quad_ok(p.b, p.b_off, p.b_strides, p.b_turn))) ? 1 : 0;
   }
   return (unsigned)std::min<int64_t>(tiles, (int64_t)ctx->num_sms * 16);
 }

@@ -54,6 +54,8 @@ struct EwParams {
   int32_t tile_r;      // >= 0: 32x32 tiles over (this dim, innermost dim); an operand whose unit stride is on this dim turns through shared memory
   int32_t a_turn, b_turn;
   int32_t pairs;       // 2-byte elements, everything 4-byte aligned: the tile kernel moves two elements per access
+  int32_t quads;       // ... and rows of the straight operands and of the output 8-byte aligned, C a multiple of 4:
+                       // the turn happens in registers (ew_reg2_kernel)
 };
 
 __device__ __forceinline__ void ew_offsets(const EwParams &p, int64_t i, int64_t &ao, int64_t &bo) {
@@ -429,6 +431,120 @@ __global__ void __launch_bounds__(256, MODE == 1 ? 4 : 6) ew_tile2_kernel(const 
       }
     }
     __syncthreads();
+  }
+}
+
+// 2-byte elements with a transposed operand, turned in registers instead of
+// shared memory.  A thread owns a block of 2 rows (R) x 4 columns (C): it reads
+// a turned operand as four 4-byte pairs along R (one per column), a straight
+// operand as two 8-byte runs along C (one per row), computes, and writes two
+// 8-byte runs of the output.  A warp is 8 threads along R by 4 along C, so every
+// access of a warp touches whole 32-byte sectors (8 x 4 bytes along R for the
+// turned operand, 4 x 8 bytes along C for the rest), and the eight warps of a
+// CTA cover whole 128-byte lines of every operand within one 64 x 64 tile.  No
+// shared memory, no barrier, 12 to 16 independent loads in flight per thread.
+// Needs: R even, C a multiple of 4, turned operands 4-byte aligned with even
+// other strides, straight operands and the output 8-byte aligned with other
+// strides that are multiples of 4.
+template <typename T, int MODE, bool A_TURN, bool B_TURN>
+__global__ void __launch_bounds__(256) ew_reg2_kernel(const EwParams p) {
+  static_assert(sizeof(T) == 2, "2-byte elements");
+  using C = typename EwTraits<T>::C;
+  constexpr int TILE = 64;
+  const T *a = static_cast<const T *>(p.a), *b = static_cast<const T *>(p.b);
+  T *out = static_cast<T *>(p.out);
+  const int nd = p.ndim - 1, rd = p.tile_r;
+  const int64_t R = p.shape[rd], Cn = p.shape[nd];
+  const uint32_t tiles_c = static_cast<uint32_t>((Cn + TILE - 1) / TILE), tiles_r = static_cast<uint32_t>((R + TILE - 1) / TILE);
+  const uint32_t per_batch = tiles_c * tiles_r;
+  const uint32_t ntiles = per_batch * static_cast<uint32_t>(p.n / (R * Cn));
+  const int64_t asr = p.a_strides[rd], asc = p.a_strides[nd], bsr = p.b_strides[rd], bsc = p.b_strides[nd];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tr = (warp & 3) * 16 + (lane & 7) * 2;   // this thread's first row within the tile
+  const int tc = (warp >> 2) * 16 + (lane >> 3) * 4;  // ... and first column; a second block sits 32 columns on
+  for (uint32_t tile = blockIdx.x; tile < ntiles; tile += gridDim.x) {
+    const uint32_t batch = tile / per_batch, in_batch = tile - batch * per_batch;
+    const uint32_t y = in_batch / tiles_c, x = in_batch - y * tiles_c;
+    const int64_t r0 = static_cast<int64_t>((y + x) % tiles_r) * TILE, c0 = static_cast<int64_t>(x) * TILE;
+    int64_t t = batch, ao = p.a_off, bo = p.b_off, oo = 0, os = Cn, osr = 0;
+    for (int d = nd - 1; d >= 0; --d) {
+      if (d == rd) {
+        osr = os;
+      } else {
+        const int64_t idx = t % p.shape[d];
+        t /= p.shape[d];
+        ao += idx * p.a_strides[d];
+        bo += idx * p.b_strides[d];
+        oo += idx * os;
+      }
+      os *= p.shape[d];
+    }
+    const int64_t r = r0 + tr;
+    const bool r_in = r < R;  // R is even: both rows or neither
+    uint32_t ta[2][4], tb[2][4];  // turned operands: [block][column] = the pair (r, r + 1) of that column
+    uint2 sa[2][2], sb[2][2];     // straight operands: [block][row] = columns c .. c + 3 of that row
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const int64_t c = c0 + tc + 32 * k;
+      const bool in = r_in && c < Cn;  // C is a multiple of 4: all four columns or none
+      if (!in) continue;
+      if constexpr (A_TURN) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) ta[k][j] = *reinterpret_cast<const uint32_t *>(a + ao + r + (c + j) * asc);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) sa[k][i] = *reinterpret_cast<const uint2 *>(a + ao + (r + i) * asr + c);
+      }
+      if constexpr (MODE == 1) {
+        if constexpr (B_TURN) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) tb[k][j] = *reinterpret_cast<const uint32_t *>(b + bo + r + (c + j) * bsc);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 2; ++i) sb[k][i] = *reinterpret_cast<const uint2 *>(b + bo + (r + i) * bsr + c);
+        }
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const int64_t c = c0 + tc + 32 * k;
+      if (!(r_in && c < Cn)) continue;
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        // row i of the block as four 16-bit patterns, from either form
+        uint16_t ea[4], eb[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if constexpr (A_TURN) ea[j] = static_cast<uint16_t>(ta[k][j] >> (16 * i));
+          else ea[j] = static_cast<uint16_t>((j < 2 ? sa[k][i].x : sa[k][i].y) >> (16 * (j & 1)));
+          if constexpr (MODE == 1) {
+            if constexpr (B_TURN) eb[j] = static_cast<uint16_t>(tb[k][j] >> (16 * i));
+            else eb[j] = static_cast<uint16_t>((j < 2 ? sb[k][i].x : sb[k][i].y) >> (16 * (j & 1)));
+          }
+        }
+        uint16_t eo[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if constexpr (MODE == 2) {
+            eo[j] = ea[j];
+          } else {
+            T va, vb, vo;
+            memcpy(&va, &ea[j], 2);
+            if constexpr (MODE == 1) {
+              memcpy(&vb, &eb[j], 2);
+              ew_store<T>(&vo, 0, binary_apply<C>(p.op, ew_load<T>(&va, 0), ew_load<T>(&vb, 0)));
+            } else {
+              ew_store<T>(&vo, 0, unary_apply<C>(p.op, ew_load<T>(&va, 0)));
+            }
+            memcpy(&eo[j], &vo, 2);
+          }
+        }
+        uint2 w;
+        w.x = static_cast<uint32_t>(eo[0]) | (static_cast<uint32_t>(eo[1]) << 16);
+        w.y = static_cast<uint32_t>(eo[2]) | (static_cast<uint32_t>(eo[3]) << 16);
+        *reinterpret_cast<uint2 *>(out + oo + (r + i) * osr + c) = w;
+      }
+    }
   }
 }
 
