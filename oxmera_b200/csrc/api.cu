@@ -8,6 +8,7 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <atomic>
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
@@ -1756,17 +1757,58 @@ unsigned ew_plan(const oxm_ctx *ctx, EwParams &p, int esz, bool binary) {
   }
   return (unsigned)std::min<int64_t>((p.n + 255) / 256, (int64_t)ctx->num_sms * 16);
 }
+// CTAs of 256 threads of `kernel` that one SM holds at once (asked of the runtime once per kernel).
+template <typename K> int resident_ctas(K kernel, std::atomic<int> &cache) {
+  int nb = cache.load(std::memory_order_relaxed);
+  if (nb > 0) return nb;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, kernel, 256, 0) != cudaSuccess || nb < 1) nb = 1;
+  cache.store(nb, std::memory_order_relaxed);
+  return nb;
+}
+
 template <typename T> struct ReduceLauncher {
-  static int run(oxm_ctx *ctx, const ReduceOpParams &p, bool row_mode, unsigned blocks_x) {
-    const dim3 grid(blocks_x, (unsigned)p.splits, 1);
-    if (row_mode) reduce_row_kernel<T><<<grid, 256, 0, ctx->stream>>>(p);
-    else if (p.col_vec) reduce_colv_kernel<T><<<grid, 256, 0, ctx->stream>>>(p);
-    else reduce_col_kernel<T><<<grid, 256, 0, ctx->stream>>>(p);
+  // The operation is a template argument of the kernels: chosen per element at run time, both
+  // combinations were computed for every element and 2-byte sums ran out of issue slots before
+  // they ran out of memory bandwidth.
+  // The slices are planned here, from what the chosen kernel really keeps resident: all CTAs of
+  // the pass must run at once (a few CTAs over and they run alone in a second pass as long as the
+  // first), so the slice count is rounded down.
+  template <int OP, typename K>
+  static int plan_and_launch(K kernel, std::atomic<int> &cache, oxm_ctx *ctx, ReduceOpParams &p, unsigned blocks_x, int64_t max_splits) {
+    const int64_t target = (int64_t)ctx->num_sms * resident_ctas(kernel, cache);
+    if (p.warp_rows) {
+      // whole rows per warp: as many warps as fit at once, each with the same number of rows
+      const int64_t rows_per_warp = (p.n_out + target * 8 - 1) / (target * 8);
+      blocks_x = (unsigned)((p.n_out + rows_per_warp * 8 - 1) / (rows_per_warp * 8));
+    }
+    p.splits = (int32_t)std::max<int64_t>(1, std::min<int64_t>({target / blocks_x, max_splits, (int64_t)1024}));
+    p.chunk = (p.n_red + p.splits - 1) / p.splits;
+    p.splits = (int32_t)((p.n_red + p.chunk - 1) / p.chunk);
     if (p.splits > 1) {
-      const unsigned fb = (unsigned)std::min<int64_t>((p.n_out + 255) / 256, (int64_t)ctx->num_sms * 8);
-      reduce_finish_kernel<T><<<fb, 256, 0, ctx->stream>>>(p);
+      const int st = grow(ctx, ctx->pack_ws[2], (size_t)p.splits * p.n_out * 8);
+      if (st) return st;
+      p.partial = ctx->pack_ws[2].ptr;
+    }
+    kernel<<<dim3(blocks_x, (unsigned)p.splits, 1), 256, 0, ctx->stream>>>(p);
+    if (p.splits > 1) {
+      if (p.n_out < 2048 && p.splits >= 32) {
+        reduce_finish_wide_kernel<T, OP><<<(unsigned)p.n_out, 256, 0, ctx->stream>>>(p);
+      } else {
+        const unsigned fb = (unsigned)std::min<int64_t>((p.n_out + 255) / 256, (int64_t)ctx->num_sms * 8);
+        reduce_finish_kernel<T, OP><<<fb, 256, 0, ctx->stream>>>(p);
+      }
     }
     return OXM_OK;
+  }
+  template <int OP> static int launch(oxm_ctx *ctx, ReduceOpParams &p, bool row_mode, unsigned blocks_x, int64_t max_splits) {
+    static std::atomic<int> occ[4];
+    if (row_mode && p.warp_rows) return plan_and_launch<OP>(reduce_roww_kernel<T, OP>, occ[0], ctx, p, blocks_x, max_splits);
+    if (row_mode) return plan_and_launch<OP>(reduce_row_kernel<T, OP>, occ[1], ctx, p, blocks_x, max_splits);
+    if (p.col_vec) return plan_and_launch<OP>(reduce_colv_kernel<T, OP>, occ[2], ctx, p, blocks_x, max_splits);
+    return plan_and_launch<OP>(reduce_col_kernel<T, OP>, occ[3], ctx, p, blocks_x, max_splits);
+  }
+  static int run(oxm_ctx *ctx, ReduceOpParams &p, bool row_mode, unsigned blocks_x, int64_t max_splits) {
+    return p.op == 0 ? launch<0>(ctx, p, row_mode, blocks_x, max_splits) : launch<1>(ctx, p, row_mode, blocks_x, max_splits);
   }
 };
 
@@ -1981,10 +2023,17 @@ extern "C" int oxm_reduce(oxm_ctx *ctx, int op, const oxm_view *a, const int32_t
     return m;
   };
   const bool row_mode = p.nkept == 0 || min_stride(p.nred, p.red_strides) < min_stride(p.nkept, p.kept_strides);
-  const int64_t target = (int64_t)ctx->num_sms * 8;  // CTAs wanted in flight
   unsigned blocks_x;
   int64_t max_splits;
-  if (row_mode) {
+  p.warp_rows = 0;
+  if (row_mode && p.nred == 1 && p.red_strides[0] == 1 && p.n_red * dtype_size(a->dtype) <= (48 << 10) &&
+      p.n_out >= (int64_t)ctx->num_sms * 64) {
+    // many short contiguous rows (under 48 KiB: longer ones keep a CTA busy on their own): a warp per
+    // row, eight rows per CTA, no slices
+    p.warp_rows = 1;
+    blocks_x = (unsigned)std::min<int64_t>((p.n_out + 7) / 8, (int64_t)ctx->num_sms * 16);
+    max_splits = 1;
+  } else if (row_mode) {
     blocks_x = (unsigned)std::min<int64_t>(p.n_out, 65535 * 16);
     max_splits = (p.n_red + 8191) / 8192;    // at least 8 Ki elements per slice
   } else {
@@ -1998,18 +2047,11 @@ extern "C" int oxm_reduce(oxm_ctx *ctx, int op, const oxm_view *a, const int32_t
     blocks_x = (unsigned)std::min<int64_t>((threads + 255) / 256, (int64_t)ctx->num_sms * 16);
     max_splits = (p.n_red + 63) / 64;        // at least 64 serial steps per thread
   }
-  p.splits = (int32_t)std::max<int64_t>(1, std::min<int64_t>({(target + blocks_x - 1) / blocks_x, max_splits, (int64_t)1024}));
-  p.chunk = (p.n_red + p.splits - 1) / p.splits;
-  p.splits = (int32_t)((p.n_red + p.chunk - 1) / p.chunk);
-  if (p.splits > 1) {
-    st = grow(ctx, ctx->pack_ws[2], (size_t)p.splits * p.n_out * 8);
-    if (st) return st;
-    p.partial = ctx->pack_ws[2].ptr;
-  }
-  dispatch_dtype<ReduceLauncher>(a->dtype, ctx, p, row_mode, blocks_x);
+  st = dispatch_dtype<ReduceLauncher>(a->dtype, ctx, p, row_mode, blocks_x, max_splits);  // plans the slices, launches
+  if (st) return st;
   CUDA_TRY(cudaGetLastError());
   ctx->launches[0] += p.splits > 1 ? 2 : 1;
-  snprintf(ctx->last_kernel, sizeof(ctx->last_kernel), "reduce_%s_%s_x%d", name, row_mode ? "row" : "col", p.splits);
+  snprintf(ctx->last_kernel, sizeof(ctx->last_kernel), "reduce_%s_%s_x%d", name, !row_mode ? "col" : p.warp_rows ? "roww" : "row", p.splits);
   return OXM_OK;
 }
 

@@ -567,6 +567,7 @@ struct ReduceOpParams {
   void *partial;   // ... or [splits][n_out] partial results in the compute type
   int32_t op, nkept, nred, splits;
   int32_t col_vec;              // COL mapping with 16 bytes of neighbouring outputs per thread
+  int32_t warp_rows;            // ROW mapping with one warp per output (many short contiguous rows)
   int64_t n_out, n_red, chunk;  // chunk: reduced elements per slice
   int64_t kept_shape[kEwMaxDims], kept_strides[kEwMaxDims];
   int64_t red_shape[kEwMaxDims], red_strides[kEwMaxDims];
@@ -575,6 +576,12 @@ struct ReduceOpParams {
 
 // max propagates NaN: once either side is NaN the result stays NaN, whatever the order of combination.
 template <typename C> __device__ __forceinline__ C reduce_max(C x, C y) { return x != x ? x : (y != y ? y : (y > x ? y : x)); }
+// f32 (the compute type of bf16 and f16 too): the NaN-propagating maximum is one instruction
+template <> __device__ __forceinline__ float reduce_max<float>(float x, float y) {
+  float r;
+  asm("max.NaN.f32 %0, %1, %2;" : "=f"(r) : "f"(x), "f"(y));
+  return r;
+}
 template <typename C> __device__ __forceinline__ C reduce_combine(int op, C x, C y) { return op == 0 ? x + y : reduce_max<C>(x, y); }
 
 template <typename C> __device__ __forceinline__ C reduce_identity(int op);
@@ -593,7 +600,7 @@ __device__ __forceinline__ int64_t unravel(int64_t i, int nd, const int64_t *sha
 
 template <typename C> __device__ __forceinline__ C shfl_down(C v, int d) { return __shfl_down_sync(0xffffffffu, v, d); }
 
-template <typename T>
+template <typename T, int OP>
 __global__ void __launch_bounds__(256) reduce_row_kernel(const ReduceOpParams p) {
   using C = typename EwTraits<T>::C;
   constexpr int V = 16 / sizeof(T);
@@ -602,35 +609,39 @@ __global__ void __launch_bounds__(256) reduce_row_kernel(const ReduceOpParams p)
   const int64_t r0 = blockIdx.y * p.chunk, r1 = min(r0 + p.chunk, p.n_red);
   for (int64_t o = blockIdx.x; o < p.n_out; o += gridDim.x) {
     const int64_t base = p.a_off + unravel(o, p.nkept, p.kept_shape, p.kept_strides);
-    C acc = reduce_identity<C>(p.op);
+    C acc = reduce_identity<C>(OP);
     if (p.nred == 1 && p.red_strides[0] == 1) {
       // a contiguous run: scalar head up to a 16-byte boundary, vector body, scalar tail
       const T *run = a + base;
       const int64_t mis = (reinterpret_cast<uintptr_t>(run + r0) / sizeof(T)) % V;
       const int64_t head = min((V - mis) % V, r1 - r0);
       const int64_t nv = (r1 - r0 - head) / V;
-      if (static_cast<int64_t>(threadIdx.x) < head) acc = reduce_combine<C>(p.op, acc, ew_load<T>(run, r0 + threadIdx.x));
+      if (static_cast<int64_t>(threadIdx.x) < head) acc = reduce_combine<C>(OP, acc, ew_load<T>(run, r0 + threadIdx.x));
       const EwVec<T> *vec = reinterpret_cast<const EwVec<T> *>(run + r0 + head);
+      // four running results per thread: one chain of dependent additions per 16 bytes (eight of
+      // them for 2-byte elements) held bf16 sums at half the rate of f32 ones
+      C lane_acc[4] = {acc, reduce_identity<C>(OP), reduce_identity<C>(OP), reduce_identity<C>(OP)};
 #pragma unroll 4
       for (int64_t i = threadIdx.x; i < nv; i += 256) {
         const EwVec<T> x = vec[i];
 #pragma unroll
-        for (int e = 0; e < V; ++e) acc = reduce_combine<C>(p.op, acc, ew_load<T>(x.v, e));
+        for (int e = 0; e < V; ++e) lane_acc[e & 3] = reduce_combine<C>(OP, lane_acc[e & 3], ew_load<T>(x.v, e));
       }
-      for (int64_t r = r0 + head + nv * V + threadIdx.x; r < r1; r += 256) acc = reduce_combine<C>(p.op, acc, ew_load<T>(run, r));
+      acc = reduce_combine<C>(OP, reduce_combine<C>(OP, lane_acc[0], lane_acc[1]), reduce_combine<C>(OP, lane_acc[2], lane_acc[3]));
+      for (int64_t r = r0 + head + nv * V + threadIdx.x; r < r1; r += 256) acc = reduce_combine<C>(OP, acc, ew_load<T>(run, r));
     } else if (p.nred == 1) {
-      for (int64_t r = r0 + threadIdx.x; r < r1; r += 256) acc = reduce_combine<C>(p.op, acc, ew_load<T>(a, base + r * p.red_strides[0]));
+      for (int64_t r = r0 + threadIdx.x; r < r1; r += 256) acc = reduce_combine<C>(OP, acc, ew_load<T>(a, base + r * p.red_strides[0]));
     } else {
       for (int64_t r = r0 + threadIdx.x; r < r1; r += 256)
-        acc = reduce_combine<C>(p.op, acc, ew_load<T>(a, base + unravel(r, p.nred, p.red_shape, p.red_strides)));
+        acc = reduce_combine<C>(OP, acc, ew_load<T>(a, base + unravel(r, p.nred, p.red_shape, p.red_strides)));
     }
 #pragma unroll
-    for (int d = 16; d > 0; d >>= 1) acc = reduce_combine<C>(p.op, acc, shfl_down<C>(acc, d));
+    for (int d = 16; d > 0; d >>= 1) acc = reduce_combine<C>(OP, acc, shfl_down<C>(acc, d));
     if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = acc;
     __syncthreads();
     if (threadIdx.x == 0) {
       C total = part[0];
-      for (int w = 1; w < 8; ++w) total = reduce_combine<C>(p.op, total, part[w]);
+      for (int w = 1; w < 8; ++w) total = reduce_combine<C>(OP, total, part[w]);
       if (p.splits == 1) ew_store<T>(static_cast<T *>(p.out), o, total);
       else static_cast<C *>(p.partial)[blockIdx.y * p.n_out + o] = total;
     }
@@ -638,19 +649,57 @@ __global__ void __launch_bounds__(256) reduce_row_kernel(const ReduceOpParams p)
   }
 }
 
-template <typename T>
+// ROW mapping for many short contiguous rows: one WARP per output.  A row of a few
+// tens of kilobytes is eight loads per thread of a 256-thread CTA, and the two
+// block barriers and the serial tail of the CTA-per-row kernel then cost as much
+// as the row itself (bf16 [16000, 16400] summed over rows: 0.59 of the HBM copy
+// rate where f32, with rows twice as long in bytes, reached 0.98).  Here a warp
+// walks its row in 512-byte steps and finishes with shuffles alone.
+template <typename T, int OP>
+__global__ void __launch_bounds__(256, 6) reduce_roww_kernel(const ReduceOpParams p) {
+  using C = typename EwTraits<T>::C;
+  constexpr int V = 16 / sizeof(T);
+  const T *a = static_cast<const T *>(p.a);
+  const int lane = threadIdx.x & 31;
+  const int64_t nwarps = static_cast<int64_t>(gridDim.x) * 8;
+  for (int64_t o = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5); o < p.n_out; o += nwarps) {
+    const T *run = a + p.a_off + unravel(o, p.nkept, p.kept_shape, p.kept_strides);
+    const int64_t mis = (reinterpret_cast<uintptr_t>(run) / sizeof(T)) % V;
+    const int64_t head = min((V - mis) % V, p.n_red);
+    const int64_t nv = (p.n_red - head) / V;
+    C acc = reduce_identity<C>(OP);
+    if (lane < head) acc = reduce_combine<C>(OP, acc, ew_load<T>(run, lane));
+    const EwVec<T> *vec = reinterpret_cast<const EwVec<T> *>(run + head);
+    C lane_acc[4] = {acc, reduce_identity<C>(OP), reduce_identity<C>(OP), reduce_identity<C>(OP)};  // see reduce_row_kernel
+    // eight loads in flight per thread and six CTAs per SM: a warp alone on its row is bound by
+    // the latency of its loads, and 8 x 48 warps hold more of them than 4 x 64
+#pragma unroll 8
+    for (int64_t i = lane; i < nv; i += 32) {
+      const EwVec<T> x = vec[i];
+#pragma unroll
+      for (int e = 0; e < V; ++e) lane_acc[e & 3] = reduce_combine<C>(OP, lane_acc[e & 3], ew_load<T>(x.v, e));
+    }
+    acc = reduce_combine<C>(OP, reduce_combine<C>(OP, lane_acc[0], lane_acc[1]), reduce_combine<C>(OP, lane_acc[2], lane_acc[3]));
+    for (int64_t r = head + nv * V + lane; r < p.n_red; r += 32) acc = reduce_combine<C>(OP, acc, ew_load<T>(run, r));
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) acc = reduce_combine<C>(OP, acc, shfl_down<C>(acc, d));
+    if (lane == 0) ew_store<T>(static_cast<T *>(p.out), o, acc);
+  }
+}
+
+template <typename T, int OP>
 __global__ void __launch_bounds__(256) reduce_col_kernel(const ReduceOpParams p) {
   using C = typename EwTraits<T>::C;
   const T *a = static_cast<const T *>(p.a);
   const int64_t r0 = blockIdx.y * p.chunk, r1 = min(r0 + p.chunk, p.n_red);
   for (int64_t o = blockIdx.x * 256ll + threadIdx.x; o < p.n_out; o += static_cast<int64_t>(gridDim.x) * 256) {
     const int64_t base = p.a_off + unravel(o, p.nkept, p.kept_shape, p.kept_strides);
-    C acc = reduce_identity<C>(p.op);
+    C acc = reduce_identity<C>(OP);
     if (p.nred == 1) {
       const int64_t rs = p.red_strides[0];
-      for (int64_t r = r0; r < r1; ++r) acc = reduce_combine<C>(p.op, acc, ew_load<T>(a, base + r * rs));
+      for (int64_t r = r0; r < r1; ++r) acc = reduce_combine<C>(OP, acc, ew_load<T>(a, base + r * rs));
     } else {
-      for (int64_t r = r0; r < r1; ++r) acc = reduce_combine<C>(p.op, acc, ew_load<T>(a, base + unravel(r, p.nred, p.red_shape, p.red_strides)));
+      for (int64_t r = r0; r < r1; ++r) acc = reduce_combine<C>(OP, acc, ew_load<T>(a, base + unravel(r, p.nred, p.red_shape, p.red_strides)));
     }
     if (p.splits == 1) ew_store<T>(static_cast<T *>(p.out), o, acc);
     else static_cast<C *>(p.partial)[blockIdx.y * p.n_out + o] = acc;
@@ -660,7 +709,7 @@ __global__ void __launch_bounds__(256) reduce_col_kernel(const ReduceOpParams p)
 // COL mapping, 16 bytes wide: the kept elements are one contiguous run, so a
 // thread owns 16 / sizeof(T) neighbouring outputs and every load is a full
 // vector (the host checks alignment and that every reduced stride keeps it).
-template <typename T>
+template <typename T, int OP>
 __global__ void __launch_bounds__(256) reduce_colv_kernel(const ReduceOpParams p) {
   using C = typename EwTraits<T>::C;
   constexpr int V = 16 / sizeof(T);
@@ -671,20 +720,20 @@ __global__ void __launch_bounds__(256) reduce_colv_kernel(const ReduceOpParams p
     const T *col = a + p.a_off + ov * V;
     C acc[V];
 #pragma unroll
-    for (int e = 0; e < V; ++e) acc[e] = reduce_identity<C>(p.op);
+    for (int e = 0; e < V; ++e) acc[e] = reduce_identity<C>(OP);
     if (p.nred == 1) {
       const int64_t rs = p.red_strides[0];
 #pragma unroll 4
       for (int64_t r = r0; r < r1; ++r) {
         const EwVec<T> x = *reinterpret_cast<const EwVec<T> *>(col + r * rs);
 #pragma unroll
-        for (int e = 0; e < V; ++e) acc[e] = reduce_combine<C>(p.op, acc[e], ew_load<T>(x.v, e));
+        for (int e = 0; e < V; ++e) acc[e] = reduce_combine<C>(OP, acc[e], ew_load<T>(x.v, e));
       }
     } else {
       for (int64_t r = r0; r < r1; ++r) {
         const EwVec<T> x = *reinterpret_cast<const EwVec<T> *>(col + unravel(r, p.nred, p.red_shape, p.red_strides));
 #pragma unroll
-        for (int e = 0; e < V; ++e) acc[e] = reduce_combine<C>(p.op, acc[e], ew_load<T>(x.v, e));
+        for (int e = 0; e < V; ++e) acc[e] = reduce_combine<C>(OP, acc[e], ew_load<T>(x.v, e));
       }
     }
     if (p.splits == 1) {
@@ -699,14 +748,39 @@ __global__ void __launch_bounds__(256) reduce_colv_kernel(const ReduceOpParams p
   }
 }
 
-template <typename T>
+template <typename T, int OP>
 __global__ void __launch_bounds__(256) reduce_finish_kernel(const ReduceOpParams p) {
   using C = typename EwTraits<T>::C;
   const C *partial = static_cast<const C *>(p.partial);
   for (int64_t o = blockIdx.x * 256ll + threadIdx.x; o < p.n_out; o += static_cast<int64_t>(gridDim.x) * 256) {
     C acc = partial[o];
-    for (int s = 1; s < p.splits; ++s) acc = reduce_combine<C>(p.op, acc, partial[s * p.n_out + o]);
+#pragma unroll 8  // the loads of a step are independent: eight of them in flight, not one
+    for (int s = 1; s < p.splits; ++s) acc = reduce_combine<C>(OP, acc, partial[s * p.n_out + o]);
     ew_store<T>(static_cast<T *>(p.out), o, acc);
+  }
+}
+
+// Few outputs, many slices (a sum over everything: one output, 1024 slices): a
+// CTA per output, its threads across the slices, so that the last step costs a
+// couple of loads per thread instead of a thousand one after another.
+template <typename T, int OP>
+__global__ void __launch_bounds__(256) reduce_finish_wide_kernel(const ReduceOpParams p) {
+  using C = typename EwTraits<T>::C;
+  __shared__ C part[8];
+  const C *partial = static_cast<const C *>(p.partial);
+  for (int64_t o = blockIdx.x; o < p.n_out; o += gridDim.x) {
+    C acc = reduce_identity<C>(OP);
+    for (int s = threadIdx.x; s < p.splits; s += 256) acc = reduce_combine<C>(OP, acc, partial[s * p.n_out + o]);
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) acc = reduce_combine<C>(OP, acc, shfl_down<C>(acc, d));
+    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      C total = part[0];
+      for (int w = 1; w < 8; ++w) total = reduce_combine<C>(OP, total, part[w]);
+      ew_store<T>(static_cast<T *>(p.out), o, total);
+    }
+    __syncthreads();
   }
 }
 
