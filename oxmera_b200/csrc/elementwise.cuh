@@ -173,9 +173,12 @@ __global__ void __launch_bounds__(256) int_div_kernel(const EwParams p, uint32_t
 // Strided or broadcast operands with a long innermost dim: one CTA per row.
 // The row's base offsets are unravelled once; along the row each operand
 // advances by its inner stride (0 for a broadcast operand), so a bias row, a
-// per-row scalar or a narrowed window all stream at full width.
+// per-row scalar or a narrowed window all stream at full width.  Bound to eight
+// CTAs per SM: at the 64 registers the compiler took unasked, four CTAs per SM
+// held too few loads in flight (a [16400] f32 row added to [16000, 16400]: 0.76
+// of the HBM copy rate at four, 0.89 at eight; the spills are in the row setup).
 template <typename T, bool BINARY>
-__global__ void __launch_bounds__(256) ew_rows_kernel(const EwParams p) {
+__global__ void __launch_bounds__(256, 8) ew_rows_kernel(const EwParams p) {
   using C = typename EwTraits<T>::C;
   constexpr int V = 16 / sizeof(T);
   const T *a = static_cast<const T *>(p.a), *b = static_cast<const T *>(p.b);

@@ -175,9 +175,33 @@ def test_reductions(backend, oracle, dtype):
                     else:
                         exact = as_f64(hv, dtype).sum(axis=tuple(axes) if axes else None)
                         assert rel_err(as_f64(out.to_host(), dtype), np.asarray(exact)) <= tol[dtype], (shape, axes)
+    # many short contiguous rows: one warp per row, row starts at every alignment (37 and 36 elements per
+    # row), and a sum over everything in enough slices for the CTA-per-output last step
+    h = host(oracle, (9600, 37), dtype, 32)
+    t = Tensor.from_host(h, (9600, 37), dtype, backend)
+    for hv, tv, kernel in ((h, t, "roww_x1"), (h[:, 1:], t.narrow(1, 1, 36), "roww_x1"), (h[::-1], t.flip(0), "roww_x1")):
+        for op, fn in ((0, backend.sum), (1, backend.max)):
+            out = fn(tv, [1])
+            assert backend.last_kernel().endswith(kernel), backend.last_kernel()
+            st, ref = oracle.reduce(op, hv, [1], TAGS[dtype])
+            assert st == 0 and out.shape == ref.shape
+            if dtype in INTS or op == 1:
+                assert np.array_equal(out.to_host(), ref), (kernel, op)
+            else:
+                assert rel_err(as_f64(out.to_host(), dtype), as_f64(hv, dtype).sum(axis=1)) <= tol[dtype]
+    h = host(oracle, (2, 600000), dtype, 33)
+    t = Tensor.from_host(h, (2, 600000), dtype, backend)
+    for op, fn in ((0, backend.sum), (1, backend.max)):
+        out = fn(t, [])
+        assert int(backend.last_kernel().rsplit("_x", 1)[1]) >= 32, backend.last_kernel()
+        st, ref = oracle.reduce(op, h, [], TAGS[dtype])
+        if dtype in INTS or op == 1:
+            assert st == 0 and np.array_equal(out.to_host(), ref)
+        else:
+            assert rel_err(as_f64(out.to_host(), dtype), np.asarray(as_f64(h, dtype).sum())) <= tol[dtype]
     if dtype in FLOATS:
         # max propagates NaN wherever it sits in the slice, through every thread mapping
-        for shape, axes in (((5, 3000), [1]), ((3000, 5), [0]), ((40, 4096), [0]), ((64, 64), [])):
+        for shape, axes in (((5, 3000), [1]), ((3000, 5), [0]), ((40, 4096), [0]), ((64, 64), []), ((9600, 37), [1]), ((2, 600000), [])):
             h = host(oracle, shape, dtype, 31)
             flat = h.reshape(-1)
             for pos in (0, flat.size // 2, flat.size - 1):
