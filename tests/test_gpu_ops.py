@@ -226,7 +226,11 @@ def test_transposed_operands_take_the_tile_kernel(backend, oracle, dtype):
     """Operands whose unit stride is not on the innermost dim (extent >= 32 on
     the unit-stride dim): ragged 32x32 tiles, a batch dim outside and between
     the tile dims, either or both operands turned."""
-    for shape, perm in (((70, 45), (1, 0)), ((3, 40, 50), (0, 2, 1)), ((40, 3, 50), (2, 1, 0)), ((33, 2, 2, 65), (3, 1, 2, 0))):
+    shapes = [((70, 45), (1, 0)), ((3, 40, 50), (0, 2, 1)), ((40, 3, 50), (2, 1, 0)), ((33, 2, 2, 65), (3, 1, 2, 0))]
+    # extents that are multiples of 4 with aligned rows: 2- and 4-byte elements turn in registers (one tile,
+    # several ragged tiles, a batch dim outside and between the tile dims)
+    shapes += [((72, 48), (1, 0)), ((200, 136), (1, 0)), ((3, 40, 52), (0, 2, 1)), ((44, 3, 60), (2, 1, 0))]
+    for shape, perm in shapes:
         h = host(oracle, shape, dtype, 40)
         t = Tensor.from_host(h, shape, dtype, backend)
         hv, tv = h.transpose(perm), t.permute(list(perm))
