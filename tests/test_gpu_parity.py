@@ -231,6 +231,47 @@ def test_broadcast_batch_dims(backend, oracle, kernel, dtype):
         assert err <= TOL[dtype], (ashape, bshape, err, backend.last_kernel())
 
 
+@pytest.mark.parametrize("dtype", [DType.F32, DType.BF16, DType.F16], ids=lambda d: d.name)
+def test_seeded_random_products_under_the_default_planner(backend, oracle, dtype):
+    """Whatever the planner picks by itself (FFMA or tensor cores, packed or in
+    place, split or not, the order it walks the batch dims in): random extents,
+    random broadcast batch dims, either operand transposed, windowed or both."""
+    rng = np.random.default_rng({DType.F32: 11, DType.BF16: 12, DType.F16: 13}[dtype])
+    kernels = set()
+    for case in range(36):
+        m, n, k = (int(x) for x in rng.integers(1, 330, size=3))
+        if case % 6 == 0:
+            k = int(rng.integers(400, 2200))  # long contractions: the split paths
+        nb = int(rng.integers(0, 3))
+        batch = [int(x) for x in rng.integers(1, 4, size=nb)]
+        a_batch = [1 if rng.random() < 0.3 else d for d in batch]
+        b_batch = [1 if rng.random() < 0.3 else d for d in batch]
+        if rng.random() < 0.3:
+            b_batch = b_batch[1:]  # B with fewer batch dims than A
+        a_t, b_t, win = rng.random() < 0.4, rng.random() < 0.4, rng.random() < 0.3
+        pad = 3 if win else 0
+        ashape = tuple(a_batch) + ((k + pad, m + pad) if a_t else (m + pad, k + pad))
+        bshape = tuple(b_batch) + ((n, k) if b_t else (k, n))
+        ha, hb = fill(oracle, ashape, dtype, 900 + case, 0), fill(oracle, bshape, dtype, 900 + case, 1)
+        ta, tb = Tensor.from_host(ha, ashape, dtype, backend), Tensor.from_host(hb, bshape, dtype, backend)
+        if a_t:
+            perm = list(range(len(ashape) - 2)) + [len(ashape) - 1, len(ashape) - 2]
+            ha, ta = ha.transpose(perm), ta.permute(perm)
+        if b_t:
+            perm = list(range(len(bshape) - 2)) + [len(bshape) - 1, len(bshape) - 2]
+            hb, tb = hb.transpose(perm), tb.permute(perm)
+        if win:  # an odd window of A: offsets and strides that are not 16-byte multiples
+            ha = ha[..., 1:m + 1, 2:k + 2]
+            ta = ta.narrow(len(ashape) - 2, 1, m).narrow(len(ashape) - 1, 2, k)
+        got = backend.batched_matmul(ta, tb)
+        kernels.add(backend.last_kernel().split("_bn")[0].split("_w")[0])
+        ref = oracle_ref(oracle, ha, hb, dtype)
+        assert got.shape == ref.shape, (case, ashape, bshape)
+        err = rel_err(to_f64(got.to_host(), dtype), ref)
+        assert err <= TOL[dtype], (case, ashape, bshape, a_t, b_t, win, err, backend.last_kernel())
+    assert len(kernels) >= 2, kernels  # the sweep reached more than one kernel family
+
+
 @pytest.mark.parametrize("tile_n", [64, 96, 128, 160, 224, 256, 288, 320, 384, 416, 448, 480, 512])
 @pytest.mark.parametrize("dtype", [DType.BF16, DType.F32], ids=lambda d: d.name)
 def test_tile_widths(backend, oracle, tile_n, dtype):
