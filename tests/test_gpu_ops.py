@@ -192,13 +192,14 @@ def test_reductions(backend, oracle, dtype):
     h = host(oracle, (2, 600000), dtype, 33)
     t = Tensor.from_host(h, (2, 600000), dtype, backend)
     for op, fn in ((0, backend.sum), (1, backend.max)):
-        out = fn(t, [])
-        assert int(backend.last_kernel().rsplit("_x", 1)[1]) >= 32, backend.last_kernel()
-        st, ref = oracle.reduce(op, h, [], TAGS[dtype])
-        if dtype in INTS or op == 1:
-            assert st == 0 and np.array_equal(out.to_host(), ref)
-        else:
-            assert rel_err(as_f64(out.to_host(), dtype), np.asarray(as_f64(h, dtype).sum())) <= tol[dtype]
+        for hv, tv, axes in ((h, t, []), (h.reshape(4, 300000), t.reshape([4, 300000]), [1])):  # one output; four, each in 37 slices
+            out = fn(tv, axes)
+            assert int(backend.last_kernel().rsplit("_x", 1)[1]) >= 32, backend.last_kernel()
+            st, ref = oracle.reduce(op, hv, axes, TAGS[dtype])
+            if dtype in INTS or op == 1:
+                assert st == 0 and np.array_equal(out.to_host(), ref)
+            else:
+                assert rel_err(as_f64(out.to_host(), dtype), np.asarray(as_f64(hv, dtype).sum(axis=tuple(axes) if axes else None))) <= tol[dtype]
     if dtype in FLOATS:
         # max propagates NaN wherever it sits in the slice, through every thread mapping
         for shape, axes in (((5, 3000), [1]), ((3000, 5), [0]), ((40, 4096), [0]), ((64, 64), []), ((9600, 37), [1]), ((2, 600000), [])):
