@@ -86,7 +86,10 @@ def test_unary_ops(backend, oracle, dtype):
 def test_binary_ops_broadcast(backend, oracle, dtype):
     fns = [backend.add, backend.sub, backend.mul, backend.div]  # the integer test data has no zero divisors: see below
     cases = [((64, 33), (64, 33)), ((2, 3), (3,)), ((2, 1), (1, 3)), ((), (2, 3)), ((4, 1, 5), (3, 1)), ((130, 1, 17), (1, 9, 1)),
-             ((2, 0), (1, 1))]
+             ((2, 0), (1, 1)),
+             # long innermost dims: a CTA per row (a bias row, a per-row scalar, an extent that keeps rows off
+             # 16-byte boundaries, more rows than CTAs)
+             ((300, 136), (136,)), ((300, 136), (300, 1)), ((300, 131), (131,)), ((9600, 136), (136,)), ((9600, 1), (9600, 136))]
     for ls, rs in cases:
         a, b = host(oracle, ls, dtype, 20), host(oracle, rs, dtype, 21, positive=dtype in FLOATS)
         if dtype in INTS:
